@@ -1,0 +1,130 @@
+"""Checkpoint writer/reader round trip, header validation, identity, TP slicing."""
+import json
+import os
+
+import pytest
+import torch
+
+from naivert_b200.models import checkpoint as ck
+from naivert_b200.models.naive_n0p5 import NAIVE_N0P5, tiny_spec
+from naivert_b200.models.reference import ReferenceModel
+from naivert_b200.models.weights import (init_state_dict, interleave_rope, prepare_weights, shard_weights)
+
+
+def test_roundtrip_and_identity(tmp_path):
+    spec = tiny_spec("fp8")
+    root = str(tmp_path / "tgt")
+    ident = ck.write_target_checkpoint(root, spec, seed=3, shard_bytes=1 << 20)
+    c = ck.LocalCheckpoint(root)
+    assert c.identity() == ident
+    assert len(set(c.weight_map.values())) > 1          # really sharded
+    ck.validate_target_layout(spec, c)
+    sd = c.load_tensors()
+    ref = init_state_dict(spec, seed=3)
+    assert set(sd) == set(ref)
+    for k in ref:
+        assert sd[k].dtype == ref[k].dtype
+        assert torch.equal(sd[k].view(torch.uint8) if sd[k].dtype == torch.float8_e4m3fn else sd[k],
+                           ref[k].view(torch.uint8) if ref[k].dtype == torch.float8_e4m3fn else ref[k])
+    assert ident.dtype_counts["F8_E4M3"] == 2 * (8 + 1) * 3
+    w, ident2 = ck.load_rank_weights(spec, root, rank=0, tp=1)
+    assert ident2 == ident
+    assert w["layers"][0]["wq"].shape[0] == 4 * 64
+    with pytest.raises(ValueError):          # 64-wide expert slices straddle the 128-wide scale blocks
+        ck.load_rank_weights(spec, root, rank=1, tp=2)
+    spec32 = tiny_spec("fp32")
+    ck.write_target_checkpoint(str(tmp_path / "t32"), spec32, seed=3)
+    w2, _ = ck.load_rank_weights(spec32, str(tmp_path / "t32"), rank=1, tp=2)
+    assert w2["layers"][0]["wq"].shape[0] == 2 * 64 and w2["layers"][0]["gate"]["w"].shape == (9, 64, 256)
+
+
+def test_pinned_identity_mismatch(tmp_path):
+    spec = tiny_spec("fp32")
+    a = ck.write_target_checkpoint(str(tmp_path / "a"), spec, seed=0)
+    b = ck.write_target_checkpoint(str(tmp_path / "b"), tiny_spec("fp8"), seed=0)
+    with pytest.raises(ck.CheckpointError):
+        ck.load_rank_weights(spec, str(tmp_path / "a"), 0, 1, expect=b)
+    ck.load_rank_weights(spec, str(tmp_path / "a"), 0, 1, expect=a)
+
+
+def test_bad_header_rejected(tmp_path):
+    p = tmp_path / "x.safetensors"
+    hdr = json.dumps({"t": {"dtype": "F16", "shape": [2], "data_offsets": [0, 4]}}).encode()
+    p.write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 4)
+    with pytest.raises(ck.CheckpointError):
+        ck.read_header(str(p))
+    hdr = json.dumps({"t": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}).encode()
+    p.write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 4)
+    with pytest.raises(ck.CheckpointError):
+        ck.read_header(str(p))
+
+
+def test_missing_tensor_detected(tmp_path):
+    spec = tiny_spec("fp32")
+    sd = init_state_dict(spec, 0)
+    sd.pop("model.layers.1.self_attn.attention_sink_bias")
+    ck.write_target_checkpoint(str(tmp_path / "t"), spec, state_dict=sd)
+    with pytest.raises(ck.CheckpointError):
+        ck.validate_target_layout(spec, ck.LocalCheckpoint(str(tmp_path / "t")))
+
+
+def test_full_geometry_tensor_census():
+    names = ck.expected_target_names(NAIVE_N0P5)
+    counts = {}
+    for dt in names.values():
+        counts[dt] = counts.get(dt, 0) + 1
+    # 47 MoE layers x 256 experts x 3 projections in e4m3, each with an fp32 block-scale tensor,
+    # plus 47 routers and 47 correction biases in fp32 (the reference pins the same census).
+    assert counts["F8_E4M3"] == 36096
+    assert counts["F32"] == 36096 + 94
+    assert sum(counts.values()) == 72664
+
+
+def test_interleave_rope_matches_rotate_half():
+    torch.manual_seed(0)
+    heads, hd, rd, H = 2, 8, 4, 5
+    w = torch.randn(heads * hd, H)
+    x = torch.randn(H)
+    y = (w @ x).reshape(heads, hd)
+    ang = torch.tensor([0.3, 1.1])
+    # rotate-half convention on the checkpoint order
+    re, im = y[:, :2], y[:, 2:4]
+    want_re, want_im = re * ang.cos() - im * ang.sin(), re * ang.sin() + im * ang.cos()
+    yi = (interleave_rope(w, heads, hd, rd) @ x).reshape(heads, hd)
+    got_re = yi[:, 0:4:2] * ang.cos() - yi[:, 1:4:2] * ang.sin()
+    got_im = yi[:, 0:4:2] * ang.sin() + yi[:, 1:4:2] * ang.cos()
+    assert torch.allclose(got_re, want_re, atol=1e-6) and torch.allclose(got_im, want_im, atol=1e-6)
+    assert torch.equal(yi[:, rd:], y[:, rd:])
+
+
+def test_tp_sharded_partials_recombine():
+    spec = tiny_spec("fp32")
+    w = prepare_weights(spec, init_state_dict(spec, 0))
+    full = ReferenceModel(spec, w, tp=1, capacity=32)
+    toks = torch.arange(8)
+    want = full.step(toks, 0)
+    # o_proj columns of both ranks tile the full matrix; lm_head rows tile the vocabulary
+    s0, s1 = shard_weights(spec, w, 0, 2), shard_weights(spec, w, 1, 2)
+    assert torch.equal(torch.cat((s0["lm_head"], s1["lm_head"])), w["lm_head"])
+    assert torch.equal(torch.cat((s0["layers"][0]["wo"]["w"], s1["layers"][0]["wo"]["w"]), 1), w["layers"][0]["wo"]["w"])
+    got = ReferenceModel(spec, w, tp=2, capacity=32).step(toks, 0)
+    assert torch.allclose(got, want, atol=1e-4)
+
+
+def test_draft_checkpoint(tmp_path):
+    spec = tiny_spec("fp32")
+    ck.write_draft_checkpoint(str(tmp_path / "d"), spec)
+    w, _ = ck.load_draft_rank_weights(spec, str(tmp_path / "d"), rank=0, tp=2)
+    assert w["fc"].shape == (256, 256)
+    bad = tiny_spec("fp32")
+    import dataclasses
+    bad = dataclasses.replace(bad, draft=dataclasses.replace(bad.draft, markov_rank=16))
+    with pytest.raises(ck.CheckpointError):
+        ck.load_draft_rank_weights(bad, str(tmp_path / "d"), 0, 1)
+
+
+def test_resolve_newest_step(tmp_path, monkeypatch):
+    for s in ("step_5", "step_40"):
+        os.makedirs(tmp_path / "run" / s)
+    monkeypatch.setenv("NAIVERT_MODEL_ROOTS", str(tmp_path))
+    assert ck.resolve_checkpoint("run").endswith("step_40")
