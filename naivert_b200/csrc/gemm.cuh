@@ -1,0 +1,382 @@
+// Skinny-M tcgen05 GEMM engine for decode / verify / draft rows (1..16 token rows).
+//
+// Operands are swapped relative to the usual orientation: the *weight* tile is the UMMA
+// A operand (M = 128 output features fill the 128 TMEM lanes) and the token rows are the
+// B operand (N = 16 columns).  One CTA owns one 128-feature output tile.  Warp roles:
+//   warp 0     : TMA producer  (weights: 128 x 128-byte swizzled tiles; tokens: 16 x 128-byte tiles)
+//   warp 1     : TMEM allocator + UMMA issuer (one elected lane)
+//   warps 2..5 : epilogue, one TMEM lane quadrant each (thread = one output feature,
+//                registers = the 16 token columns)
+// Block-scaled e4m3 (W8A8): every 128-wide K block gets a fresh TMEM accumulator
+// (ring of NBUF buffers); the epilogue multiplies by weight-block scale x activation-block
+// scale and promotes in fp32 registers in ascending K order, so results do not depend on
+// pipeline timing.  bf16 weights accumulate all of K in one TMEM buffer.
+//
+// Grouped modes cover the MoE: kGroupItem (grid.y = active expert slot; gate/up) and
+// kGroupLoop (the CTA walks every active expert, weighting by the routing probability;
+// down projection).  Epilogues: plain store, SiLU(gate)*up + e4m3 re-quantisation, and the
+// fused tensor-parallel all-reduce (+ residual) over peer memory.
+//
+// Reference counterparts (mma.sync based unless noted): naivert/body/unproj_o_allreduce/,
+// naivert/body/down_allreduce/, naivert/body/expert_select_up_gate_silu/,
+// naivert/body/expert_down_allreduce/expert_down_w8a8.cuh (tcgen05 M128xN8),
+// naivert/body/rmsnorm_head_proj/, naivert/common/tp8_mailbox.cuh.
+#pragma once
+#include "ptx.cuh"
+
+namespace nrt {
+
+constexpr int kTileN = 128;        // output features per CTA (UMMA M)
+constexpr int kTok = 16;           // token columns (UMMA N)
+constexpr int kKBytes = 128;       // bytes of K per stage row (one swizzle atom)
+constexpr int kATileBytes = kTileN * kKBytes;   // 16 KiB
+constexpr int kBTileBytes = kTok * kKBytes;     // 2 KiB
+constexpr int kMaxPeers = 8;
+constexpr int kRowPairs = kTok / 2;             // tagged words per feature per source rank
+constexpr int kMailboxSlabs = 4;
+
+enum GroupMode : int { kGroupNone = 0, kGroupItem = 1, kGroupLoop = 2 };
+enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4 };
+
+struct FabricArgs {
+  uint64_t* mailbox[kMaxPeers];   // mailbox[p] = base of rank p's mailbox (peer-mapped); mailbox[rank] is local
+  const uint32_t* epoch;          // device word; advanced once per step/round
+  uint32_t* status;               // local error status word
+  int tp;
+  int rank;
+  int call_idx;                   // position of this all-reduce inside one step (tag + slab selection)
+  int features;                   // row width of the all-reduced tensor (mailbox stride)
+  unsigned long long timeout_ns;
+};
+
+struct GemmArgs {
+  int n_total;                    // output features of one group (weight rows)
+  int k_total;                    // K in elements
+  int rows;                       // valid token rows (<= 16)
+  int a_group;                    // fixed weight group (z coordinate) for kGroupNone
+  // grouped modes
+  const int* n_active;            // number of active expert slots
+  const int* active_ids;          // [slots] expert id per slot (ascending)
+  const float* probs;             // [slots][16] routing probability of token r for slot
+  int max_slots;
+  // block scales (fp8 only)
+  const float* w_scale0;          // [groups][n_total/128][k_total/128]
+  const float* w_scale1;          // second matrix in dual mode
+  const float* a_scale;           // [slots or 1][16][k_total/128]
+  // outputs
+  float* out_f32;                 // kEpiStoreF32: [rows][ld_out]
+  __nv_bfloat16* out_bf16;        // kEpiStoreBF16 / kEpiAllReduce result / kEpiSiluBF16
+  int ld_out;
+  float out_scale;                // multiplies the stored value (kEpiStore*)
+  uint8_t* out_q;                 // kEpiSiluQuant: e4m3 [slots*16][n_total]
+  float* out_qscale;              // kEpiSiluQuant: [slots*16][n_total/128]
+  const __nv_bfloat16* resid;     // kEpiAllReduce: residual [rows][ld_out]
+  __nv_bfloat16* out_copy;        // kEpiAllReduce: optional second copy (draft feature tap)
+  FabricArgs fab;
+  uint32_t* status;
+};
+
+template <bool FP8, bool DUAL>
+struct GemmCfg {
+  static constexpr int kStageBytes = (DUAL ? 2 : 1) * kATileBytes + kBTileBytes;
+  static constexpr int kStages = DUAL ? 5 : 8;
+  static constexpr int kAccCols = DUAL ? 2 * kTok : kTok;          // TMEM columns per accumulator buffer
+  static constexpr int kAccBufs = FP8 ? (DUAL ? 4 : 8) : 1;
+  static constexpr int kTmemCols = (kAccCols * kAccBufs < 32) ? 32 : kAccCols * kAccBufs;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers + scratch*/;
+};
+
+struct GemmSmemTail {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[8];
+  uint64_t acc_empty[8];
+  uint32_t tmem_base;
+  uint32_t pad;
+  float red[4][kTok];
+};
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// smallest power of two >= amax / 448 (exact exponent arithmetic); 1 for amax == 0
+__device__ __forceinline__ float pow2_scale(float amax) {
+  if (!(amax > 0.0f)) return 1.0f;
+  float t = amax * (1.0f / 448.0f);
+  int e;
+  float m = frexpf(t, &e);            // t = m * 2^e, m in [0.5, 1)
+  if (m == 0.5f) e -= 1;
+  return ldexpf(1.0f, e);
+}
+
+template <bool FP8, bool DUAL, int EPI, int GROUP>
+__global__ void __launch_bounds__(192, 1)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                   const __grid_constant__ CUtensorMap tmB, const GemmArgs p) {
+  using Cfg = GemmCfg<FP8, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(smem + Cfg::kStages * Cfg::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x;
+  const int n0 = n_tile * kTileN;
+  const int kb_count = p.k_total / (FP8 ? 128 : 64);
+  constexpr int kElemsPerStage = FP8 ? 128 : 64;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
+    for (int i = 0; i < Cfg::kAccBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA0);
+    tma_prefetch_desc(&tmB);
+    if (DUAL) tma_prefetch_desc(&tmA1);
+  }
+  if (warp == 1) { tmem_alloc(&tail->tmem_base, Cfg::kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tail->tmem_base;
+
+  // Everything below reads data produced by earlier kernels of the stream.
+  griddep_launch();
+  griddep_wait();
+
+  int n_groups = 1, g_first = 0, g_step = 1;
+  if (GROUP == kGroupItem) {
+    const int na = min(*p.n_active, p.max_slots);
+    n_groups = (int)blockIdx.y < na ? 1 : 0;
+    g_first = blockIdx.y;
+  } else if (GROUP == kGroupLoop) {
+    const int na = min(*p.n_active, p.max_slots);
+    g_first = blockIdx.y;
+    g_step = gridDim.y;
+    n_groups = na > g_first ? (na - g_first + g_step - 1) / g_step : 0;
+  }
+  const int units = n_groups * kb_count;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      for (int u = 0; u < units; ++u) {
+        const int st = u % Cfg::kStages;
+        if (u >= Cfg::kStages &&
+            !mbar_wait(&tail->empty[st], ((u / Cfg::kStages) & 1) ^ 1, p.status, kSiteStageEmpty | st)) break;
+        const int g = u / kb_count, kb = u - g * kb_count;
+        const int slot = g_first + g * g_step;
+        const int z = GROUP == kGroupNone ? p.a_group : p.active_ids[slot];
+        uint8_t* sa = smem + st * Cfg::kStageBytes;
+        mbar_expect_tx(&tail->full[st], Cfg::kStageBytes);
+        tma_load_3d(sa, &tmA0, &tail->full[st], kb * kElemsPerStage, n0, z);
+        if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kb * kElemsPerStage, n0, z);
+        const int brow = (GROUP == kGroupLoop) ? slot * kTok : 0;
+        tma_load_2d(sa + (DUAL ? 2 : 1) * kATileBytes, &tmB, &tail->full[st], kb * kElemsPerStage, brow);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(FP8 ? 0u : 1u, kTileN, kTok);
+      for (int u = 0; u < units; ++u) {
+        const int st = u % Cfg::kStages;
+        const int kb = u % kb_count;
+        const int buf = FP8 ? (u % Cfg::kAccBufs) : 0;
+        if (FP8 && u >= Cfg::kAccBufs &&
+            !mbar_wait(&tail->acc_empty[buf], ((u / Cfg::kAccBufs) & 1) ^ 1, p.status, kSiteAccEmpty | buf)) break;
+        if (!mbar_wait(&tail->full[st], (u / Cfg::kStages) & 1, p.status, kSiteTmaFull | st)) break;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + st * Cfg::kStageBytes);
+        const uint64_t da0 = umma_desc_sw128(sa);
+        const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
+        const uint64_t db = umma_desc_sw128(sa + (DUAL ? 2 : 1) * kATileBytes);
+        const uint32_t d0 = tmem + buf * Cfg::kAccCols;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {          // 4 x 32 bytes of K per 128-byte swizzle atom
+          const uint32_t acc = FP8 ? (j > 0) : (kb > 0 || j > 0);
+          if (FP8) {
+            umma_f8(d0, da0 + 2 * j, db + 2 * j, idesc, acc);
+            if (DUAL) umma_f8(d0 + kTok, da1 + 2 * j, db + 2 * j, idesc, acc);
+          } else {
+            umma_bf16(d0, da0 + 2 * j, db + 2 * j, idesc, acc);
+            if (DUAL) umma_bf16(d0 + kTok, da1 + 2 * j, db + 2 * j, idesc, acc);
+          }
+        }
+        umma_commit(&tail->empty[st]);                                  // frees the smem stage
+        if (FP8 || kb == kb_count - 1) umma_commit(&tail->acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int row = quad * 32 + lane;                // feature within the tile
+    const int n = n0 + row;
+    const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
+    const int nt_count = p.n_total / kTileN;
+    float mix0[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) mix0[r] = 0.f;
+    float mix1[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) mix1[r] = 0.f;
+    bool ok = true;
+    int u = 0;
+    for (int g = 0; g < n_groups && ok; ++g) {
+      const int slot = g_first + g * g_step;
+      const int z = GROUP == kGroupNone ? p.a_group : p.active_ids[slot];
+      float acc0[kTok], acc1[kTok];
+#pragma unroll
+      for (int r = 0; r < kTok; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+      if (FP8) {
+        const float* as = p.a_scale + (size_t)(GROUP == kGroupLoop ? slot : 0) * kTok * kb_count;
+        const float* ws0 = p.w_scale0 + ((size_t)z * nt_count + n_tile) * kb_count;
+        const float* ws1 = DUAL ? p.w_scale1 + ((size_t)z * nt_count + n_tile) * kb_count : nullptr;
+        for (int kb = 0; kb < kb_count; ++kb, ++u) {
+          const int buf = u % Cfg::kAccBufs;
+          if (!mbar_wait(&tail->acc_full[buf], (u / Cfg::kAccBufs) & 1, p.status, kSiteAccFull | buf)) { ok = false; break; }
+          tc_fence_after();
+          float v0[kTok], v1[kTok];
+          tmem_ld16(lane_addr + buf * Cfg::kAccCols, v0);
+          if (DUAL) tmem_ld16(lane_addr + buf * Cfg::kAccCols + kTok, v1);
+          tc_fence_before();
+          mbar_arrive(&tail->acc_empty[buf]);
+          const float w0 = ws0[kb];
+          const float w1 = DUAL ? ws1[kb] : 0.f;
+#pragma unroll
+          for (int r = 0; r < kTok; ++r) {
+            const float a = as[r * kb_count + kb];
+            acc0[r] += v0[r] * (a * w0);
+            if (DUAL) acc1[r] += v1[r] * (a * w1);
+          }
+        }
+      } else {
+        if (!mbar_wait(&tail->acc_full[0], 0, p.status, kSiteAccFull)) { ok = false; break; }
+        tc_fence_after();
+        tmem_ld16(lane_addr, acc0);
+        if (DUAL) tmem_ld16(lane_addr + kTok, acc1);
+        tc_fence_before();
+      }
+      if (GROUP == kGroupLoop) {
+        const float* pr = p.probs + (size_t)slot * kTok;
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) mix0[r] += pr[r] * acc0[r];
+      } else {
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) { mix0[r] = acc0[r]; mix1[r] = acc1[r]; }
+      }
+    }
+
+    // ---------------------------------------------------------------- epilogue op
+    const bool live = n_groups > 0 && n < p.n_total;
+    if (EPI == kEpiStoreF32) {
+#pragma unroll
+      for (int r = 0; r < kTok; ++r)
+        if (live && r < p.rows) p.out_f32[(size_t)r * p.ld_out + n] = mix0[r] * p.out_scale;
+    } else if (EPI == kEpiStoreBF16) {
+#pragma unroll
+      for (int r = 0; r < kTok; ++r)
+        if (live && r < p.rows) p.out_bf16[(size_t)r * p.ld_out + n] = __float2bfloat16_rn(mix0[r] * p.out_scale);
+    } else if (EPI == kEpiSiluBF16) {
+#pragma unroll
+      for (int r = 0; r < kTok; ++r)
+        if (live && r < p.rows) p.out_bf16[(size_t)r * p.ld_out + n] = __float2bfloat16_rn(silu(mix0[r]) * mix1[r]);
+    } else if (EPI == kEpiSiluQuant) {
+      if (n_groups > 0) {
+        // y = silu(gate) * up in fp32; one power-of-two scale per (token, this 128-feature tile)
+        float y[kTok];
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) {
+          y[r] = silu(mix0[r]) * mix1[r];
+          float m = fabsf(y[r]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+          if (lane == 0) tail->red[quad][r] = m;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const size_t qrow = (size_t)(GROUP == kGroupNone ? 0 : g_first) * kTok;
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) {
+          const float am = fmaxf(fmaxf(tail->red[0][r], tail->red[1][r]), fmaxf(tail->red[2][r], tail->red[3][r]));
+          const float s = pow2_scale(am);
+          const __nv_fp8_e4m3 q(y[r] / s);
+          p.out_q[(qrow + r) * p.n_total + n] = *reinterpret_cast<const uint8_t*>(&q);
+          if (row == 0) p.out_qscale[(qrow + r) * nt_count + n_tile] = s;
+        }
+      }
+    } else if (EPI == kEpiAllReduce) {
+      const FabricArgs& f = p.fab;
+      // Each rank rounds its partial to bf16, pushes it to every peer as tagged words and adds
+      // the partials of all ranks in rank order in fp32 on top of the residual.
+      uint32_t w[kMaxPeers][kRowPairs];
+      const int pairs = (p.rows + 1) >> 1;
+      float sum[kTok];
+#pragma unroll
+      for (int r = 0; r < kTok; ++r)
+        sum[r] = (r < p.rows && n < p.n_total) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
+      uint32_t own[kRowPairs];
+#pragma unroll
+      for (int j = 0; j < kRowPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
+      if (f.tp > 1 && n < p.n_total) {
+        const uint32_t tag = (*f.epoch) * 1024u + (uint32_t)f.call_idx + 1u;
+        const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
+        for (int d = 1; d < f.tp; ++d) {
+          const int peer = (f.rank + d) % f.tp;
+          uint64_t* dst = f.mailbox[peer] + ((slab + f.rank) * f.features + n) * kRowPairs;
+#pragma unroll
+          for (int j = 0; j < kRowPairs; ++j)
+            if (j < pairs) st_tagged(dst + j, tag, own[j]);
+        }
+        // Batched poll: every missing word of every source is re-read per sweep, so the
+        // loads of one sweep overlap instead of paying one fabric round trip each.
+        uint64_t missing = 0;
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+          for (int j = 0; j < kRowPairs; ++j) {
+            if (s == f.rank) w[s][j] = own[j];
+            else if (s < f.tp && j < pairs) missing |= 1ull << (s * kRowPairs + j);
+            else w[s][j] = 0u;
+          }
+        const uint64_t deadline = globaltimer() + f.timeout_ns;
+        const uint64_t* base = f.mailbox[f.rank] + (slab * f.features + n) * kRowPairs;
+        for (uint32_t sweep = 0; missing != 0; ++sweep) {
+#pragma unroll
+          for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+            for (int j = 0; j < kRowPairs; ++j)
+              if (missing & (1ull << (s * kRowPairs + j))) {
+                uint32_t t, v;
+                ld_tagged(base + (size_t)s * f.features * kRowPairs + j, t, v);
+                if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kRowPairs + j)); }
+              }
+          if ((sweep & 255u) == 255u) {
+            if (*reinterpret_cast<volatile uint32_t*>(f.status) != 0u) break;
+            if (globaltimer() > deadline) { report(f.status, kSiteMailbox | (uint32_t)__ffsll((long long)missing)); break; }
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+          for (int j = 0; j < kRowPairs; ++j)
+            if (s < f.tp) { sum[2 * j] += bf16_lo(w[s][j]); sum[2 * j + 1] += bf16_hi(w[s][j]); }
+      } else {
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) sum[r] += round_bf16(mix0[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < kTok; ++r)
+        if (r < p.rows && n < p.n_total) {
+          const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
+          p.out_bf16[(size_t)r * p.ld_out + n] = o;
+          if (p.out_copy) p.out_copy[(size_t)r * p.ld_out + n] = o;
+        }
+    }
+    (void)ok;
+  }
+
+  drain_on_error(p.status);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, Cfg::kTmemCols); }
+}
+
+}  // namespace nrt

@@ -1,0 +1,760 @@
+// Non-GEMM kernels of the target (and draft) decode/verify body: embedding gather, RoPE table,
+// RMSNorm + e4m3 packet, q/k/v post-processing (RoPE, KV-cache append, indexer key/query
+// quantisation), row attention (sliding window with sink, dense range, or top-k index list),
+// lightning-indexer logits, exact top-k selection, and the MoE router.
+//
+// Reference counterparts: naivert/kernels/model_ops/extension/embed_gather_bindings.cu,
+// naivert/body/attn_dsa/attn_dsa_body.cuh (publish_query/kv/ki, compute_attention),
+// naivert/body/attn_swa/attn_swa_body.cuh, naivert/body/attn_dsa/topk_grid_select.cuh,
+// naivert/body/rmsnorm_expert_proj/, naivert/body/expert_select_up_gate_silu/ (compute_route).
+#include "gemm.cuh"
+#include "launch.hpp"
+
+#include <float.h>
+
+using namespace nrt;
+
+namespace {
+
+constexpr int kMaxRows = 16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) t += red[i];
+  return t;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) t = fmaxf(t, red[i]);
+  return t;
+}
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  const __nv_fp8_e4m3 q(v);
+  return *reinterpret_cast<const uint8_t*>(&q);
+}
+__device__ __forceinline__ float from_e4m3(uint8_t b) {
+  __nv_fp8_e4m3 q;
+  *reinterpret_cast<uint8_t*>(&q) = b;
+  return float(q);
+}
+
+// ----------------------------------------------------------------------------- embedding gather
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                                  __nv_bfloat16* __restrict__ x, int hidden, int rows, int vocab) {
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  int t = tokens[r];
+  t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)t * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(x + (size_t)r * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ----------------------------------------------------------------------------- RoPE tables for this step
+// table[r][i] = (cos, sin)(pos_r * theta^(-2i/dim)), evaluated in fp64 and rounded to fp32.
+__global__ void rope_table_kernel(const int* __restrict__ pos0, int rows, int dim, double theta, float2* __restrict__ out) {
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x, i = threadIdx.x;
+  if (r >= rows || i >= dim / 2) return;
+  const double inv = pow(theta, -2.0 * (double)i / (double)dim);
+  const double ang = (double)(*pos0 + r) * inv;
+  out[r * (dim / 2) + i] = make_float2((float)cos(ang), (float)sin(ang));
+}
+
+// ----------------------------------------------------------------------------- RMSNorm (+ e4m3 packet)
+// One CTA per row (16 CTAs; rows >= `rows` are zero-filled so the padded GEMM operand is clean).
+// xn = bf16(x * rsqrt(mean(x^2) + eps) * g); optional packet: e4m3(xn / s) with one power-of-two
+// scale s per 128 channels.
+__global__ void __launch_bounds__(256)
+prep_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, int hidden, int rows,
+                 float eps, __nv_bfloat16* __restrict__ xn, uint8_t* __restrict__ x8, float* __restrict__ xs) {
+  __shared__ float red[8];
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x;
+  const int per = hidden / 8;              // 8-element vectors per row
+  if (r >= rows) {
+    for (int i = threadIdx.x; i < per; i += 256) {
+      if (xn) reinterpret_cast<uint4*>(xn + (size_t)r * hidden)[i] = make_uint4(0, 0, 0, 0);
+      if (x8) reinterpret_cast<uint2*>(x8 + (size_t)r * hidden)[i] = make_uint2(0, 0);
+    }
+    if (xs) for (int i = threadIdx.x; i < hidden / 128; i += 256) xs[(size_t)r * (hidden / 128) + i] = 1.f;
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r * hidden);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < per; i += 256) {
+    uint4 v = src[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); ss += f.x * f.x + f.y * f.y; }
+  }
+  ss = block_sum<256>(ss, red);
+  const float rs = rsqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < per; i += 256) {
+    uint4 v = src[i];
+    uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    float o[8];
+    float am = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(h[j]);
+      float2 g = __bfloat1622float2(gh[j]);
+      o[2 * j] = round_bf16(f.x * rs * g.x);
+      o[2 * j + 1] = round_bf16(f.y * rs * g.y);
+      am = fmaxf(am, fmaxf(fabsf(o[2 * j]), fabsf(o[2 * j + 1])));
+    }
+    if (xn) {
+      uint4 w;
+      __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wh[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+      reinterpret_cast<uint4*>(xn + (size_t)r * hidden)[i] = w;
+    }
+    if (x8) {
+      // 16 consecutive threads cover one 128-channel block
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+      const float s = pow2_scale(am);
+      uint2 q;
+      uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qb[j] = to_e4m3(o[j] / s);
+      reinterpret_cast<uint2*>(x8 + (size_t)r * hidden)[i] = q;
+      if ((i & 15) == 0) xs[(size_t)r * (hidden / 128) + (i >> 4)] = s;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- q/k/v post-processing
+struct AttnPostArgs {
+  const float* qkv;          // [rows][ld] fp32 projection outputs: q | k | v | iq | ik | iw
+  int ld;
+  int rows;
+  const int* pos0;
+  int heads, kv_heads, head_dim, v_dim, rope_dim;
+  float value_scale;
+  const float2* rope;        // [rows][rope_dim/2]
+  __nv_bfloat16* q_out;      // [rows][heads][head_dim]
+  __nv_bfloat16* k_cache;    // [cap][kv_heads][head_dim]
+  __nv_bfloat16* v_cache;    // [cap][kv_heads][v_dim]
+  int ring;                  // > 0: position p is stored at p % ring
+  // optional per-head RMS norms (draft q_norm / k_norm), applied before RoPE
+  const __nv_bfloat16* q_norm;
+  const __nv_bfloat16* k_norm;
+  float norm_eps;
+  // indexer (idx_heads == 0: none)
+  int idx_heads, idx_dim, idx_rope;
+  const float2* idx_rope_tab;   // [rows][idx_rope/2]
+  const __nv_bfloat16* ik_w;
+  const __nv_bfloat16* ik_b;
+  float ln_eps, idx_weight_scale;
+  uint8_t* iq8;              // [16*idx_heads][idx_dim] e4m3 (row r, head h at r*idx_heads + h)
+  float* ihw;                // [16][idx_heads] head weight * query scale
+  uint8_t* ik_cache;         // [cap][idx_dim]
+  float* ik_scale;           // [cap]
+  int col_q, col_k, col_v, col_iq, col_ik, col_iw;
+};
+
+__device__ __forceinline__ void rope_pair(float& a, float& b, float2 cs) {
+  const float re = a * cs.x - b * cs.y;
+  const float im = a * cs.y + b * cs.x;
+  a = re;
+  b = im;
+}
+
+// One CTA per row; warps take whole heads.
+__global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
+  __shared__ float red[8];
+  __shared__ float kbuf[256];
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x;
+  if (r >= a.rows) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* src = a.qkv + (size_t)r * a.ld;
+  const int pos = *a.pos0 + r;
+  const size_t slot = a.ring > 0 ? (size_t)(pos % a.ring) : (size_t)pos;
+  const float2* rt = a.rope + (size_t)r * (a.rope_dim / 2);
+
+  // q heads and k heads: [optional head RMS norm] -> bf16 -> RoPE on adjacent pairs -> bf16
+  const int qk_heads = a.heads + a.kv_heads;
+  for (int h = warp; h < qk_heads; h += 8) {
+    const bool is_q = h < a.heads;
+    const float* hs = is_q ? src + a.col_q + h * a.head_dim : src + a.col_k + (h - a.heads) * a.head_dim;
+    __nv_bfloat16* dst = is_q ? a.q_out + ((size_t)r * a.heads + h) * a.head_dim
+                              : a.k_cache + (slot * a.kv_heads + (h - a.heads)) * a.head_dim;
+    const __nv_bfloat16* nw = is_q ? a.q_norm : a.k_norm;
+    float rs = 1.f;
+    if (nw) {
+      float ss = 0.f;
+      for (int d = lane; d < a.head_dim; d += 32) { const float v = round_bf16(hs[d]); ss += v * v; }
+      ss = warp_sum(ss);
+      rs = rsqrtf(ss / (float)a.head_dim + a.norm_eps);
+    }
+    for (int i = lane; i < a.head_dim / 2; i += 32) {
+      float x0 = round_bf16(hs[2 * i]), x1 = round_bf16(hs[2 * i + 1]);
+      if (nw) {
+        x0 = round_bf16(x0 * rs * __bfloat162float(nw[2 * i]));
+        x1 = round_bf16(x1 * rs * __bfloat162float(nw[2 * i + 1]));
+      }
+      if (2 * i < a.rope_dim) rope_pair(x0, x1, rt[i]);
+      reinterpret_cast<__nv_bfloat162*>(dst)[i] = __floats2bfloat162_rn(x0, x1);
+    }
+  }
+  // v heads
+  for (int i = threadIdx.x; i < a.kv_heads * a.v_dim; i += 256)
+    a.v_cache[slot * a.kv_heads * a.v_dim + i] = __float2bfloat16_rn(src[a.col_v + i] * a.value_scale);
+
+  if (a.idx_heads == 0) return;
+  const float2* it = a.idx_rope_tab + (size_t)r * (a.idx_rope / 2);
+  // indexer queries: bf16 -> RoPE -> bf16 -> e4m3 with a per-(row, head) scale folded into the head weight
+  for (int h = warp; h < a.idx_heads; h += 8) {
+    const float* hs = src + a.col_iq + h * a.idx_dim;
+    float v[8];                                   // idx_dim <= 256: 4 pairs per lane
+    float am = 0.f;
+    const int pairs = a.idx_dim / 2;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int i = lane + 32 * t;
+      float x0 = 0.f, x1 = 0.f;
+      if (i < pairs) {
+        x0 = round_bf16(hs[2 * i]);
+        x1 = round_bf16(hs[2 * i + 1]);
+        if (2 * i < a.idx_rope) { rope_pair(x0, x1, it[i]); x0 = round_bf16(x0); x1 = round_bf16(x1); }
+      }
+      v[2 * t] = x0;
+      v[2 * t + 1] = x1;
+      am = fmaxf(am, fmaxf(fabsf(x0), fabsf(x1)));
+    }
+    am = warp_max(am);
+    const float s = am > 0.f ? am / 448.f : 1.f;
+    uint8_t* dst = a.iq8 + ((size_t)r * a.idx_heads + h) * a.idx_dim;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int i = lane + 32 * t;
+      if (i < pairs) { dst[2 * i] = to_e4m3(v[2 * t] / s); dst[2 * i + 1] = to_e4m3(v[2 * t + 1] / s); }
+    }
+    if (lane == 0) a.ihw[r * a.idx_heads + h] = src[a.col_iw + h] * a.idx_weight_scale * s;
+  }
+  // indexer key: LayerNorm (fp32) -> bf16 -> RoPE -> bf16 -> e4m3 with a per-row scale amax/448
+  {
+    const int d = threadIdx.x;
+    const float kv = d < a.idx_dim ? src[a.col_ik + d] : 0.f;
+    const float mean = block_sum<256>(kv, red) / (float)a.idx_dim;
+    const float dv = d < a.idx_dim ? kv - mean : 0.f;
+    const float var = block_sum<256>(dv * dv, red) / (float)a.idx_dim;
+    float kn = 0.f;
+    if (d < a.idx_dim)
+      kn = round_bf16(dv * rsqrtf(var + a.ln_eps) * __bfloat162float(a.ik_w[d]) + __bfloat162float(a.ik_b[d]));
+    kbuf[d] = kn;
+    __syncthreads();
+    if (d < a.idx_rope) {
+      float x0 = kbuf[d & ~1], x1 = kbuf[d | 1];
+      rope_pair(x0, x1, it[d >> 1]);
+      kn = round_bf16((d & 1) ? x1 : x0);
+    }
+    const float am = block_max<256>(d < a.idx_dim ? fabsf(kn) : 0.f, red);
+    const float s = am > 0.f ? am / 448.f : 1.f;
+    if (d < a.idx_dim) a.ik_cache[(size_t)pos * a.idx_dim + d] = to_e4m3(kn / s);
+    if (d == 0) a.ik_scale[pos] = s;
+  }
+}
+
+// ----------------------------------------------------------------------------- row attention
+struct AttnArgs {
+  const __nv_bfloat16* q;        // [rows][heads][head_dim]
+  const __nv_bfloat16* k_cache;  // [cap][kv_heads][head_dim]
+  const __nv_bfloat16* v_cache;  // [cap][kv_heads][v_dim]
+  const int* pos0;
+  int rows, heads, kv_heads, head_dim, v_dim;
+  float scale;
+  int mode;                      // 0: sliding window (ring)   1: dense [0, pos] or index list   2: draft block
+  int window, ring;
+  const __nv_bfloat16* sink;     // [heads] or null
+  const int* sel;                // mode 1: [16][top_k] ascending key ids (used when pos + 1 > top_k)
+  int top_k;
+  const __nv_bfloat16* k_blk;    // mode 2: block rows' own keys/values [rows][kv_heads][dim]
+  const __nv_bfloat16* v_blk;
+  // outputs: bf16 o [rows][heads*v_dim], and/or the e4m3 packet (one K block per head when v_dim == 128)
+  __nv_bfloat16* o_bf16;
+  uint8_t* o8;
+  float* o_scale;                // [16][heads*v_dim/128]
+};
+
+// One CTA (128 threads) per (head, row); keys are processed in chunks of 128 with an online softmax.
+__global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
+  __shared__ float qs[256];
+  __shared__ float sc[128];
+  __shared__ float red[4];
+  __shared__ int kid[128];
+  griddep_launch();
+  griddep_wait();
+  const int h = blockIdx.x, r = blockIdx.y;
+  if (r >= a.rows) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = h / (a.heads / a.kv_heads);
+  const int p0 = *a.pos0;
+  const int pos = p0 + r;
+  for (int d = tid; d < a.head_dim; d += 128)
+    qs[d] = __bfloat162float(a.q[((size_t)r * a.heads + h) * a.head_dim + d]);
+  __syncthreads();
+
+  int lo = 0, count = 0, ctx = 0;
+  bool use_sel = false;
+  if (a.mode == 0) { lo = max(0, pos - a.window + 1); count = pos - lo + 1; }
+  else if (a.mode == 1) { use_sel = pos + 1 > a.top_k; count = use_sel ? a.top_k : pos + 1; }
+  else { lo = max(0, p0 - a.window); ctx = p0 - lo; count = ctx + a.rows; }
+
+  float m_run = -FLT_MAX, l_run = 0.f, acc = 0.f;      // acc: output channel tid (v_dim <= 128)
+  for (int c0 = 0; c0 < count; c0 += 128) {
+    const int n = min(128, count - c0);
+    // key ids of this chunk (negative = block row -(id+1) in mode 2)
+    if (tid < n) {
+      const int j = c0 + tid;
+      int id;
+      if (a.mode == 1) id = use_sel ? a.sel[r * a.top_k + j] : j;
+      else if (a.mode == 2) id = j < ctx ? lo + j : -(j - ctx) - 1;
+      else id = lo + j;
+      kid[tid] = id;
+    }
+    __syncthreads();
+    // scores: each warp takes keys warp, warp+4, ...; lanes split the head dimension
+    for (int t = warp; t < n; t += 4) {
+      const int id = kid[t];
+      const __nv_bfloat16* kp;
+      if (id < 0) kp = a.k_blk + ((size_t)(-id - 1) * a.kv_heads + g) * a.head_dim;
+      else {
+        const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
+        kp = a.k_cache + (slot * a.kv_heads + g) * a.head_dim;
+      }
+      float s = 0.f;
+      for (int d = lane * 2; d < a.head_dim; d += 64) {
+        const float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kp + d));
+        s += qs[d] * kv.x + qs[d + 1] * kv.y;
+      }
+      s = warp_sum(s);
+      if (lane == 0) sc[t] = s * a.scale;
+    }
+    __syncthreads();
+    const float v = tid < n ? sc[tid] : -FLT_MAX;
+    const float cm = block_max<128>(v, red);
+    const float m_new = fmaxf(m_run, cm);
+    const float e = tid < n ? __expf(v - m_new) : 0.f;
+    __syncthreads();
+    sc[tid] = e;
+    const float cs = block_sum<128>(e, red);      // contains a __syncthreads after sc[] is written
+    const float corr = __expf(m_run - m_new);
+    l_run = l_run * corr + cs;
+    acc *= corr;
+    if (tid < a.v_dim) {
+      for (int t = 0; t < n; ++t) {
+        const int id = kid[t];
+        const __nv_bfloat16* vp;
+        if (id < 0) vp = a.v_blk + ((size_t)(-id - 1) * a.kv_heads + g) * a.v_dim;
+        else {
+          const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
+          vp = a.v_cache + (slot * a.kv_heads + g) * a.v_dim;
+        }
+        acc += sc[t] * __bfloat162float(vp[tid]);
+      }
+    }
+    m_run = m_new;
+    __syncthreads();
+  }
+  if (a.sink) {                                   // extra softmax column that carries no value
+    const float sv = __bfloat162float(a.sink[h]);
+    const float m_new = fmaxf(m_run, sv);
+    const float corr = __expf(m_run - m_new);
+    l_run = l_run * corr + __expf(sv - m_new);
+    acc *= corr;
+  }
+  const float o = tid < a.v_dim ? round_bf16(acc / l_run) : 0.f;
+  const size_t col = (size_t)h * a.v_dim + tid;
+  const size_t ldo = (size_t)a.heads * a.v_dim;
+  if (a.o_bf16 && tid < a.v_dim) a.o_bf16[r * ldo + col] = __float2bfloat16_rn(o);
+  if (a.o8) {
+    const float am = block_max<128>(fabsf(o), red);
+    const float s = pow2_scale(am);
+    if (tid < a.v_dim) a.o8[r * ldo + col] = to_e4m3(o / s);
+    if (tid == 0) a.o_scale[r * (ldo / 128) + h] = s;
+  }
+}
+
+// ----------------------------------------------------------------------------- indexer logits (CUDA-core form)
+// logit[r][t] = sum_h relu(q8[r,h] . k8[t]) * hw[r,h] * ks[t] for t <= pos_r.  Used for short
+// contexts and as the cross-check of the tcgen05 sweep.
+struct IndexArgs {
+  const uint8_t* iq8;   // [16*heads][dim]
+  const float* ihw;     // [16][heads]
+  const uint8_t* ik;    // [cap][dim]
+  const float* iks;     // [cap]
+  const int* pos0;
+  int rows, heads, dim, top_k;
+  float* logits;        // [16][ld]
+  int ld;
+};
+
+__global__ void __launch_bounds__(256) index_logits_simple_kernel(const IndexArgs a) {
+  extern __shared__ float qf[];                    // [rows*heads][dim] as float
+  griddep_launch();
+  griddep_wait();
+  const int p0 = *a.pos0;
+  if (p0 + a.rows <= a.top_k) return;              // every row is still dense
+  const int total = p0 + a.rows;
+  const int nq = a.rows * a.heads;
+  for (int i = threadIdx.x; i < nq * a.dim; i += 256) qf[i] = from_e4m3(a.iq8[i]);
+  __syncthreads();
+  for (int t = blockIdx.x * 256 + threadIdx.x; t < total; t += gridDim.x * 256) {
+    float kf[128];
+    const uint4* kp = reinterpret_cast<const uint4*>(a.ik + (size_t)t * a.dim);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      if (v * 16 < a.dim) {
+        uint4 w = kp[v];
+        const uint8_t* b = reinterpret_cast<const uint8_t*>(&w);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) kf[v * 16 + j] = from_e4m3(b[j]);
+      }
+    }
+    const float ks = a.iks[t];
+    for (int r = 0; r < a.rows; ++r) {
+      float lg = 0.f;
+      for (int h = 0; h < a.heads; ++h) {
+        const float* q = qf + (r * a.heads + h) * a.dim;
+        float d = 0.f;
+#pragma unroll 16
+        for (int j = 0; j < a.dim; ++j) d += q[j] * kf[j];
+        lg += fmaxf(d, 0.f) * a.ihw[r * a.heads + h];
+      }
+      a.logits[(size_t)r * a.ld + t] = lg * ks;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- exact top-k
+// Per row: the k largest logits among positions [0, pos_r], ties to the lowest index, emitted
+// in ascending position order.  Four 8-bit radix passes over order-preserving 32-bit keys
+// find the threshold; one ordered sweep compacts the winners.
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict__ logits, int ld, const int* pos0,
+                                                         int rows, int top_k, int* __restrict__ sel) {
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t s_prefix, s_need;
+  __shared__ uint32_t wsum_gt[32], wsum_eq[32];
+  __shared__ uint32_t base_out, base_eq;
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const int n = *pos0 + r + 1;
+  if (n <= top_k) return;                           // dense row: no selection needed
+  const float* row = logits + (size_t)r * ld;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  uint32_t prefix = 0, mask = 0, need = top_k;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += 1024) {
+      const uint32_t k = order_key(row[i]);
+      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t acc = 0;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (acc + hist[b] >= need) break;
+        acc += hist[b];
+      }
+      s_prefix = prefix | ((uint32_t)b << shift);
+      s_need = need - acc;                          // winners still to take from inside bin b
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    need = s_need;
+    mask |= 255u << shift;
+  }
+  // prefix = exact threshold key; `need` elements equal to it are taken, lowest index first
+  const uint32_t thr = prefix;
+  if (tid == 0) { base_out = 0; base_eq = 0; }
+  __syncthreads();
+  for (int c0 = 0; c0 < n; c0 += 1024) {
+    const int i = c0 + tid;
+    const uint32_t k = i < n ? order_key(row[i]) : 0u;
+    const bool gt = i < n && k > thr;
+    const bool eq = i < n && k == thr;
+    const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) { wsum_gt[warp] = __popc(bg); wsum_eq[warp] = __popc(be); }
+    __syncthreads();
+    uint32_t eq_before = base_eq, gt_before = 0;
+    for (int w = 0; w < warp; ++w) { eq_before += wsum_eq[w]; gt_before += wsum_gt[w]; }
+    const uint32_t lm = (1u << lane) - 1u;
+    const uint32_t my_eq_rank = eq_before + __popc(be & lm);
+    // output position = winners before me in index order
+    // winners before me = gt before me + min(eq before me, need)
+    const uint32_t eq_in_chunk_before = my_eq_rank - base_eq;
+    const uint32_t taken_eq_before = min(my_eq_rank, need) - min(base_eq, need);
+    (void)eq_in_chunk_before;
+    const uint32_t outpos = base_out + gt_before + __popc(bg & lm) + taken_eq_before;
+    if (gt || (eq && my_eq_rank < need)) sel[r * top_k + outpos] = i;
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t tg = 0, te = 0;
+      for (int w = 0; w < 32; ++w) { tg += wsum_gt[w]; te += wsum_eq[w]; }
+      const uint32_t new_eq = base_eq + te;
+      base_out += tg + (min(new_eq, need) - min(base_eq, need));
+      base_eq = new_eq;
+    }
+    __syncthreads();
+  }
+}
+
+// ----------------------------------------------------------------------------- MoE router
+struct RouterArgs {
+  const __nv_bfloat16* xn;   // [16][hidden] normed activations
+  const float* w;            // [experts][hidden] fp32
+  const float* bias;         // [experts] or null
+  int hidden, experts, rows, top_k;
+  int sigmoid;               // 1: sigmoid(+bias for the choice); 0: softmax
+  int normalize;
+  float route_scale;
+  float* scores;             // [16][experts] scratch
+  unsigned int* ticket;      // zero-initialised counter (reset by the last CTA)
+  int* n_active;             // outputs
+  int* active_ids;           // [max_slots]
+  float* probs;              // [max_slots][16]
+  int* topk_ids;             // [16][top_k]
+  float* topk_p;             // [16][top_k]
+  int max_slots;
+};
+
+// grid = experts / 2 CTAs; each warp-pair of a CTA... one CTA computes 2 experts x 16 rows; the last CTA
+// to finish performs the per-row top-k and builds the ascending active-expert list.
+__global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
+  __shared__ float part[8][2][kMaxRows];
+  __shared__ bool last;
+  __shared__ unsigned int used[8];                  // bitmap over <= 256 experts
+  __shared__ int slot_of[256];
+  griddep_launch();
+  griddep_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e0 = blockIdx.x * 2;
+  float acc[2][kMaxRows];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) acc[j][r] = 0.f;
+  for (int k = tid * 4; k < a.hidden; k += 1024) {
+    float4 w0 = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k);
+    float4 w1 = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * a.hidden + k)
+                                     : make_float4(0, 0, 0, 0);
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) {
+      if (r < a.rows) {
+        const uint2 xv = *reinterpret_cast<const uint2*>(a.xn + (size_t)r * a.hidden + k);
+        const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+        const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+        acc[0][r] += x01.x * w0.x + x01.y * w0.y + x23.x * w0.z + x23.y * w0.w;
+        acc[1][r] += x01.x * w1.x + x01.y * w1.y + x23.x * w1.z + x23.y * w1.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) {
+      const float v = warp_sum(acc[j][r]);
+      if (lane == 0) part[warp][j][r] = v;
+    }
+  __syncthreads();
+  if (tid < 2 * kMaxRows) {
+    const int j = tid / kMaxRows, r = tid % kMaxRows;
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += part[w][j][r];
+    if (e0 + j < a.experts && r < a.rows) a.scores[r * a.experts + e0 + j] = s;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int t = atomicAdd(a.ticket, 1u);
+    last = (t == gridDim.x - 1);
+    if (last) *a.ticket = 0u;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (tid < 8) used[tid] = 0u;
+  __syncthreads();
+  // one warp per row: iterative arg-max with lowest-index ties
+  for (int r = warp; r < a.rows; r += 8) {
+    float sc[8], ch[8];                             // experts lane, lane+32, ... (<= 256 experts)
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      const float v = e < a.experts ? __ldcg(a.scores + r * a.experts + e) : -FLT_MAX;
+      sc[j] = v;
+      mx = fmaxf(mx, v);
+    }
+    if (a.sigmoid) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = lane + 32 * j;
+        if (e < a.experts) { sc[j] = 1.f / (1.f + __expf(-sc[j])); ch[j] = sc[j] + (a.bias ? a.bias[e] : 0.f); }
+        else ch[j] = -FLT_MAX;
+      }
+    } else {
+      mx = warp_max(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = lane + 32 * j;
+        sc[j] = e < a.experts ? __expf(sc[j] - mx) : 0.f;
+        sum += sc[j];
+      }
+      sum = warp_sum(sum);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { sc[j] /= sum; ch[j] = (lane + 32 * j) < a.experts ? sc[j] : -FLT_MAX; }
+    }
+    float psum = 0.f;
+    float my_p = 0.f;
+    int my_id = -1;
+    for (int t = 0; t < a.top_k; ++t) {
+      float best = -FLT_MAX;
+      int bi = 1 << 30;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (ch[j] > best) { best = ch[j]; bi = lane + 32 * j; }     // ascending j keeps the lowest index on ties
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      float pv = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j == bi) { pv = sc[j]; ch[j] = -FLT_MAX; }
+      pv = warp_sum(pv);                              // only the owner lane holds a non-zero value
+      psum += pv;
+      if (lane == t) { my_p = pv; my_id = bi; }
+    }
+    const float denom = a.normalize ? psum + 1e-20f : 1.f;
+    if (lane < a.top_k) {
+      const float p = my_p / denom * a.route_scale;
+      a.topk_ids[r * a.top_k + lane] = my_id;
+      a.topk_p[r * a.top_k + lane] = p;
+      atomicOr(&used[my_id >> 5], 1u << (my_id & 31));
+    }
+  }
+  __syncthreads();
+  // ascending list of distinct experts -> slots
+  if (tid < 256) {
+    const bool on = tid < a.experts && (used[tid >> 5] >> (tid & 31)) & 1u;
+    int before = 0;
+    for (int w = 0; w < (tid >> 5); ++w) before += __popc(used[w]);
+    before += __popc(used[tid >> 5] & ((1u << (tid & 31)) - 1u));
+    slot_of[tid] = on ? before : -1;
+    if (on && before < a.max_slots) a.active_ids[before] = tid;
+    if (tid == 0) {
+      int tot = 0;
+      for (int w = 0; w < 8; ++w) tot += __popc(used[w]);
+      *a.n_active = min(tot, a.max_slots);
+    }
+  }
+  for (int i = tid; i < a.max_slots * kTok; i += 256) a.probs[i] = 0.f;
+  __syncthreads();
+  for (int i = tid; i < a.rows * a.top_k; i += 256) {
+    const int r = i / a.top_k;
+    const int s = slot_of[a.topk_ids[i]];
+    if (s >= 0 && s < a.max_slots) a.probs[s * kTok + r] = a.topk_p[i];
+  }
+}
+
+}  // namespace
+
+// ============================================================================= C ABI
+#define S(stream) reinterpret_cast<cudaStream_t>(stream)
+
+extern "C" int nrt_embed_rows(const int* tokens, const void* table, void* x, int hidden, int rows, int vocab,
+                              void* stream, int pdl) {
+  return launch_pdl(embed_rows_kernel, dim3(kMaxRows), dim3(128), 0, S(stream), pdl != 0, tokens,
+                    (const __nv_bfloat16*)table, (__nv_bfloat16*)x, hidden, rows, vocab);
+}
+extern "C" int nrt_rope_table(const int* pos0, int rows, int dim, double theta, void* out, void* stream, int pdl) {
+  return launch_pdl(rope_table_kernel, dim3(rows), dim3(dim / 2 < 32 ? 32 : dim / 2), 0, S(stream), pdl != 0, pos0, rows,
+                    dim, theta, (float2*)out);
+}
+extern "C" int nrt_prep_norm(const void* x, const void* gamma, int hidden, int rows, float eps, void* xn, void* x8,
+                             void* xs, void* stream, int pdl) {
+  return launch_pdl(prep_norm_kernel, dim3(kMaxRows), dim3(256), 0, S(stream), pdl != 0, (const __nv_bfloat16*)x,
+                    (const __nv_bfloat16*)gamma, hidden, rows, eps, (__nv_bfloat16*)xn, (uint8_t*)x8, (float*)xs);
+}
+extern "C" int nrt_attn_post_args_size() { return (int)sizeof(AttnPostArgs); }
+extern "C" int nrt_attn_post(const void* args, void* stream, int pdl) {
+  AttnPostArgs a;
+  memcpy(&a, args, sizeof(a));
+  return launch_pdl(attn_post_kernel, dim3(a.rows), dim3(256), 0, S(stream), pdl != 0, a);
+}
+extern "C" int nrt_attn_args_size() { return (int)sizeof(AttnArgs); }
+extern "C" int nrt_attn_rows(const void* args, void* stream, int pdl) {
+  AttnArgs a;
+  memcpy(&a, args, sizeof(a));
+  return launch_pdl(attn_rows_kernel, dim3(a.heads, a.rows), dim3(128), 0, S(stream), pdl != 0, a);
+}
+extern "C" int nrt_index_args_size() { return (int)sizeof(IndexArgs); }
+extern "C" int nrt_index_logits_simple(const void* args, int blocks, void* stream, int pdl) {
+  IndexArgs a;
+  memcpy(&a, args, sizeof(a));
+  const size_t smem = (size_t)a.rows * a.heads * a.dim * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(index_logits_simple_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    configured = true;
+  }
+  return launch_pdl(index_logits_simple_kernel, dim3(blocks), dim3(256), smem, S(stream), pdl != 0, a);
+}
+extern "C" int nrt_topk_rows(const float* logits, int ld, const int* pos0, int rows, int top_k, int* sel, void* stream,
+                             int pdl) {
+  return launch_pdl(topk_rows_kernel, dim3(rows), dim3(1024), 0, S(stream), pdl != 0, logits, ld, pos0, rows, top_k, sel);
+}
+extern "C" int nrt_router_args_size() { return (int)sizeof(RouterArgs); }
+extern "C" int nrt_router(const void* args, void* stream, int pdl) {
+  RouterArgs a;
+  memcpy(&a, args, sizeof(a));
+  return launch_pdl(router_kernel, dim3((a.experts + 1) / 2), dim3(256), 0, S(stream), pdl != 0, a);
+}

@@ -1,0 +1,181 @@
+"""ctypes bindings of the sm_100a kernel library.
+
+Every wrapper takes torch CUDA tensors (already allocated: nothing here allocates on the
+launch path, so the calls are graph-capturable) and launches on the current stream.  The
+argument structures mirror the C structs field by field; their sizes are checked against the
+library at import so a layout drift fails loudly instead of corrupting a launch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from .build import load_library
+
+VP, I32, F32, U64 = C.c_void_p, C.c_int, C.c_float, C.c_ulonglong
+
+K_TOK = 16
+K_MAX_PEERS = 8
+K_ROW_PAIRS = 8
+K_MAILBOX_SLABS = 4
+
+# GEMM variants: fp8 | dual<<1 | epi<<2 | group<<5
+EPI_STORE_F32, EPI_STORE_BF16, EPI_SILU_QUANT, EPI_ALLREDUCE, EPI_SILU_BF16 = 0, 1, 2, 3, 4
+GROUP_NONE, GROUP_ITEM, GROUP_LOOP = 0, 1, 2
+
+
+def gemm_variant(fp8: bool, dual: bool, epi: int, group: int) -> int:
+    return int(fp8) | (int(dual) << 1) | (epi << 2) | (group << 5)
+
+
+class FabricArgs(C.Structure):
+    _fields_ = [("mailbox", VP * K_MAX_PEERS), ("epoch", VP), ("status", VP), ("tp", I32), ("rank", I32),
+                ("call_idx", I32), ("features", I32), ("timeout_ns", U64)]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [("n_total", I32), ("k_total", I32), ("rows", I32), ("a_group", I32),
+                ("n_active", VP), ("active_ids", VP), ("probs", VP), ("max_slots", I32),
+                ("w_scale0", VP), ("w_scale1", VP), ("a_scale", VP),
+                ("out_f32", VP), ("out_bf16", VP), ("ld_out", I32), ("out_scale", F32),
+                ("out_q", VP), ("out_qscale", VP), ("resid", VP), ("out_copy", VP),
+                ("fab", FabricArgs), ("status", VP)]
+
+
+class AttnPostArgs(C.Structure):
+    _fields_ = [("qkv", VP), ("ld", I32), ("rows", I32), ("pos0", VP),
+                ("heads", I32), ("kv_heads", I32), ("head_dim", I32), ("v_dim", I32), ("rope_dim", I32),
+                ("value_scale", F32), ("rope", VP), ("q_out", VP), ("k_cache", VP), ("v_cache", VP), ("ring", I32),
+                ("q_norm", VP), ("k_norm", VP), ("norm_eps", F32),
+                ("idx_heads", I32), ("idx_dim", I32), ("idx_rope", I32), ("idx_rope_tab", VP),
+                ("ik_w", VP), ("ik_b", VP), ("ln_eps", F32), ("idx_weight_scale", F32),
+                ("iq8", VP), ("ihw", VP), ("ik_cache", VP), ("ik_scale", VP),
+                ("col_q", I32), ("col_k", I32), ("col_v", I32), ("col_iq", I32), ("col_ik", I32), ("col_iw", I32)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("q", VP), ("k_cache", VP), ("v_cache", VP), ("pos0", VP),
+                ("rows", I32), ("heads", I32), ("kv_heads", I32), ("head_dim", I32), ("v_dim", I32),
+                ("scale", F32), ("mode", I32), ("window", I32), ("ring", I32), ("sink", VP), ("sel", VP),
+                ("top_k", I32), ("k_blk", VP), ("v_blk", VP), ("o_bf16", VP), ("o8", VP), ("o_scale", VP)]
+
+
+class IndexArgs(C.Structure):
+    _fields_ = [("iq8", VP), ("ihw", VP), ("ik", VP), ("iks", VP), ("pos0", VP),
+                ("rows", I32), ("heads", I32), ("dim", I32), ("top_k", I32), ("logits", VP), ("ld", I32)]
+
+
+class RouterArgs(C.Structure):
+    _fields_ = [("xn", VP), ("w", VP), ("bias", VP), ("hidden", I32), ("experts", I32), ("rows", I32),
+                ("top_k", I32), ("sigmoid", I32), ("normalize", I32), ("route_scale", F32),
+                ("scores", VP), ("ticket", VP), ("n_active", VP), ("active_ids", VP), ("probs", VP),
+                ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32)]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = load_library()
+        for name, st in (("nrt_gemm_args_size", GemmArgs), ("nrt_attn_post_args_size", AttnPostArgs),
+                         ("nrt_attn_args_size", AttnArgs), ("nrt_index_args_size", IndexArgs),
+                         ("nrt_router_args_size", RouterArgs)):
+            got = getattr(_lib, name)()
+            if got != C.sizeof(st):
+                raise RuntimeError(f"{st.__name__}: library has {got} bytes, bindings {C.sizeof(st)}")
+    return _lib
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with CUDA/driver error {code}")
+
+
+# ----------------------------------------------------------------------------- tensor maps
+class TensorMap:
+    """A 128-byte CUtensorMap kept alive with the tensor it describes."""
+
+    def __init__(self, t: torch.Tensor, dims: Sequence[int], strides_bytes: Sequence[int], box: Sequence[int],
+                 dtype_code: int, swizzle: int = 3):
+        self.tensor = t
+        self.buf = (C.c_ubyte * 128)()
+        rank = len(dims)
+        d = (C.c_uint64 * 5)(*dims)
+        s = (C.c_uint64 * 5)(*strides_bytes)
+        b = (C.c_uint32 * 5)(*box)
+        check(lib().nrt_tmap_encode(C.byref(self.buf), dtype_code, rank, d, s, b, swizzle, VP(t.data_ptr())),
+              "cuTensorMapEncodeTiled")
+
+
+def weight_tmap(w: torch.Tensor) -> TensorMap:
+    """[N, K] or [E, N, K] weights (e4m3 bytes or bf16) -> 3-D map with 128-row x 128-byte boxes."""
+    if w.dim() == 2:
+        w = w.unsqueeze(0)
+    assert w.is_contiguous()
+    e, n, k = w.shape
+    es = w.element_size()
+    code = 0 if es == 1 else 1
+    return TensorMap(w, (k, n, e), (k * es, n * k * es), (128 // es, 128, 1), code)
+
+
+def act_tmap(x: torch.Tensor) -> TensorMap:
+    """[rows (multiple of 16), K] activations -> 2-D map with 16-row x 128-byte boxes."""
+    assert x.dim() == 2 and x.is_contiguous() and x.shape[0] % K_TOK == 0
+    r, k = x.shape
+    es = x.element_size()
+    return TensorMap(x, (k, r), (k * es,), (128 // es, K_TOK), 0 if es == 1 else 1)
+
+
+# ----------------------------------------------------------------------------- launches
+def gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: TensorMap, args: GemmArgs, grid_x: int,
+         grid_y: int = 1, pdl: bool = True) -> None:
+    check(lib().nrt_gemm_launch(variant, C.byref(a0.buf), C.byref(a1.buf) if a1 is not None else None,
+                                C.byref(b.buf), C.byref(args), grid_x, grid_y, VP(_stream()), int(pdl)), "gemm launch")
+
+
+def embed_rows(tokens, table, x, rows, pdl=True):
+    check(lib().nrt_embed_rows(VP(ptr(tokens)), VP(ptr(table)), VP(ptr(x)), table.shape[1], rows, table.shape[0],
+                               VP(_stream()), int(pdl)), "embed_rows")
+
+
+def rope_table(pos0, rows, dim, theta, out, pdl=True):
+    check(lib().nrt_rope_table(VP(ptr(pos0)), rows, dim, C.c_double(theta), VP(ptr(out)), VP(_stream()), int(pdl)),
+          "rope_table")
+
+
+def prep_norm(x, gamma, rows, eps, xn=None, x8=None, xs=None, pdl=True):
+    check(lib().nrt_prep_norm(VP(ptr(x)), VP(ptr(gamma)), x.shape[1], rows, C.c_float(eps), VP(ptr(xn)), VP(ptr(x8)),
+                              VP(ptr(xs)), VP(_stream()), int(pdl)), "prep_norm")
+
+
+def attn_post(args: AttnPostArgs, pdl=True):
+    check(lib().nrt_attn_post(C.byref(args), VP(_stream()), int(pdl)), "attn_post")
+
+
+def attn_rows(args: AttnArgs, pdl=True):
+    check(lib().nrt_attn_rows(C.byref(args), VP(_stream()), int(pdl)), "attn_rows")
+
+
+def index_logits_simple(args: IndexArgs, blocks: int, pdl=True):
+    check(lib().nrt_index_logits_simple(C.byref(args), blocks, VP(_stream()), int(pdl)), "index_logits")
+
+
+def topk_rows(logits, pos0, rows, top_k, sel, pdl=True):
+    check(lib().nrt_topk_rows(VP(ptr(logits)), logits.shape[1], VP(ptr(pos0)), rows, top_k, VP(ptr(sel)),
+                              VP(_stream()), int(pdl)), "topk_rows")
+
+
+def router(args: RouterArgs, pdl=True):
+    check(lib().nrt_router(C.byref(args), VP(_stream()), int(pdl)), "router")
