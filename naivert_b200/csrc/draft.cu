@@ -1,0 +1,132 @@
+// Block-draft specific kernels: block input rows (anchor embedding + mask embeddings) and the
+// sequential Markov head (low-rank previous-token bias + Gumbel-max proposal per row).
+//
+// The reference precomputes a [vocab, vocab/8] bf16 bias table (5.8 GB per rank,
+// naivert/entry/dspark_head_markov_entry.cu:31,87) and looks up one row per step; here the
+// rank-256 factors stay factored: each step evaluates bias = W2_shard . W1[prev] on the fly
+// (W2_shard is 9.7 MB per rank at tp = 8 and stays L2 resident across the seven steps).
+// Reference math: naivert/body/dspark_head_markov/markov_body.cuh:6-27,
+// naivert/body/dspark_sampling/random.cuh:17-20 (Gumbel-max over (logits + bias) / T).
+#include "fabric.cuh"
+#include "launch.hpp"
+
+#include <float.h>
+#include <string.h>
+
+using namespace nrt;
+
+namespace {
+
+// x[0] = embed[anchor], x[1..rows) = mask embedding, x[rows..16) = 0
+__global__ void draft_block_input_kernel(const int* __restrict__ block_ids, const __nv_bfloat16* __restrict__ embed,
+                                         const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ x, int hidden,
+                                         int rows, int vocab) {
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x;
+  uint4* dst = reinterpret_cast<uint4*>(x + (size_t)r * hidden);
+  const uint4* src = nullptr;
+  if (r == 0) {
+    int t = block_ids[0];
+    t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+    src = reinterpret_cast<const uint4*>(embed + (size_t)t * hidden);
+  } else if (r < rows) {
+    src = reinterpret_cast<const uint4*>(mask);
+  }
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0, 0, 0, 0);
+}
+
+struct MarkovArgs {
+  const float* logits;            // [16][ld] draft head logits (row j proposes token j+1)
+  int ld;
+  const __nv_bfloat16* w1;        // [vocab][rank]
+  const __nv_bfloat16* w2;        // [vlocal][rank]
+  int rank_dim, vlocal, vbase, vocab;
+  int* block_ids;                 // [8]; block_ids[step] is the previous token, block_ids[step+1] is written
+  float* zq;                      // [8][ld] logits + bias (the draft distribution the sampler sees)
+  const float* params;            // sampler params ([6] = 1/T of the draft)
+  const unsigned long long* seed;
+  const int* ctrl;                // round counter at [8]
+  unsigned long long* best;       // scratch: packed (ordered value << 32 | ~token)
+  unsigned int* ticket;
+  XchgArgs x;
+};
+
+// grid = ceil(vlocal / 1024) CTAs of 256 threads, 4 tokens per thread.
+__global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, int step) {
+  __shared__ float w1s[512];
+  __shared__ unsigned long long sbest;
+  __shared__ bool s_last;
+  __shared__ uint64_t xv[16];
+  griddep_launch();
+  griddep_wait();
+  int prev = a.block_ids[step];
+  prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
+  for (int i = threadIdx.x; i < a.rank_dim; i += 256) w1s[i] = __bfloat162float(a.w1[(size_t)prev * a.rank_dim + i]);
+  if (threadIdx.x == 0) sbest = 0ull;
+  __syncthreads();
+  const float inv_t = a.params[6];
+  const unsigned long long seed = *a.seed;
+  const uint32_t ctr = (uint32_t)a.ctrl[8] * 8u + (uint32_t)step;
+  unsigned long long best = 0ull;
+  for (int i = 0; i < 4; ++i) {
+    const int t = blockIdx.x * 1024 + i * 256 + threadIdx.x;
+    if (t < a.vlocal) {
+      const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)t * a.rank_dim);
+      float acc = 0.f;
+      for (int k = 0; k < a.rank_dim / 8; ++k) {
+        const uint4 v = wr[k];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc += f.x * w1s[k * 8 + 2 * j] + f.y * w1s[k * 8 + 2 * j + 1];
+        }
+      }
+      const float z = a.logits[(size_t)step * a.ld + t] + round_bf16(acc);
+      a.zq[(size_t)step * a.ld + t] = z;
+      const float u = philox_uniform(seed, 3u, ctr, (uint32_t)(t + a.vbase));
+      const float g = -__logf(-__logf(u));
+      const float s = z * inv_t + g;
+      // larger score wins; ties go to the lower token id
+      const unsigned long long key = ((unsigned long long)float_order(s) << 32) | (uint32_t)(~(uint32_t)(t + a.vbase));
+      best = key > best ? key : best;
+    }
+  }
+  atomicMax(&sbest, best);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    atomicMax(a.best, sbest);
+    __threadfence();
+    const unsigned int tk = atomicAdd(a.ticket, 1u);
+    s_last = tk == gridDim.x - 1;
+    if (s_last) *a.ticket = 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 16) xv[threadIdx.x] = threadIdx.x == 0 ? *reinterpret_cast<volatile unsigned long long*>(a.best) : 0ull;
+  __syncthreads();
+  xchg_reduce_u64<kXMax>(xv, 1, a.x, 16 + step);
+  if (threadIdx.x == 0) {
+    a.block_ids[step + 1] = (int)(~(uint32_t)xv[0]);
+    *a.best = 0ull;
+  }
+}
+
+}  // namespace
+
+#define S(stream) reinterpret_cast<cudaStream_t>(stream)
+
+extern "C" int nrt_draft_block_input(const int* block_ids, const void* embed, const void* mask, void* x, int hidden,
+                                     int rows, int vocab, void* stream, int pdl) {
+  return launch_pdl(draft_block_input_kernel, dim3(16), dim3(128), 0, S(stream), pdl != 0, block_ids,
+                    (const __nv_bfloat16*)embed, (const __nv_bfloat16*)mask, (__nv_bfloat16*)x, hidden, rows, vocab);
+}
+extern "C" int nrt_markov_args_size() { return (int)sizeof(MarkovArgs); }
+extern "C" int nrt_markov_step(const void* args, int step, void* stream, int pdl) {
+  MarkovArgs a;
+  memcpy(&a, args, sizeof(a));
+  if (a.rank_dim > 512 || a.rank_dim % 8) return -3;
+  return launch_pdl(markov_step_kernel, dim3((a.vlocal + 1023) / 1024), dim3(256), 0, S(stream), pdl != 0, a, step);
+}

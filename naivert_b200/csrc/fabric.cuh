@@ -1,0 +1,114 @@
+// Small-message exchange over the peer-memory fabric: every rank pushes its values to every
+// peer as tagged words and combines the tp contributions locally (integers: order-free; the
+// float variants combine in rank order).  Used by the sampler, the draft head and the tail
+// for maxima, integer masses, histograms and token broadcasts.  All waits are bounded.
+//
+// Reference counterpart: the per-stage rendezvous and tagged inbox exchange of
+// naivert/body/dspark_sampling/{sharded,persistent}.cuh and naivert/body/dspark_common/rendezvous.cuh.
+#pragma once
+#include "ptx.cuh"
+
+namespace nrt {
+
+constexpr int kXchgMaxWords = 4096;     // 64-bit values per exchange
+constexpr int kXchgSlabs = 4;
+constexpr int kXchgPeers = 8;
+
+struct XchgArgs {
+  uint64_t* box[kXchgPeers];   // box[p] = rank p's exchange region (peer mapped); box[rank] is local
+  const uint32_t* epoch;
+  uint32_t* status;
+  int tp;
+  int rank;
+  unsigned long long timeout_ns;
+};
+
+enum XchgOp : int { kXSum = 0, kXMax = 1 };
+
+// Called by all threads of ONE CTA.  vals[0..n) (shared or global, local to this rank) are
+// replaced by the reduction over ranks.  `call` must be unique inside one epoch (< 64).
+template <int OP>
+__device__ __forceinline__ bool xchg_reduce_u64(uint64_t* vals, int n, const XchgArgs& x, int call) {
+  if (x.tp <= 1) return true;
+  const uint32_t tag = (*x.epoch) * 64u + (uint32_t)call + 1u;
+  const size_t slab = (size_t)(call % kXchgSlabs) * x.tp;
+  bool ok = true;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint64_t v = vals[i];
+    for (int d = 1; d < x.tp; ++d) {
+      const int peer = (x.rank + d) % x.tp;
+      uint64_t* dst = x.box[peer] + ((slab + x.rank) * kXchgMaxWords + i) * 2;
+      st_tagged(dst, tag, (uint32_t)v);
+      st_tagged(dst + 1, tag, (uint32_t)(v >> 32));
+    }
+  }
+  const uint64_t deadline = globaltimer() + x.timeout_ns;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    // batched poll: all outstanding words of all sources are re-read per sweep
+    uint32_t lo[kXchgPeers], hi[kXchgPeers];
+    uint32_t need = 0;
+#pragma unroll
+    for (int s = 0; s < kXchgPeers; ++s) {
+      lo[s] = hi[s] = 0u;
+      if (s < x.tp && s != x.rank) need |= 3u << (2 * s);
+    }
+    const uint64_t* base = x.box[x.rank] + (slab * kXchgMaxWords + i) * 2;
+    for (uint32_t sweep = 0; need != 0; ++sweep) {
+#pragma unroll
+      for (int s = 0; s < kXchgPeers; ++s) {
+        const uint64_t* src = base + (size_t)s * kXchgMaxWords * 2;
+        uint32_t t, v;
+        if (need & (1u << (2 * s))) { ld_tagged(src, t, v); if (t == tag) { lo[s] = v; need &= ~(1u << (2 * s)); } }
+        if (need & (2u << (2 * s))) { ld_tagged(src + 1, t, v); if (t == tag) { hi[s] = v; need &= ~(2u << (2 * s)); } }
+      }
+      if ((sweep & 255u) == 255u) {
+        if (*reinterpret_cast<volatile uint32_t*>(x.status) != 0u) { ok = false; break; }
+        if (globaltimer() > deadline) { report(x.status, kSiteRendezvous | (uint32_t)call); ok = false; break; }
+      }
+    }
+    uint64_t acc = vals[i];
+#pragma unroll
+    for (int s = 0; s < kXchgPeers; ++s) {
+      if (s < x.tp && s != x.rank) {
+        const uint64_t o = ((uint64_t)hi[s] << 32) | lo[s];
+        acc = OP == kXSum ? acc + o : (o > acc ? o : acc);
+      }
+    }
+    vals[i] = acc;
+  }
+  __syncthreads();
+  return ok;
+}
+
+// order-preserving map float -> uint32 (so a max over uints is a max over floats)
+__device__ __forceinline__ uint32_t float_order(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float float_unorder(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+// Philox4x32-10; uniform in (0, 1) from (seed, domain, a, b)
+__host__ __device__ inline uint32_t philox_u32(uint64_t seed, uint32_t domain, uint32_t a, uint32_t b) {
+  uint32_t c0 = domain, c1 = a, c2 = b, c3 = 0;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0;
+    const uint32_t n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1;
+    const uint32_t n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+__host__ __device__ inline float philox_uniform(uint64_t seed, uint32_t domain, uint32_t a, uint32_t b) {
+  return ((philox_u32(seed, domain, a, b) >> 9) + 0.5f) * (1.0f / 8388608.0f);   // 23 bits + 1/2: exact in fp32
+}
+
+}  // namespace nrt

@@ -72,6 +72,7 @@ struct GemmArgs {
   float* out_qscale;              // kEpiSiluQuant: [slots*16][n_total/128]
   const __nv_bfloat16* resid;     // kEpiAllReduce: residual [rows][ld_out]
   __nv_bfloat16* out_copy;        // kEpiAllReduce: optional second copy (draft feature tap)
+  int ld_copy;                    // row stride of out_copy
   FabricArgs fab;
   uint32_t* status;
 };
@@ -311,7 +312,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       float sum[kTok];
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
-        sum[r] = (r < p.rows && n < p.n_total) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
+        sum[r] = (p.resid && r < p.rows && n < p.n_total) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
       uint32_t own[kRowPairs];
 #pragma unroll
       for (int j = 0; j < kRowPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
@@ -367,7 +368,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         if (r < p.rows && n < p.n_total) {
           const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
           p.out_bf16[(size_t)r * p.ld_out + n] = o;
-          if (p.out_copy) p.out_copy[(size_t)r * p.ld_out + n] = o;
+          if (p.out_copy) p.out_copy[(size_t)r * p.ld_copy + n] = o;
         }
     }
     (void)ok;

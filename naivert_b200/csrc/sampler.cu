@@ -1,0 +1,526 @@
+// Vocabulary-sharded speculative sampler, verify and tail commit.
+//
+// Every distribution is handled in *integer masses*: after the exact row maximum m is known
+// on all ranks, e(t) = rint(exp(z(t) - m) * 2^31) is a 32-bit integer per token.  Sums of
+// integers do not depend on summation order, so the nucleus threshold, the normaliser, the
+// accept test and the inverse-CDF draw are bit-identical from run to run and identical for
+// every tensor-parallel degree.
+//
+//   z      = penalised logit / T
+//   e      = rint(exp(z - max z) * 2^31)
+//   nucleus: the largest threshold tau with  sum_{e >= tau} e  >=  top_p * sum e  (radix select
+//            over the 32-bit codes, four 8-bit passes on mass histograms); kept = {e >= tau}, Z = kept mass
+//   accept draft token d_j  iff  u * q'(d_j) < p'(d_j),  p' = e_p/Z_p on the kept set (0 outside)
+//   first rejection at row m: draw from max(p' - q', 0) in vocabulary order; all accepted: draw from p' of the last row
+//   forced mode: the accept decision of every position is replaced by a seeded Bernoulli(p_force) draw
+//
+// Rows 0..7 are the target distributions, rows 8..14 the draft distributions.
+// Reference: naivert/body/dspark_sampling/{sharded,persistent,parallel}.cuh (math),
+// random.cuh (Philox domains), naivert/body/dspark_tail/{body,commit}.cuh (accept prefix, commit).
+#include "fabric.cuh"
+#include "launch.hpp"
+
+#include <string.h>
+
+using namespace nrt;
+
+namespace {
+
+constexpr int kRowsP = 8, kRowsQ = 7, kDist = kRowsP + kRowsQ;
+constexpr int kTile = 2048;                 // vocabulary entries per CTA
+constexpr int kThreads = 256;
+
+enum Domain : uint32_t { kDomAccept = 0, kDomResample = 1, kDomForced = 2, kDomDraft = 3, kDomAnchor = 4 };
+
+struct SamplerState {          // device-resident scratch of one rank
+  float rowmax[16];
+  unsigned long long total[16];      // sum of e
+  unsigned long long above[16];      // mass strictly above the current prefix bin
+  unsigned long long kept[16];       // Z (valid after the last pass)
+  unsigned int prefix[16];           // threshold code tau (valid after the last pass)
+  unsigned long long hist[kDist * 256];
+  unsigned long long tile_mass[16 * 128];   // per-tile masses of the row being resampled (<= 128 tiles... see launcher)
+  unsigned int ticket[8];
+  int accepted;                      // m: accepted draft tokens (0..7)
+  int extra_token;                   // resampled / bonus token
+  int accept_flags[8];
+};
+
+struct SamplerArgs {
+  const float* zp;             // target logits [16][ldp]
+  int ldp;
+  const float* zq;             // draft logits (+ Markov bias) [8][ldq]
+  int ldq;
+  int vlocal;                  // vocabulary entries of this rank
+  int vbase;                   // first global token id of this rank
+  unsigned int* e;             // [kDist][vlocal] integer codes
+  const unsigned short* counts;   // [vlocal] occurrences of each token in the context (penalties) or null
+  const float* params;         // [8]: inv_T, top_p, rep_penalty, freq_penalty, pres_penalty, forced_p (<0: off), inv_T_draft
+  const unsigned long long* seed;
+  const int* ctrl;             // control block (round counter at [8])
+  const int* block_ids;        // [8]: anchor + 7 proposals
+  int n_rows_p, n_rows_q;      // 8,7 for a round; 1,0 for the anchor sample
+  SamplerState* st;
+  XchgArgs x;
+};
+
+__device__ __forceinline__ float penalised(const SamplerArgs& a, const float* params, float z, int t) {
+  if (a.counts) {
+    const float c = (float)a.counts[t];
+    if (c > 0.f) {
+      const float rp = params[2];
+      z = z > 0.f ? z / rp : z * rp;
+      z -= params[3] * c + params[4];
+    }
+  }
+  return z;
+}
+__device__ __forceinline__ const float* row_logits(const SamplerArgs& a, int d, float& inv_t) {
+  if (d < kRowsP) { inv_t = a.params[0]; return a.zp + (size_t)d * a.ldp; }
+  inv_t = a.params[6];
+  return a.zq + (size_t)(d - kRowsP) * a.ldq;
+}
+__device__ __forceinline__ bool row_active(const SamplerArgs& a, int d) {
+  return d < kRowsP ? d < a.n_rows_p : (d - kRowsP) < a.n_rows_q;
+}
+
+// ticket: true for the last CTA of the grid to arrive (and resets the counter)
+__device__ __forceinline__ bool last_block(unsigned int* ticket) {
+  __shared__ bool s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    const unsigned int t = atomicAdd(ticket, 1u);
+    s_last = (t == total - 1);
+    if (s_last) *ticket = 0u;
+  }
+  __syncthreads();
+  __threadfence();
+  return s_last;
+}
+
+// ---------------------------------------------------------------- pass A: row maxima
+__global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a) {
+  __shared__ unsigned int smax;
+  __shared__ uint64_t xv[16];
+  griddep_launch();
+  griddep_wait();
+  const int d = blockIdx.y;
+  if (threadIdx.x == 0) smax = 0u;
+  __syncthreads();
+  if (row_active(a, d)) {
+    float inv_t;
+    const float* z = row_logits(a, d, inv_t);
+    unsigned int best = 0u;
+    const int t0 = blockIdx.x * kTile;
+    for (int i = threadIdx.x; i < kTile; i += kThreads) {
+      const int t = t0 + i;
+      if (t < a.vlocal) {
+        float v = d < kRowsP ? penalised(a, a.params, z[t], t) : z[t];
+        best = max(best, float_order(__fmul_rn(v, inv_t)));
+      }
+    }
+    atomicMax(&smax, best);
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(&a.st->hist[d]), smax);   // hist[] doubles as scratch
+  }
+  if (!last_block(&a.st->ticket[0])) return;
+  if (threadIdx.x < 16) {
+    const unsigned int v = threadIdx.x < kDist ? *reinterpret_cast<volatile unsigned int*>(&a.st->hist[threadIdx.x]) : 0u;
+    xv[threadIdx.x] = v;
+  }
+  __syncthreads();
+  xchg_reduce_u64<kXMax>(xv, 16, a.x, 0);
+  if (threadIdx.x < 16) {
+    a.st->rowmax[threadIdx.x] = float_unorder((uint32_t)xv[threadIdx.x]);
+    a.st->hist[threadIdx.x] = 0ull;
+    a.st->total[threadIdx.x] = 0ull;
+  }
+}
+
+// ---------------------------------------------------------------- pass B: integer codes + totals
+__global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a) {
+  __shared__ unsigned long long ssum;
+  __shared__ uint64_t xv[16];
+  griddep_launch();
+  griddep_wait();
+  const int d = blockIdx.y;
+  if (threadIdx.x == 0) ssum = 0ull;
+  __syncthreads();
+  if (row_active(a, d)) {
+    float inv_t;
+    const float* z = row_logits(a, d, inv_t);
+    const float m = a.st->rowmax[d];
+    unsigned long long acc = 0ull;
+    const int t0 = blockIdx.x * kTile;
+    for (int i = threadIdx.x; i < kTile; i += kThreads) {
+      const int t = t0 + i;
+      if (t < a.vlocal) {
+        float v = d < kRowsP ? penalised(a, a.params, z[t], t) : z[t];
+        const unsigned int e = (unsigned int)rintf(expf(__fsub_rn(__fmul_rn(v, inv_t), m)) * 2147483648.0f);
+        a.e[(size_t)d * a.vlocal + t] = e;
+        acc += e;
+      }
+    }
+    atomicAdd(&ssum, acc);
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(&a.st->total[d], ssum);
+  }
+  if (!last_block(&a.st->ticket[1])) return;
+  if (threadIdx.x < 16) xv[threadIdx.x] = *reinterpret_cast<volatile unsigned long long*>(&a.st->total[threadIdx.x]);
+  __syncthreads();
+  xchg_reduce_u64<kXSum>(xv, 16, a.x, 1);
+  if (threadIdx.x < 16) {
+    a.st->total[threadIdx.x] = xv[threadIdx.x];
+    a.st->above[threadIdx.x] = 0ull;
+    a.st->prefix[threadIdx.x] = 0u;
+  }
+  for (int i = threadIdx.x; i < kDist * 256; i += kThreads) a.st->hist[i] = 0ull;
+}
+
+// ---------------------------------------------------------------- passes C0..C3: nucleus radix select
+__global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a, int pass) {
+  __shared__ unsigned long long sh[256];
+  __shared__ uint64_t xv[kDist * 256];
+  griddep_launch();
+  griddep_wait();
+  const int d = blockIdx.y;
+  const int shift = 24 - 8 * pass;
+  const unsigned int mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+  for (int i = threadIdx.x; i < 256; i += kThreads) sh[i] = 0ull;
+  __syncthreads();
+  if (row_active(a, d)) {
+    const unsigned int prefix = a.st->prefix[d];
+    const unsigned int* e = a.e + (size_t)d * a.vlocal;
+    const int t0 = blockIdx.x * kTile;
+    for (int i = threadIdx.x; i < kTile; i += kThreads) {
+      const int t = t0 + i;
+      if (t < a.vlocal) {
+        const unsigned int v = e[t];
+        if ((v & mask) == prefix && v != 0u) atomicAdd(&sh[(v >> shift) & 255u], (unsigned long long)v);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += kThreads)
+      if (sh[i]) atomicAdd(&a.st->hist[d * 256 + i], sh[i]);
+  }
+  if (!last_block(&a.st->ticket[2])) return;
+  for (int i = threadIdx.x; i < kDist * 256; i += kThreads)
+    xv[i] = *reinterpret_cast<volatile unsigned long long*>(&a.st->hist[i]);
+  __syncthreads();
+  xchg_reduce_u64<kXSum>(xv, kDist * 256, a.x, 2 + pass);
+  if (threadIdx.x < kDist && row_active(a, threadIdx.x)) {
+    const int r = threadIdx.x;
+    const double top_p = (double)a.params[1];
+    const unsigned long long target = (unsigned long long)ceil(top_p * (double)a.st->total[r]);
+    unsigned long long above = a.st->above[r], cum = 0ull;
+    int b = 255;
+    for (; b > 0; --b) {
+      cum += xv[r * 256 + b];
+      if (above + cum >= target) break;
+    }
+    if (b == 0) cum += xv[r * 256];
+    const unsigned long long in_bin = xv[r * 256 + b];
+    a.st->above[r] = above + cum - in_bin;
+    a.st->prefix[r] |= (unsigned int)b << shift;
+    if (pass == 3) a.st->kept[r] = above + cum;      // Z: everything with e >= tau
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kDist * 256; i += kThreads) a.st->hist[i] = 0ull;
+}
+
+// ---------------------------------------------------------------- verify: accept prefix
+// One CTA.  Gathers e_p(d_j), e_q(d_j) from the owning ranks, decides acceptance.
+__global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
+  __shared__ uint64_t xv[16];
+  griddep_launch();
+  griddep_wait();
+  const int j = threadIdx.x;                  // proposal j+1 is judged by target row j / draft row j
+  if (j < 16) xv[j] = 0ull;
+  __syncthreads();
+  if (j < a.n_rows_q) {
+    const int tok = a.block_ids[j + 1] - a.vbase;
+    if (tok >= 0 && tok < a.vlocal) {
+      unsigned int ep = a.e[(size_t)j * a.vlocal + tok];
+      unsigned int eq = a.e[(size_t)(kRowsP + j) * a.vlocal + tok];
+      if (ep < a.st->prefix[j]) ep = 0u;
+      if (eq < a.st->prefix[kRowsP + j]) eq = 0u;
+      xv[j] = ((uint64_t)ep << 32) | eq;
+    }
+  }
+  __syncthreads();
+  xchg_reduce_u64<kXSum>(xv, 8, a.x, 6);
+  if (threadIdx.x == 0) {
+    const unsigned long long seed = *a.seed;
+    const uint32_t round = (uint32_t)a.ctrl[8];
+    const float forced = a.params[5];
+    int m = 0;
+    for (; m < a.n_rows_q; ++m) {
+      const double ep = (double)(uint32_t)(xv[m] >> 32), eq = (double)(uint32_t)xv[m];
+      bool acc;
+      if (forced >= 0.f) {
+        acc = philox_uniform(seed, kDomForced, round, (uint32_t)m) < forced;
+      } else {
+        const double u = (double)philox_uniform(seed, kDomAccept, round, (uint32_t)m);
+        acc = u * eq * (double)a.st->kept[m] < ep * (double)a.st->kept[kRowsP + m];
+      }
+      a.st->accept_flags[m] = acc ? 1 : 0;
+      if (!acc) break;
+    }
+    a.st->accepted = m;
+  }
+}
+
+// residual / bonus mass of token t of the row being resampled (40-bit fixed point of a probability)
+__device__ __forceinline__ unsigned long long resample_mass(const SamplerArgs& a, int m, int t, bool from_p) {
+  unsigned int ep = a.e[(size_t)m * a.vlocal + t];
+  if (ep < a.st->prefix[m]) ep = 0u;
+  if (from_p || m >= a.n_rows_q) return (unsigned long long)ep;    // bonus / anchor row / empty residual: sample from p'
+  unsigned int eq = a.e[(size_t)(kRowsP + m) * a.vlocal + t];
+  if (eq < a.st->prefix[kRowsP + m]) eq = 0u;
+  const double r = (double)ep / (double)a.st->kept[m] - (double)eq / (double)a.st->kept[kRowsP + m];
+  return r > 0.0 ? (unsigned long long)(r * 1099511627776.0) : 0ull;
+}
+
+// ---------------------------------------------------------------- resample: per-tile masses
+__global__ void __launch_bounds__(kThreads) samp_tile_mass_kernel(const SamplerArgs a) {
+  __shared__ unsigned long long ssum;
+  griddep_launch();
+  griddep_wait();
+  if (threadIdx.x == 0) ssum = 0ull;
+  __syncthreads();
+  const int m = a.st->accepted;
+  __shared__ unsigned long long ssum_p;
+  if (threadIdx.x == 0) ssum_p = 0ull;
+  __syncthreads();
+  unsigned long long acc = 0ull, acc_p = 0ull;
+  const int t0 = blockIdx.x * kTile;
+  for (int i = threadIdx.x; i < kTile; i += kThreads) {
+    const int t = t0 + i;
+    if (t < a.vlocal) { acc += resample_mass(a, m, t, false); acc_p += resample_mass(a, m, t, true); }
+  }
+  atomicAdd(&ssum, acc);
+  atomicAdd(&ssum_p, acc_p);
+  __syncthreads();
+  if (threadIdx.x == 0) { a.st->tile_mass[blockIdx.x] = ssum; a.st->tile_mass[128 + blockIdx.x] = ssum_p; }
+}
+
+// ---------------------------------------------------------------- resample: inverse CDF in vocabulary order
+__global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a, int tiles, int domain) {
+  __shared__ uint64_t xv[16];
+  __shared__ unsigned long long part[kThreads];
+  __shared__ int s_tok;
+  griddep_launch();
+  griddep_wait();
+  const int m = a.st->accepted;
+  if (threadIdx.x < 16) xv[threadIdx.x] = 0ull;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long tot = 0ull, tot_p = 0ull;
+    for (int i = 0; i < tiles; ++i) { tot += a.st->tile_mass[i]; tot_p += a.st->tile_mass[128 + i]; }
+    xv[a.x.rank] = tot;
+    xv[8 + a.x.rank] = tot_p;
+    s_tok = -1;
+  }
+  __syncthreads();
+  xchg_reduce_u64<kXSum>(xv, 16, a.x, 7);         // everyone learns every rank's totals
+  unsigned long long total = 0ull, before = 0ull;
+  for (int r = 0; r < a.x.tp; ++r) total += xv[r];
+  const bool from_p = total == 0ull;               // empty residual (p' <= q' everywhere): draw from p'
+  const int xo = from_p ? 8 : 0, mo = from_p ? 128 : 0;
+  total = 0ull;
+  for (int r = 0; r < a.x.tp; ++r) { if (r < a.x.rank) before += xv[xo + r]; total += xv[xo + r]; }
+  const double u = (double)philox_uniform(*a.seed, (uint32_t)domain, (uint32_t)a.ctrl[8], (uint32_t)m);
+  unsigned long long target = (unsigned long long)(u * (double)total);
+  if (total > 0ull && target >= total) target = total - 1ull;
+  const bool mine = total > 0ull && target >= before && target < before + xv[xo + a.x.rank];
+  if (mine) {
+    unsigned long long local = target - before;       // uniform across the CTA
+    int tile = 0;
+    for (; tile < tiles - 1; ++tile) {
+      const unsigned long long tm = a.st->tile_mass[mo + tile];
+      if (local < tm) break;
+      local -= tm;
+    }
+    // scan the tile: each thread owns 8 consecutive tokens
+    const int t0 = tile * kTile + threadIdx.x * (kTile / kThreads);
+    unsigned long long mine_sum = 0ull;
+    for (int i = 0; i < kTile / kThreads; ++i)
+      if (t0 + i < a.vlocal) mine_sum += resample_mass(a, m, t0 + i, from_p);
+    part[threadIdx.x] = mine_sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long run = 0ull;
+      int th = 0;
+      for (; th < kThreads - 1; ++th) {
+        if (local < run + part[th]) break;
+        run += part[th];
+      }
+      unsigned long long rem = local - run;
+      const int b0 = tile * kTile + th * (kTile / kThreads);
+      int tok = b0;
+      for (int i = 0; i < kTile / kThreads; ++i) {
+        if (b0 + i >= a.vlocal) break;
+        const unsigned long long w = resample_mass(a, m, b0 + i, from_p);
+        tok = b0 + i;
+        if (rem < w) break;
+        rem -= w;
+      }
+      s_tok = tok + a.vbase;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 16) xv[threadIdx.x] = (threadIdx.x == 0 && s_tok >= 0) ? (uint64_t)(s_tok + 1) : 0ull;
+  __syncthreads();
+  xchg_reduce_u64<kXSum>(xv, 1, a.x, 8);
+  if (threadIdx.x == 0) {
+    int tok = (int)xv[0] - 1;
+    if (tok < 0) tok = 0;                          // unreachable while the kept set is non-empty
+    a.st->extra_token = tok;
+  }
+}
+
+// ---------------------------------------------------------------- tail: commit + next-round geometry
+struct RingRecord {              // 64 bytes, host-visible
+  unsigned int generation;       // written last: round index + 1
+  int count;                     // tokens committed by this round (0..8)
+  int tokens[8];
+  int pos0;                      // position of the anchor row of this round
+  int stop_reason;               // 0 none, 1 eos, 2 output limit, 3 position limit, 4 cancelled, 5 device wait failed
+  unsigned long long t_end_ns;
+  int accepted;
+  int pad[1];
+};
+
+struct TailArgs {
+  int* ctrl;                     // [0] pos0 [1] n_ingest [2] ingest_pos0 [4] stopped [5] reason [6] produced [7] max_tokens [8] round [9] capacity
+  int* block_ids;                // [8]
+  uint32_t* epoch;
+  SamplerState* st;
+  RingRecord* ring;              // mapped pinned host memory
+  int ring_size;
+  const volatile int* cancel;    // mapped pinned host word (non-zero: stop)
+  const int* stop_ids;           // device [n_stop]
+  int n_stop;
+  unsigned short* counts;        // [vlocal] penalty counts of this rank's shard or null
+  int vbase, vlocal;
+  const uint32_t* status;
+  int n_rows_q;
+};
+
+__global__ void tail_commit_kernel(const TailArgs a) {
+  griddep_launch();
+  griddep_wait();
+  if (threadIdx.x != 0) return;
+  int* c = a.ctrl;
+  const int round = c[8];
+  if (c[4]) {                                  // already stopped: keep the fabric epoch moving, publish nothing
+    *a.epoch += 1u;
+    c[8] = round + 1;
+    return;
+  }
+  const int m = a.st->accepted;
+  const int pos0 = c[0];
+  int reason = 0, n = 0;
+  int out[8];
+  if (*a.status != 0u) reason = 5;
+  else if (*a.cancel != 0) reason = 4;
+  for (int j = 0; j <= m && reason == 0; ++j) {
+    const int tok = j < m ? a.block_ids[j + 1] : a.st->extra_token;
+    out[n++] = tok;
+    c[6] += 1;
+    const int local = tok - a.vbase;
+    if (a.counts && local >= 0 && local < a.vlocal && a.counts[local] < 65535) a.counts[local] += 1;
+    for (int s = 0; s < a.n_stop; ++s)
+      if (tok == a.stop_ids[s]) reason = 1;
+    if (reason == 0 && c[6] >= c[7]) reason = 2;
+  }
+  if (reason == 0 && pos0 + n + 16 >= c[9]) reason = 3;
+  RingRecord* rec = a.ring + (round % a.ring_size);
+  rec->count = n;
+  for (int j = 0; j < 8; ++j) rec->tokens[j] = j < n ? out[j] : -1;
+  rec->pos0 = pos0;
+  rec->stop_reason = reason;
+  rec->accepted = m;
+  rec->t_end_ns = globaltimer();
+  __threadfence_system();
+  *reinterpret_cast<volatile unsigned int*>(&rec->generation) = (unsigned int)round + 1u;
+  // next round: rows 0..n-1 of this verify are committed context
+  if (n > 0) {
+    c[2] = pos0;
+    c[1] = n;
+    c[0] = pos0 + n;
+    a.block_ids[0] = out[n - 1];
+  }
+  if (reason) { c[4] = 1; c[5] = reason; }
+  c[8] = round + 1;
+  *a.epoch += 1u;
+}
+
+// Prompt replay cursor: loads the next `rows` prompt tokens into the step's token buffer, points
+// the step (ctrl[0]) and the draft ingest (ctrl[2]) at their position and advances ctrl[10].
+__global__ void prefill_cursor_kernel(const int* __restrict__ prompt, int n_prompt, int rows, int* ctrl, int* tokens) {
+  griddep_launch();
+  griddep_wait();
+  const int cur = ctrl[10];
+  if (n_prompt < 0) n_prompt = ctrl[11];          // length kept in the control block (graph replays)
+  if (threadIdx.x < 16) {
+    const int t = cur + (int)threadIdx.x;
+    tokens[threadIdx.x] = ((int)threadIdx.x < rows && t < n_prompt) ? prompt[t] : 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { ctrl[0] = cur; ctrl[2] = cur; ctrl[10] = cur + rows; }
+}
+
+// advance the fabric epoch (eager steps outside a round)
+__global__ void epoch_advance_kernel(uint32_t* epoch) {
+  griddep_launch();
+  griddep_wait();
+  if (threadIdx.x == 0) *epoch += 1u;
+}
+
+}  // namespace
+
+#define S(stream) reinterpret_cast<cudaStream_t>(stream)
+
+extern "C" int nrt_sampler_args_size() { return (int)sizeof(SamplerArgs); }
+extern "C" int nrt_sampler_state_size() { return (int)sizeof(SamplerState); }
+extern "C" int nrt_tail_args_size() { return (int)sizeof(TailArgs); }
+extern "C" int nrt_ring_record_size() { return (int)sizeof(RingRecord); }
+
+// Runs the whole sampler chain: maxima, codes, four nucleus passes, accept, resample.
+// domain: Philox domain of the final draw (1 = residual/bonus of a round, 4 = anchor sample).
+extern "C" int nrt_sampler_run(const void* args, int domain, void* stream, int pdl) {
+  SamplerArgs a;
+  memcpy(&a, args, sizeof(a));
+  const int tiles = (a.vlocal + kTile - 1) / kTile;
+  if (tiles > 128) return -3;
+  const bool p = pdl != 0;
+  int rc;
+  if ((rc = launch_pdl(samp_max_kernel, dim3(tiles, kDist), dim3(kThreads), 0, S(stream), p, a))) return rc;
+  if ((rc = launch_pdl(samp_exp_kernel, dim3(tiles, kDist), dim3(kThreads), 0, S(stream), p, a))) return rc;
+  for (int pass = 0; pass < 4; ++pass)
+    if ((rc = launch_pdl(samp_hist_kernel, dim3(tiles, kDist), dim3(kThreads), 0, S(stream), p, a, pass))) return rc;
+  if ((rc = launch_pdl(samp_accept_kernel, dim3(1), dim3(64), 0, S(stream), p, a))) return rc;
+  if ((rc = launch_pdl(samp_tile_mass_kernel, dim3(tiles), dim3(kThreads), 0, S(stream), p, a))) return rc;
+  return launch_pdl(samp_draw_kernel, dim3(1), dim3(kThreads), 0, S(stream), p, a, tiles, domain);
+}
+
+extern "C" int nrt_tail_commit(const void* args, void* stream, int pdl) {
+  TailArgs a;
+  memcpy(&a, args, sizeof(a));
+  return launch_pdl(tail_commit_kernel, dim3(1), dim3(32), 0, S(stream), pdl != 0, a);
+}
+
+extern "C" int nrt_epoch_advance(void* epoch, void* stream, int pdl) {
+  return launch_pdl(epoch_advance_kernel, dim3(1), dim3(32), 0, S(stream), pdl != 0, (uint32_t*)epoch);
+}
+
+extern "C" int nrt_prefill_cursor(const int* prompt, int n_prompt, int rows, int* ctrl, int* tokens, void* stream, int pdl) {
+  return launch_pdl(prefill_cursor_kernel, dim3(1), dim3(32), 0, S(stream), pdl != 0, prompt, n_prompt, rows, ctrl, tokens);
+}
+
+extern "C" float nrt_philox_uniform(unsigned long long seed, unsigned int domain, unsigned int a, unsigned int b) {
+  return philox_uniform(seed, domain, a, b);
+}

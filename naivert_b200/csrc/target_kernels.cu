@@ -165,7 +165,7 @@ struct AttnPostArgs {
   __nv_bfloat16* q_out;      // [rows][heads][head_dim]
   __nv_bfloat16* k_cache;    // [cap][kv_heads][head_dim]
   __nv_bfloat16* v_cache;    // [cap][kv_heads][v_dim]
-  int ring;                  // > 0: position p is stored at p % ring
+  int ring;                  // > 0: position p is stored at p % ring; < 0: row r is stored at r (block buffers)
   // optional per-head RMS norms (draft q_norm / k_norm), applied before RoPE
   const __nv_bfloat16* q_norm;
   const __nv_bfloat16* k_norm;
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* src = a.qkv + (size_t)r * a.ld;
   const int pos = *a.pos0 + r;
-  const size_t slot = a.ring > 0 ? (size_t)(pos % a.ring) : (size_t)pos;
+  const size_t slot = a.ring > 0 ? (size_t)(pos % a.ring) : (a.ring < 0 ? (size_t)r : (size_t)pos);
   const float2* rt = a.rope + (size_t)r * (a.rope_dim / 2);
 
   // q heads and k heads: [optional head RMS norm] -> bf16 -> RoPE on adjacent pairs -> bf16

@@ -68,7 +68,7 @@ def tiny_spec(weight_dtype: str = "fp32") -> ModelSpec:
     )
 
 
-def small_w8a8_spec(layers: int = 3) -> ModelSpec:
+def small_w8a8_spec(layers: int = 4) -> ModelSpec:
     """A W8A8 geometry with every tile dimension a multiple of 128 but tiny weights:
     used by GPU kernel tests and the smoke run (same kernels as the full model)."""
     kinds = tuple(FULL_DSA if i % 3 == 0 else SLIDING_WINDOW for i in range(layers))
@@ -95,6 +95,5 @@ def small_w8a8_spec(layers: int = 3) -> ModelSpec:
         think_end_token_id=8190,
         draft=DraftSpec(layer_count=2, hidden=1024, head_count=8, kv_head_count=4, head_dim=128,
                         intermediate=1024, markov_rank=128, block_size=7, window=1024,
-                        mask_token_id=8189, target_layer_ids=tuple(min(layers - 1, j * layers // 8)
-                                                                   for j in range(8))),
+                        mask_token_id=8189, target_layer_ids=tuple(range(layers))),
     )

@@ -124,6 +124,7 @@ class ReferenceModel:
                 self.ik.append(None)
                 self.iks.append(None)
         self.last_selection = {}
+        self.trace = {}
 
     # ------------------------------------------------------------------ attention
     def _attention(self, L: int, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
@@ -164,7 +165,9 @@ class ReferenceModel:
                     pr = pr[:-1]
                 o[r, h] = pr @ vv[:, g]
         o = rc.r(o).reshape(R, a.head_count * a.v_head_dim)
-        return self._row_parallel(x, o, lw["wo"], a.head_count * a.v_head_dim)
+        out = self._row_parallel(x, o, lw["wo"], a.head_count * a.v_head_dim)
+        self.trace[(L, "q")], self.trace[(L, "o")], self.trace[(L, "attn")] = q, o, out
+        return out
 
     def _index_select(self, L, xn, pos, tab_positions):
         s, rc, lw = self.spec, self.rc, self.w["layers"][L]
@@ -250,6 +253,7 @@ class ReferenceModel:
             return rc.r(total)
         rt = s.routing
         idx, p = self.route(L, xn)
+        self.trace[(L, "route")] = (idx, p)
         I = rt.intermediate // self.tp
         R = x.shape[0]
         for rank in range(self.tp):

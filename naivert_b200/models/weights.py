@@ -73,7 +73,7 @@ def init_state_dict(spec: ModelSpec, seed: int = 0, std: float = 0.02, device="c
             sd[p + "mlp.up_proj.weight"] = rnd(I, H).to(wdt)
             sd[p + "mlp.down_proj.weight"] = rnd(H, I).to(wdt)
         else:
-            sd[p + "mlp.gate.weight"] = rnd(rt.expert_count, H, s=0.5).float()
+            sd[p + "mlp.gate.weight"] = rnd(rt.expert_count, H, s=0.03).float()
             if rt.score_func == "sigmoid":
                 sd[p + "mlp.gate.e_score_correction_bias"] = rnd(rt.expert_count, s=0.05).float()
             for e in range(rt.expert_count):

@@ -40,7 +40,7 @@ class GemmArgs(C.Structure):
                 ("n_active", VP), ("active_ids", VP), ("probs", VP), ("max_slots", I32),
                 ("w_scale0", VP), ("w_scale1", VP), ("a_scale", VP),
                 ("out_f32", VP), ("out_bf16", VP), ("ld_out", I32), ("out_scale", F32),
-                ("out_q", VP), ("out_qscale", VP), ("resid", VP), ("out_copy", VP),
+                ("out_q", VP), ("out_qscale", VP), ("resid", VP), ("out_copy", VP), ("ld_copy", I32),
                 ("fab", FabricArgs), ("status", VP)]
 
 
@@ -132,10 +132,11 @@ def weight_tmap(w: torch.Tensor) -> TensorMap:
 
 def act_tmap(x: torch.Tensor) -> TensorMap:
     """[rows (multiple of 16), K] activations -> 2-D map with 16-row x 128-byte boxes."""
-    assert x.dim() == 2 and x.is_contiguous() and x.shape[0] % K_TOK == 0
+    assert x.dim() == 2 and x.stride(1) == 1 and x.shape[0] % K_TOK == 0
     r, k = x.shape
     es = x.element_size()
-    return TensorMap(x, (k, r), (k * es,), (128 // es, K_TOK), 0 if es == 1 else 1)
+    assert (x.stride(0) * es) % 16 == 0 and x.data_ptr() % 16 == 0
+    return TensorMap(x, (k, r), (x.stride(0) * es,), (128 // es, K_TOK), 0 if es == 1 else 1)
 
 
 # ----------------------------------------------------------------------------- launches
@@ -179,3 +180,95 @@ def topk_rows(logits, pos0, rows, top_k, sel, pdl=True):
 
 def router(args: RouterArgs, pdl=True):
     check(lib().nrt_router(C.byref(args), VP(_stream()), int(pdl)), "router")
+
+
+# ----------------------------------------------------------------------------- fabric / sampler / draft / tail
+class XchgArgs(C.Structure):
+    _fields_ = [("box", VP * K_MAX_PEERS), ("epoch", VP), ("status", VP), ("tp", I32), ("rank", I32),
+                ("timeout_ns", U64)]
+
+
+class SamplerArgs(C.Structure):
+    _fields_ = [("zp", VP), ("ldp", I32), ("zq", VP), ("ldq", I32), ("vlocal", I32), ("vbase", I32), ("e", VP),
+                ("counts", VP), ("params", VP), ("seed", VP), ("ctrl", VP), ("block_ids", VP),
+                ("n_rows_p", I32), ("n_rows_q", I32), ("st", VP), ("x", XchgArgs)]
+
+
+class TailArgs(C.Structure):
+    _fields_ = [("ctrl", VP), ("block_ids", VP), ("epoch", VP), ("st", VP), ("ring", VP), ("ring_size", I32),
+                ("cancel", VP), ("stop_ids", VP), ("n_stop", I32), ("counts", VP), ("vbase", I32), ("vlocal", I32),
+                ("status", VP), ("n_rows_q", I32)]
+
+
+class MarkovArgs(C.Structure):
+    _fields_ = [("logits", VP), ("ld", I32), ("w1", VP), ("w2", VP), ("rank_dim", I32), ("vlocal", I32),
+                ("vbase", I32), ("vocab", I32), ("block_ids", VP), ("zq", VP), ("params", VP), ("seed", VP),
+                ("ctrl", VP), ("best", VP), ("ticket", VP), ("x", XchgArgs)]
+
+
+class RingRecord(C.Structure):
+    _fields_ = [("generation", C.c_uint), ("count", I32), ("tokens", I32 * 8), ("pos0", I32), ("stop_reason", I32),
+                ("t_end_ns", U64), ("accepted", I32), ("pad", I32 * 1)]
+
+
+_checked_aux = False
+
+
+def aux_lib():
+    """Library handle with the sampler/draft/tail struct sizes verified."""
+    global _checked_aux
+    L = lib()
+    if not _checked_aux:
+        for name, st in (("nrt_sampler_args_size", SamplerArgs), ("nrt_tail_args_size", TailArgs),
+                         ("nrt_markov_args_size", MarkovArgs), ("nrt_ring_record_size", RingRecord)):
+            got = getattr(L, name)()
+            if got != C.sizeof(st):
+                raise RuntimeError(f"{st.__name__}: library has {got} bytes, bindings {C.sizeof(st)}")
+        L.nrt_philox_uniform.restype = C.c_float
+        _checked_aux = True
+    return L
+
+
+def sampler_state_bytes() -> int:
+    return aux_lib().nrt_sampler_state_size()
+
+
+def sampler_run(args: SamplerArgs, domain: int = 1, pdl=True):
+    check(aux_lib().nrt_sampler_run(C.byref(args), domain, VP(_stream()), int(pdl)), "sampler")
+
+
+def tail_commit(args: TailArgs, pdl=True):
+    check(aux_lib().nrt_tail_commit(C.byref(args), VP(_stream()), int(pdl)), "tail_commit")
+
+
+def epoch_advance(epoch, pdl=True):
+    check(aux_lib().nrt_epoch_advance(VP(ptr(epoch)), VP(_stream()), int(pdl)), "epoch_advance")
+
+
+def draft_block_input(block_ids, embed, mask, x, rows, pdl=True):
+    check(aux_lib().nrt_draft_block_input(VP(ptr(block_ids)), VP(ptr(embed)), VP(ptr(mask)), VP(ptr(x)), x.shape[1],
+                                          rows, embed.shape[0], VP(_stream()), int(pdl)), "draft_block_input")
+
+
+def markov_step(args: MarkovArgs, step: int, pdl=True):
+    check(aux_lib().nrt_markov_step(C.byref(args), step, VP(_stream()), int(pdl)), "markov_step")
+
+
+def philox_uniform(seed: int, domain: int, a: int, b: int) -> float:
+    return float(aux_lib().nrt_philox_uniform(C.c_ulonglong(seed), C.c_uint(domain), C.c_uint(a), C.c_uint(b)))
+
+
+def prefill_cursor(prompt, n_prompt, rows, ctrl, tokens, pdl=True):
+    check(aux_lib().nrt_prefill_cursor(VP(ptr(prompt)), n_prompt, rows, VP(ptr(ctrl)), VP(ptr(tokens)), VP(_stream()),
+                                       int(pdl)), "prefill_cursor")
+
+
+def host_alloc_mapped(nbytes: int):
+    """Mapped pinned host memory: (host address, device alias)."""
+    h, d = C.c_void_p(), C.c_void_p()
+    check(lib().nrt_host_alloc_mapped(C.byref(h), C.byref(d), C.c_size_t(nbytes)), "cudaHostAlloc")
+    return h.value, d.value
+
+
+def host_free(addr: int):
+    lib().nrt_host_free(C.c_void_p(addr))

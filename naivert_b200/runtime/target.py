@@ -1,0 +1,318 @@
+"""Per-rank target runtime: packed weights, KV caches, scratch and the verify/decode step.
+
+``TargetRuntime.step()`` enqueues one forward pass of ``rows`` consecutive token rows
+(1 = seq-1 decode, 8 = verify, up to 16) on the current stream.  Nothing on that path
+allocates or synchronises, positions and token ids live in device memory, so the same
+call is captured into the CUDA graph of a speculative round.
+
+Kernel sequence per layer: RMSNorm(+e4m3 packet) -> fused q/k/v(/indexer) projection
+(tcgen05, bf16) -> RoPE / KV append / indexer quantisation -> [indexer logits -> exact top-k]
+-> row attention (+ e4m3 packet of o) -> o_proj (tcgen05 fp8) fused with the tensor-parallel
+all-reduce and residual -> RMSNorm -> router -> grouped gate/up (SiLU, e4m3 packet) -> grouped
+down fused with probability weighting, all-reduce and residual.
+
+Parity: ``RankRuntime.phases`` (tests/gpu/naive_n0p5_e2e/run_naive_n0p5_decode.py:327-440) and
+``VerifyRuntime.phases`` (tests/gpu/naive_n0p5_e2e/run_naive_n0p5_verify.py:148-272); cache
+layout naivert/models/naive_n0p5/checkpoint_fp8.py:254-260.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..models.spec import FULL_DSA, ModelSpec
+from ..ops import kernels as K
+
+PAD_ROWS = K.K_TOK
+
+
+def _pad128(n: int) -> int:
+    return -(-n // 128) * 128
+
+
+def LocalFabric(device="cuda"):
+    """Fabric of a single rank (tp = 1): status and epoch words, no peers."""
+    from ..parallel.fabric import Fabric
+    return Fabric(0, 1, 0, device=torch.device(device) if not isinstance(device, torch.device) else device)
+
+
+class _Linear8:
+    """Packed e4m3 weight (+ block scales) with its tensor map."""
+
+    def __init__(self, q: dict, device):
+        self.w = q["w"].to(device).contiguous()
+        self.s = q["s"].to(device).float().contiguous()
+        self.map = K.weight_tmap(self.w.view(torch.uint8))
+        self.n, self.k = self.w.shape[-2], self.w.shape[-1]
+
+
+class TargetRuntime:
+    def __init__(self, spec: ModelSpec, rank_weights: dict, fabric, rows: int = 8, capacity: int = 16384,
+                 device="cuda", pdl: bool = True):
+        if spec.weight_dtype != "fp8":
+            raise ValueError("the CUDA runtime implements the W8A8 recipe only")
+        if spec.routing.shared_expert_count:
+            raise ValueError("shared experts are only supported by the torch oracle")
+        self.spec, self.fab, self.rows, self.capacity, self.dev, self.pdl = spec, fabric, rows, capacity, device, pdl
+        self.tp, self.rank = fabric.tp, fabric.rank
+        s = spec
+        H = s.hidden
+        dev = device
+        bf, f32, i32, u8 = torch.bfloat16, torch.float32, torch.int32, torch.uint8
+
+        # ---- control + step inputs
+        self.ctrl = torch.zeros(16, dtype=i32, device=dev)          # [0] = position of row 0
+        self.tokens = torch.zeros(PAD_ROWS, dtype=i32, device=dev)
+        # ---- activations (16 padded rows)
+        self.x = torch.zeros(PAD_ROWS, H, dtype=bf, device=dev)
+        self.xn = torch.zeros(PAD_ROWS, H, dtype=bf, device=dev)
+        self.x8 = torch.zeros(PAD_ROWS, H, dtype=u8, device=dev)
+        self.xs = torch.ones(PAD_ROWS, H // 128, dtype=f32, device=dev)
+        self.map_xn, self.map_x8 = K.act_tmap(self.xn), K.act_tmap(self.x8)
+        rt = s.routing
+        self.max_slots = min(rt.expert_count, PAD_ROWS * rt.top_k)
+        self.step_slots = min(rt.expert_count, rows * rt.top_k)
+        I = s.expert_inter_local(self.tp)
+        Id = s.dense_inter_local(self.tp)
+        self.y8 = torch.zeros(self.max_slots * PAD_ROWS, I, dtype=u8, device=dev)
+        self.ys = torch.ones(self.max_slots * PAD_ROWS, max(1, I // 128), dtype=f32, device=dev)
+        self.map_y8 = K.act_tmap(self.y8)
+        if s.dense_layer_count:
+            self.yd8 = torch.zeros(PAD_ROWS, Id, dtype=u8, device=dev)
+            self.yds = torch.ones(PAD_ROWS, Id // 128, dtype=f32, device=dev)
+            self.map_yd8 = K.act_tmap(self.yd8)
+        self.scores = torch.zeros(PAD_ROWS, rt.expert_count, dtype=f32, device=dev)
+        self.ticket = torch.zeros(1, dtype=i32, device=dev)
+        self.n_active = torch.zeros(1, dtype=i32, device=dev)
+        self.active_ids = torch.zeros(self.max_slots, dtype=i32, device=dev)
+        self.probs = torch.zeros(self.max_slots, PAD_ROWS, dtype=f32, device=dev)
+        self.topk_ids = torch.zeros(PAD_ROWS, rt.top_k, dtype=i32, device=dev)
+        self.topk_p = torch.zeros(PAD_ROWS, rt.top_k, dtype=f32, device=dev)
+        V = s.vocab_shard(self.tp)
+        self.logits = torch.zeros(PAD_ROWS, V, dtype=f32, device=dev)
+        taps = s.draft.target_layer_ids if s.draft is not None else ()
+        if len(set(taps)) != len(taps):
+            raise ValueError("draft feature taps must be distinct layers")
+        # feature rows of all taps side by side: [16][taps * hidden] (the draft fc operand)
+        self.feats = torch.zeros(PAD_ROWS, max(1, len(taps)) * H, dtype=bf, device=dev)
+        self.tap_of_layer = {L: j for j, L in enumerate(taps)}
+
+        # ---- weights
+        w = rank_weights
+        self.embed = w["embed"].to(dev).to(bf).contiguous()
+        self.g_final = w["norm"].to(dev).to(bf).contiguous()
+        self.lm_head = w["lm_head"].to(dev).to(bf).contiguous()
+        self.map_lm = K.weight_tmap(self.lm_head)
+        ix = s.indexer
+        self.layers: List[dict] = []
+        max_qkv = 0
+        for L, lw in enumerate(w["layers"]):
+            a = s.attention[lw["kind"]]
+            nh, nkv = a.local_heads(self.tp), a.local_kv_heads(self.tp)
+            parts = [lw["wq"], lw["wk"], lw["wv"]]
+            cols = {"q": 0, "k": nh * a.head_dim, "v": nh * a.head_dim + nkv * a.head_dim}
+            n = cols["v"] + nkv * a.v_head_dim
+            if lw["kind"] == FULL_DSA:
+                cols["iq"], cols["ik"] = n, n + ix.head_count * ix.head_dim
+                cols["iw"] = cols["ik"] + ix.head_dim
+                parts += [lw["iwq"], lw["iwk"], lw["iww"]]
+                n = cols["iw"] + ix.head_count
+            wqkv = torch.zeros(_pad128(n), H, dtype=bf, device=dev)
+            wqkv[:n] = torch.cat([p.to(dev).to(bf) for p in parts])
+            max_qkv = max(max_qkv, wqkv.shape[0])
+            d = {"kind": lw["kind"], "a": a, "nh": nh, "nkv": nkv, "cols": cols, "wqkv": wqkv,
+                 "map_qkv": K.weight_tmap(wqkv), "g_in": lw["g_in"].to(dev).to(bf).contiguous(),
+                 "g_post": lw["g_post"].to(dev).to(bf).contiguous(), "wo": _Linear8(lw["wo"], dev),
+                 "sink": None if lw["sink"] is None else lw["sink"].to(dev).to(bf).contiguous()}
+            if lw["kind"] == FULL_DSA:
+                d["ik_w"] = lw["ik_w"].to(dev).to(bf).contiguous()
+                d["ik_b"] = lw["ik_b"].to(dev).to(bf).contiguous()
+                d["k"] = torch.zeros(capacity, nkv, a.head_dim, dtype=bf, device=dev)
+                d["v"] = torch.zeros(capacity, nkv, a.v_head_dim, dtype=bf, device=dev)
+                d["ik"] = torch.zeros(capacity, ix.head_dim, dtype=u8, device=dev)
+                d["iks"] = torch.ones(capacity, dtype=f32, device=dev)
+                d["ring"] = 0
+            else:
+                ring = a.sliding_window + PAD_ROWS
+                d["k"] = torch.zeros(ring, nkv, a.head_dim, dtype=bf, device=dev)
+                d["v"] = torch.zeros(ring, nkv, a.v_head_dim, dtype=bf, device=dev)
+                d["ring"] = ring
+            if "dense" in lw:
+                d["dense"] = {n_: _Linear8(lw["dense"][n_], dev) for n_ in ("gate", "up", "down")}
+            else:
+                d["router_w"] = lw["router_w"].to(dev).float().contiguous()
+                d["router_b"] = lw["router_b"].to(dev).float().contiguous()
+                d["gate"], d["up"], d["down"] = (_Linear8(lw[n_], dev) for n_ in ("gate", "up", "down"))
+            self.layers.append(d)
+        self.qkv = torch.zeros(PAD_ROWS, max_qkv, dtype=f32, device=dev)
+        a0 = s.attention[s.layer_kinds[0]]
+        nh_max = max(s.attention[k].local_heads(self.tp) for k in set(s.layer_kinds))
+        self.q = torch.zeros(PAD_ROWS, nh_max, a0.head_dim, dtype=bf, device=dev)
+        self.o8 = torch.zeros(PAD_ROWS, nh_max * a0.v_head_dim, dtype=u8, device=dev)
+        self.os = torch.ones(PAD_ROWS, nh_max * a0.v_head_dim // 128, dtype=f32, device=dev)
+        self.map_o8 = K.act_tmap(self.o8)
+        self.rope = {kind: torch.zeros(PAD_ROWS, s.attention[kind].rope_dim // 2, 2, dtype=f32, device=dev)
+                     for kind in set(s.layer_kinds)}
+        self.idx_rope = torch.zeros(PAD_ROWS, ix.rope_dim // 2, 2, dtype=f32, device=dev)
+        if FULL_DSA in s.layer_kinds:
+            self.iq8 = torch.zeros(PAD_ROWS * ix.head_count, ix.head_dim, dtype=u8, device=dev)
+            self.ihw = torch.zeros(PAD_ROWS, ix.head_count, dtype=f32, device=dev)
+            self.idx_logits = torch.zeros(PAD_ROWS, capacity, dtype=f32, device=dev)
+            self.sel = torch.zeros(PAD_ROWS, ix.top_k, dtype=i32, device=dev)
+        self._build_args()
+
+    # ------------------------------------------------------------------ argument blocks (built once)
+    def _gemm_args(self, n, k, rows) -> K.GemmArgs:
+        g = K.GemmArgs()
+        g.n_total, g.k_total, g.rows, g.a_group = n, k, rows, 0
+        g.out_scale = 1.0
+        g.status = self.fab.status.data_ptr()
+        return g
+
+    def _build_args(self):
+        s, R = self.spec, self.rows
+        H = s.hidden
+        ix = s.indexer
+        pos0 = self.ctrl.data_ptr()
+        for L, d in enumerate(self.layers):
+            a, nh, nkv, cols = d["a"], d["nh"], d["nkv"], d["cols"]
+            g = self._gemm_args(d["wqkv"].shape[0], H, R)
+            g.out_f32, g.ld_out = self.qkv.data_ptr(), self.qkv.shape[1]
+            d["args_qkv"] = g
+            p = K.AttnPostArgs()
+            p.qkv, p.ld, p.rows, p.pos0 = self.qkv.data_ptr(), self.qkv.shape[1], R, pos0
+            p.heads, p.kv_heads, p.head_dim, p.v_dim, p.rope_dim = nh, nkv, a.head_dim, a.v_head_dim, a.rope_dim
+            p.value_scale = a.value_scale
+            p.rope = self.rope[d["kind"]].data_ptr()
+            p.q_out, p.k_cache, p.v_cache, p.ring = self.q.data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["ring"]
+            p.norm_eps = s.norm_eps
+            p.col_q, p.col_k, p.col_v = cols["q"], cols["k"], cols["v"]
+            if d["kind"] == FULL_DSA:
+                p.idx_heads, p.idx_dim, p.idx_rope = ix.head_count, ix.head_dim, ix.rope_dim
+                p.idx_rope_tab = self.idx_rope.data_ptr()
+                p.ik_w, p.ik_b = d["ik_w"].data_ptr(), d["ik_b"].data_ptr()
+                p.ln_eps, p.idx_weight_scale = s.norm_eps, ix.weight_scale
+                p.iq8, p.ihw = self.iq8.data_ptr(), self.ihw.data_ptr()
+                p.ik_cache, p.ik_scale = d["ik"].data_ptr(), d["iks"].data_ptr()
+                p.col_iq, p.col_ik, p.col_iw = cols["iq"], cols["ik"], cols["iw"]
+                ia = K.IndexArgs()
+                ia.iq8, ia.ihw, ia.ik, ia.iks, ia.pos0 = (self.iq8.data_ptr(), self.ihw.data_ptr(), d["ik"].data_ptr(),
+                                                          d["iks"].data_ptr(), pos0)
+                ia.rows, ia.heads, ia.dim, ia.top_k = R, ix.head_count, ix.head_dim, ix.top_k
+                ia.logits, ia.ld = self.idx_logits.data_ptr(), self.idx_logits.shape[1]
+                d["args_index"] = ia
+            d["args_post"] = p
+            t = K.AttnArgs()
+            t.q, t.k_cache, t.v_cache, t.pos0 = self.q.data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), pos0
+            t.rows, t.heads, t.kv_heads, t.head_dim, t.v_dim = R, nh, nkv, a.head_dim, a.v_head_dim
+            t.scale = a.softmax_scale
+            if a.sliding_window is not None:
+                t.mode, t.window, t.ring = 0, a.sliding_window, d["ring"]
+            else:
+                t.mode, t.top_k, t.sel = 1, ix.top_k, self.sel.data_ptr()
+            t.sink = None if d["sink"] is None else d["sink"].data_ptr()
+            t.o8, t.o_scale = self.o8.data_ptr(), self.os.data_ptr()
+            d["args_attn"] = t
+            # o_proj + all-reduce + residual
+            g = self._gemm_args(H, d["wo"].k, R)
+            g.w_scale0, g.a_scale = d["wo"].s.data_ptr(), self.os.data_ptr()
+            g.out_bf16, g.ld_out, g.resid = self.x.data_ptr(), H, self.x.data_ptr()
+            g.fab = self.fab.fabric_args(2 * L, H)
+            d["args_o"] = g
+            tap = self.tap_of_layer.get(L)
+            copy_ptr = None if tap is None else self.feats.data_ptr() + tap * H * 2
+            if "dense" in d:
+                dn = d["dense"]
+                g = self._gemm_args(dn["gate"].n, H, R)
+                g.w_scale0, g.w_scale1, g.a_scale = dn["gate"].s.data_ptr(), dn["up"].s.data_ptr(), self.xs.data_ptr()
+                g.out_q, g.out_qscale = self.yd8.data_ptr(), self.yds.data_ptr()
+                d["args_gu"] = g
+                g = self._gemm_args(H, dn["down"].k, R)
+                g.w_scale0, g.a_scale = dn["down"].s.data_ptr(), self.yds.data_ptr()
+                g.out_bf16, g.ld_out, g.resid = self.x.data_ptr(), H, self.x.data_ptr()
+                g.out_copy, g.ld_copy = copy_ptr, self.feats.shape[1]
+                g.fab = self.fab.fabric_args(2 * L + 1, H)
+                d["args_down"] = g
+            else:
+                rt = s.routing
+                r = K.RouterArgs()
+                r.xn, r.w, r.bias = self.xn.data_ptr(), d["router_w"].data_ptr(), d["router_b"].data_ptr()
+                r.hidden, r.experts, r.rows, r.top_k = H, rt.expert_count, R, rt.top_k
+                r.sigmoid, r.normalize, r.route_scale = int(rt.score_func == "sigmoid"), int(rt.normalize_top_k), rt.route_scale
+                r.scores, r.ticket = self.scores.data_ptr(), self.ticket.data_ptr()
+                r.n_active, r.active_ids, r.probs = self.n_active.data_ptr(), self.active_ids.data_ptr(), self.probs.data_ptr()
+                r.topk_ids, r.topk_p, r.max_slots = self.topk_ids.data_ptr(), self.topk_p.data_ptr(), self.max_slots
+                d["args_router"] = r
+                g = self._gemm_args(d["gate"].n, H, R)
+                g.n_active, g.active_ids, g.max_slots = self.n_active.data_ptr(), self.active_ids.data_ptr(), self.max_slots
+                g.w_scale0, g.w_scale1, g.a_scale = d["gate"].s.data_ptr(), d["up"].s.data_ptr(), self.xs.data_ptr()
+                g.out_q, g.out_qscale = self.y8.data_ptr(), self.ys.data_ptr()
+                d["args_gu"] = g
+                g = self._gemm_args(H, d["down"].k, R)
+                g.n_active, g.active_ids, g.probs, g.max_slots = (self.n_active.data_ptr(), self.active_ids.data_ptr(),
+                                                                 self.probs.data_ptr(), self.max_slots)
+                g.w_scale0, g.a_scale = d["down"].s.data_ptr(), self.ys.data_ptr()
+                g.out_bf16, g.ld_out, g.resid = self.x.data_ptr(), H, self.x.data_ptr()
+                g.out_copy, g.ld_copy = copy_ptr, self.feats.shape[1]
+                g.fab = self.fab.fabric_args(2 * L + 1, H)
+                d["args_down"] = g
+        g = self._gemm_args(self.lm_head.shape[0], H, R)
+        g.out_f32, g.ld_out = self.logits.data_ptr(), self.logits.shape[1]
+        self.args_head = g
+
+    # ------------------------------------------------------------------ the step
+    V_FP8_STORE = K.gemm_variant(True, False, K.EPI_STORE_F32, K.GROUP_NONE)
+    V_FP8_AR = K.gemm_variant(True, False, K.EPI_ALLREDUCE, K.GROUP_NONE)
+    V_FP8_GU = K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_NONE)
+    V_FP8_GU_ITEM = K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM)
+    V_FP8_DOWN_LOOP = K.gemm_variant(True, False, K.EPI_ALLREDUCE, K.GROUP_LOOP)
+    V_BF16_STORE = K.gemm_variant(False, False, K.EPI_STORE_F32, K.GROUP_NONE)
+
+    def step(self, head: bool = True, stop_after=None) -> None:
+        s, R, pdl = self.spec, self.rows, self.pdl
+        K.embed_rows(self.tokens, self.embed, self.x, R, pdl=pdl)
+        for kind, tab in self.rope.items():
+            a = s.attention[kind]
+            K.rope_table(self.ctrl, R, a.rope_dim, a.rope_theta, tab, pdl=pdl)
+        if FULL_DSA in self.rope:
+            K.rope_table(self.ctrl, R, s.indexer.rope_dim, s.attention[FULL_DSA].rope_theta, self.idx_rope, pdl=pdl)
+        for L, d in enumerate(self.layers):
+            K.prep_norm(self.x, d["g_in"], R, s.norm_eps, xn=self.xn, pdl=pdl)
+            K.gemm(self.V_BF16_STORE, d["map_qkv"], None, self.map_xn, d["args_qkv"], d["wqkv"].shape[0] // 128, pdl=pdl)
+            K.attn_post(d["args_post"], pdl=pdl)
+            if d["kind"] == FULL_DSA:
+                K.index_logits_simple(d["args_index"], 148, pdl=pdl)
+                K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
+            K.attn_rows(d["args_attn"], pdl=pdl)
+            K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128, pdl=pdl)
+            if stop_after == (L, "attn"):
+                return
+            if "dense" in d:
+                dn = d["dense"]
+                K.prep_norm(self.x, d["g_post"], R, s.norm_eps, x8=self.x8, xs=self.xs, pdl=pdl)
+                K.gemm(self.V_FP8_GU, dn["gate"].map, dn["up"].map, self.map_x8, d["args_gu"], dn["gate"].n // 128, pdl=pdl)
+                K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128, pdl=pdl)
+            else:
+                K.prep_norm(self.x, d["g_post"], R, s.norm_eps, xn=self.xn, x8=self.x8, xs=self.xs, pdl=pdl)
+                K.router(d["args_router"], pdl=pdl)
+                K.gemm(self.V_FP8_GU_ITEM, d["gate"].map, d["up"].map, self.map_x8, d["args_gu"], d["gate"].n // 128,
+                       self.step_slots, pdl=pdl)
+                K.gemm(self.V_FP8_DOWN_LOOP, d["down"].map, None, self.map_y8, d["args_down"], s.hidden // 128, 1, pdl=pdl)
+        if head:
+            K.prep_norm(self.x, self.g_final, R, s.norm_eps, xn=self.xn, pdl=pdl)
+            K.gemm(self.V_BF16_STORE, self.map_lm, None, self.map_xn, self.args_head, -(-self.lm_head.shape[0] // 128), pdl=pdl)
+
+    # ------------------------------------------------------------------ host helpers (not on the hot path)
+    def set_inputs(self, tokens, pos0: int) -> None:
+        t = torch.as_tensor(tokens, dtype=torch.int32)
+        self.tokens[: t.numel()].copy_(t.to(self.dev))
+        self.ctrl[0] = pos0
+
+    def kv_bytes(self) -> int:
+        n = 0
+        for d in self.layers:
+            for k in ("k", "v", "ik", "iks"):
+                if k in d:
+                    n += d[k].numel() * d[k].element_size()
+        return n
