@@ -165,9 +165,9 @@ class ModelSpec:
         if draft is not None:
             ids = tuple(i for i in draft.target_layer_ids if i < n)
             if len(ids) < len(draft.target_layer_ids):
-                # keep the feature count: spread the taps over the surviving layers
-                k = len(draft.target_layer_ids)
-                ids = tuple(min(n - 1, (j * n) // k) for j in range(k))
+                # spread the taps over the surviving layers (fewer taps when fewer layers remain)
+                k = min(len(draft.target_layer_ids), n)
+                ids = tuple((j * n) // k for j in range(k))
             draft = replace(draft, target_layer_ids=ids)
         return replace(self, name=f"{self.name}-L{n}", layer_kinds=self.layer_kinds[:n], draft=draft)
 

@@ -98,7 +98,11 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = {"count": 0}          # kernels launched through this module (sampler chain counts as 9)
+
+
 def check(code: int, what: str) -> None:
+    LAUNCHES["count"] += 9 if what == "sampler" else 1
     if code != 0:
         raise RuntimeError(f"{what} failed with CUDA/driver error {code}")
 

@@ -96,6 +96,7 @@ class SpeculativeRound:
         self.prompt_dev = torch.zeros(capacity, dtype=torch.int32, device=dev)
         self.n_prompt = 0
         self.use_penalties = False
+        self.kernels_per_round = 0
         self._build_args()
         self.stream = torch.cuda.Stream(device=dev)
 
@@ -218,7 +219,9 @@ class SpeculativeRound:
         (KV rows it wrote lie at or beyond the anchor and are rewritten by round 0)."""
         saved_ctrl, saved_ids, saved_feats = self.t.ctrl.clone(), self.block_ids.clone(), self.t.feats.clone()
         self.ring.cancel.value = 1                       # the warm-up round commits nothing
+        before = K.LAUNCHES["count"]
         self.graph = self._capture(self.phases)
+        self.kernels_per_round = (K.LAUNCHES["count"] - before) // 2     # warm-up + capture
         self.stream.synchronize()
         self.ring.cancel.value = 0
         self.ring.clear()
