@@ -1,0 +1,31 @@
+"""Tensor-parallel engine over the peer-memory fabric on 2+ GPUs (child processes via torchrun)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _run(n):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29517", os.path.join(os.path.dirname(__file__), "mp_tp_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-4000:]
+    return json.loads(lines[-1][7:])
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_tensor_parallel_engine(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    r = _run(n)
+    assert r["status"] == 0
+    assert r["residual_identical"] and r["lockstep"] and r["deterministic"] and r["spec_equals_greedy"], r
+    assert r["verify_mean_rel"] < 0.1, r
+    assert r["real_sampling_tokens"] == 64
