@@ -34,6 +34,7 @@ constexpr int kBTileBytes = kTok * kKBytes;     // 2 KiB
 constexpr int kMaxPeers = 8;
 constexpr int kRowPairs = kTok / 2;             // tagged words per feature per source rank
 constexpr int kMailboxSlabs = 4;
+constexpr int kMaxSplit = 4;                    // CTAs of one cluster that share an output tile (split K / split experts)
 
 enum GroupMode : int { kGroupNone = 0, kGroupItem = 1, kGroupLoop = 2 };
 enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4 };
@@ -84,7 +85,8 @@ struct GemmCfg {
   static constexpr int kAccCols = DUAL ? 2 * kTok : kTok;          // TMEM columns per accumulator buffer
   static constexpr int kAccBufs = FP8 ? (DUAL ? 4 : 8) : 1;
   static constexpr int kTmemCols = (kAccCols * kAccBufs < 32) ? 32 : kAccCols * kAccBufs;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers + scratch*/;
+  static constexpr int kPartBytes = (kMaxSplit - 1) * kTok * kTileN * 4;   // split partials of the cluster peers
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers + scratch*/ + kPartBytes;
 };
 
 struct GemmSmemTail {
@@ -92,6 +94,7 @@ struct GemmSmemTail {
   uint64_t empty[8];
   uint64_t acc_full[8];
   uint64_t acc_empty[8];
+  uint64_t split_bar;          // leader: arrivals of the cluster peers' partials
   uint32_t tmem_base;
   uint32_t pad;
   float red[4][kTok];
@@ -122,12 +125,20 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x;
   const int n0 = n_tile * kTileN;
-  const int kb_count = p.k_total / (FP8 ? 128 : 64);
+  const int kb_total = p.k_total / (FP8 ? 128 : 64);
   constexpr int kElemsPerStage = FP8 ? 128 : 64;
+  // Cluster split: grid.y CTAs (one cluster) share this output tile.  kGroupNone splits K,
+  // kGroupLoop splits the expert list; the leader (cluster rank 0) adds the partials in rank order.
+  const int split = GROUP == kGroupItem ? 1 : (int)gridDim.y;
+  const int crank = split > 1 ? (int)cluster_ctarank() : 0;
+  const int kb_count = GROUP == kGroupNone ? kb_total / split : kb_total;   // K blocks this CTA walks per group
+  const int kb_first = GROUP == kGroupNone ? crank * kb_count : 0;
+  float* part = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + 1024);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
     for (int i = 0; i < Cfg::kAccBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
+    mbar_init(&tail->split_bar, 128 * (split > 1 ? split - 1 : 1));
     mbar_fence_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB);
@@ -136,6 +147,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   if (warp == 1) { tmem_alloc(&tail->tmem_base, Cfg::kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
+  if (split > 1) cluster_sync_all();           // peers' barriers are initialised before any remote arrive
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
 
@@ -168,10 +180,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         const int z = GROUP == kGroupNone ? p.a_group : p.active_ids[slot];
         uint8_t* sa = smem + st * Cfg::kStageBytes;
         mbar_expect_tx(&tail->full[st], Cfg::kStageBytes);
-        tma_load_3d(sa, &tmA0, &tail->full[st], kb * kElemsPerStage, n0, z);
-        if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kb * kElemsPerStage, n0, z);
+        const int kx = (kb_first + kb) * kElemsPerStage;
+        tma_load_3d(sa, &tmA0, &tail->full[st], kx, n0, z);
+        if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
         const int brow = (GROUP == kGroupLoop) ? slot * kTok : 0;
-        tma_load_2d(sa + (DUAL ? 2 : 1) * kATileBytes, &tmB, &tail->full[st], kb * kElemsPerStage, brow);
+        tma_load_2d(sa + (DUAL ? 2 : 1) * kATileBytes, &tmB, &tail->full[st], kx, brow);
       }
     }
   } else if (warp == 1) {
@@ -228,9 +241,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
       for (int r = 0; r < kTok; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
       if (FP8) {
-        const float* as = p.a_scale + (size_t)(GROUP == kGroupLoop ? slot : 0) * kTok * kb_count;
-        const float* ws0 = p.w_scale0 + ((size_t)z * nt_count + n_tile) * kb_count;
-        const float* ws1 = DUAL ? p.w_scale1 + ((size_t)z * nt_count + n_tile) * kb_count : nullptr;
+        const float* as = p.a_scale + (size_t)(GROUP == kGroupLoop ? slot : 0) * kTok * kb_total + kb_first;
+        const float* ws0 = p.w_scale0 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first;
+        const float* ws1 = DUAL ? p.w_scale1 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first : nullptr;
         for (int kb = 0; kb < kb_count; ++kb, ++u) {
           const int buf = u % Cfg::kAccBufs;
           if (!mbar_wait(&tail->acc_full[buf], (u / Cfg::kAccBufs) & 1, p.status, kSiteAccFull | buf)) { ok = false; break; }
@@ -244,7 +257,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           const float w1 = DUAL ? ws1[kb] : 0.f;
 #pragma unroll
           for (int r = 0; r < kTok; ++r) {
-            const float a = as[r * kb_count + kb];
+            const float a = as[r * kb_total + kb];
             acc0[r] += v0[r] * (a * w0);
             if (DUAL) acc1[r] += v1[r] * (a * w1);
           }
@@ -266,8 +279,27 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
     }
 
+    // ---------------------------------------------------------------- cluster split: partials -> leader
+    bool leader = true;
+    if (split > 1) {
+      if (crank != 0) {
+        leader = false;
+        const uint32_t dst = mapa_shared(smem_u32(part), 0);
+#pragma unroll
+        for (int r = 0; r < kTok; ++r)
+          st_cluster_f32(dst + (uint32_t)((((crank - 1) * kTok + r) * kTileN + row) * 4), mix0[r]);
+        mbar_arrive_cluster(mapa_shared(smem_u32(&tail->split_bar), 0));
+      } else {
+        if (mbar_wait_cluster(&tail->split_bar, 0, p.status, kSiteCluster)) {
+          for (int y = 1; y < split; ++y)
+#pragma unroll
+            for (int r = 0; r < kTok; ++r) mix0[r] += part[((y - 1) * kTok + r) * kTileN + row];
+        }
+      }
+    }
+
     // ---------------------------------------------------------------- epilogue op
-    const bool live = n_groups > 0 && n < p.n_total;
+    const bool live = leader && (n_groups > 0 || split > 1) && n < p.n_total;
     if (EPI == kEpiStoreF32) {
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
@@ -305,6 +337,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
     } else if (EPI == kEpiAllReduce) {
       const FabricArgs& f = p.fab;
+      const bool col_ok = leader && n < p.n_total;
       // Each rank rounds its partial to bf16, pushes it to every peer as tagged words and adds
       // the partials of all ranks in rank order in fp32 on top of the residual.
       uint32_t w[kMaxPeers][kRowPairs];
@@ -312,11 +345,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       float sum[kTok];
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
-        sum[r] = (p.resid && r < p.rows && n < p.n_total) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
+        sum[r] = (p.resid && r < p.rows && col_ok) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
       uint32_t own[kRowPairs];
 #pragma unroll
       for (int j = 0; j < kRowPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
-      if (f.tp > 1 && n < p.n_total) {
+      if (f.tp > 1 && col_ok) {
         const uint32_t tag = (*f.epoch) * 1024u + (uint32_t)f.call_idx + 1u;
         const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
         for (int d = 1; d < f.tp; ++d) {
@@ -365,7 +398,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
-        if (r < p.rows && n < p.n_total) {
+        if (r < p.rows && col_ok) {
           const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
           p.out_bf16[(size_t)r * p.ld_out + n] = o;
           if (p.out_copy) p.out_copy[(size_t)r * p.ld_copy + n] = o;

@@ -196,10 +196,14 @@ __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a
     const int t0 = blockIdx.x * kTile;
     for (int i = threadIdx.x; i < kTile; i += kThreads) {
       const int t = t0 + i;
-      if (t < a.vlocal) {
-        const unsigned int v = e[t];
-        if ((v & mask) == prefix && v != 0u) atomicAdd(&sh[(v >> shift) & 255u], (unsigned long long)v);
-      }
+      const unsigned int v = t < a.vlocal ? e[t] : 0u;
+      const bool in = (v & mask) == prefix && v != 0u;
+      // most codes share a bin (tiny probabilities): lanes with equal bins combine before the atomic
+      const unsigned int bin = in ? ((v >> shift) & 255u) : 0xFFFFFFFFu;
+      const unsigned int peers = __match_any_sync(0xffffffffu, bin);
+      unsigned long long sum = 0ull;
+      for (unsigned int m = peers; m; m &= m - 1) sum += __shfl_sync(peers, v, __ffs(m) - 1);
+      if (in && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&sh[bin], sum);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < 256; i += kThreads)

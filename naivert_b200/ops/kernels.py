@@ -143,6 +143,15 @@ def act_tmap(x: torch.Tensor) -> TensorMap:
     return TensorMap(x, (k, r), (x.stride(0) * es,), (128 // es, K_TOK), 0 if es == 1 else 1)
 
 
+def pick_split(n_tiles: int, k_blocks: int, max_ctas: int = 160) -> int:
+    """CTAs per output tile (one cluster): the largest of 4, 2, 1 that divides the K blocks and
+    keeps the grid within about one wave of the 148 SMs."""
+    for s in (4, 2):
+        if k_blocks % s == 0 and n_tiles * s <= max_ctas:
+            return s
+    return 1
+
+
 # ----------------------------------------------------------------------------- launches
 def gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: TensorMap, args: GemmArgs, grid_x: int,
          grid_y: int = 1, pdl: bool = True) -> None:

@@ -170,9 +170,11 @@ class DraftRuntime:
         ctrl[2].. ; rows beyond the committed count land beyond the context and are rewritten later."""
         d, R, pdl = self.d, self.rows, self.pdl
         K.rope_table(self.ctrl_ingest_pos, R, d.head_dim, d.rope_theta, self.rope_ing, pdl=pdl)
-        K.gemm(self.V_AR, self.map_fc, None, self.map_feats, self.args_fc, d.hidden // 128, pdl=pdl)
+        K.gemm(self.V_AR, self.map_fc, None, self.map_feats, self.args_fc, d.hidden // 128,
+               K.pick_split(d.hidden // 128, self.kf // 64), pdl=pdl)
         K.prep_norm(self.h, self.hidden_norm, R, d.norm_eps, xn=self.xn, pdl=pdl)
-        K.gemm(self.V_STORE, self.map_kv, None, self.map_xn, self.args_kv, self.wkv.shape[0] // 128, pdl=pdl)
+        K.gemm(self.V_STORE, self.map_kv, None, self.map_xn, self.args_kv, self.wkv.shape[0] // 128,
+               K.pick_split(self.wkv.shape[0] // 128, d.hidden // 64), pdl=pdl)
         for L in self.layers:
             K.attn_post(L["args_ingest_post"], pdl=pdl)
 
@@ -182,13 +184,16 @@ class DraftRuntime:
         K.rope_table(self.ctrl, R, d.head_dim, d.rope_theta, self.rope_blk, pdl=pdl)
         for L in self.layers:
             K.prep_norm(self.xd, L["g_in"], R, d.norm_eps, xn=self.xn, pdl=pdl)
-            K.gemm(self.V_STORE, L["map_qkv"], None, self.map_xn, L["args_qkv"], L["wqkv"].shape[0] // 128, pdl=pdl)
+            K.gemm(self.V_STORE, L["map_qkv"], None, self.map_xn, L["args_qkv"], L["wqkv"].shape[0] // 128,
+                   K.pick_split(L["wqkv"].shape[0] // 128, d.hidden // 64), pdl=pdl)
             K.attn_post(L["args_post"], pdl=pdl)
             K.attn_rows(L["args_attn"], pdl=pdl)
-            K.gemm(self.V_AR, L["map_wo"], None, self.map_o, L["args_o"], d.hidden // 128, pdl=pdl)
+            K.gemm(self.V_AR, L["map_wo"], None, self.map_o, L["args_o"], d.hidden // 128,
+                   K.pick_split(d.hidden // 128, self.nh * d.head_dim // 64), pdl=pdl)
             K.prep_norm(self.xd, L["g_post"], R, d.norm_eps, xn=self.xn, pdl=pdl)
             K.gemm(self.V_GU, L["map_gate"], L["map_up"], self.map_xn, L["args_gu"], self.I // 128, pdl=pdl)
-            K.gemm(self.V_AR, L["map_down"], None, self.map_y, L["args_down"], d.hidden // 128, pdl=pdl)
+            K.gemm(self.V_AR, L["map_down"], None, self.map_y, L["args_down"], d.hidden // 128,
+                   K.pick_split(d.hidden // 128, self.I // 64), pdl=pdl)
 
     def propose(self) -> None:
         """Head logits of all rows, then seven sequential Markov / Gumbel-max steps."""

@@ -279,26 +279,30 @@ class TargetRuntime:
             K.rope_table(self.ctrl, R, s.indexer.rope_dim, s.attention[FULL_DSA].rope_theta, self.idx_rope, pdl=pdl)
         for L, d in enumerate(self.layers):
             K.prep_norm(self.x, d["g_in"], R, s.norm_eps, xn=self.xn, pdl=pdl)
-            K.gemm(self.V_BF16_STORE, d["map_qkv"], None, self.map_xn, d["args_qkv"], d["wqkv"].shape[0] // 128, pdl=pdl)
+            nt = d["wqkv"].shape[0] // 128
+            K.gemm(self.V_BF16_STORE, d["map_qkv"], None, self.map_xn, d["args_qkv"], nt, K.pick_split(nt, s.hidden // 64), pdl=pdl)
             K.attn_post(d["args_post"], pdl=pdl)
             if d["kind"] == FULL_DSA:
                 K.index_logits_simple(d["args_index"], 148, pdl=pdl)
                 K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
             K.attn_rows(d["args_attn"], pdl=pdl)
-            K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128, pdl=pdl)
+            K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128,
+                   K.pick_split(s.hidden // 128, d["wo"].k // 128), pdl=pdl)
             if stop_after == (L, "attn"):
                 return
             if "dense" in d:
                 dn = d["dense"]
                 K.prep_norm(self.x, d["g_post"], R, s.norm_eps, x8=self.x8, xs=self.xs, pdl=pdl)
                 K.gemm(self.V_FP8_GU, dn["gate"].map, dn["up"].map, self.map_x8, d["args_gu"], dn["gate"].n // 128, pdl=pdl)
-                K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128, pdl=pdl)
+                K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128,
+                       K.pick_split(s.hidden // 128, dn["down"].k // 128), pdl=pdl)
             else:
                 K.prep_norm(self.x, d["g_post"], R, s.norm_eps, xn=self.xn, x8=self.x8, xs=self.xs, pdl=pdl)
                 K.router(d["args_router"], pdl=pdl)
                 K.gemm(self.V_FP8_GU_ITEM, d["gate"].map, d["up"].map, self.map_x8, d["args_gu"], d["gate"].n // 128,
                        self.step_slots, pdl=pdl)
-                K.gemm(self.V_FP8_DOWN_LOOP, d["down"].map, None, self.map_y8, d["args_down"], s.hidden // 128, 1, pdl=pdl)
+                K.gemm(self.V_FP8_DOWN_LOOP, d["down"].map, None, self.map_y8, d["args_down"], s.hidden // 128,
+                       K.pick_split(s.hidden // 128, 4), pdl=pdl)
         if head:
             K.prep_norm(self.x, self.g_final, R, s.norm_eps, xn=self.xn, pdl=pdl)
             K.gemm(self.V_BF16_STORE, self.map_lm, None, self.map_xn, self.args_head, -(-self.lm_head.shape[0] // 128), pdl=pdl)
