@@ -74,6 +74,8 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = per-GPU-count default)")
     ap.add_argument("--model", default="naive-n0.5")
+    ap.add_argument("--no-pdl", action="store_true", help="diagnostic: plain stream-ordered launches")
+    ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -107,7 +109,7 @@ def main() -> int:
     capacity = a.prompt + total_rounds * 8 + 64
     capacity = -(-capacity // 128) * 128
     t_build = time.perf_counter()
-    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev)
+    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=not a.no_pdl)
     build_s = time.perf_counter() - t_build
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
 
@@ -123,7 +125,7 @@ def main() -> int:
 
     # ------------------------------------------------------------------ device-timed rounds
     t0 = time.perf_counter()
-    eng.open(prompt, max_tokens, sp)
+    eng.open(prompt, max_tokens, sp, use_graphs=not a.no_graph)
     prefill_s = time.perf_counter() - t0
     r = eng.round
     r.launch(a.warmup)
@@ -159,7 +161,7 @@ def main() -> int:
     # the host cancel word (4 bytes) each round.  The rate below is host-clock tokens/s of the decode stream.
     e2e_tokens = a.steps * 3
     t1 = time.perf_counter()
-    eng.open(prompt, e2e_tokens, sp)
+    eng.open(prompt, e2e_tokens, sp, use_graphs=not a.no_graph)
     t2 = time.perf_counter()
     got, rounds = 0, 0
     t_first = None

@@ -69,20 +69,30 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
   const unsigned long long seed = *a.seed;
   const uint32_t ctr = (uint32_t)a.ctrl[8] * 8u + (uint32_t)step;
   unsigned long long best = 0ull;
-  for (int i = 0; i < 4; ++i) {
-    const int t = blockIdx.x * 1024 + i * 256 + threadIdx.x;
+  // 8 lanes cooperate on one token row (rank_dim bf16 = 64 bytes per lane at rank 256), 4 rows per warp
+  // at a time: every 16-byte load of a warp is part of a fully used 128-byte line.
+  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;         // 32 groups per CTA
+  const int per_lane = a.rank_dim / 8;                              // elements per lane
+  for (int i = 0; i < 32; ++i) {
+    const int t = blockIdx.x * 1024 + i * 32 + grp;
+    float acc = 0.f;
     if (t < a.vlocal) {
-      const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)t * a.rank_dim);
-      float acc = 0.f;
-      for (int k = 0; k < a.rank_dim / 8; ++k) {
+      const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)t * a.rank_dim + sub * per_lane);
+      for (int k = 0; k < per_lane / 8; ++k) {
         const uint4 v = wr[k];
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const float* w = w1s + sub * per_lane + k * 8;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = __bfloat1622float2(h[j]);
-          acc += f.x * w1s[k * 8 + 2 * j] + f.y * w1s[k * 8 + 2 * j + 1];
+          acc += f.x * w[2 * j] + f.y * w[2 * j + 1];
         }
       }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (sub == 0 && t < a.vlocal) {
       const float z = a.logits[(size_t)step * a.ld + t] + round_bf16(acc);
       a.zq[(size_t)step * a.ld + t] = z;
       const float u = philox_uniform(seed, 3u, ctr, (uint32_t)(t + a.vbase));
@@ -127,6 +137,6 @@ extern "C" int nrt_markov_args_size() { return (int)sizeof(MarkovArgs); }
 extern "C" int nrt_markov_step(const void* args, int step, void* stream, int pdl) {
   MarkovArgs a;
   memcpy(&a, args, sizeof(a));
-  if (a.rank_dim > 512 || a.rank_dim % 8) return -3;
+  if (a.rank_dim > 512 || a.rank_dim % 64) return -3;
   return launch_pdl(markov_step_kernel, dim3((a.vlocal + 1023) / 1024), dim3(256), 0, S(stream), pdl != 0, a, step);
 }

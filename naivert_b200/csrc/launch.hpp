@@ -6,11 +6,26 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <mutex>
+#include <unordered_set>
+
 namespace nrt {
+
+// Every kernel asks for the same (maximum) shared-memory carve-out: kernels that follow one
+// another with different carve-outs force the SM to drain and reconfigure between them, which
+// defeats the overlap programmatic dependent launch is meant to give.
+inline void prefer_max_shared(const void* kernel) {
+  static std::mutex mu;
+  static std::unordered_set<const void*> done;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.insert(kernel).second)
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
 
 template <typename... KArgs, typename... Args>
 int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
                Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -31,6 +46,7 @@ int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cud
 template <typename... KArgs, typename... Args>
 int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t stream,
                    bool pdl, Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

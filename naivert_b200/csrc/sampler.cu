@@ -194,17 +194,24 @@ __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a
     const unsigned int prefix = a.st->prefix[d];
     const unsigned int* e = a.e + (size_t)d * a.vlocal;
     const int t0 = blockIdx.x * kTile;
+    // Nearly all codes of a pass fall into one bin (tiny probabilities): keep a run-length
+    // accumulator per thread and touch shared memory only when the bin changes.
+    unsigned int cur = 0xFFFFFFFFu;
+    unsigned long long run = 0ull;
     for (int i = threadIdx.x; i < kTile; i += kThreads) {
       const int t = t0 + i;
       const unsigned int v = t < a.vlocal ? e[t] : 0u;
-      const bool in = (v & mask) == prefix && v != 0u;
-      // most codes share a bin (tiny probabilities): lanes with equal bins combine before the atomic
-      const unsigned int bin = in ? ((v >> shift) & 255u) : 0xFFFFFFFFu;
-      const unsigned int peers = __match_any_sync(0xffffffffu, bin);
-      unsigned long long sum = 0ull;
-      for (unsigned int m = peers; m; m &= m - 1) sum += __shfl_sync(peers, v, __ffs(m) - 1);
-      if (in && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&sh[bin], sum);
+      if ((v & mask) == prefix && v != 0u) {
+        const unsigned int bin = (v >> shift) & 255u;
+        if (bin != cur) {
+          if (run) atomicAdd(&sh[cur], run);
+          cur = bin;
+          run = 0ull;
+        }
+        run += v;
+      }
     }
+    if (run) atomicAdd(&sh[cur], run);
     __syncthreads();
     for (int i = threadIdx.x; i < 256; i += kThreads)
       if (sh[i]) atomicAdd(&a.st->hist[d * 256 + i], sh[i]);

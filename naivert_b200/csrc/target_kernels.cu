@@ -206,7 +206,8 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
 
   // q heads and k heads: [optional head RMS norm] -> bf16 -> RoPE on adjacent pairs -> bf16
   const int qk_heads = a.heads + a.kv_heads;
-  for (int h = warp; h < qk_heads; h += 8) {
+  const int part = blockIdx.y, parts = gridDim.y;          // heads are spread over grid.y CTAs per row
+  for (int h = part * 8 + warp; h < qk_heads; h += 8 * parts) {
     const bool is_q = h < a.heads;
     const float* hs = is_q ? src + a.col_q + h * a.head_dim : src + a.col_k + (h - a.heads) * a.head_dim;
     __nv_bfloat16* dst = is_q ? a.q_out + ((size_t)r * a.heads + h) * a.head_dim
@@ -230,13 +231,14 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
     }
   }
   // v heads
-  for (int i = threadIdx.x; i < a.kv_heads * a.v_dim; i += 256)
-    a.v_cache[slot * a.kv_heads * a.v_dim + i] = __float2bfloat16_rn(src[a.col_v + i] * a.value_scale);
+  if (part == parts - 1)
+    for (int i = threadIdx.x; i < a.kv_heads * a.v_dim; i += 256)
+      a.v_cache[slot * a.kv_heads * a.v_dim + i] = __float2bfloat16_rn(src[a.col_v + i] * a.value_scale);
 
   if (a.idx_heads == 0) return;
   const float2* it = a.idx_rope_tab + (size_t)r * (a.idx_rope / 2);
   // indexer queries: bf16 -> RoPE -> bf16 -> e4m3 with a per-(row, head) scale folded into the head weight
-  for (int h = warp; h < a.idx_heads; h += 8) {
+  for (int h = part * 8 + warp; h < a.idx_heads; h += 8 * parts) {
     const float* hs = src + a.col_iq + h * a.idx_dim;
     float v[8];                                   // idx_dim <= 256: 4 pairs per lane
     float am = 0.f;
@@ -265,7 +267,7 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
     if (lane == 0) a.ihw[r * a.idx_heads + h] = src[a.col_iw + h] * a.idx_weight_scale * s;
   }
   // indexer key: LayerNorm (fp32) -> bf16 -> RoPE -> bf16 -> e4m3 with a per-row scale amax/448
-  {
+  if (part == 0) {
     const int d = threadIdx.x;
     const float kv = d < a.idx_dim ? src[a.col_ik + d] : 0.f;
     const float mean = block_sum<256>(kv, red) / (float)a.idx_dim;
@@ -310,11 +312,24 @@ struct AttnArgs {
 };
 
 // One CTA (128 threads) per (head, row); keys are processed in chunks of 128 with an online softmax.
+// Each chunk's K and V rows are staged in shared memory with one wave of independent 16-byte
+// loads (a single L2 round trip), then scored warp-per-key and accumulated thread-per-channel.
+constexpr int kAttnChunk = 128;
+constexpr int kAttnKPad = 8;       // bf16 elements of row padding (keeps 16-byte alignment, breaks bank aliasing)
+
+__device__ __forceinline__ const __nv_bfloat16* attn_key_ptr(const AttnArgs& a, int id, int g, bool value) {
+  const int dim = value ? a.v_dim : a.head_dim;
+  if (id < 0) return (value ? a.v_blk : a.k_blk) + ((size_t)(-id - 1) * a.kv_heads + g) * dim;
+  const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
+  return (value ? a.v_cache : a.k_cache) + (slot * a.kv_heads + g) * dim;
+}
+
 __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
+  extern __shared__ uint4 attn_smem[];
   __shared__ float qs[256];
-  __shared__ float sc[128];
+  __shared__ float sc[kAttnChunk];
   __shared__ float red[4];
-  __shared__ int kid[128];
+  __shared__ int kid[kAttnChunk];
   griddep_launch();
   griddep_wait();
   const int h = blockIdx.x, r = blockIdx.y;
@@ -323,9 +338,12 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
   const int g = h / (a.heads / a.kv_heads);
   const int p0 = *a.pos0;
   const int pos = p0 + r;
+  const int kvec = a.head_dim / 8, vvec = a.v_dim / 8;            // uint4 per row
+  const int kstride = (a.head_dim + kAttnKPad) / 8;                // uint4 per padded K row
+  uint4* ks = attn_smem;
+  uint4* vs = attn_smem + kAttnChunk * kstride;
   for (int d = tid; d < a.head_dim; d += 128)
     qs[d] = __bfloat162float(a.q[((size_t)r * a.heads + h) * a.head_dim + d]);
-  __syncthreads();
 
   int lo = 0, count = 0, ctx = 0;
   bool use_sel = false;
@@ -334,27 +352,30 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
   else { lo = max(0, p0 - a.window); ctx = p0 - lo; count = ctx + a.rows; }
 
   float m_run = -FLT_MAX, l_run = 0.f, acc = 0.f;      // acc: output channel tid (v_dim <= 128)
-  for (int c0 = 0; c0 < count; c0 += 128) {
-    const int n = min(128, count - c0);
-    // key ids of this chunk (negative = block row -(id+1) in mode 2)
+  for (int c0 = 0; c0 < count; c0 += kAttnChunk) {
+    const int n = min(kAttnChunk, count - c0);
+    __syncthreads();                                   // previous chunk fully consumed
     if (tid < n) {
       const int j = c0 + tid;
-      int id;
+      int id;                                          // negative = block row -(id+1) in mode 2
       if (a.mode == 1) id = use_sel ? a.sel[r * a.top_k + j] : j;
       else if (a.mode == 2) id = j < ctx ? lo + j : -(j - ctx) - 1;
       else id = lo + j;
       kid[tid] = id;
     }
     __syncthreads();
+    for (int i = tid; i < n * kvec; i += 128) {
+      const int t = i / kvec, c = i - t * kvec;
+      ks[t * kstride + c] = reinterpret_cast<const uint4*>(attn_key_ptr(a, kid[t], g, false))[c];
+    }
+    for (int i = tid; i < n * vvec; i += 128) {
+      const int t = i / vvec, c = i - t * vvec;
+      vs[t * vvec + c] = reinterpret_cast<const uint4*>(attn_key_ptr(a, kid[t], g, true))[c];
+    }
+    __syncthreads();
     // scores: each warp takes keys warp, warp+4, ...; lanes split the head dimension
     for (int t = warp; t < n; t += 4) {
-      const int id = kid[t];
-      const __nv_bfloat16* kp;
-      if (id < 0) kp = a.k_blk + ((size_t)(-id - 1) * a.kv_heads + g) * a.head_dim;
-      else {
-        const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
-        kp = a.k_cache + (slot * a.kv_heads + g) * a.head_dim;
-      }
+      const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(ks + t * kstride);
       float s = 0.f;
       for (int d = lane * 2; d < a.head_dim; d += 64) {
         const float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kp + d));
@@ -370,24 +391,16 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
     const float e = tid < n ? __expf(v - m_new) : 0.f;
     __syncthreads();
     sc[tid] = e;
-    const float cs = block_sum<128>(e, red);      // contains a __syncthreads after sc[] is written
+    const float cs = block_sum<128>(e, red);           // contains a __syncthreads after sc[] is written
     const float corr = __expf(m_run - m_new);
     l_run = l_run * corr + cs;
     acc *= corr;
     if (tid < a.v_dim) {
-      for (int t = 0; t < n; ++t) {
-        const int id = kid[t];
-        const __nv_bfloat16* vp;
-        if (id < 0) vp = a.v_blk + ((size_t)(-id - 1) * a.kv_heads + g) * a.v_dim;
-        else {
-          const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
-          vp = a.v_cache + (slot * a.kv_heads + g) * a.v_dim;
-        }
-        acc += sc[t] * __bfloat162float(vp[tid]);
-      }
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(vs) + tid;
+#pragma unroll 8
+      for (int t = 0; t < n; ++t) acc += sc[t] * __bfloat162float(vp[t * a.v_dim]);
     }
     m_run = m_new;
-    __syncthreads();
   }
   if (a.sink) {                                   // extra softmax column that carries no value
     const float sv = __bfloat162float(a.sink[h]);
@@ -728,13 +741,22 @@ extern "C" int nrt_attn_post_args_size() { return (int)sizeof(AttnPostArgs); }
 extern "C" int nrt_attn_post(const void* args, void* stream, int pdl) {
   AttnPostArgs a;
   memcpy(&a, args, sizeof(a));
-  return launch_pdl(attn_post_kernel, dim3(a.rows), dim3(256), 0, S(stream), pdl != 0, a);
+  const int heads = a.heads + a.kv_heads;
+  const int parts = heads > 32 ? 8 : (heads > 8 ? 2 : 1);
+  return launch_pdl(attn_post_kernel, dim3(a.rows, parts), dim3(256), 0, S(stream), pdl != 0, a);
 }
 extern "C" int nrt_attn_args_size() { return (int)sizeof(AttnArgs); }
 extern "C" int nrt_attn_rows(const void* args, void* stream, int pdl) {
   AttnArgs a;
   memcpy(&a, args, sizeof(a));
-  return launch_pdl(attn_rows_kernel, dim3(a.heads, a.rows), dim3(128), 0, S(stream), pdl != 0, a);
+  const size_t smem = (size_t)kAttnChunk * ((a.head_dim + kAttnKPad) + a.v_dim) * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+    configured = true;
+  }
+  if (a.head_dim % 8 || a.v_dim % 8 || a.head_dim > 256 || a.v_dim > 128 || smem > 128 * 1024) return -3;
+  return launch_pdl(attn_rows_kernel, dim3(a.heads, a.rows), dim3(128), smem, S(stream), pdl != 0, a);
 }
 extern "C" int nrt_index_args_size() { return (int)sizeof(IndexArgs); }
 extern "C" int nrt_index_logits_simple(const void* args, int blocks, void* stream, int pdl) {
