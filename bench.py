@@ -74,6 +74,8 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = per-GPU-count default)")
     ap.add_argument("--model", default="naive-n0.5")
+    ap.add_argument("--shape-tp", type=int, default=0,
+                    help="diagnostic: run ONE rank's share of a tp-way model on one GPU without peers (not a result)")
     ap.add_argument("--no-pdl", action="store_true", help="diagnostic: plain stream-ordered launches")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
     a = ap.parse_args()
@@ -102,14 +104,14 @@ def main() -> int:
         group = dist.group.WORLD
 
     spec = resolve_model(a.model)
-    layers = a.layers or LAYERS_FOR_GPUS.get(world, spec.layer_count)
+    layers = a.layers or LAYERS_FOR_GPUS.get(a.shape_tp or world, spec.layer_count)
     if layers < spec.layer_count:
         spec = spec.with_layers(layers)
     total_rounds = a.steps + a.warmup
     capacity = a.prompt + total_rounds * 8 + 64
     capacity = -(-capacity // 128) * 128
     t_build = time.perf_counter()
-    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=not a.no_pdl)
+    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=not a.no_pdl, shape_tp=a.shape_tp)
     build_s = time.perf_counter() - t_build
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
 
@@ -197,6 +199,7 @@ def main() -> int:
                                 "decode_s": round(t3 - t2, 4), "tokens": got, "rounds": rounds}},
             "gpu_launches": int(r.kernels_per_round * a.steps),
             "kernels_per_round": int(r.kernels_per_round),
+            "diagnostic_shape_tp": a.shape_tp or None,
             "build_s": round(build_s, 2), "prefill_s": round(prefill_s, 3),
             "kv_bytes_per_gpu": eng.kv_bytes(),
         }

@@ -52,7 +52,7 @@ struct MarkovArgs {
   XchgArgs x;
 };
 
-// grid = ceil(vlocal / 1024) CTAs of 256 threads, 4 tokens per thread.
+// grid = ceil(vlocal / 128) CTAs of 256 threads; 8 lanes per token row, 4 rounds of 32 rows.
 __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, int step) {
   __shared__ float w1s[512];
   __shared__ unsigned long long sbest;
@@ -73,8 +73,8 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
   // at a time: every 16-byte load of a warp is part of a fully used 128-byte line.
   const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;         // 32 groups per CTA
   const int per_lane = a.rank_dim / 8;                              // elements per lane
-  for (int i = 0; i < 32; ++i) {
-    const int t = blockIdx.x * 1024 + i * 32 + grp;
+  for (int i = 0; i < 4; ++i) {
+    const int t = blockIdx.x * 128 + i * 32 + grp;
     float acc = 0.f;
     if (t < a.vlocal) {
       const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)t * a.rank_dim + sub * per_lane);
@@ -138,5 +138,5 @@ extern "C" int nrt_markov_step(const void* args, int step, void* stream, int pdl
   MarkovArgs a;
   memcpy(&a, args, sizeof(a));
   if (a.rank_dim > 512 || a.rank_dim % 64) return -3;
-  return launch_pdl(markov_step_kernel, dim3((a.vlocal + 1023) / 1024), dim3(256), 0, S(stream), pdl != 0, a, step);
+  return launch_pdl(markov_step_kernel, dim3((a.vlocal + 127) / 128), dim3(256), 0, S(stream), pdl != 0, a, step);
 }

@@ -151,8 +151,23 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
 
-  // Everything below reads data produced by earlier kernels of the stream.
+  // Dependent kernels may start their own preamble now.  Weights never depend on earlier
+  // kernels, so (ungrouped) the producer streams the first weight tiles *before* waiting for
+  // the upstream grid; token tiles, scales, residuals and expert lists are read after the wait.
   griddep_launch();
+  // stages whose weight tile is issued before the wait
+  const int early = GROUP == kGroupNone ? min(kb_count, Cfg::kStages) : 0;
+  if (GROUP == kGroupNone) {
+    if (warp == 0 && elect_one()) {
+      for (int u = 0; u < early; ++u) {
+        uint8_t* sa = smem + u * Cfg::kStageBytes;
+        mbar_expect_tx(&tail->full[u], Cfg::kStageBytes);
+        const int kx = (kb_first + u) * kElemsPerStage;
+        tma_load_3d(sa, &tmA0, &tail->full[u], kx, n0, p.a_group);
+        if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[u], kx, n0, p.a_group);
+      }
+    }
+  }
   griddep_wait();
 
   int n_groups = 1, g_first = 0, g_step = 1;
@@ -179,10 +194,12 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         const int slot = g_first + g * g_step;
         const int z = GROUP == kGroupNone ? p.a_group : p.active_ids[slot];
         uint8_t* sa = smem + st * Cfg::kStageBytes;
-        mbar_expect_tx(&tail->full[st], Cfg::kStageBytes);
         const int kx = (kb_first + kb) * kElemsPerStage;
-        tma_load_3d(sa, &tmA0, &tail->full[st], kx, n0, z);
-        if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
+        if (u >= early) {
+          mbar_expect_tx(&tail->full[st], Cfg::kStageBytes);
+          tma_load_3d(sa, &tmA0, &tail->full[st], kx, n0, z);
+          if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
+        }
         const int brow = (GROUP == kGroupLoop) ? slot * kTok : 0;
         tma_load_2d(sa + (DUAL ? 2 : 1) * kATileBytes, &tmB, &tail->full[st], kx, brow);
       }
@@ -246,6 +263,12 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         const float* ws1 = DUAL ? p.w_scale1 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first : nullptr;
         for (int kb = 0; kb < kb_count; ++kb, ++u) {
           const int buf = u % Cfg::kAccBufs;
+          // scales are fetched before the wait so their latency hides behind the MMA of this block
+          float sc[kTok];
+#pragma unroll
+          for (int r = 0; r < kTok; ++r) sc[r] = __ldg(as + r * kb_total + kb);
+          const float w0 = __ldg(ws0 + kb);
+          const float w1 = DUAL ? __ldg(ws1 + kb) : 0.f;
           if (!mbar_wait(&tail->acc_full[buf], (u / Cfg::kAccBufs) & 1, p.status, kSiteAccFull | buf)) { ok = false; break; }
           tc_fence_after();
           float v0[kTok], v1[kTok];
@@ -253,13 +276,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           if (DUAL) tmem_ld16(lane_addr + buf * Cfg::kAccCols + kTok, v1);
           tc_fence_before();
           mbar_arrive(&tail->acc_empty[buf]);
-          const float w0 = ws0[kb];
-          const float w1 = DUAL ? ws1[kb] : 0.f;
 #pragma unroll
           for (int r = 0; r < kTok; ++r) {
-            const float a = as[r * kb_total + kb];
-            acc0[r] += v0[r] * (a * w0);
-            if (DUAL) acc1[r] += v1[r] * (a * w1);
+            acc0[r] += v0[r] * (sc[r] * w0);
+            if (DUAL) acc1[r] += v1[r] * (sc[r] * w1);
           }
         }
       } else {

@@ -309,6 +309,10 @@ struct AttnArgs {
   __nv_bfloat16* o_bf16;
   uint8_t* o8;
   float* o_scale;                // [16][heads*v_dim/128]
+  // key-split: grid.z CTAs share one (head, row); partial (max, sum, acc) go through `part`
+  // and the last CTA to arrive merges them in split order.
+  float* part;                   // [16][heads][splits][v_dim + 2]
+  unsigned int* tickets;         // [16][heads], zero between launches
 };
 
 // One CTA (128 threads) per (head, row); keys are processed in chunks of 128 with an online softmax.
@@ -352,8 +356,12 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
   else { lo = max(0, p0 - a.window); ctx = p0 - lo; count = ctx + a.rows; }
 
   float m_run = -FLT_MAX, l_run = 0.f, acc = 0.f;      // acc: output channel tid (v_dim <= 128)
-  for (int c0 = 0; c0 < count; c0 += kAttnChunk) {
-    const int n = min(kAttnChunk, count - c0);
+  const int splits = gridDim.z, sp = blockIdx.z;
+  const int chunks = (count + kAttnChunk - 1) / kAttnChunk;
+  const int per = (chunks + splits - 1) / splits;
+  const int c_begin = sp * per * kAttnChunk, c_end = min(count, (sp + 1) * per * kAttnChunk);
+  for (int c0 = c_begin; c0 < c_end; c0 += kAttnChunk) {
+    const int n = min(kAttnChunk, c_end - c0);
     __syncthreads();                                   // previous chunk fully consumed
     if (tid < n) {
       const int j = c0 + tid;
@@ -401,6 +409,33 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
       for (int t = 0; t < n; ++t) acc += sc[t] * __bfloat162float(vp[t * a.v_dim]);
     }
     m_run = m_new;
+  }
+  if (splits > 1) {
+    __shared__ bool s_last;
+    float* mine = a.part + (((size_t)r * a.heads + h) * splits + sp) * (a.v_dim + 2);
+    if (tid < a.v_dim) mine[2 + tid] = acc;
+    if (tid == 0) { mine[0] = m_run; mine[1] = l_run; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned int t = atomicAdd(&a.tickets[r * a.heads + h], 1u);
+      s_last = t == (unsigned)splits - 1;
+      if (s_last) a.tickets[r * a.heads + h] = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    m_run = -FLT_MAX; l_run = 0.f; acc = 0.f;
+    for (int q = 0; q < splits; ++q) {                   // fixed merge order: deterministic
+      const float* o = a.part + (((size_t)r * a.heads + h) * splits + q) * (a.v_dim + 2);
+      const float mq = __ldcg(o), lq = __ldcg(o + 1);
+      const float aq = tid < a.v_dim ? __ldcg(o + 2 + tid) : 0.f;
+      const float m_new = fmaxf(m_run, mq);
+      const float c_old = __expf(m_run - m_new), c_new = __expf(mq - m_new);
+      l_run = l_run * c_old + lq * c_new;
+      acc = acc * c_old + aq * c_new;
+      m_run = m_new;
+    }
   }
   if (a.sink) {                                   // extra softmax column that carries no value
     const float sv = __bfloat162float(a.sink[h]);
@@ -746,7 +781,7 @@ extern "C" int nrt_attn_post(const void* args, void* stream, int pdl) {
   return launch_pdl(attn_post_kernel, dim3(a.rows, parts), dim3(256), 0, S(stream), pdl != 0, a);
 }
 extern "C" int nrt_attn_args_size() { return (int)sizeof(AttnArgs); }
-extern "C" int nrt_attn_rows(const void* args, void* stream, int pdl) {
+extern "C" int nrt_attn_rows(const void* args, int splits, void* stream, int pdl) {
   AttnArgs a;
   memcpy(&a, args, sizeof(a));
   const size_t smem = (size_t)kAttnChunk * ((a.head_dim + kAttnKPad) + a.v_dim) * 2;
@@ -756,7 +791,8 @@ extern "C" int nrt_attn_rows(const void* args, void* stream, int pdl) {
     configured = true;
   }
   if (a.head_dim % 8 || a.v_dim % 8 || a.head_dim > 256 || a.v_dim > 128 || smem > 128 * 1024) return -3;
-  return launch_pdl(attn_rows_kernel, dim3(a.heads, a.rows), dim3(128), smem, S(stream), pdl != 0, a);
+  if (splits > 1 && (!a.part || !a.tickets)) return -3;
+  return launch_pdl(attn_rows_kernel, dim3(a.heads, a.rows, splits < 1 ? 1 : splits), dim3(128), smem, S(stream), pdl != 0, a);
 }
 extern "C" int nrt_index_args_size() { return (int)sizeof(IndexArgs); }
 extern "C" int nrt_index_logits_simple(const void* args, int blocks, void* stream, int pdl) {

@@ -59,7 +59,8 @@ class AttnArgs(C.Structure):
     _fields_ = [("q", VP), ("k_cache", VP), ("v_cache", VP), ("pos0", VP),
                 ("rows", I32), ("heads", I32), ("kv_heads", I32), ("head_dim", I32), ("v_dim", I32),
                 ("scale", F32), ("mode", I32), ("window", I32), ("ring", I32), ("sink", VP), ("sel", VP),
-                ("top_k", I32), ("k_blk", VP), ("v_blk", VP), ("o_bf16", VP), ("o8", VP), ("o_scale", VP)]
+                ("top_k", I32), ("k_blk", VP), ("v_blk", VP), ("o_bf16", VP), ("o8", VP), ("o_scale", VP),
+                ("part", VP), ("tickets", VP)]
 
 
 class IndexArgs(C.Structure):
@@ -178,8 +179,28 @@ def attn_post(args: AttnPostArgs, pdl=True):
     check(lib().nrt_attn_post(C.byref(args), VP(_stream()), int(pdl)), "attn_post")
 
 
-def attn_rows(args: AttnArgs, pdl=True):
-    check(lib().nrt_attn_rows(C.byref(args), VP(_stream()), int(pdl)), "attn_rows")
+def attn_rows(args: AttnArgs, splits: int = 1, pdl=True):
+    check(lib().nrt_attn_rows(C.byref(args), splits, VP(_stream()), int(pdl)), "attn_rows")
+
+
+class SweepArgs(C.Structure):
+    _fields_ = [("ihw", VP), ("iks", VP), ("pos0", VP), ("rows", I32), ("heads", I32), ("top_k", I32),
+                ("logits", VP), ("ld", I32), ("status", VP)]
+
+
+def sweep_maps(ik_cache: torch.Tensor, iq8: torch.Tensor):
+    """Tensor maps of the tcgen05 indexer sweep: key cache [cap, 128] e4m3 bytes, queries [256, 128]."""
+    assert ik_cache.shape[1] == 128 and iq8.shape == (256, 128)
+    km = TensorMap(ik_cache, (128, ik_cache.shape[0]), (128,), (128, 128), 0)
+    qm = TensorMap(iq8, (128, 256), (128,), (128, 256), 0)
+    return km, qm
+
+
+def index_sweep(km: TensorMap, qm: TensorMap, args: SweepArgs, blocks: int, pdl=True):
+    L = lib()
+    if L.nrt_sweep_args_size() != C.sizeof(SweepArgs):
+        raise RuntimeError("SweepArgs layout drift")
+    check(L.nrt_index_sweep(C.byref(km.buf), C.byref(qm.buf), C.byref(args), blocks, VP(_stream()), int(pdl)), "index_sweep")
 
 
 def index_logits_simple(args: IndexArgs, blocks: int, pdl=True):

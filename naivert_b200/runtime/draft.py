@@ -79,6 +79,9 @@ class DraftRuntime:
         self.map_o = K.act_tmap(self.o)
         self.y = torch.zeros(PAD_ROWS, self.I, dtype=bf, device=dev)
         self.map_y = K.act_tmap(self.y)
+        self.attn_splits = 3
+        self.attn_part = torch.zeros(PAD_ROWS * self.nh * self.attn_splits * (hd + 2), dtype=f32, device=dev)
+        self.attn_tickets = torch.zeros(PAD_ROWS * self.nh, dtype=i32, device=dev)
         self.rope_blk = torch.zeros(PAD_ROWS, hd // 2, 2, dtype=f32, device=dev)
         self.rope_ing = torch.zeros(PAD_ROWS, hd // 2, 2, dtype=f32, device=dev)
         feats = target.feats[:, self.rank * self.kf:(self.rank + 1) * self.kf]
@@ -135,6 +138,7 @@ class DraftRuntime:
             t.rows, t.heads, t.kv_heads, t.head_dim, t.v_dim = R, self.nh, self.nkv, hd, hd
             t.scale, t.mode, t.window, t.ring = hd ** -0.5, 2, d.window, 0
             t.k_blk, t.v_blk, t.o_bf16 = self.k_blk.data_ptr(), self.v_blk.data_ptr(), self.o.data_ptr()
+            t.part, t.tickets = self.attn_part.data_ptr(), self.attn_tickets.data_ptr()
             L["args_attn"] = t
             g = self._g(Hd, self.nh * hd, R)
             g.out_bf16, g.ld_out, g.resid = self.xd.data_ptr(), Hd, self.xd.data_ptr()
@@ -187,7 +191,7 @@ class DraftRuntime:
             K.gemm(self.V_STORE, L["map_qkv"], None, self.map_xn, L["args_qkv"], L["wqkv"].shape[0] // 128,
                    K.pick_split(L["wqkv"].shape[0] // 128, d.hidden // 64), pdl=pdl)
             K.attn_post(L["args_post"], pdl=pdl)
-            K.attn_rows(L["args_attn"], pdl=pdl)
+            K.attn_rows(L["args_attn"], self.attn_splits, pdl=pdl)
             K.gemm(self.V_AR, L["map_wo"], None, self.map_o, L["args_o"], d.hidden // 128,
                    K.pick_split(d.hidden // 128, self.nh * d.head_dim // 64), pdl=pdl)
             K.prep_norm(self.xd, L["g_post"], R, d.norm_eps, xn=self.xn, pdl=pdl)

@@ -53,11 +53,16 @@ class Engine:
     @classmethod
     def build(cls, spec: ModelSpec, rank: int = 0, tp: int = 1, group=None, capacity: int = 16384, seed: int = 0,
               target_ckpt: Optional[str] = None, draft_ckpt: Optional[str] = None, device=None,
-              weights: Optional[dict] = None, draft_weights: Optional[dict] = None, pdl: bool = True) -> "Engine":
+              weights: Optional[dict] = None, draft_weights: Optional[dict] = None, pdl: bool = True,
+              shape_tp: int = 0) -> "Engine":
         device = device or torch.device("cuda", torch.cuda.current_device())
         if spec.draft is None:
             raise RuntimeContractError("the engine needs a model with a draft specification")
         fabric = Fabric(rank, tp, max(spec.hidden, spec.draft.hidden), group=group, device=device)
+        if shape_tp:
+            if tp != 1:
+                raise RuntimeContractError("shape_tp emulation needs a single-rank fabric")
+            rank, tp = 0, shape_tp
         if weights is None:
             if target_ckpt is not None:
                 from ..models.checkpoint import load_rank_weights
@@ -72,7 +77,8 @@ class Engine:
             else:
                 from ..models.device_init import init_draft_rank_weights_device
                 draft_weights = init_draft_rank_weights_device(spec, rank, tp, seed=seed + 1, device=device)
-        target = TargetRuntime(spec, weights, fabric, rows=spec.draft.rows, capacity=capacity, device=device, pdl=pdl)
+        target = TargetRuntime(spec, weights, fabric, rows=spec.draft.rows, capacity=capacity, device=device, pdl=pdl,
+                               shape_tp=shape_tp)
         del weights
         rnd = SpeculativeRound(spec, target, draft_weights, capacity, pdl=pdl)
         return cls(spec, fabric, target, rnd)

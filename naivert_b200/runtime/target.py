@@ -49,13 +49,15 @@ class _Linear8:
 
 class TargetRuntime:
     def __init__(self, spec: ModelSpec, rank_weights: dict, fabric, rows: int = 8, capacity: int = 16384,
-                 device="cuda", pdl: bool = True):
+                 device="cuda", pdl: bool = True, shape_tp: int = 0):
         if spec.weight_dtype != "fp8":
             raise ValueError("the CUDA runtime implements the W8A8 recipe only")
         if spec.routing.shared_expert_count:
             raise ValueError("shared experts are only supported by the torch oracle")
         self.spec, self.fab, self.rows, self.capacity, self.dev, self.pdl = spec, fabric, rows, capacity, device, pdl
-        self.tp, self.rank = fabric.tp, fabric.rank
+        # shape_tp > 1 with a single-rank fabric runs one rank's share of a tp-way model without peers
+        # (kernel profiling of the per-rank shapes; the results are not a model output)
+        self.tp, self.rank = (shape_tp, 0) if shape_tp else (fabric.tp, fabric.rank)
         s = spec
         H = s.hidden
         dev = device
@@ -160,6 +162,10 @@ class TargetRuntime:
             self.ihw = torch.zeros(PAD_ROWS, ix.head_count, dtype=f32, device=dev)
             self.idx_logits = torch.zeros(PAD_ROWS, capacity, dtype=f32, device=dev)
             self.sel = torch.zeros(PAD_ROWS, ix.top_k, dtype=i32, device=dev)
+            self.use_sweep = ix.head_dim == 128 and ix.head_count % 16 == 0 and PAD_ROWS * ix.head_count == 256
+        self.attn_splits = 4
+        self.attn_part = torch.zeros(PAD_ROWS * nh_max * self.attn_splits * (a0.v_head_dim + 2), dtype=f32, device=dev)
+        self.attn_tickets = torch.zeros(PAD_ROWS * nh_max, dtype=i32, device=dev)
         self._build_args()
 
     # ------------------------------------------------------------------ argument blocks (built once)
@@ -202,6 +208,13 @@ class TargetRuntime:
                 ia.rows, ia.heads, ia.dim, ia.top_k = R, ix.head_count, ix.head_dim, ix.top_k
                 ia.logits, ia.ld = self.idx_logits.data_ptr(), self.idx_logits.shape[1]
                 d["args_index"] = ia
+                if self.use_sweep:
+                    d["sweep_maps"] = K.sweep_maps(d["ik"], self.iq8)
+                    sw = K.SweepArgs()
+                    sw.ihw, sw.iks, sw.pos0 = self.ihw.data_ptr(), d["iks"].data_ptr(), pos0
+                    sw.rows, sw.heads, sw.top_k = R, ix.head_count, ix.top_k
+                    sw.logits, sw.ld, sw.status = self.idx_logits.data_ptr(), self.idx_logits.shape[1], self.fab.status.data_ptr()
+                    d["args_sweep"] = sw
             d["args_post"] = p
             t = K.AttnArgs()
             t.q, t.k_cache, t.v_cache, t.pos0 = self.q.data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), pos0
@@ -213,6 +226,7 @@ class TargetRuntime:
                 t.mode, t.top_k, t.sel = 1, ix.top_k, self.sel.data_ptr()
             t.sink = None if d["sink"] is None else d["sink"].data_ptr()
             t.o8, t.o_scale = self.o8.data_ptr(), self.os.data_ptr()
+            t.part, t.tickets = self.attn_part.data_ptr(), self.attn_tickets.data_ptr()
             d["args_attn"] = t
             # o_proj + all-reduce + residual
             g = self._gemm_args(H, d["wo"].k, R)
@@ -283,9 +297,12 @@ class TargetRuntime:
             K.gemm(self.V_BF16_STORE, d["map_qkv"], None, self.map_xn, d["args_qkv"], nt, K.pick_split(nt, s.hidden // 64), pdl=pdl)
             K.attn_post(d["args_post"], pdl=pdl)
             if d["kind"] == FULL_DSA:
-                K.index_logits_simple(d["args_index"], 148, pdl=pdl)
+                if self.use_sweep:
+                    K.index_sweep(*d["sweep_maps"], d["args_sweep"], min(148, -(-self.capacity // 128)), pdl=pdl)
+                else:
+                    K.index_logits_simple(d["args_index"], 148, pdl=pdl)
                 K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
-            K.attn_rows(d["args_attn"], pdl=pdl)
+            K.attn_rows(d["args_attn"], self.attn_splits if d["kind"] == FULL_DSA else 1, pdl=pdl)
             K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128,
                    K.pick_split(s.hidden // 128, d["wo"].k // 128), pdl=pdl)
             if stop_after == (L, "attn"):

@@ -106,6 +106,57 @@ def test_attention_rows_match_torch():
                 assert (got - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3, (mode, r, h)
 
 
+def test_tcgen05_index_sweep_matches_cuda_core_form():
+    from naivert_b200.ops import kernels as K
+    spec, rt, _ = _build(layers=1, capacity=2048)
+    assert rt.use_sweep
+    g = torch.Generator(device="cuda").manual_seed(7)
+    d = rt.layers[0]
+    n = 1500
+    d["ik"][:n] = (torch.randn(n, 128, device="cuda", generator=g) * 60).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    d["iks"][:n] = torch.rand(n, device="cuda", generator=g) + 0.5
+    rt.iq8.copy_((torch.randn(256, 128, device="cuda", generator=g) * 60).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8))
+    rt.ihw.copy_(torch.randn(16, 16, device="cuda", generator=g))
+    rt.ctrl[0] = n - 8
+    rt.idx_logits.zero_()
+    K.index_logits_simple(d["args_index"], 148, pdl=False)
+    torch.cuda.synchronize()
+    want = rt.idx_logits[:8, :n].clone()
+    rt.idx_logits.zero_()
+    K.index_sweep(*d["sweep_maps"], d["args_sweep"], 148, pdl=False)
+    torch.cuda.synchronize()
+    rt.fab.check()
+    got = rt.idx_logits[:8, :n]
+    assert want.abs().max() > 0
+    assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item()
+
+
+def test_split_attention_matches_single():
+    from naivert_b200.ops import kernels as K
+    K.lib()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    heads, kvh, hd, vd, rows, pos0, cap = 4, 1, 192, 128, 8, 900, 1024
+    q = torch.randn(16, heads, hd, device="cuda", generator=g).bfloat16()
+    kc = torch.randn(cap, kvh, hd, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(cap, kvh, vd, device="cuda", generator=g).bfloat16()
+    p = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    outs = []
+    for splits in (1, 4):
+        o = torch.zeros(16, heads * vd, device="cuda", dtype=torch.bfloat16)
+        part = torch.zeros(16 * heads * 4 * (vd + 2), device="cuda")
+        tick = torch.zeros(16 * heads, dtype=torch.int32, device="cuda")
+        a = K.AttnArgs()
+        a.q, a.k_cache, a.v_cache, a.pos0 = q.data_ptr(), kc.data_ptr(), vc.data_ptr(), p.data_ptr()
+        a.rows, a.heads, a.kv_heads, a.head_dim, a.v_dim = rows, heads, kvh, hd, vd
+        a.scale, a.mode, a.top_k, a.o_bf16 = hd ** -0.5, 1, 4096, o.data_ptr()
+        a.part, a.tickets = part.data_ptr(), tick.data_ptr()
+        K.attn_rows(a, splits, pdl=False)
+        torch.cuda.synchronize()
+        assert int(tick.sum()) == 0
+        outs.append(o[:rows].float())
+    assert (outs[0] - outs[1]).abs().max().item() <= 0.02 * outs[0].abs().max().item()
+
+
 def test_step_is_bitwise_repeatable():
     spec, rt, _ = _build(layers=2, capacity=128)
     toks = torch.arange(8) * 37 % spec.vocab
