@@ -374,10 +374,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
         for (int d = 1; d < f.tp; ++d) {
           const int peer = (f.rank + d) % f.tp;
-          uint64_t* dst = f.mailbox[peer] + ((slab + f.rank) * f.features + n) * kRowPairs;
+          // layout [slab][source][row pair][feature]: a warp's 32 stores of one pair are contiguous
+          uint64_t* dst = f.mailbox[peer] + (slab + f.rank) * kRowPairs * f.features + n;
 #pragma unroll
           for (int j = 0; j < kRowPairs; ++j)
-            if (j < pairs) st_tagged(dst + j, tag, own[j]);
+            if (j < pairs) st_tagged(dst + (size_t)j * f.features, tag, own[j]);
         }
         // Batched poll: every missing word of every source is re-read per sweep, so the
         // loads of one sweep overlap instead of paying one fabric round trip each.
@@ -391,7 +392,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
             else w[s][j] = 0u;
           }
         const uint64_t deadline = globaltimer() + f.timeout_ns;
-        const uint64_t* base = f.mailbox[f.rank] + (slab * f.features + n) * kRowPairs;
+        const uint64_t* base = f.mailbox[f.rank] + slab * kRowPairs * f.features + n;
         for (uint32_t sweep = 0; missing != 0; ++sweep) {
 #pragma unroll
           for (int s = 0; s < kMaxPeers; ++s)
@@ -399,7 +400,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
             for (int j = 0; j < kRowPairs; ++j)
               if (missing & (1ull << (s * kRowPairs + j))) {
                 uint32_t t, v;
-                ld_tagged(base + (size_t)s * f.features * kRowPairs + j, t, v);
+                ld_tagged(base + ((size_t)s * kRowPairs + j) * f.features, t, v);
                 if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kRowPairs + j)); }
               }
           if ((sweep & 255u) == 255u) {
