@@ -427,6 +427,9 @@ __global__ void tail_commit_kernel(const TailArgs a) {
   int* c = a.ctrl;
   const int round = c[8];
   if (c[4]) {                                  // already stopped: keep the fabric epoch moving, publish nothing
+    // The round that just ran completed the draft context of the last committed rows; any further
+    // round must not overwrite it with features of rows that were never committed.
+    c[2] = c[0];
     *a.epoch += 1u;
     c[8] = round + 1;
     return;

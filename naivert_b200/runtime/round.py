@@ -163,9 +163,12 @@ class SpeculativeRound:
         return g
 
     # ------------------------------------------------------------------ request lifecycle
-    def initialize(self, prompt: torch.Tensor, max_tokens: int, sp: SamplingParams, use_graphs: bool = True) -> None:
+    def initialize(self, prompt: torch.Tensor, max_tokens: int, sp: SamplingParams, use_graphs: bool = True,
+                   start_pos: int = 0) -> None:
         """Reset the session state, replay the prompt (all but its last token, which becomes
-        the first anchor) and arm the control block.  ``prompt`` may live in pinned host memory."""
+        the first anchor) and arm the control block.  ``prompt`` may live in pinned host memory.
+        ``start_pos`` context rows are already valid in the caches (a restored prefix): replay
+        starts there."""
         n = int(prompt.numel())
         if n < 1 or n + max_tokens + 2 * PAD_ROWS > self.capacity:
             raise RuntimeContractError(f"prompt {n} + decode {max_tokens} does not fit capacity {self.capacity}")
@@ -175,11 +178,13 @@ class SpeculativeRound:
         self.prompt_dev[:n].copy_(prompt.to(torch.int32), non_blocking=True)
         self.n_prompt, self.n_prompt_ctx = n, n - 1
         ctrl = torch.zeros(16, dtype=torch.int32)
-        ctrl[7], ctrl[9], ctrl[11] = max_tokens, self.capacity, n - 1
+        if not 0 <= start_pos <= n - 1:
+            raise RuntimeContractError(f"resume position {start_pos} outside the prompt context 0..{n - 1}")
+        ctrl[7], ctrl[9], ctrl[10], ctrl[11] = max_tokens, self.capacity, start_pos, n - 1
         self.t.ctrl.copy_(ctrl)
         self.counts.zero_()
         self.fab.status.zero_()
-        steps = -(-(n - 1) // self.t.rows)
+        steps = -(-(n - 1 - start_pos) // self.t.rows)
         if steps:
             if use_graphs:
                 if self.prefill_graph is None:
@@ -193,7 +198,11 @@ class SpeculativeRound:
                         self.prefill_phases()
         with torch.cuda.stream(self.stream):
             # arm: anchor = last prompt token at position n-1; the last replay chunk is re-ingested by round 0
-            last_chunk = max(0, (steps - 1) * self.t.rows)
+            last_chunk = start_pos + max(0, (steps - 1) * self.t.rows)
+            if steps == 0:
+                # nothing was replayed: the feature rows are stale, so round 0 must not overwrite valid
+                # draft context; point its (harmless) ingest beyond the context instead
+                last_chunk = n - 1
             arm = torch.tensor([n - 1, min(self.t.rows, max(0, n - 1 - last_chunk)), last_chunk], dtype=torch.int32)
             self.t.ctrl[:3].copy_(arm.to(self.t.dev))
             self.block_ids[0:1].copy_(self.prompt_dev[n - 1:n])

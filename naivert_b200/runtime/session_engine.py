@@ -1,0 +1,224 @@
+"""Session engine: the object the serving layer talks to.  Adds session-prefix reuse, the
+resume policy and per-request statistics on top of ``Engine``.
+
+    engine = SessionEngine(Engine.build(...), store_gb=8)
+    session = engine.open_session(tokens, max_decode, session_id, sampling)
+    while not session.done: tokens += session.step(timeout)
+    stats = session.finish()           # parks the KV state under the session key
+
+Parity: ``SessionEngine`` / ``Session`` (naivert/backends/naive_n0p5_session_engine.py:52-118
+resume selection, :123-212 prefill cost model and path policy, :263-340 step loop, :411-454
+``align_prompt``, :590-630 ``_finish``).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.spec import FULL_DSA, SamplingParams
+from .engine import Engine
+from .prefix_store import PrefixStore, common_prefix, park_name, select_resume
+from .round import RuntimeContractError
+
+# Measured on B200 (ms); inputs of the resume / prefill-path policy.
+REPLAY_MS_PER_TOKEN = 1.2            # 8-row verify replay per prompt token (tp8, 48 layers)
+NATIVE_FIRST_CHUNK_MS = 62.0
+NATIVE_NEXT_CHUNK_MS = 60.0
+NATIVE_CHUNK = 4096
+RESTORE_MS_PER_GB = 2.0
+
+
+def prefill_estimate(new_tokens: int, path: str) -> float:
+    """Estimated milliseconds to ingest ``new_tokens`` prompt tokens on ``path``."""
+    if new_tokens <= 0:
+        return 0.0
+    if path == "replay":
+        return new_tokens * REPLAY_MS_PER_TOKEN
+    chunks = -(-new_tokens // NATIVE_CHUNK)
+    return NATIVE_FIRST_CHUNK_MS + (chunks - 1) * NATIVE_NEXT_CHUNK_MS
+
+
+def prefill_path(new_tokens: int, policy: str = "cost", native_ready: bool = False) -> str:
+    """``replay`` (verify-8 replay) or ``native`` (chunked TP/EP prefill); ``cost`` picks the cheaper."""
+    if policy in ("replay", "native"):
+        return policy if (policy == "replay" or native_ready) else "replay"
+    if not native_ready:
+        return "replay"
+    return "native" if prefill_estimate(new_tokens, "native") < prefill_estimate(new_tokens, "replay") else "replay"
+
+
+@dataclass
+class EngineConfig:
+    capacity: int
+    max_output_tokens: int
+    eos_token_ids: Sequence[int]
+    think_end_token_id: int
+
+
+def segment_stats(tokens: Sequence[int], round_sizes: Sequence[int], round_ns: Sequence[int], think_end: int,
+                  accepted: Sequence[int]) -> Dict[str, dict]:
+    """Think / answer / total statistics from per-round device timestamps: the reply is split at the
+    first ``think_end`` token; a round belongs to the segment its first token falls into."""
+    out: Dict[str, dict] = {}
+    split = tokens.index(think_end) + 1 if think_end in tokens else 0
+    segs = {"think": (0, split), "answer": (split, len(tokens)), "total": (0, len(tokens))}
+    starts, pos = [], 0
+    for n in round_sizes:
+        starts.append(pos)
+        pos += n
+    for name, (lo, hi) in segs.items():
+        idx = [i for i, s in enumerate(starts) if lo <= s < hi and i > 0]
+        toks = sum(round_sizes[i] for i in idx)
+        ns = sum(round_ns[i] - round_ns[i - 1] for i in idx)
+        if hi - lo <= 0:
+            continue
+        out[name] = {"tokens": hi - lo, "rounds": len(idx), "tokens_per_round": round(toks / max(1, len(idx)), 3),
+                     "device_ms": round(ns * 1e-6, 3), "device_tok_s": round(toks / (ns * 1e-9), 2) if ns > 0 else 0.0,
+                     "acceptance": round(sum(accepted[i] for i in idx) / max(1, 7 * len(idx)), 4)}
+    return out
+
+
+class Session:
+    def __init__(self, owner: "SessionEngine", tokens: List[int], cached: int, session_id: Optional[str], info: dict):
+        self.owner, self.prompt, self.cached_tokens, self.session_id = owner, tokens, cached, session_id
+        self.prefill_info = info
+        self.done, self.stop_reason = False, None
+        self.out: List[int] = []
+        self.round_sizes: List[int] = []
+        self.round_ns: List[int] = []
+        self.accepted: List[int] = []
+        self._launched = False
+        self.closed = False
+
+    def step(self, timeout_s: float = 120.0) -> List[int]:
+        """Tokens of the next published round (launches rounds ahead of the host as needed)."""
+        if self.done:
+            return []
+        r = self.owner.engine.round
+        if not self._launched:
+            r.launch(self.owner.ahead)
+            self._launched = True
+        rec = r.wait_round(timeout_s)
+        self.out.extend(rec.tokens)
+        self.round_sizes.append(len(rec.tokens))
+        self.round_ns.append(rec.t_end_ns)
+        self.accepted.append(rec.accepted)
+        if rec.stop_reason is not None:
+            self.done, self.stop_reason = True, rec.stop_reason
+        else:
+            r.launch(1)
+        return rec.tokens
+
+    def cancel(self) -> None:
+        if not self.done:
+            self.owner.engine.round.cancel()
+
+    def finish(self) -> dict:
+        """Drain the chain, check the fabric, park the KV state; returns device statistics."""
+        if self.closed:
+            return {}
+        self.closed = True
+        eng = self.owner.engine
+        r = eng.round
+        if self._launched and not self.done:
+            r.cancel()
+            deadline = time.monotonic() + self.owner.cancel_timeout_s
+            while not self.done:
+                rec = r.poll()
+                if rec is None:
+                    if time.monotonic() > deadline:
+                        raise RuntimeError("the running chain did not honour the cancel request")
+                    time.sleep(1e-4)
+                    continue
+                self.out.extend(rec.tokens)
+                self.round_sizes.append(len(rec.tokens))
+                self.round_ns.append(rec.t_end_ns)
+                self.accepted.append(rec.accepted)
+                if rec.stop_reason is not None:
+                    self.done, self.stop_reason = True, rec.stop_reason
+        if self._launched:
+            r.launch(1)                                   # one more pass completes the draft context of the last rows
+        r.stream.synchronize()
+        eng.fabric.check()
+        stats = {"prefill_path": self.prefill_info.get("path"), "initialize_ms": self.prefill_info.get("init_ms"),
+                 "segments": segment_stats(self.out, self.round_sizes, self.round_ns, self.owner.config.think_end_token_id,
+                                           self.accepted)}
+        tot = stats["segments"].get("total")
+        if tot:
+            stats["decode_tok_s_device"] = tot["device_tok_s"]
+        self.owner._park(self)
+        return stats
+
+
+class SessionEngine:
+    def __init__(self, engine: Engine, store_gb: float = 8.0, ahead: int = 4, max_output_tokens: int = 524288,
+                 resume_policy: str = "cost", cancel_timeout_s: float = 30.0, host_store: bool = False):
+        self.engine, self.ahead, self.resume_policy, self.cancel_timeout_s = engine, ahead, resume_policy, cancel_timeout_s
+        spec = engine.spec
+        self.config = EngineConfig(engine.round.capacity, max_output_tokens, tuple(spec.stop_token_ids), spec.think_end_token_id)
+        full, rings = [], []
+        for d in engine.target.layers:
+            if d["kind"] == FULL_DSA:
+                full += [d["k"], d["v"], d["ik"], d["iks"]]
+            else:
+                rings += [d["k"], d["v"]]
+        for L in engine.round.draft.layers:
+            full += [L["k"], L["v"]]
+        self.store = PrefixStore(full, rings, int(store_gb * (1 << 30)), host=host_store)
+        self.active: Optional[Session] = None
+        self._sampled: Dict[str, List[int]] = {}
+
+    # ------------------------------------------------------------------
+    def align_prompt(self, tokens: Sequence[int], session_id: Optional[str]) -> List[int]:
+        """Re-tokenising text that the model generated may not reproduce the sampled ids.  When the
+        new prompt *decodes* like a continuation of the parked sequence, the parked (sampled) ids are
+        kept for the shared part; here ids are compared directly, so this is the identity unless a
+        formatter supplies aligned ids."""
+        return list(tokens)
+
+    def open_session(self, tokens: Sequence[int], max_decode: int, session_id: Optional[str],
+                     sampling: Optional[SamplingParams] = None, use_graphs: bool = True) -> Session:
+        if self.active is not None and not self.active.closed:
+            raise RuntimeContractError("one sequence at a time: finish the active session first")
+        tokens = [int(t) for t in tokens]
+        n = len(tokens)
+        cap = self.config.capacity
+        if n < 1 or n + max_decode + 32 > cap:
+            raise RuntimeContractError(f"prompt {n} + decode {max_decode} exceeds capacity {cap}")
+        t0 = time.perf_counter()
+        choice = select_resume(self.store.entries, tokens, session_id)
+        start = 0
+        if choice is not None:
+            new_after = n - 1 - choice.position
+            # restoring costs a device copy; replaying a handful of tokens can be cheaper
+            gb = self.store.entries[choice.key].nbytes() / (1 << 30)
+            if prefill_estimate(n - 1, "replay") - prefill_estimate(new_after, "replay") > gb * RESTORE_MS_PER_GB:
+                start = self.store.restore(choice)
+        t1 = time.perf_counter()
+        path = prefill_path(n - 1 - start, self.resume_policy, native_ready=False)
+        prompt = torch.tensor(tokens, dtype=torch.int32)
+        self.engine.round.initialize(prompt, max_decode, sampling or SamplingParams(), use_graphs=use_graphs, start_pos=start)
+        t2 = time.perf_counter()
+        key = session_id or "anon"
+        if n - 1 >= 16:
+            self.store.checkpoint(key, n - 1)            # ring state at prompt end, for later rewinds
+        info = {"path": path, "restore_ms": round((t1 - t0) * 1e3, 3), "init_ms": round((t2 - t1) * 1e3, 3),
+                "resumed_from": choice.key if start else None, "estimate_ms": round(prefill_estimate(n - 1 - start, path), 2)}
+        self.active = Session(self, tokens, start, session_id, info)
+        return self.active
+
+    def _park(self, s: Session) -> None:
+        ctrl = self.engine.target.ctrl.tolist()
+        position = int(ctrl[0])                           # rows valid in the caches (the anchor row is not)
+        seq = s.prompt + s.out
+        if position < 16 or position > len(seq):
+            return
+        name = park_name(self.store.entries, s.session_id, seq)
+        self.store.save(name, seq, position)
+
+    def close(self) -> None:
+        self.store.clear()
+        self.engine.close()

@@ -100,3 +100,39 @@ def test_stop_on_eos_and_cancel():
         if i == 3:
             eng.round.cancel()
     assert recs[-1].stop_reason == "cancelled" and len(recs) < 40
+
+
+def test_session_prefix_reuse_is_bitwise_identical():
+    """A parked session prefix resumed by a longer prompt gives exactly the tokens of a cold run."""
+    from naivert_b200.models.spec import SamplingParams
+    from naivert_b200.runtime.session_engine import SessionEngine
+    spec, eng = _engine(layers=3, capacity=2048)
+    se = SessionEngine(eng, store_gb=1.0)
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, spec.vocab - 16, (300,), generator=g).tolist()     # beyond top_k = 256: sparse path
+    sp = SamplingParams(temperature=0.7, seed=21)
+
+    def run(engine, toks, sid, n=48):
+        s = engine.open_session(toks, n, sid, sp)
+        out = []
+        while not s.done:
+            out += s.step(30)
+        stats = s.finish()
+        return s, out, stats
+
+    s1, out1, st1 = run(se, prompt, "conv")
+    assert s1.cached_tokens == 0 and len(out1) == 48 and st1["segments"]["total"]["tokens"] == 48
+    follow = prompt + out1 + torch.randint(0, spec.vocab - 16, (25,), generator=g).tolist()
+    s2, out2, _ = run(se, follow, "conv")
+    assert s2.cached_tokens >= 300, s2.prefill_info
+    s3, out3, _ = run(se, follow, "conv")                       # same prompt again: resumes from its own checkpoint/park
+    _, cold_eng = _engine(layers=3, capacity=2048)
+    cold = SessionEngine(cold_eng, store_gb=1.0)
+    _, out_cold, _ = run(cold, follow, None)
+    assert out2 == out_cold and out3 == out_cold
+    # a branch that diverges inside the first prompt falls back to the ring checkpoint or a cold start
+    branch = prompt[:280] + [5, 6, 7, 8, 9] * 8
+    s4, out4, _ = run(se, branch, "conv")
+    _, out4_cold, _ = run(cold, branch, None)
+    assert out4 == out4_cold
+    assert se.store.bytes() > 0 and any("#" in k for k in se.store.entries) or len(se.store.entries) >= 1

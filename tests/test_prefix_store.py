@@ -1,0 +1,74 @@
+"""Prefix parking on CPU tensors: save/restore/rewind through ring checkpoints, resume selection, eviction."""
+import torch
+
+from naivert_b200.runtime.prefix_store import ParkedPrefix, PrefixStore, park_name, select_resume
+
+
+def _store(budget=1 << 20):
+    full = [torch.zeros(64, 4), torch.zeros(64, 2)]
+    rings = [torch.zeros(8, 4)]
+    return full, rings, PrefixStore(full, rings, budget)
+
+
+def test_save_restore_roundtrip_and_rewind():
+    full, rings, st = _store()
+    for t in full:
+        t.copy_(torch.arange(t.numel(), dtype=torch.float32).reshape(t.shape))
+    rings[0].fill_(1.0)
+    st.checkpoint("a", 10)                       # ring state at prompt end
+    rings[0].fill_(2.0)
+    st.save("a", list(range(30)), 29)
+    saved = [t.clone() for t in full]
+    for t in full:
+        t.zero_()
+    rings[0].zero_()
+    ch = select_resume(st.entries, list(range(30)) + [99, 98], "a")
+    assert ch.position == 29 and ch.checkpoint is None
+    assert st.restore(ch) == 29
+    assert torch.equal(full[0][:29], saved[0][:29]) and float(full[0][29:].abs().sum()) == 0
+    assert float(rings[0][0, 0]) == 2.0
+    # a branch that shares only 20 tokens rewinds to the ring checkpoint at 10
+    ch = select_resume(st.entries, list(range(20)) + [7, 7, 7], "a", min_gain=4)
+    assert ch.position == 10 and ch.checkpoint == 0
+    st.restore(ch)
+    assert float(rings[0][0, 0]) == 1.0
+
+
+def test_selection_prefers_longest_then_own_key():
+    e1 = ParkedPrefix("s1", list(range(100)), 99, [], [])
+    e2 = ParkedPrefix("s2", list(range(100)), 99, [], [])
+    e3 = ParkedPrefix("s3", list(range(50)), 49, [], [])
+    entries = {"s1": e1, "s2": e2, "s3": e3}
+    assert select_resume(entries, list(range(120)), "s2").key == "s2"
+    assert select_resume(entries, list(range(60)) + [1], "s3").key == "s3"      # s1/s2 parks lie beyond the match
+    assert select_resume(entries, [5, 6, 7], None) is None
+    assert select_resume(entries, list(range(100)), "s1") is None or select_resume(entries, list(range(100)), "s1").position <= 99
+
+
+def test_park_name_branches():
+    entries = {"k": ParkedPrefix("k", list(range(40)), 39, [], [])}
+    assert park_name(entries, "k", list(range(60))) == "k"
+    assert park_name(entries, "k", list(range(20)) + [0] * 30) == "k#1"
+    assert park_name(entries, None, [1, 2]) == "anon"
+
+
+def test_eviction_lru_to_budget():
+    full, rings, st = _store(budget=3000)
+    st.save("a", list(range(40)), 39)
+    st.save("b", list(range(40)), 39)
+    st.entries["a"].last_used += 100            # a is fresher than b
+    st.save("c", list(range(40)), 39)
+    assert "c" in st.entries and st.bytes() <= 3000 and "b" not in st.entries
+
+
+def test_prefill_policy_and_segment_stats():
+    from naivert_b200.runtime.session_engine import prefill_estimate, prefill_path, segment_stats
+    assert prefill_estimate(0, "replay") == 0
+    assert prefill_path(100, "cost", native_ready=True) == "native" if prefill_estimate(100, "native") < prefill_estimate(100, "replay") else "replay"
+    assert prefill_path(10, "cost", native_ready=True) == "replay"
+    assert prefill_path(100000, "cost", native_ready=True) == "native"
+    assert prefill_path(100000, "cost", native_ready=False) == "replay" and prefill_path(5, "native", native_ready=True) == "native"
+    toks = [1, 2, 9, 4, 5, 6, 7, 8]
+    st = segment_stats(toks, [3, 3, 2], [1000, 4000, 8000], think_end=9, accepted=[2, 2, 1])
+    assert st["think"]["tokens"] == 3 and st["answer"]["tokens"] == 5 and st["total"]["rounds"] == 2
+    assert st["total"]["device_ms"] == 0.007 and st["answer"]["device_tok_s"] > 0
