@@ -1,0 +1,109 @@
+#!/usr/bin/env python3
+"""Serve the Anthropic-Messages-compatible API from one node.
+
+    python examples/serve_sessions.py --model naive-n0.5 --target /ckpt/target --draft /ckpt/draft
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 examples/serve_sessions.py ...
+
+Rank 0 runs the HTTP server; with more than one process the other ranks follow its engine calls.
+Without checkpoints (``--random-init``) weights are drawn on device, which is what the smoke
+tests and benchmarks use.  Flags mirror examples/serve_sessions.py:75-114 of the reference.
+"""
+from __future__ import annotations
+
+import argparse
+import logging
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--host", default=os.environ.get("NAIVERT_HOST", "127.0.0.1"))
+    ap.add_argument("--port", type=int, default=int(os.environ.get("NAIVERT_PORT", "8080")))
+    ap.add_argument("--cors-origin", default=None)
+    ap.add_argument("--cors-credentials", action="store_true")
+    ap.add_argument("--model", default="naive-n0.5", help="registry name of the architecture")
+    ap.add_argument("--target", default=os.environ.get("NAIVERT_TARGET_CHECKPOINT"), help="target checkpoint directory or short name")
+    ap.add_argument("--draft", default=os.environ.get("NAIVERT_DRAFT_CHECKPOINT"), help="draft checkpoint directory or short name")
+    ap.add_argument("--random-init", action="store_true", help="draw weights on device instead of loading checkpoints")
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model to its first N layers")
+    ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--max-decode-tokens", type=int, default=524288)
+    ap.add_argument("--capacity", type=int, default=1048576, help="KV positions per sequence")
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--temperature", type=float, default=1.0)
+    ap.add_argument("--top-p", type=float, default=0.95)
+    ap.add_argument("--repetition-penalty", type=float, default=1.0)
+    ap.add_argument("--frequency-penalty", type=float, default=0.0)
+    ap.add_argument("--presence-penalty", type=float, default=0.0)
+    ap.add_argument("--store-gb", type=float, default=8.0, help="parked-prefix budget per rank")
+    ap.add_argument("--queue-depth", type=int, default=8)
+    ap.add_argument("--resume-policy", choices=("cost", "replay", "native"), default="cost")
+    ap.add_argument("--prefill", choices=("verify8", "native"), default="verify8")
+    ap.add_argument("--thinking", action="store_true", help="enable thinking by default in the chat template")
+    ap.add_argument("--log-level", default="info")
+    return ap.parse_args(argv)
+
+
+def main(argv=None) -> int:
+    a = parse_args(argv)
+    logging.basicConfig(level=a.log_level.upper(), format="%(asctime)s %(name)s %(levelname)s %(message)s")
+    import torch
+    import torch.distributed as dist
+
+    from naivert_b200.models.checkpoint import resolve_checkpoint
+    from naivert_b200.models.registry import resolve_model
+    from naivert_b200.runtime.engine import Engine
+    from naivert_b200.runtime.session_engine import SessionEngine
+    from naivert_b200.runtime.tp_frontend import Commands, LeaderEngine, follower_loop
+    from naivert_b200.serve.chat import ChatFormatter
+    from naivert_b200.serve.context import ServerContext
+    from naivert_b200.serve.http import build_app, run_app
+    from naivert_b200.serve.messages_api import ServerDefaults
+
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = cpu_group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+        cpu_group = dist.new_group(backend="gloo")
+    spec = resolve_model(a.model)
+    if a.layers:
+        spec = spec.with_layers(a.layers)
+    target = draft = None
+    if not a.random_init:
+        if not a.target or not a.draft:
+            raise SystemExit("--target and --draft are required unless --random-init is given")
+        target, draft = resolve_checkpoint(a.target), resolve_checkpoint(a.draft, "NAIVERT_DRAFT_ROOTS")
+
+    def build_engine() -> SessionEngine:
+        eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=a.capacity, seed=a.seed, target_ckpt=target,
+                           draft_ckpt=draft, device=dev)
+        return SessionEngine(eng, store_gb=a.store_gb, max_output_tokens=a.max_decode_tokens, resume_policy=a.resume_policy)
+
+    if rank != 0:
+        follower_loop(build_engine(), Commands(cpu_group))
+        return 0
+
+    defaults = ServerDefaults(served_model=a.served_model_name or a.model, temperature=a.temperature, top_p=a.top_p, seed=a.seed,
+                              repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
+                              presence_penalty=a.presence_penalty, max_output_tokens=a.max_decode_tokens)
+
+    def factory() -> ServerContext:
+        torch.cuda.set_device(local)                      # the worker thread owns the device context
+        se = build_engine()
+        engine = LeaderEngine(se, Commands(cpu_group)) if world > 1 else se
+        return ServerContext(engine, ChatFormatter.from_path(target, enable_thinking=a.thinking))
+
+    app = build_app(factory, defaults, queue_depth=a.queue_depth, cors_origin=a.cors_origin, cors_credentials=a.cors_credentials)
+    run_app(app, a.host, a.port, a.log_level)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

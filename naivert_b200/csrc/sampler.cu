@@ -418,11 +418,21 @@ struct TailArgs {
   int vbase, vlocal;
   const uint32_t* status;
   int n_rows_q;
+  XchgArgs x;                    // cancel / failure consensus across ranks
 };
 
 __global__ void tail_commit_kernel(const TailArgs a) {
+  __shared__ uint64_t xv[16];
   griddep_launch();
   griddep_wait();
+  // Every rank must take the same stop decision in the same round: the host cancel word (set on one
+  // rank only) and a failed device wait on any rank are max-reduced over the ranks first.
+  if (threadIdx.x < 16)
+    xv[threadIdx.x] = threadIdx.x == 0 ? (uint64_t)(*a.cancel != 0) : (threadIdx.x == 1 ? (uint64_t)(*a.status != 0u) : 0ull);
+  __syncthreads();
+  xchg_reduce_u64<kXMax>(xv, 2, a.x, 9);
+  __syncthreads();
+  const bool cancel_any = xv[0] != 0ull, failed_any = xv[1] != 0ull;
   if (threadIdx.x != 0) return;
   int* c = a.ctrl;
   const int round = c[8];
@@ -438,8 +448,8 @@ __global__ void tail_commit_kernel(const TailArgs a) {
   const int pos0 = c[0];
   int reason = 0, n = 0;
   int out[8];
-  if (*a.status != 0u) reason = 5;
-  else if (*a.cancel != 0) reason = 4;
+  if (failed_any) reason = 5;
+  else if (cancel_any) reason = 4;
   for (int j = 0; j <= m && reason == 0; ++j) {
     const int tok = j < m ? a.block_ids[j + 1] : a.st->extra_token;
     out[n++] = tok;

@@ -118,6 +118,7 @@ class SpeculativeRound:
         t.cancel, t.stop_ids, t.n_stop = self.ring.cancel_dev, self.stop_ids.data_ptr(), len(self.spec.stop_token_ids)
         t.counts, t.vbase, t.vlocal = None, self.vbase, self.vlocal
         t.status, t.n_rows_q = self.fab.status.data_ptr(), 7
+        t.x = self.fab.xchg_args()
         self.args_tail = t
 
     # ------------------------------------------------------------------ sampling controls
