@@ -32,6 +32,7 @@ int launch_variant(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorM
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  if ((EPI == kEpiAllReduce || (GROUP != kGroupItem && gy > 1)) && args.rows > kArRows) return -5;
   if (GROUP != kGroupItem && gy > 1) {
     if (gy > kMaxSplit) return -4;
     return launch_cluster(kern, dim3(gx, gy, 1), dim3(192, 1, 1), dim3(1, gy, 1), Cfg::kSmemBytes, stream, pdl != 0, a0,

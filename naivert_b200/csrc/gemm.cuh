@@ -32,7 +32,9 @@ constexpr int kKBytes = 128;       // bytes of K per stage row (one swizzle atom
 constexpr int kATileBytes = kTileN * kKBytes;   // 16 KiB
 constexpr int kBTileBytes = kTok * kKBytes;     // 2 KiB
 constexpr int kMaxPeers = 8;
-constexpr int kRowPairs = kTok / 2;             // tagged words per feature per source rank
+constexpr int kRowPairs = kTok / 2;             // mailbox stride: tagged words per feature per source rank
+constexpr int kArRows = 8;                      // rows the fused all-reduce / cluster split handle (verify = 8)
+constexpr int kArPairs = kArRows / 2;
 constexpr int kMailboxSlabs = 4;
 constexpr int kMaxSplit = 4;                    // CTAs of one cluster that share an output tile (split K / split experts)
 
@@ -48,6 +50,9 @@ struct FabricArgs {
   int call_idx;                   // position of this all-reduce inside one step (tag + slab selection)
   int features;                   // row width of the all-reduced tensor (mailbox stride)
   unsigned long long timeout_ns;
+  int mode;                       // 0: all-reduce (every rank gets every feature)  1: reduce-scatter (rank r owns slice r)
+  int ag_call;                    // >= 0: the token operand is all-gathered; K slice s is valid once ag_flags[s] carries this call's tag
+  const uint64_t* ag_flags;       // [tp] tagged words in local memory, written by the peers' ag_push
 };
 
 struct GemmArgs {
@@ -81,11 +86,13 @@ struct GemmArgs {
 template <bool FP8, bool DUAL>
 struct GemmCfg {
   static constexpr int kStageBytes = (DUAL ? 2 : 1) * kATileBytes + kBTileBytes;
-  static constexpr int kStages = DUAL ? 5 : 8;
+  // single-matrix tiles keep the footprint near 100 KiB so two CTAs (typically of consecutive kernels,
+  // overlapped by programmatic dependent launch) share an SM
+  static constexpr int kStages = 5;
   static constexpr int kAccCols = DUAL ? 2 * kTok : kTok;          // TMEM columns per accumulator buffer
   static constexpr int kAccBufs = FP8 ? (DUAL ? 4 : 8) : 1;
   static constexpr int kTmemCols = (kAccCols * kAccBufs < 32) ? 32 : kAccCols * kAccBufs;
-  static constexpr int kPartBytes = (kMaxSplit - 1) * kTok * kTileN * 4;   // split partials of the cluster peers
+  static constexpr int kPartBytes = (kMaxSplit - 1) * kArRows * kTileN * 4;   // split partials of the cluster peers
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers + scratch*/ + kPartBytes;
 };
 
@@ -113,7 +120,7 @@ __device__ __forceinline__ float pow2_scale(float amax) {
 }
 
 template <bool FP8, bool DUAL, int EPI, int GROUP>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, DUAL ? 1 : 2)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                    const __grid_constant__ CUtensorMap tmB, const GemmArgs p) {
   using Cfg = GemmCfg<FP8, DUAL>;
@@ -186,6 +193,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
+      int ag_seen = -1;
       for (int u = 0; u < units; ++u) {
         const int st = u % Cfg::kStages;
         if (u >= Cfg::kStages &&
@@ -201,6 +209,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
         }
         const int brow = (GROUP == kGroupLoop) ? slot * kTok : 0;
+        if (GROUP == kGroupNone && p.fab.ag_call >= 0 && p.fab.tp > 1) {
+          // all-gather -> GEMM: the K slice of source rank `src` was pushed into local memory by that rank;
+          // wait for its flag (acquire), then order the generic-proxy writes before the TMA read
+          const int src = (kb_first + kb) / (kb_total / p.fab.tp);
+          if (src != ag_seen) {
+            const uint32_t tag = (*p.fab.epoch) * 1024u + (uint32_t)p.fab.ag_call + 1u;
+            uint32_t v;
+            if (!wait_tagged(p.fab.ag_flags + src, tag, v, globaltimer() + p.fab.timeout_ns, p.status, kSiteMailbox | 0x40 | src)) break;
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            asm volatile("fence.proxy.async;" ::: "memory");
+            ag_seen = src;
+          }
+        }
         tma_load_2d(sa + (DUAL ? 2 : 1) * kATileBytes, &tmB, &tail->full[st], kx, brow);
       }
     }
@@ -265,11 +286,20 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           const int buf = u % Cfg::kAccBufs;
           // scales are fetched before the wait so their latency hides behind the MMA of this block
           float sc[kTok];
+          const bool gathered = GROUP == kGroupNone && p.fab.ag_call >= 0 && p.fab.tp > 1;
+          if (!gathered) {
 #pragma unroll
-          for (int r = 0; r < kTok; ++r) sc[r] = __ldg(as + r * kb_total + kb);
+            for (int r = 0; r < kTok; ++r) sc[r] = __ldg(as + r * kb_total + kb);
+          }
           const float w0 = __ldg(ws0 + kb);
           const float w1 = DUAL ? __ldg(ws1 + kb) : 0.f;
           if (!mbar_wait(&tail->acc_full[buf], (u / Cfg::kAccBufs) & 1, p.status, kSiteAccFull | buf)) { ok = false; break; }
+          if (gathered) {
+            // scales of a gathered operand arrive with the peer's slice: read them (coherently) only after
+            // the accumulator of that slice is complete, i.e. after the producer has seen the slice's flag
+#pragma unroll
+            for (int r = 0; r < kTok; ++r) sc[r] = __ldcv(as + r * kb_total + kb);
+          }
           tc_fence_after();
           float v0[kTok], v1[kTok];
           tmem_ld16(lane_addr + buf * Cfg::kAccCols, v0);
@@ -306,14 +336,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         leader = false;
         const uint32_t dst = mapa_shared(smem_u32(part), 0);
 #pragma unroll
-        for (int r = 0; r < kTok; ++r)
-          st_cluster_f32(dst + (uint32_t)((((crank - 1) * kTok + r) * kTileN + row) * 4), mix0[r]);
+        for (int r = 0; r < kArRows; ++r)
+          st_cluster_f32(dst + (uint32_t)((((crank - 1) * kArRows + r) * kTileN + row) * 4), mix0[r]);
         mbar_arrive_cluster(mapa_shared(smem_u32(&tail->split_bar), 0));
       } else {
         if (mbar_wait_cluster(&tail->split_bar, 0, p.status, kSiteCluster)) {
           for (int y = 1; y < split; ++y)
 #pragma unroll
-            for (int r = 0; r < kTok; ++r) mix0[r] += part[((y - 1) * kTok + r) * kTileN + row];
+            for (int r = 0; r < kArRows; ++r) mix0[r] += part[((y - 1) * kArRows + r) * kTileN + row];
         }
       }
     }
@@ -357,27 +387,30 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
     } else if (EPI == kEpiAllReduce) {
       const FabricArgs& f = p.fab;
+      const int owner = f.mode == 1 ? n / (p.n_total / f.tp) : f.rank;        // reduce-scatter: one owner per feature
       const bool col_ok = leader && n < p.n_total;
+      const bool mine = owner == f.rank;
       // Each rank rounds its partial to bf16, pushes it to every peer as tagged words and adds
       // the partials of all ranks in rank order in fp32 on top of the residual.
-      uint32_t w[kMaxPeers][kRowPairs];
+      uint32_t w[kMaxPeers][kArPairs];
       const int pairs = (p.rows + 1) >> 1;
-      float sum[kTok];
+      float sum[kArRows];
 #pragma unroll
-      for (int r = 0; r < kTok; ++r)
+      for (int r = 0; r < kArRows; ++r)
         sum[r] = (p.resid && r < p.rows && col_ok) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
-      uint32_t own[kRowPairs];
+      uint32_t own[kArPairs];
 #pragma unroll
-      for (int j = 0; j < kRowPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
+      for (int j = 0; j < kArPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
       if (f.tp > 1 && col_ok) {
         const uint32_t tag = (*f.epoch) * 1024u + (uint32_t)f.call_idx + 1u;
         const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
         for (int d = 1; d < f.tp; ++d) {
           const int peer = (f.rank + d) % f.tp;
+          if (f.mode == 1 && peer != owner) continue;
           // layout [slab][source][row pair][feature]: a warp's 32 stores of one pair are contiguous
           uint64_t* dst = f.mailbox[peer] + (slab + f.rank) * kRowPairs * f.features + n;
 #pragma unroll
-          for (int j = 0; j < kRowPairs; ++j)
+          for (int j = 0; j < kArPairs; ++j)
             if (j < pairs) st_tagged(dst + (size_t)j * f.features, tag, own[j]);
         }
         // Batched poll: every missing word of every source is re-read per sweep, so the
@@ -386,9 +419,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
         for (int s = 0; s < kMaxPeers; ++s)
 #pragma unroll
-          for (int j = 0; j < kRowPairs; ++j) {
+          for (int j = 0; j < kArPairs; ++j) {
             if (s == f.rank) w[s][j] = own[j];
-            else if (s < f.tp && j < pairs) missing |= 1ull << (s * kRowPairs + j);
+            else if (mine && s < f.tp && j < pairs) missing |= 1ull << (s * kArPairs + j);
             else w[s][j] = 0u;
           }
         const uint64_t deadline = globaltimer() + f.timeout_ns;
@@ -397,11 +430,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
           for (int s = 0; s < kMaxPeers; ++s)
 #pragma unroll
-            for (int j = 0; j < kRowPairs; ++j)
-              if (missing & (1ull << (s * kRowPairs + j))) {
+            for (int j = 0; j < kArPairs; ++j)
+              if (missing & (1ull << (s * kArPairs + j))) {
                 uint32_t t, v;
                 ld_tagged(base + ((size_t)s * kRowPairs + j) * f.features, t, v);
-                if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kRowPairs + j)); }
+                if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kArPairs + j)); }
               }
           if ((sweep & 255u) == 255u) {
             if (*reinterpret_cast<volatile uint32_t*>(f.status) != 0u) break;
@@ -411,15 +444,15 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
         for (int s = 0; s < kMaxPeers; ++s)
 #pragma unroll
-          for (int j = 0; j < kRowPairs; ++j)
+          for (int j = 0; j < kArPairs; ++j)
             if (s < f.tp) { sum[2 * j] += bf16_lo(w[s][j]); sum[2 * j + 1] += bf16_hi(w[s][j]); }
       } else {
 #pragma unroll
-        for (int r = 0; r < kTok; ++r) sum[r] += round_bf16(mix0[r]);
+        for (int r = 0; r < kArRows; ++r) sum[r] += round_bf16(mix0[r]);
       }
 #pragma unroll
-      for (int r = 0; r < kTok; ++r)
-        if (r < p.rows && col_ok) {
+      for (int r = 0; r < kArRows; ++r)
+        if (r < p.rows && col_ok && mine) {
           const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
           p.out_bf16[(size_t)r * p.ld_out + n] = o;
           if (p.out_copy) p.out_copy[(size_t)r * p.ld_copy + n] = o;

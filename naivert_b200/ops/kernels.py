@@ -32,7 +32,8 @@ def gemm_variant(fp8: bool, dual: bool, epi: int, group: int) -> int:
 
 class FabricArgs(C.Structure):
     _fields_ = [("mailbox", VP * K_MAX_PEERS), ("epoch", VP), ("status", VP), ("tp", I32), ("rank", I32),
-                ("call_idx", I32), ("features", I32), ("timeout_ns", U64)]
+                ("call_idx", I32), ("features", I32), ("timeout_ns", U64), ("mode", I32), ("ag_call", I32),
+                ("ag_flags", VP)]
 
 
 class GemmArgs(C.Structure):
@@ -306,3 +307,19 @@ def host_alloc_mapped(nbytes: int):
 
 def host_free(addr: int):
     lib().nrt_host_free(C.c_void_p(addr))
+
+
+class AgPushArgs(C.Structure):
+    _fields_ = [("src", VP), ("src_stride", I32), ("slice_bytes", I32), ("row_bytes", I32), ("gather", VP * K_MAX_PEERS),
+                ("flags", VP * K_MAX_PEERS), ("epoch", VP), ("tp", I32), ("rank", I32), ("call", I32)]
+
+
+def ag_push(args: AgPushArgs, pdl=True):
+    L = lib()
+    if L.nrt_ag_push_args_size() != C.sizeof(AgPushArgs):
+        raise RuntimeError("AgPushArgs layout drift")
+    check(L.nrt_ag_push(C.byref(args), VP(_stream()), int(pdl)), "ag_push")
+
+
+def l2_flush(buf: torch.Tensor):
+    check(lib().nrt_l2_flush(VP(buf.data_ptr()), C.c_size_t(buf.numel() * buf.element_size()), VP(_stream())), "l2_flush")

@@ -83,6 +83,7 @@ class Fabric:
         f.epoch, f.status = self.epoch.data_ptr(), self.status.data_ptr()
         f.tp, f.rank, f.call_idx, f.features = self.tp, self.rank, call_idx, self.features
         f.timeout_ns = self.timeout_ns
+        f.mode, f.ag_call = 0, -1
         return f
 
     def xchg_args(self) -> K.XchgArgs:
