@@ -593,7 +593,12 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
 
 // ----------------------------------------------------------------------------- MoE router
 struct RouterArgs {
-  const __nv_bfloat16* xn;   // [16][hidden] normed activations
+  const __nv_bfloat16* xn;   // [16][hidden] normed activations (plain router) or null (fused form)
+  const __nv_bfloat16* x;    // fused form: residual rows [16][hidden]
+  const __nv_bfloat16* gamma;
+  float eps;
+  uint8_t* x8;               // fused form: e4m3 packet [16][hidden] + scales [16][hidden/128] for the expert GEMMs
+  float* xs;
   const float* w;            // [experts][hidden] fp32
   const float* bias;         // [experts] or null
   int hidden, experts, rows, top_k;
@@ -621,11 +626,76 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
   griddep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 2;
+  extern __shared__ uint4 router_smem[];
+  const __nv_bfloat16* xsrc = a.xn;
+  int xld = a.hidden;
+  if (a.x) {
+    // Fused RMSNorm: every CTA normalises all rows into shared memory (64 KiB read from L2); the CTA
+    // whose index equals a row also writes that row's e4m3 packet for the expert GEMMs.
+    __nv_bfloat16* xn_s = reinterpret_cast<__nv_bfloat16*>(router_smem);
+    const int per = a.hidden / 8;
+    for (int r = warp; r < kMaxRows; r += 8) {
+      const bool live = r < a.rows;
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)r * a.hidden);
+      float ss = 0.f;
+      if (live)
+        for (int i = lane; i < per; i += 32) {
+          const uint4 v = src[i];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); ss += f.x * f.x + f.y * f.y; }
+        }
+      ss = warp_sum(ss);
+      const float rs = rsqrtf(ss / (float)a.hidden + a.eps);
+      const bool packet = (int)blockIdx.x == r && a.x8 != nullptr;
+      for (int i = lane; i < per; i += 32) {
+        float o[8];
+        float am = 0.f;
+        if (live) {
+          const uint4 v = src[i];
+          const uint4 gv = reinterpret_cast<const uint4*>(a.gamma)[i];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]), g = __bfloat1622float2(gh[j]);
+            o[2 * j] = round_bf16(f.x * rs * g.x);
+            o[2 * j + 1] = round_bf16(f.y * rs * g.y);
+            am = fmaxf(am, fmaxf(fabsf(o[2 * j]), fabsf(o[2 * j + 1])));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = 0.f;
+        }
+        if (r < a.rows) {
+          uint4 w;
+          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) wh[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+          reinterpret_cast<uint4*>(xn_s + (size_t)r * a.hidden)[i] = w;
+        }
+        if (packet) {
+#pragma unroll
+          for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+          const float sc = live ? pow2_scale(am) : 1.f;
+          uint2 q;
+          uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) qb[j] = to_e4m3(o[j] / sc);
+          reinterpret_cast<uint2*>(a.x8 + (size_t)r * a.hidden)[i] = q;
+          if ((i & 15) == 0) a.xs[(size_t)r * (a.hidden / 128) + (i >> 4)] = sc;
+        }
+      }
+    }
+    __syncthreads();
+    xsrc = xn_s;
+  }
   float acc[2][kMaxRows];
 #pragma unroll
   for (int j = 0; j < 2; ++j)
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) acc[j][r] = 0.f;
+#pragma unroll 4
   for (int k = tid * 4; k < a.hidden; k += 1024) {
     float4 w0 = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k);
     float4 w1 = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * a.hidden + k)
@@ -633,7 +703,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) {
       if (r < a.rows) {
-        const uint2 xv = *reinterpret_cast<const uint2*>(a.xn + (size_t)r * a.hidden + k);
+        const uint2 xv = *reinterpret_cast<const uint2*>(xsrc + (size_t)r * xld + k);
         const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
         const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
         acc[0][r] += x01.x * w0.x + x01.y * w0.y + x23.x * w0.z + x23.y * w0.w;
@@ -645,8 +715,10 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
   for (int j = 0; j < 2; ++j)
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) {
-      const float v = warp_sum(acc[j][r]);
-      if (lane == 0) part[warp][j][r] = v;
+      if (r < a.rows) {                              // uniform across the CTA: dead rows cost no shuffles
+        const float v = warp_sum(acc[j][r]);
+        if (lane == 0) part[warp][j][r] = v;
+      }
     }
   __syncthreads();
   if (tid < 2 * kMaxRows) {
@@ -814,5 +886,16 @@ extern "C" int nrt_router_args_size() { return (int)sizeof(RouterArgs); }
 extern "C" int nrt_router(const void* args, void* stream, int pdl) {
   RouterArgs a;
   memcpy(&a, args, sizeof(a));
-  return launch_pdl(router_kernel, dim3((a.experts + 1) / 2), dim3(256), 0, S(stream), pdl != 0, a);
+  size_t smem = 0;
+  if (a.x) {
+    if ((a.experts + 1) / 2 < kMaxRows && a.x8) return -3;          // one CTA per packet row is required
+    smem = (size_t)kMaxRows * a.hidden * 2;
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      configured = true;
+    }
+    if (smem > 200 * 1024 || a.hidden % 256) return -3;
+  }
+  return launch_pdl(router_kernel, dim3((a.experts + 1) / 2), dim3(256), smem, S(stream), pdl != 0, a);
 }

@@ -70,7 +70,8 @@ class IndexArgs(C.Structure):
 
 
 class RouterArgs(C.Structure):
-    _fields_ = [("xn", VP), ("w", VP), ("bias", VP), ("hidden", I32), ("experts", I32), ("rows", I32),
+    _fields_ = [("xn", VP), ("x", VP), ("gamma", VP), ("eps", F32), ("x8", VP), ("xs", VP),
+                ("w", VP), ("bias", VP), ("hidden", I32), ("experts", I32), ("rows", I32),
                 ("top_k", I32), ("sigmoid", I32), ("normalize", I32), ("route_scale", F32),
                 ("scores", VP), ("ticket", VP), ("n_active", VP), ("active_ids", VP), ("probs", VP),
                 ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32)]

@@ -58,6 +58,9 @@ class TargetRuntime:
         # shape_tp > 1 with a single-rank fabric runs one rank's share of a tp-way model without peers
         # (kernel profiling of the per-rank shapes; the results are not a model output)
         self.tp, self.rank = (shape_tp, 0) if shape_tp else (fabric.tp, fabric.rank)
+        # the router can normalise its own input (one launch fewer per MoE layer); measured slower on B200
+        # (every CTA re-normalises all rows), so the separate RMSNorm kernel stays the default
+        self.fuse_router_norm = False
         s = spec
         H = s.hidden
         dev = device
@@ -251,7 +254,14 @@ class TargetRuntime:
             else:
                 rt = s.routing
                 r = K.RouterArgs()
-                r.xn, r.w, r.bias = self.xn.data_ptr(), d["router_w"].data_ptr(), d["router_b"].data_ptr()
+                r.w, r.bias = d["router_w"].data_ptr(), d["router_b"].data_ptr()
+                if self.fuse_router_norm and rt.expert_count >= 2 * PAD_ROWS:   # fused RMSNorm + packet + router
+                    r.xn, r.x, r.gamma, r.eps = None, self.x.data_ptr(), d["g_post"].data_ptr(), s.norm_eps
+                    r.x8, r.xs = self.x8.data_ptr(), self.xs.data_ptr()
+                    d["router_fused"] = True
+                else:
+                    r.xn = self.xn.data_ptr()
+                    d["router_fused"] = False
                 r.hidden, r.experts, r.rows, r.top_k = H, rt.expert_count, R, rt.top_k
                 r.sigmoid, r.normalize, r.route_scale = int(rt.score_func == "sigmoid"), int(rt.normalize_top_k), rt.route_scale
                 r.scores, r.ticket = self.scores.data_ptr(), self.ticket.data_ptr()
@@ -314,7 +324,8 @@ class TargetRuntime:
                 K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128,
                        K.pick_split(s.hidden // 128, dn["down"].k // 128), pdl=pdl)
             else:
-                K.prep_norm(self.x, d["g_post"], R, s.norm_eps, xn=self.xn, x8=self.x8, xs=self.xs, pdl=pdl)
+                if not d["router_fused"]:
+                    K.prep_norm(self.x, d["g_post"], R, s.norm_eps, xn=self.xn, x8=self.x8, xs=self.xs, pdl=pdl)
                 K.router(d["args_router"], pdl=pdl)
                 K.gemm(self.V_FP8_GU_ITEM, d["gate"].map, d["up"].map, self.map_x8, d["args_gu"], d["gate"].n // 128,
                        self.step_slots, pdl=pdl)
