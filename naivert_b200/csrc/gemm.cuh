@@ -39,7 +39,7 @@ constexpr int kMailboxSlabs = 4;
 constexpr int kMaxSplit = 4;                    // CTAs of one cluster that share an output tile (split K / split experts)
 
 enum GroupMode : int { kGroupNone = 0, kGroupItem = 1, kGroupLoop = 2 };
-enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4 };
+enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4, kEpiReturn = 5 };
 
 struct FabricArgs {
   uint64_t* mailbox[kMaxPeers];   // mailbox[p] = base of rank p's mailbox (peer-mapped); mailbox[rank] is local
@@ -81,6 +81,13 @@ struct GemmArgs {
   int ld_copy;                    // row stride of out_copy
   FabricArgs fab;
   uint32_t* status;
+  // expert-parallel prefill (group-item mode over a receive buffer)
+  const int* row_offsets;         // [items] first token row of each 16-row group (null: shared packet / slot * 16)
+  const int4* ep_meta;            // kEpiReturn: [rows] {owner rank, token, k, dispatch tag}
+  uint64_t* ep_combine[kMaxPeers];  // kEpiReturn: owner's combine slots [tokens*top_k][n_total/2] tagged words
+  int ep_top_k;
+  int ep_dispatch_call;           // tag call index the metadata rows must carry
+  int ep_return_call;             // tag call index of the returned words
 };
 
 template <bool FP8, bool DUAL>
@@ -208,7 +215,20 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           tma_load_3d(sa, &tmA0, &tail->full[st], kx, n0, z);
           if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
         }
-        const int brow = (GROUP == kGroupLoop) ? slot * kTok : 0;
+        const int brow = (GROUP == kGroupLoop) ? slot * kTok : ((GROUP == kGroupItem && p.row_offsets) ? p.row_offsets[slot] : 0);
+        if (GROUP == kGroupItem && p.fab.ag_call >= 0 && p.fab.tp > 1 && ag_seen < 0) {
+          // expert-parallel dispatch: rows of every source rank must have landed before the first token tile
+          const uint32_t tag = (*p.fab.epoch) * 1024u + (uint32_t)p.fab.ag_call + 1u;
+          bool all = true;
+          for (int s = 0; s < p.fab.tp && all; ++s) {
+            uint32_t v;
+            all = wait_tagged(p.fab.ag_flags + s, tag, v, globaltimer() + p.fab.timeout_ns, p.status, kSiteMailbox | 0x60 | s);
+          }
+          if (!all) break;
+          asm volatile("fence.acq_rel.sys;" ::: "memory");
+          asm volatile("fence.proxy.async;" ::: "memory");
+          ag_seen = 0;
+        }
         if (GROUP == kGroupNone && p.fab.ag_call >= 0 && p.fab.tp > 1) {
           // all-gather -> GEMM: the K slice of source rank `src` was pushed into local memory by that rank;
           // wait for its flag (acquire), then order the generic-proxy writes before the TMA read
@@ -279,14 +299,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
       for (int r = 0; r < kTok; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
       if (FP8) {
-        const float* as = p.a_scale + (size_t)(GROUP == kGroupLoop ? slot : 0) * kTok * kb_total + kb_first;
+        const size_t in_row = GROUP == kGroupLoop ? (size_t)slot * kTok
+                                                   : ((GROUP == kGroupItem && p.row_offsets) ? (size_t)p.row_offsets[slot] : 0);
+        const float* as = p.a_scale + in_row * kb_total + kb_first;
         const float* ws0 = p.w_scale0 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first;
         const float* ws1 = DUAL ? p.w_scale1 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first : nullptr;
         for (int kb = 0; kb < kb_count; ++kb, ++u) {
           const int buf = u % Cfg::kAccBufs;
           // scales are fetched before the wait so their latency hides behind the MMA of this block
           float sc[kTok];
-          const bool gathered = GROUP == kGroupNone && p.fab.ag_call >= 0 && p.fab.tp > 1;
+          const bool gathered = GROUP != kGroupLoop && p.fab.ag_call >= 0 && p.fab.tp > 1;
           if (!gathered) {
 #pragma unroll
             for (int r = 0; r < kTok; ++r) sc[r] = __ldg(as + r * kb_total + kb);
@@ -375,7 +397,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           if (lane == 0) tail->red[quad][r] = m;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const size_t qrow = (size_t)(GROUP == kGroupNone ? 0 : g_first) * kTok;
+        const size_t qrow = GROUP == kGroupNone ? 0 : (p.row_offsets ? (size_t)p.row_offsets[g_first] : (size_t)g_first * kTok);
 #pragma unroll
         for (int r = 0; r < kTok; ++r) {
           const float am = fmaxf(fmaxf(tail->red[0][r], tail->red[1][r]), fmaxf(tail->red[2][r], tail->red[3][r]));
@@ -383,6 +405,24 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           const __nv_fp8_e4m3 q(y[r] / s);
           p.out_q[(qrow + r) * p.n_total + n] = *reinterpret_cast<const uint8_t*>(&q);
           if (row == 0) p.out_qscale[(qrow + r) * nt_count + n_tile] = s;
+        }
+      }
+    } else if (EPI == kEpiReturn) {
+      // Expert outputs go straight back to the token owner: bf16 pairs of adjacent features as tagged
+      // words into slot (token, k) of the owner's combine buffer (peer memory).
+      if (n_groups > 0) {
+        const uint32_t dtag = (*p.fab.epoch) * 1024u + (uint32_t)p.ep_dispatch_call + 1u;
+        const uint32_t rtag = (*p.fab.epoch) * 1024u + (uint32_t)p.ep_return_call + 1u;
+        const size_t row0 = p.row_offsets ? (size_t)p.row_offsets[g_first] : 0;
+        const int words = p.n_total / 2;
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) {
+          const int4 m = p.ep_meta[row0 + r];
+          const float other = __shfl_down_sync(0xffffffffu, mix0[r], 1);
+          if ((uint32_t)m.w == dtag && (lane & 1) == 0 && n + 1 < p.n_total + 1) {
+            uint64_t* dst = p.ep_combine[m.x] + ((size_t)(m.y * p.ep_top_k + m.z)) * words + (n >> 1);
+            st_tagged(dst, rtag, pack_bf16x2(mix0[r], other));
+          }
         }
       }
     } else if (EPI == kEpiAllReduce) {

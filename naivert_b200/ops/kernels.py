@@ -22,7 +22,7 @@ K_ROW_PAIRS = 8
 K_MAILBOX_SLABS = 4
 
 # GEMM variants: fp8 | dual<<1 | epi<<2 | group<<5
-EPI_STORE_F32, EPI_STORE_BF16, EPI_SILU_QUANT, EPI_ALLREDUCE, EPI_SILU_BF16 = 0, 1, 2, 3, 4
+EPI_STORE_F32, EPI_STORE_BF16, EPI_SILU_QUANT, EPI_ALLREDUCE, EPI_SILU_BF16, EPI_RETURN = 0, 1, 2, 3, 4, 5
 GROUP_NONE, GROUP_ITEM, GROUP_LOOP = 0, 1, 2
 
 
@@ -42,7 +42,9 @@ class GemmArgs(C.Structure):
                 ("w_scale0", VP), ("w_scale1", VP), ("a_scale", VP),
                 ("out_f32", VP), ("out_bf16", VP), ("ld_out", I32), ("out_scale", F32),
                 ("out_q", VP), ("out_qscale", VP), ("resid", VP), ("out_copy", VP), ("ld_copy", I32),
-                ("fab", FabricArgs), ("status", VP)]
+                ("fab", FabricArgs), ("status", VP),
+                ("row_offsets", VP), ("ep_meta", VP), ("ep_combine", VP * K_MAX_PEERS), ("ep_top_k", I32),
+                ("ep_dispatch_call", I32), ("ep_return_call", I32)]
 
 
 class AttnPostArgs(C.Structure):
@@ -324,3 +326,35 @@ def ag_push(args: AgPushArgs, pdl=True):
 
 def l2_flush(buf: torch.Tensor):
     check(lib().nrt_l2_flush(VP(buf.data_ptr()), C.c_size_t(buf.numel() * buf.element_size()), VP(_stream())), "l2_flush")
+
+
+class EpArgs(C.Structure):
+    _fields_ = [("topk_ids", VP), ("topk_p", VP), ("tokens", I32), ("top_k", I32), ("experts", I32), ("experts_local", I32),
+                ("hidden", I32), ("slot_of", VP), ("n_items", VP), ("item_expert", VP), ("item_row", VP), ("seg_rows", VP),
+                ("max_items", I32), ("cap_rows", I32), ("x", VP), ("gamma", VP), ("eps", F32),
+                ("recv8", VP * K_MAX_PEERS), ("recvs", VP * K_MAX_PEERS), ("meta", VP * K_MAX_PEERS), ("flags", VP * K_MAX_PEERS),
+                ("ticket", VP), ("call", I32), ("x_args", XchgArgs)]
+
+
+class EpCombineArgs(C.Structure):
+    _fields_ = [("slots", VP), ("topk_p", VP), ("resid", VP), ("out", VP), ("epoch", VP), ("status", VP),
+                ("tokens", I32), ("top_k", I32), ("hidden", I32), ("call", I32), ("timeout_ns", U64)]
+
+
+def _ep_lib():
+    L = lib()
+    if L.nrt_ep_args_size() != C.sizeof(EpArgs) or L.nrt_ep_combine_args_size() != C.sizeof(EpCombineArgs):
+        raise RuntimeError("EP argument layout drift")
+    return L
+
+
+def ep_count(args: EpArgs, pdl=True):
+    check(_ep_lib().nrt_ep_count(C.byref(args), VP(_stream()), int(pdl)), "ep_count")
+
+
+def ep_dispatch(args: EpArgs, pdl=True):
+    check(_ep_lib().nrt_ep_dispatch(C.byref(args), VP(_stream()), int(pdl)), "ep_dispatch")
+
+
+def ep_combine(args: EpCombineArgs, pdl=True):
+    check(_ep_lib().nrt_ep_combine(C.byref(args), VP(_stream()), int(pdl)), "ep_combine")

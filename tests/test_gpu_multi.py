@@ -29,3 +29,24 @@ def test_tensor_parallel_engine(n):
     assert r["residual_identical"] and r["lockstep"] and r["deterministic"] and r["spec_equals_greedy"], r
     assert r["verify_mean_rel"] < 0.1, r
     assert r["real_sampling_tokens"] == 64
+
+
+def _run_worker(n, script):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    path = os.path.join(os.path.dirname(__file__), script)
+    cmd = [sys.executable, path] if n == 1 else [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                                                 "--master-addr", "127.0.0.1", "--master-port", "29519", path]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-4000:]
+    return json.loads(lines[-1][7:])
+
+
+@pytest.mark.parametrize("n", [1, 2])
+def test_expert_parallel_all_to_all(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    r = _run_worker(n, "mp_ep_worker.py")
+    assert r["status"] == 0 and r["repeat_identical"], r
+    assert r.get("worst_err", r["max_rel_err"]) < 0.02, r
+    assert r.get("total_rows", r["rows"]) == 96 * 4 * n
