@@ -899,3 +899,56 @@ extern "C" int nrt_router(const void* args, void* stream, int pdl) {
   }
   return launch_pdl(router_kernel, dim3((a.experts + 1) / 2), dim3(256), smem, S(stream), pdl != 0, a);
 }
+
+// ============================================================================= allocation-free routing
+#include "no_alloc.h"
+
+#include <mutex>
+
+// Scratch of nrt_router_route_noalloc: score matrix followed by the arrival counter.  In host code this
+// name is only a handle for cudaGetSymbolAddress; the device address is resolved once per device.
+static __device__ __align__(256) unsigned char g_noalloc_router_scratch[NRT_NOALLOC_SCRATCH_BYTES];
+
+extern "C" int nrt_router_route_noalloc(const void* xn, const float* w, const float* bias, int hidden, int experts, int rows,
+                                        int top_k, int sigmoid, int normalize, float route_scale, int* n_active,
+                                        int* active_ids, float* probs, int* topk_ids, float* topk_p, int max_slots,
+                                        void* stream) {
+  if (!xn || !w || !n_active || !active_ids || !probs || !topk_ids || !topk_p) return NRT_NOALLOC_E_ARG;
+  if (rows < 1 || top_k < 1 || top_k > experts || max_slots < 1 || hidden < 4 || hidden % 4) return NRT_NOALLOC_E_ARG;
+  if (rows > NRT_NOALLOC_MAX_ROWS || experts > NRT_NOALLOC_MAX_EXPERTS || top_k > 32) return NRT_NOALLOC_E_LIMIT;
+  static std::mutex mu;
+  static void* scratch_of_device[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return NRT_NOALLOC_E_SETUP;
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_router_scratch);       // with `dev` current
+      if (e != cudaSuccess || !p) return e != cudaSuccess ? (int)e : NRT_NOALLOC_E_SETUP;
+      scratch_of_device[dev] = p;
+    }
+    base = scratch_of_device[dev];
+  }
+  float* scores = reinterpret_cast<float*>(base);
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(reinterpret_cast<unsigned char*>(base) +
+                                                         NRT_NOALLOC_MAX_ROWS * NRT_NOALLOC_MAX_EXPERTS * 4);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), s);           // the counter must start at zero
+  if (e != cudaSuccess) return (int)e;
+  RouterArgs a;
+  memset(&a, 0, sizeof(a));
+  a.xn = reinterpret_cast<const __nv_bfloat16*>(xn);
+  a.w = w;
+  a.bias = bias;
+  a.hidden = hidden; a.experts = experts; a.rows = rows; a.top_k = top_k;
+  a.sigmoid = sigmoid; a.normalize = normalize; a.route_scale = route_scale;
+  a.scores = scores; a.ticket = ticket;
+  a.n_active = n_active; a.active_ids = active_ids; a.probs = probs;
+  a.topk_ids = topk_ids; a.topk_p = topk_p; a.max_slots = max_slots;
+  router_kernel<<<dim3((experts + 1) / 2), dim3(256), 0, s>>>(a);
+  return (int)cudaGetLastError();
+}
