@@ -76,7 +76,7 @@ def main() -> int:
     ap.add_argument("--model", default="naive-n0.5")
     ap.add_argument("--shape-tp", type=int, default=0,
                     help="diagnostic: run ONE rank's share of a tp-way model on one GPU without peers (not a result)")
-    ap.add_argument("--no-pdl", action="store_true", help="diagnostic: plain stream-ordered launches")
+    ap.add_argument("--pdl", action="store_true", help="chain kernels with programmatic dependent launch (default: plain stream order, measured faster)")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -111,7 +111,7 @@ def main() -> int:
     capacity = a.prompt + total_rounds * 8 + 64
     capacity = -(-capacity // 128) * 128
     t_build = time.perf_counter()
-    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=not a.no_pdl, shape_tp=a.shape_tp)
+    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=a.pdl, shape_tp=a.shape_tp)
     build_s = time.perf_counter() - t_build
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
 

@@ -87,13 +87,31 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
     }
   }
   __syncthreads();
-  // destination row of each local (token, k): segment base + rows of lower ranks + stable local rank
+  // destination row of each local (token, k): segment base + rows of lower ranks + stable local rank.
+  // `hist` becomes the running count per expert; pairs are ranked in index order: chunks of 1024 in order,
+  // warps of a chunk in order, lanes of a warp by their position among equal experts.
   for (int e = threadIdx.x; e < a.experts; e += 1024) {
     int pos = seg_base[e];
     for (int s = 0; s < rank; ++s) pos += (int)xv[s * a.experts + e];
-    if (hist[e] == 0u) continue;
-    for (int i = 0; i < n; ++i)
-      if (a.topk_ids[i] == e) a.slot_of[i] = pos++;
+    hist[e] = (unsigned)pos;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c0 = 0; c0 < n; c0 += 1024) {
+    const int i = c0 + threadIdx.x;
+    const int e = i < n ? a.topk_ids[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int below = __popc(peers & ((1u << lane) - 1u));
+    const bool lead = below == 0;
+    for (int w = 0; w < 32; ++w) {
+      if (warp == w && e >= 0) {
+        unsigned base = 0;
+        if (lead) { base = hist[e]; hist[e] = base + __popc(peers); }
+        base = __shfl_sync(peers, base, __ffs(peers) - 1);
+        a.slot_of[i] = (int)base + below;
+      }
+      __syncthreads();
+    }
   }
   // work list of my own experts
   if (threadIdx.x == 0) {

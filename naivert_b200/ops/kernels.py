@@ -148,11 +148,15 @@ def act_tmap(x: torch.Tensor) -> TensorMap:
     return TensorMap(x, (k, r), (x.stride(0) * es,), (128 // es, K_TOK), 0 if es == 1 else 1)
 
 
+_SPLIT_MIN_KB = int(__import__("os").environ.get("NAIVERT_SPLIT_MIN_KB", "1"))
+
+
 def pick_split(n_tiles: int, k_blocks: int, max_ctas: int = 160) -> int:
-    """CTAs per output tile (one cluster): the largest of 4, 2, 1 that divides the K blocks and
-    keeps the grid within about one wave of the 148 SMs."""
+    """CTAs per output tile (one cluster): the largest of 4, 2, 1 that divides the K blocks, leaves
+    every CTA at least ``NAIVERT_SPLIT_MIN_KB`` K blocks and keeps the grid within about one wave of
+    the 148 SMs."""
     for s in (4, 2):
-        if k_blocks % s == 0 and n_tiles * s <= max_ctas:
+        if k_blocks % s == 0 and n_tiles * s <= max_ctas and k_blocks // s >= _SPLIT_MIN_KB:
             return s
     return 1
 
