@@ -77,6 +77,7 @@ def main() -> int:
     ap.add_argument("--shape-tp", type=int, default=0,
                     help="diagnostic: run ONE rank's share of a tp-way model on one GPU without peers (not a result)")
     ap.add_argument("--pdl", action="store_true", help="chain kernels with programmatic dependent launch (default: plain stream order, measured faster)")
+    ap.add_argument("--device-chain", action="store_true", help="the round graph relaunches itself from the device")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -111,7 +112,8 @@ def main() -> int:
     capacity = a.prompt + total_rounds * 8 + 64
     capacity = -(-capacity // 128) * 128
     t_build = time.perf_counter()
-    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=a.pdl, shape_tp=a.shape_tp)
+    eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=a.pdl, shape_tp=a.shape_tp,
+                       device_chain=a.device_chain)
     build_s = time.perf_counter() - t_build
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
 
@@ -130,25 +132,42 @@ def main() -> int:
     eng.open(prompt, max_tokens, sp, use_graphs=not a.no_graph)
     prefill_s = time.perf_counter() - t0
     r = eng.round
-    r.launch(a.warmup)
-    barrier()
-    tok0 = int(r.t.ctrl[6])
     clocks = ClockSampler(local) if rank == 0 else None
-    if clocks:
-        clocks.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    with torch.cuda.stream(r.stream):
-        ev0.record()
-    r.launch(a.steps)
-    with torch.cuda.stream(r.stream):
-        ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
+    if a.device_chain:
+        # the chain runs by itself after one host launch: time K rounds from the device timestamps of their
+        # ring records (globaltimer at each round's tail), after W warm-up rounds
+        barrier()
+        if clocks:
+            clocks.start()
+        r.launch(1)
+        recs = [r.wait_round(120.0) for _ in range(a.warmup + a.steps)]
+        r.cancel()
+        while recs[-1].stop_reason is None:
+            recs.append(r.wait_round(120.0))
+        barrier()
+        ms = (recs[a.warmup + a.steps - 1].t_end_ns - recs[a.warmup - 1].t_end_ns) * 1e-6
+        tok0 = int(r.t.ctrl[6]) - sum(len(x.tokens) for x in recs[a.warmup:a.warmup + a.steps])
+        timed_tokens = sum(len(x.tokens) for x in recs[a.warmup:a.warmup + a.steps])
+    else:
+        r.launch(a.warmup)
+        barrier()
+        tok0 = int(r.t.ctrl[6])
+        if clocks:
+            clocks.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(r.stream):
+            ev0.record()
+        r.launch(a.steps)
+        with torch.cuda.stream(r.stream):
+            ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        timed_tokens = None
     if clocks:
         clocks.stop_flag.set()
         clocks.join()
-    tokens = int(r.t.ctrl[6]) - tok0
+    tokens = timed_tokens if timed_tokens is not None else int(r.t.ctrl[6]) - tok0
     eng.fabric.check()
     stopped = int(r.t.ctrl[4])
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -190,7 +209,9 @@ def main() -> int:
                        "parallelism": f"tp{world}", "prompt_tokens": a.prompt, "temperature": 0.4, "top_p": 0.95,
                        "forced_accept_p": 0.7, "tokens_per_round": round(tokens / a.steps, 3),
                        "l2": "per-round weight traffic (GBs) exceeds the 126 MB L2; no explicit flush",
-                       "timing": "CUDA events on the round stream around K graph replays, max over ranks",
+                       "timing": ("device globaltimer stamps of the ring records of K self-relaunched rounds, max over ranks"
+                                  if a.device_chain else "CUDA events on the round stream around K graph replays, max over ranks"),
+                       "host_graph_launches": r.host_launches,
                        "ignore_eos": True, "stopped_early": bool(stopped)},
             "clocks": clocks.summary() if clocks else None,
             "e2e": {"value": round(e2e_rate, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 64,

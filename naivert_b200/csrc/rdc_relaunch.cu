@@ -1,0 +1,30 @@
+// Device-side continuation of the speculative round: the last kernel of the round's graph launches the
+// same executable graph again (tail launch) unless the control block says the chain stopped, so the host
+// launches one graph per request and afterwards only polls the pinned ring.
+//
+// Backpressure: the host publishes the index of the last ring record it consumed; the chain pauses
+// (does not relaunch) when it is a ring length ahead, and the host restarts it with an ordinary launch.
+// Reference counterpart: naivert/entry/dspark_tail_entry.cu:16-23
+// (cudaGraphLaunch(cudaGetCurrentGraphExec(), cudaStreamGraphTailLaunch)).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+// ctrl[4] stopped, ctrl[5] reason, ctrl[8] round counter, ctrl[12] relaunch failures, ctrl[13] paused
+__global__ void relaunch_kernel(int* ctrl, const volatile int* host_consumed, int ring_size) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (ctrl[4]) return;
+  const int ahead = ctrl[8] - *host_consumed;
+  if (ahead >= ring_size - 8) { ctrl[13] = 1; return; }          // let the host catch up
+  ctrl[13] = 0;
+  const cudaError_t e = cudaGraphLaunch(cudaGetCurrentGraphExec(), cudaStreamGraphTailLaunch);
+  if (e != cudaSuccess) { ctrl[12] += 1; ctrl[4] = 1; ctrl[5] = 6; }   // fail closed: chain launch failed
+}
+
+}  // namespace
+
+extern "C" int nrt_relaunch(int* ctrl, const int* host_consumed_dev, int ring_size, void* stream) {
+  relaunch_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ctrl, host_consumed_dev, ring_size);
+  return (int)cudaGetLastError();
+}

@@ -362,3 +362,46 @@ def ep_dispatch(args: EpArgs, pdl=True):
 
 def ep_combine(args: EpCombineArgs, pdl=True):
     check(_ep_lib().nrt_ep_combine(C.byref(args), VP(_stream()), int(pdl)), "ep_combine")
+
+
+# ----------------------------------------------------------------------------- native CUDA graphs
+class NativeGraph:
+    """A captured CUDA graph instantiated through the runtime API (optionally for device-side launch)."""
+
+    def __init__(self):
+        self.graph, self.exec = C.c_void_p(), C.c_void_p()
+        self.counts = (C.c_int * 4)()
+
+    def begin(self, stream: int) -> None:
+        check_nc(lib().nrt_graph_begin(VP(stream)), "cudaStreamBeginCapture")
+
+    def end(self, stream: int) -> None:
+        check_nc(lib().nrt_graph_end(VP(stream), C.byref(self.graph)), "cudaStreamEndCapture")
+        lib().nrt_graph_inspect(self.graph, self.counts)
+
+    def instantiate(self, device_launch: bool, stream: int) -> None:
+        check_nc(lib().nrt_graph_instantiate(self.graph, int(device_launch), C.byref(self.exec)), "cudaGraphInstantiate")
+        if device_launch:
+            check_nc(lib().nrt_graph_upload(self.exec, VP(stream)), "cudaGraphUpload")
+
+    def launch(self, stream: int) -> None:
+        check_nc(lib().nrt_graph_launch(self.exec, VP(stream)), "cudaGraphLaunch")
+
+    @property
+    def info(self) -> dict:
+        return {"nodes": self.counts[0], "kernel_nodes": self.counts[1], "edges": self.counts[2],
+                "programmatic_edges": self.counts[3]}
+
+    def destroy(self) -> None:
+        lib().nrt_graph_destroy(self.graph, self.exec)
+        self.graph, self.exec = C.c_void_p(), C.c_void_p()
+
+
+def check_nc(code: int, what: str) -> None:
+    """Like ``check`` but does not count a kernel launch."""
+    if code != 0:
+        raise RuntimeError(f"{what} failed with CUDA error {code}")
+
+
+def relaunch(ctrl, consumed_dev_ptr: int, ring_size: int):
+    check(lib().nrt_relaunch(VP(ptr(ctrl)), VP(consumed_dev_ptr), ring_size, VP(_stream())), "relaunch")

@@ -54,7 +54,7 @@ class Engine:
     def build(cls, spec: ModelSpec, rank: int = 0, tp: int = 1, group=None, capacity: int = 16384, seed: int = 0,
               target_ckpt: Optional[str] = None, draft_ckpt: Optional[str] = None, device=None,
               weights: Optional[dict] = None, draft_weights: Optional[dict] = None, pdl: Optional[bool] = None,
-              shape_tp: int = 0) -> "Engine":
+              shape_tp: int = 0, device_chain: Optional[bool] = None) -> "Engine":
         device = device or torch.device("cuda", torch.cuda.current_device())
         if pdl is None:
             # Programmatic dependent launch is available on every kernel (NAIVERT_PDL=1).  Measured on
@@ -87,7 +87,10 @@ class Engine:
         target = TargetRuntime(spec, weights, fabric, rows=spec.draft.rows, capacity=capacity, device=device, pdl=pdl,
                                shape_tp=shape_tp)
         del weights
-        rnd = SpeculativeRound(spec, target, draft_weights, capacity, pdl=pdl)
+        if device_chain is None:
+            import os
+            device_chain = os.environ.get("NAIVERT_DEVICE_CHAIN", "0") == "1"
+        rnd = SpeculativeRound(spec, target, draft_weights, capacity, pdl=pdl, device_chain=device_chain)
         return cls(spec, fabric, target, rnd)
 
     # ------------------------------------------------------------------ one request

@@ -55,6 +55,8 @@ class HostRing:
         self.cancel_host = self.host + size * C.sizeof(K.RingRecord)
         self.cancel_dev = self.dev + size * C.sizeof(K.RingRecord)
         self.cancel = C.c_int.from_address(self.cancel_host)
+        self.consumed = C.c_int.from_address(self.cancel_host + 16)      # rounds the host has read (device chain backpressure)
+        self.consumed_dev = self.cancel_dev + 16
 
     def clear(self):
         C.memset(self.host, 0, self.size * C.sizeof(K.RingRecord) + 64)
@@ -73,7 +75,8 @@ class HostRing:
 
 
 class SpeculativeRound:
-    def __init__(self, spec: ModelSpec, target: TargetRuntime, draft_weights: dict, capacity: int, pdl: bool = True):
+    def __init__(self, spec: ModelSpec, target: TargetRuntime, draft_weights: dict, capacity: int, pdl: bool = True,
+                 device_chain: bool = False):
         if target.rows != spec.draft.rows:
             raise RuntimeContractError("the verify runtime must run block_size + 1 rows")
         self.spec, self.t, self.fab, self.pdl = spec, target, target.fab, pdl
@@ -97,6 +100,12 @@ class SpeculativeRound:
         self.n_prompt = 0
         self.use_penalties = False
         self.kernels_per_round = 0
+        # device chain: the round graph is instantiated for device launch and relaunches itself from its
+        # last kernel; the host launches once per request and polls the ring
+        self.device_chain = device_chain
+        self.native_graph: Optional[K.NativeGraph] = None
+        self.chain_started = False
+        self.host_launches = 0
         self._build_args()
         self.stream = torch.cuda.Stream(device=dev)
 
@@ -216,6 +225,9 @@ class SpeculativeRound:
         self.next_round = 0
         self.launched = 0
         self.use_graphs = use_graphs
+        self.chain_started = False
+        self.host_launches = 0
+        self.ring.consumed.value = 0
 
     def _capture_prefill(self):
         saved = self.t.ctrl.clone()
@@ -230,7 +242,10 @@ class SpeculativeRound:
         saved_ctrl, saved_ids, saved_feats = self.t.ctrl.clone(), self.block_ids.clone(), self.t.feats.clone()
         self.ring.cancel.value = 1                       # the warm-up round commits nothing
         before = K.LAUNCHES["count"]
-        self.graph = self._capture(self.phases)
+        if self.device_chain:
+            self.graph = self._capture_native()
+        else:
+            self.graph = self._capture(self.phases)
         self.kernels_per_round = (K.LAUNCHES["count"] - before) // 2     # warm-up + capture
         self.stream.synchronize()
         self.ring.cancel.value = 0
@@ -241,13 +256,41 @@ class SpeculativeRound:
         self.fab.status.zero_()
         torch.cuda.synchronize()
 
+    def _capture_native(self):
+        """Capture through the runtime API, append the relaunch kernel, instantiate for device launch."""
+        torch.cuda.synchronize()
+        with torch.cuda.stream(self.stream):
+            self.phases()                                   # warm-up (a cancelled round)
+        self.stream.synchronize()
+        g = K.NativeGraph()
+        sid = self.stream.cuda_stream
+        with torch.cuda.stream(self.stream):
+            g.begin(sid)
+            try:
+                self.phases()
+                K.relaunch(self.t.ctrl, self.ring.consumed_dev, self.ring.size)
+            finally:
+                g.end(sid)
+        g.instantiate(True, sid)
+        self.stream.synchronize()
+        self.native_graph = g
+        return g
+
     def _count_prompt(self, n: int):
         toks = self.prompt_dev[:n].long() - self.vbase
         toks = toks[(toks >= 0) & (toks < self.vlocal)]
         self.counts.zero_()
         self.counts.index_add_(0, toks, torch.ones_like(toks, dtype=torch.int16))
 
-    def launch(self, n: int = 1) -> None:
+    def launch(self, n: int = 1, force: bool = False) -> None:
+        """Enqueue ``n`` rounds.  With the device chain one host launch starts a self-relaunching chain;
+        further calls are no-ops unless ``force`` (a stalled or finished chain is restarted by the host)."""
+        if self.device_chain and self.use_graphs:
+            if not self.chain_started or force:
+                self.native_graph.launch(self.stream.cuda_stream)
+                self.chain_started = True
+                self.host_launches += 1
+            return
         with torch.cuda.stream(self.stream):
             for _ in range(n):
                 if self.use_graphs:
@@ -255,19 +298,25 @@ class SpeculativeRound:
                 else:
                     self.phases()
         self.launched += n
+        self.host_launches += n
 
     def poll(self) -> Optional[RoundRecord]:
         rec = self.ring.poll(self.next_round)
         if rec is not None:
             self.next_round += 1
+            self.ring.consumed.value = self.next_round
         return rec
 
     def wait_round(self, timeout_s: float = 120.0) -> RoundRecord:
         t0 = time.monotonic()
+        nudged = False
         while True:
             rec = self.poll()
             if rec is not None:
                 return rec
+            if self.device_chain and self.use_graphs and not nudged and time.monotonic() - t0 > 0.5:
+                self.launch(force=True)                      # the chain paused for backpressure: restart it
+                nudged = True
             if time.monotonic() - t0 > timeout_s:
                 raise RuntimeError(f"round {self.next_round} did not publish within {timeout_s}s")
             time.sleep(50e-6)

@@ -140,7 +140,7 @@ class Session:
                 if rec.stop_reason is not None:
                     self.done, self.stop_reason = True, rec.stop_reason
         if self._launched:
-            r.launch(1)                                   # one more pass completes the draft context of the last rows
+            r.launch(1, force=True)                       # one more pass completes the draft context of the last rows
         r.stream.synchronize()
         eng.fabric.check()
         stats = {"prefill_path": self.prefill_info.get("path"), "initialize_ms": self.prefill_info.get("init_ms"),

@@ -136,3 +136,24 @@ def test_session_prefix_reuse_is_bitwise_identical():
     _, out4_cold, _ = run(cold, branch, None)
     assert out4 == out4_cold
     assert se.store.bytes() > 0 and any("#" in k for k in se.store.entries) or len(se.store.entries) >= 1
+
+
+def test_device_chain_matches_host_launched_rounds():
+    """The self-relaunching graph (one host launch per request) commits exactly the tokens of host-launched rounds."""
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    from naivert_b200.models.spec import SamplingParams
+    from naivert_b200.runtime.engine import Engine
+    spec = small_w8a8_spec(2)
+    host = Engine.build(spec, capacity=1024, seed=0)
+    chain = Engine.build(spec, capacity=1024, seed=0, device_chain=True)
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, spec.vocab - 16, (41,), generator=g)
+    sp = SamplingParams(temperature=0.6, seed=3)
+    a = host.generate(prompt, 200, sp)
+    b = chain.generate(prompt, 200, sp)
+    assert a.tokens == b.tokens and b.stop_reason == "output_limit"
+    assert chain.round.host_launches == 1 and host.round.host_launches > 10
+    info = chain.round.native_graph.info
+    assert info["kernel_nodes"] == info["nodes"] and info["kernel_nodes"] > 50
+    c = chain.generate(prompt, 64, sp)                      # a second request restarts the chain
+    assert c.tokens == a.tokens[:64]
