@@ -591,6 +591,143 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
   }
 }
 
+// ----------------------------------------------------------------------------- exact top-k, many CTAs per row
+// Long contexts (hundreds of thousands of keys): `gridDim.x` CTAs share one row.  Four histogram launches
+// fix the 32-bit threshold one byte at a time (per-CTA shared histograms merged with one global add per
+// non-empty bin; the last CTA of a row picks the bin), one launch counts winners per CTA segment and one
+// writes them in ascending position order at offsets derived from the per-segment counts.  Same result as
+// topk_rows_kernel: value descending, ties to the lowest index, emitted in ascending index order.
+struct TopkGridState {          // per row
+  unsigned int prefix, need, ticket, pad;
+  unsigned int hist[256];
+  unsigned int seg_gt[64], seg_eq[64];
+};
+
+__global__ void __launch_bounds__(1024) topk_grid_hist_kernel(const float* __restrict__ logits, int ld, const int* pos0,
+                                                               int rows, int top_k, TopkGridState* st, int pass) {
+  __shared__ unsigned int sh[256];
+  __shared__ bool s_last;
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.y;
+  const int n = *pos0 + r + 1;
+  if (r >= rows || n <= top_k) return;
+  TopkGridState& S = st[r];
+  const int shift = 24 - 8 * pass;
+  const unsigned int mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+  const unsigned int prefix = pass == 0 ? 0u : S.prefix;
+  if (threadIdx.x < 256) sh[threadIdx.x] = 0u;
+  __syncthreads();
+  const int seg = (n + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * seg, hi = min(n, lo + seg);
+  const float* row = logits + (size_t)r * ld;
+  for (int i = lo + threadIdx.x; i < hi; i += 1024) {
+    const unsigned int k = order_key(row[i]);
+    if ((k & mask) == prefix) atomicAdd(&sh[(k >> shift) & 255u], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x < 256 && sh[threadIdx.x]) atomicAdd(&S.hist[threadIdx.x], sh[threadIdx.x]);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(&S.ticket, 1u);
+    s_last = t == gridDim.x - 1;
+    if (s_last) S.ticket = 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) {
+    unsigned int need = pass == 0 ? (unsigned)top_k : S.need, acc = 0;
+    int b = 255;
+    for (; b > 0; --b) {
+      const unsigned int h = *reinterpret_cast<volatile unsigned int*>(&S.hist[b]);
+      if (acc + h >= need) break;
+      acc += h;
+    }
+    S.prefix = prefix | ((unsigned int)b << shift);
+    S.need = need - acc;
+  }
+  __syncthreads();
+  if (threadIdx.x < 256) S.hist[threadIdx.x] = 0u;
+}
+
+__global__ void __launch_bounds__(1024) topk_grid_count_kernel(const float* __restrict__ logits, int ld, const int* pos0,
+                                                                int rows, int top_k, TopkGridState* st) {
+  __shared__ unsigned int s_gt, s_eq;
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.y;
+  const int n = *pos0 + r + 1;
+  if (r >= rows || n <= top_k) return;
+  TopkGridState& S = st[r];
+  if (threadIdx.x == 0) { s_gt = 0u; s_eq = 0u; }
+  __syncthreads();
+  const unsigned int thr = S.prefix;
+  const int seg = (n + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * seg, hi = min(n, lo + seg);
+  const float* row = logits + (size_t)r * ld;
+  unsigned int gt = 0, eq = 0;
+  for (int i = lo + threadIdx.x; i < hi; i += 1024) {
+    const unsigned int k = order_key(row[i]);
+    gt += k > thr;
+    eq += k == thr;
+  }
+  if (gt) atomicAdd(&s_gt, gt);
+  if (eq) atomicAdd(&s_eq, eq);
+  __syncthreads();
+  if (threadIdx.x == 0) { S.seg_gt[blockIdx.x] = s_gt; S.seg_eq[blockIdx.x] = s_eq; }
+}
+
+__global__ void __launch_bounds__(1024) topk_grid_write_kernel(const float* __restrict__ logits, int ld, const int* pos0,
+                                                                int rows, int top_k, TopkGridState* st, int* __restrict__ sel) {
+  __shared__ uint32_t wsum_gt[32], wsum_eq[32];
+  __shared__ uint32_t base_out, base_eq;
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.y;
+  const int n = *pos0 + r + 1;
+  if (r >= rows || n <= top_k) return;
+  const TopkGridState& S = st[r];
+  const unsigned int thr = S.prefix, need = S.need;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    unsigned int g = 0, e = 0;
+    for (int c = 0; c < (int)blockIdx.x; ++c) { g += S.seg_gt[c]; e += S.seg_eq[c]; }
+    base_eq = e;
+    base_out = g + min(e, need);
+  }
+  __syncthreads();
+  const int seg = (n + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * seg, hi = min(n, lo + seg);
+  const float* row = logits + (size_t)r * ld;
+  for (int c0 = lo; c0 < hi; c0 += 1024) {
+    const int i = c0 + tid;
+    const unsigned int k = i < hi ? order_key(row[i]) : 0u;
+    const bool gt = i < hi && k > thr;
+    const bool eq = i < hi && k == thr;
+    const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) { wsum_gt[warp] = __popc(bg); wsum_eq[warp] = __popc(be); }
+    __syncthreads();
+    uint32_t eq_before = base_eq, gt_before = 0;
+    for (int w = 0; w < warp; ++w) { eq_before += wsum_eq[w]; gt_before += wsum_gt[w]; }
+    const uint32_t lm = (1u << lane) - 1u;
+    const uint32_t my_eq_rank = eq_before + __popc(be & lm);
+    const uint32_t taken_eq_before = min(my_eq_rank, need) - min(base_eq, need);
+    const uint32_t outpos = base_out + gt_before + __popc(bg & lm) + taken_eq_before;
+    if ((gt || (eq && my_eq_rank < need)) && outpos < (uint32_t)top_k) sel[r * top_k + outpos] = i;
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t tg = 0, te = 0;
+      for (int w = 0; w < 32; ++w) { tg += wsum_gt[w]; te += wsum_eq[w]; }
+      const uint32_t new_eq = base_eq + te;
+      base_out += tg + (min(new_eq, need) - min(base_eq, need));
+      base_eq = new_eq;
+    }
+    __syncthreads();
+  }
+}
+
 // ----------------------------------------------------------------------------- MoE router
 struct RouterArgs {
   const __nv_bfloat16* xn;   // [16][hidden] normed activations (plain router) or null (fused form)
@@ -881,6 +1018,23 @@ extern "C" int nrt_index_logits_simple(const void* args, int blocks, void* strea
 extern "C" int nrt_topk_rows(const float* logits, int ld, const int* pos0, int rows, int top_k, int* sel, void* stream,
                              int pdl) {
   return launch_pdl(topk_rows_kernel, dim3(rows), dim3(1024), 0, S(stream), pdl != 0, logits, ld, pos0, rows, top_k, sel);
+}
+extern "C" int nrt_topk_grid_state_bytes() { return (int)sizeof(TopkGridState); }
+// ctas: CTAs per row (<= 64).  `state` holds rows x TopkGridState, zero-initialised once.
+extern "C" int nrt_topk_rows_grid(const float* logits, int ld, const int* pos0, int rows, int top_k, int* sel, void* state,
+                                  int ctas, void* stream, int pdl) {
+  if (ctas < 1 || ctas > 64) return -3;
+  TopkGridState* st = reinterpret_cast<TopkGridState*>(state);
+  int rc;
+  for (int pass = 0; pass < 4; ++pass)
+    if ((rc = launch_pdl(topk_grid_hist_kernel, dim3(ctas, rows), dim3(1024), 0, S(stream), pdl != 0, logits, ld, pos0, rows,
+                         top_k, st, pass)))
+      return rc;
+  if ((rc = launch_pdl(topk_grid_count_kernel, dim3(ctas, rows), dim3(1024), 0, S(stream), pdl != 0, logits, ld, pos0, rows,
+                       top_k, st)))
+    return rc;
+  return launch_pdl(topk_grid_write_kernel, dim3(ctas, rows), dim3(1024), 0, S(stream), pdl != 0, logits, ld, pos0, rows,
+                    top_k, st, sel);
 }
 extern "C" int nrt_router_args_size() { return (int)sizeof(RouterArgs); }
 extern "C" int nrt_router(const void* args, void* stream, int pdl) {

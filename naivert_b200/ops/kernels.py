@@ -405,3 +405,14 @@ def check_nc(code: int, what: str) -> None:
 
 def relaunch(ctrl, consumed_dev_ptr: int, ring_size: int):
     check(lib().nrt_relaunch(VP(ptr(ctrl)), VP(consumed_dev_ptr), ring_size, VP(_stream())), "relaunch")
+
+
+def topk_grid_state_bytes() -> int:
+    return lib().nrt_topk_grid_state_bytes()
+
+
+def topk_rows_grid(logits, pos0, rows, top_k, sel, state, ctas: int = 16, pdl=True):
+    """Exact top-k with ``ctas`` CTAs per row (six launches); for long contexts."""
+    LAUNCHES["count"] += 5
+    check(lib().nrt_topk_rows_grid(VP(ptr(logits)), logits.shape[1], VP(ptr(pos0)), rows, top_k, VP(ptr(sel)), VP(ptr(state)),
+                                   ctas, VP(_stream()), int(pdl)), "topk_rows_grid")

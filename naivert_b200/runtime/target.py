@@ -165,6 +165,9 @@ class TargetRuntime:
             self.ihw = torch.zeros(PAD_ROWS, ix.head_count, dtype=f32, device=dev)
             self.idx_logits = torch.zeros(PAD_ROWS, capacity, dtype=f32, device=dev)
             self.sel = torch.zeros(PAD_ROWS, ix.top_k, dtype=i32, device=dev)
+            # long contexts select with many CTAs per row (six launches); short ones with one CTA per row
+            self.topk_grid = capacity > 65536
+            self.topk_state = torch.zeros(PAD_ROWS * K.topk_grid_state_bytes() // 4, dtype=i32, device=dev)
             self.use_sweep = ix.head_dim == 128 and ix.head_count % 16 == 0 and PAD_ROWS * ix.head_count == 256
         self.attn_splits = 4
         self.attn_part = torch.zeros(PAD_ROWS * nh_max * self.attn_splits * (a0.v_head_dim + 2), dtype=f32, device=dev)
@@ -311,7 +314,10 @@ class TargetRuntime:
                     K.index_sweep(*d["sweep_maps"], d["args_sweep"], min(148, -(-self.capacity // 128)), pdl=pdl)
                 else:
                     K.index_logits_simple(d["args_index"], 148, pdl=pdl)
-                K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
+                if self.topk_grid:
+                    K.topk_rows_grid(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, self.topk_state, 16, pdl=pdl)
+                else:
+                    K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
             K.attn_rows(d["args_attn"], self.attn_splits if d["kind"] == FULL_DSA else 1, pdl=pdl)
             K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128,
                    K.pick_split(s.hidden // 128, d["wo"].k // 128), pdl=pdl)

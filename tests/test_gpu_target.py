@@ -64,6 +64,23 @@ def test_topk_rows_exact_with_ties():
         assert torch.equal(sel[r].long(), want), r
 
 
+def test_topk_grid_matches_single_cta_kernel():
+    from naivert_b200.models.reference import topk_stable
+    from naivert_b200.ops import kernels as K
+    K.lib()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    ld, top_k, pos0 = 70000, 2048, 69000
+    logits = (torch.randn(16, ld, device="cuda", generator=g) * 8).round() / 8      # many ties at the threshold
+    p = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    state = torch.zeros(16 * K.topk_grid_state_bytes() // 4, dtype=torch.int32, device="cuda")
+    for trial in range(2):                                                         # state is reusable
+        sel = torch.full((16, top_k), -1, dtype=torch.int32, device="cuda")
+        K.topk_rows_grid(logits, p, 8, top_k, sel, state, 16, pdl=False)
+        torch.cuda.synchronize()
+        for r in (0, 3, 7):
+            assert torch.equal(sel[r].long(), topk_stable(logits[r, : pos0 + r + 1], top_k)), (trial, r)
+
+
 def test_attention_rows_match_torch():
     """Sliding-window (ring + sink) and dense attention kernels against torch on identical inputs."""
     from naivert_b200.ops import kernels as K
