@@ -91,6 +91,9 @@ extern "C" int nrt_gemm_launch(int variant, const void* tmA0, const void* tmA1, 
     NRT_CASE(1, 1, kEpiSiluQuant, kGroupItem)
     NRT_CASE(1, 0, kEpiAllReduce, kGroupLoop)
     NRT_CASE(1, 0, kEpiReturn, kGroupItem)
+    NRT_CASE(1, 0, kEpiStoreBF16, kGroupItem)
+    NRT_CASE(0, 0, kEpiStoreF32, kGroupItem)
+    NRT_CASE(0, 0, kEpiStoreBF16, kGroupItem)
     NRT_CASE(0, 0, kEpiStoreF32, kGroupNone)
     NRT_CASE(0, 0, kEpiStoreBF16, kGroupNone)
     NRT_CASE(0, 0, kEpiAllReduce, kGroupNone)

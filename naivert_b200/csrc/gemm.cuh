@@ -372,14 +372,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 
     // ---------------------------------------------------------------- epilogue op
     const bool live = leader && (n_groups > 0 || split > 1) && n < p.n_total;
+    // group-item mode over a long row buffer: this CTA's 16 rows start at row_offsets[item]
+    const size_t out_row0 = (GROUP == kGroupItem && p.row_offsets && n_groups > 0) ? (size_t)p.row_offsets[g_first] : 0;
     if (EPI == kEpiStoreF32) {
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
-        if (live && r < p.rows) p.out_f32[(size_t)r * p.ld_out + n] = mix0[r] * p.out_scale;
+        if (live && r < p.rows) p.out_f32[(out_row0 + r) * p.ld_out + n] = mix0[r] * p.out_scale;
     } else if (EPI == kEpiStoreBF16) {
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
-        if (live && r < p.rows) p.out_bf16[(size_t)r * p.ld_out + n] = __float2bfloat16_rn(mix0[r] * p.out_scale);
+        if (live && r < p.rows) p.out_bf16[(out_row0 + r) * p.ld_out + n] = __float2bfloat16_rn(mix0[r] * p.out_scale);
     } else if (EPI == kEpiSiluBF16) {
 #pragma unroll
       for (int r = 0; r < kTok; ++r)

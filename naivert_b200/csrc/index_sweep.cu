@@ -53,7 +53,10 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint8_t* qsm = smem + kSweepStages * kATileBytes;                       // up to 256 x 128 B of queries
   SweepTail* tail = reinterpret_cast<SweepTail*>(qsm + 256 * 128);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ncol = p.rows * p.heads;                                       // UMMA N (<= 256)
+  // grid.y row groups (prefill chunks): group g holds rows g*16.. with queries at row g*256 of the query map
+  const int rg = blockIdx.y;
+  const int grows = min(16, p.rows - rg * 16);
+  const int ncol = grows * p.heads;                                        // UMMA N (<= 256)
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kSweepStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
@@ -71,8 +74,8 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   griddep_launch();
   griddep_wait();
 
-  const int p0 = *p.pos0;
-  const int total = p0 + p.rows;                       // positions that exist after this step's append
+  const int p0 = *p.pos0 + rg * 16;
+  const int total = p0 + grows;                        // positions visible to the last row of this group
   const bool active = total > p.top_k;                 // otherwise every row is still dense
   const int tiles = active ? (total + kTilePos - 1) / kTilePos : 0;
   int my_tiles = 0;
@@ -81,7 +84,7 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   if (warp == 0) {
     if (elect_one() && my_tiles > 0) {
       mbar_expect_tx(&tail->qbar, 256 * 128);
-      tma_load_2d(qsm, &tmQ, &tail->qbar, 0, 0);
+      tma_load_2d(qsm, &tmQ, &tail->qbar, 0, rg * 256);
       int u = 0;
       for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++u) {
         const int st = u % kSweepStages;
@@ -110,7 +113,7 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   } else {
     const int quad = warp & 3;
     const int e = threadIdx.x - 64;                     // 0..127
-    for (int i = e; i < 256; i += 128) tail->hw[i] = i < ncol ? p.ihw[i] : 0.f;
+    for (int i = e; i < 256; i += 128) tail->hw[i] = i < ncol ? p.ihw[(size_t)rg * 16 * p.heads + i] : 0.f;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
     int u = 0;
@@ -120,7 +123,7 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const float ks = pos < total ? p.iks[pos] : 0.f;
       if (!mbar_wait(&tail->acc_full[buf], (u >> 1) & 1, p.status, kSiteAccFull | buf)) break;
       tc_fence_after();
-      for (int r = 0; r < p.rows; ++r) {
+      for (int r = 0; r < grows; ++r) {
         float acc = 0.f;
         for (int c = 0; c < p.heads; c += 16) {
           float v[16];
@@ -128,7 +131,7 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 16; ++j) acc += fmaxf(v[j], 0.f) * tail->hw[r * p.heads + c + j];
         }
-        if (pos < total) p.logits[(size_t)r * p.ld + pos] = acc * ks;
+        if (pos < total) p.logits[(size_t)(rg * 16 + r) * p.ld + pos] = acc * ks;
       }
       tc_fence_before();
       mbar_arrive(&tail->acc_empty[buf]);
@@ -152,7 +155,9 @@ extern "C" int nrt_index_sweep(const void* tmK, const void* tmQ, const void* arg
   memcpy(&q, tmQ, sizeof(q));
   SweepArgs a;
   memcpy(&a, args, sizeof(a));
-  const int ncol = a.rows * a.heads;
+  const int groups = (a.rows + 15) / 16;
+  if (a.heads != 16 && groups > 1) return -3;           // row groups assume 256 query rows per group
+  const int ncol = (a.rows > 16 ? 16 : a.rows) * a.heads;
   if (a.heads % 16 || ncol > 256 || ncol % 16) return -3;
   constexpr int smem = kSweepStages * kATileBytes + 256 * 128 + 2048 + 1024;
   static bool configured = false;
@@ -161,6 +166,6 @@ extern "C" int nrt_index_sweep(const void* tmK, const void* tmQ, const void* arg
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(index_sweep_kernel, dim3(blocks), dim3(kSweepThreads), smem, reinterpret_cast<cudaStream_t>(stream),
+  return launch_pdl(index_sweep_kernel, dim3(blocks, groups), dim3(kSweepThreads), smem, reinterpret_cast<cudaStream_t>(stream),
                     pdl != 0, k, q, a);
 }

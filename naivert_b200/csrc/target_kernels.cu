@@ -754,7 +754,18 @@ struct RouterArgs {
 
 // grid = experts / 2 CTAs; each warp-pair of a CTA... one CTA computes 2 experts x 16 rows; the last CTA
 // to finish performs the per-row top-k and builds the ascending active-expert list.
-__global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
+__global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
+  // grid.y row groups of 16 rows (prefill chunks): each group is routed independently
+  RouterArgs a = a_in;
+  if (gridDim.y > 1) {
+    const int g0 = blockIdx.y * kMaxRows;
+    a.xn = a_in.xn + (size_t)g0 * a_in.hidden;
+    a.rows = min(kMaxRows, a_in.rows - g0);
+    a.scores = a_in.scores + (size_t)g0 * a_in.experts;
+    a.ticket = a_in.ticket + blockIdx.y;
+    a.topk_ids = a_in.topk_ids + (size_t)g0 * a_in.top_k;
+    a.topk_p = a_in.topk_p + (size_t)g0 * a_in.top_k;
+  }
   __shared__ float part[8][2][kMaxRows];
   __shared__ bool last;
   __shared__ unsigned int used[8];                  // bitmap over <= 256 experts
@@ -939,6 +950,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
     }
   }
   __syncthreads();
+  if (a.probs == nullptr) return;                     // prefill: only the per-token choices are needed
   // ascending list of distinct experts -> slots
   if (tid < 256) {
     const bool on = tid < a.experts && (used[tid >> 5] >> (tid & 31)) & 1u;
@@ -969,16 +981,18 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a) {
 
 extern "C" int nrt_embed_rows(const int* tokens, const void* table, void* x, int hidden, int rows, int vocab,
                               void* stream, int pdl) {
-  return launch_pdl(embed_rows_kernel, dim3(kMaxRows), dim3(128), 0, S(stream), pdl != 0, tokens,
+  return launch_pdl(embed_rows_kernel, dim3(rows > kMaxRows ? rows : kMaxRows), dim3(128), 0, S(stream), pdl != 0, tokens,
                     (const __nv_bfloat16*)table, (__nv_bfloat16*)x, hidden, rows, vocab);
 }
 extern "C" int nrt_rope_table(const int* pos0, int rows, int dim, double theta, void* out, void* stream, int pdl) {
   return launch_pdl(rope_table_kernel, dim3(rows), dim3(dim / 2 < 32 ? 32 : dim / 2), 0, S(stream), pdl != 0, pos0, rows,
                     dim, theta, (float2*)out);
 }
+// rows <= 16: the operand is padded to 16 rows (dead rows zero-filled); larger row counts (prefill chunks)
+// launch one CTA per row.
 extern "C" int nrt_prep_norm(const void* x, const void* gamma, int hidden, int rows, float eps, void* xn, void* x8,
                              void* xs, void* stream, int pdl) {
-  return launch_pdl(prep_norm_kernel, dim3(kMaxRows), dim3(256), 0, S(stream), pdl != 0, (const __nv_bfloat16*)x,
+  return launch_pdl(prep_norm_kernel, dim3(rows > kMaxRows ? rows : kMaxRows), dim3(256), 0, S(stream), pdl != 0, (const __nv_bfloat16*)x,
                     (const __nv_bfloat16*)gamma, hidden, rows, eps, (__nv_bfloat16*)xn, (uint8_t*)x8, (float*)xs);
 }
 extern "C" int nrt_attn_post_args_size() { return (int)sizeof(AttnPostArgs); }
@@ -1051,7 +1065,9 @@ extern "C" int nrt_router(const void* args, void* stream, int pdl) {
     }
     if (smem > 200 * 1024 || a.hidden % 256) return -3;
   }
-  return launch_pdl(router_kernel, dim3((a.experts + 1) / 2), dim3(256), smem, S(stream), pdl != 0, a);
+  const int groups = a.rows > kMaxRows ? (a.rows + kMaxRows - 1) / kMaxRows : 1;
+  if (groups > 1 && (a.x || a.probs)) return -3;                      // row groups: plain routing of normed rows only
+  return launch_pdl(router_kernel, dim3((a.experts + 1) / 2, groups), dim3(256), smem, S(stream), pdl != 0, a);
 }
 
 // ============================================================================= allocation-free routing

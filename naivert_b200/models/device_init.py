@@ -78,6 +78,22 @@ def init_rank_weights_device(spec: ModelSpec, rank: int, tp: int, seed: int = 0,
     return out
 
 
+def init_expert_rank_weights_device(spec: ModelSpec, rank: int, tp: int, seed: int = 0, device="cuda", std: float = 0.02) -> list:
+    """Whole experts of rank ``rank`` (expert-parallel prefill layout), one entry per layer (``None`` for dense
+    layers).  Drawn independently of the tensor-parallel slices: a benchmark model, not a consistent one."""
+    H, rt = spec.hidden, spec.routing
+    g = _gen(seed * 1000003 + 9001 + rank, device)
+    n, I = rt.expert_count // tp, rt.intermediate
+    out = []
+    for L in range(spec.layer_count):
+        if spec.is_dense(L):
+            out.append(None)
+            continue
+        out.append({"gate": _rand_q8(g, n, I, H, std=std), "up": _rand_q8(g, n, I, H, std=std),
+                    "down": _rand_q8(g, n, H, I, std=std)})
+    return out
+
+
 def init_draft_rank_weights_device(spec: ModelSpec, rank: int, tp: int, seed: int = 1, device="cuda", std: float = 0.02) -> dict:
     d = spec.draft
     rep = _gen(seed * 1000003 + 23, device)

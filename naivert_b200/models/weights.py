@@ -267,6 +267,24 @@ def shard_weights(spec: ModelSpec, w: dict, rank: int, tp: int) -> dict:
     return out
 
 
+def shard_expert_weights(spec: ModelSpec, w: dict, rank: int, tp: int) -> list:
+    """Expert-parallel layout for prefill: rank ``rank`` holds ``expert_count / tp`` *whole* experts of every MoE
+    layer (``None`` for dense layers).  Block scales ride along unchanged, so the values are those of the
+    tensor-parallel slices.  Parity: naivert/prefill/operands.py ``load_expert_rank``."""
+    E = spec.routing.expert_count
+    if E % tp:
+        raise ValueError(f"{E} experts do not divide over {tp} ranks")
+    n = E // tp
+    out = []
+    for lw in w["layers"]:
+        if "dense" in lw:
+            out.append(None)
+            continue
+        out.append({name: {"w": lw[name]["w"][rank * n:(rank + 1) * n].contiguous(),
+                           "s": lw[name]["s"][rank * n:(rank + 1) * n].contiguous()} for name in ("gate", "up", "down")})
+    return out
+
+
 def shard_draft_weights(spec: ModelSpec, w: dict, rank: int, tp: int) -> dict:
     d = spec.draft
     taps = len(d.target_layer_ids)

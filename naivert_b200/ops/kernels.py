@@ -198,9 +198,9 @@ class SweepArgs(C.Structure):
 
 def sweep_maps(ik_cache: torch.Tensor, iq8: torch.Tensor):
     """Tensor maps of the tcgen05 indexer sweep: key cache [cap, 128] e4m3 bytes, queries [256, 128]."""
-    assert ik_cache.shape[1] == 128 and iq8.shape == (256, 128)
+    assert ik_cache.shape[1] == 128 and iq8.shape[1] == 128 and iq8.shape[0] % 256 == 0
     km = TensorMap(ik_cache, (128, ik_cache.shape[0]), (128,), (128, 128), 0)
-    qm = TensorMap(iq8, (128, 256), (128,), (128, 256), 0)
+    qm = TensorMap(iq8, (128, iq8.shape[0]), (128,), (128, 256), 0)
     return km, qm
 
 

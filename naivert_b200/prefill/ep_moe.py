@@ -37,11 +37,24 @@ def _raw_map(ptr: int, rows: int, cols_bytes: int) -> K.TensorMap:
     return m
 
 
+class EPWeights:
+    """One MoE layer's experts held by this rank, with their tensor maps.
+    ``gate/up`` {"w": e4m3 [E_local, inter, hidden], "s": [E_local, inter/128, hidden/128]},
+    ``down`` {"w": [E_local, hidden, inter], "s": ...}."""
+
+    def __init__(self, gate: dict, up: dict, down: dict):
+        self.gate_w, self.up_w, self.down_w = gate["w"].contiguous(), up["w"].contiguous(), down["w"].contiguous()
+        self.gate_s, self.up_s, self.down_s = gate["s"].float().contiguous(), up["s"].float().contiguous(), down["s"].float().contiguous()
+        self.map_gate = K.weight_tmap(self.gate_w.view(torch.uint8))
+        self.map_up = K.weight_tmap(self.up_w.view(torch.uint8))
+        self.map_down = K.weight_tmap(self.down_w.view(torch.uint8))
+
+
 class EPMoE:
     def __init__(self, fabric: Fabric, hidden: int, inter: int, experts: int, top_k: int, tokens_local: int,
-                 gate: dict, up: dict, down: dict, eps: float = 1e-5):
-        """``gate/up`` {"w": e4m3 [E_local, inter, hidden], "s": [E_local, inter/128, hidden/128]},
-        ``down`` {"w": [E_local, hidden, inter], "s": ...}: this rank's whole experts."""
+                 gate: Optional[dict] = None, up: Optional[dict] = None, down: Optional[dict] = None, eps: float = 1e-5):
+        """Exchange buffers for up to ``tokens_local`` rows per rank; the experts of a layer are passed to
+        ``run`` (``EPWeights``) or, for a single layer, given here."""
         self.fab, self.H, self.I, self.E, self.K, self.T, self.eps = fabric, hidden, inter, experts, top_k, tokens_local, eps
         tp, dev = fabric.tp, fabric.device
         self.El = experts // tp
@@ -64,11 +77,7 @@ class EPMoE:
         self.combine = alloc(tokens_local * top_k * (hidden // 2) * 8)
         self.y8 = torch.zeros(self.cap_rows, inter, dtype=torch.uint8, device=dev)
         self.ys = torch.ones(self.cap_rows, inter // 128, dtype=f32, device=dev)
-        self.gate_w, self.up_w, self.down_w = gate["w"].contiguous(), up["w"].contiguous(), down["w"].contiguous()
-        self.gate_s, self.up_s, self.down_s = gate["s"].float().contiguous(), up["s"].float().contiguous(), down["s"].float().contiguous()
-        self.map_gate = K.weight_tmap(self.gate_w.view(torch.uint8))
-        self.map_up = K.weight_tmap(self.up_w.view(torch.uint8))
-        self.map_down = K.weight_tmap(self.down_w.view(torch.uint8))
+        self.w = EPWeights(gate, up, down) if gate is not None else None
         self.map_recv = _raw_map(self.recv8[fabric.rank], self.cap_rows, hidden)
         self.map_y = K.act_tmap(self.y8)
 
@@ -77,10 +86,10 @@ class EPMoE:
         self._keep.append(t)
         return [t.data_ptr()] + [0] * (K.K_MAX_PEERS - 1)
 
-    def _ep_args(self, x, gamma, ids, probs) -> K.EpArgs:
+    def _ep_args(self, x, gamma, ids, probs, tokens) -> K.EpArgs:
         a = K.EpArgs()
         a.topk_ids, a.topk_p = ids.data_ptr(), probs.data_ptr()
-        a.tokens, a.top_k, a.experts, a.experts_local, a.hidden = self.T, self.K, self.E, self.El, self.H
+        a.tokens, a.top_k, a.experts, a.experts_local, a.hidden = tokens, self.K, self.E, self.El, self.H
         a.slot_of, a.n_items = self.slot_of.data_ptr(), self.n_items.data_ptr()
         a.item_expert, a.item_row, a.seg_rows = self.item_expert.data_ptr(), self.item_row.data_ptr(), self.seg_rows.data_ptr()
         a.max_items, a.cap_rows = self.max_items, self.cap_rows
@@ -92,10 +101,16 @@ class EPMoE:
         return a
 
     def run(self, x: torch.Tensor, gamma: Optional[torch.Tensor], ids: torch.Tensor, probs: torch.Tensor,
-            resid: torch.Tensor, out: torch.Tensor, pdl: bool = False) -> None:
-        """x [T, H] bf16 residual rows of this rank, ids/probs [T, top_k]; out = resid + sum_k p_k * expert_k(norm(x))."""
+            resid: torch.Tensor, out: torch.Tensor, pdl: bool = False, weights: Optional[EPWeights] = None,
+            tokens: Optional[int] = None) -> None:
+        """x [T, H] bf16 residual rows of this rank, ids/probs [T, top_k]; out = resid + sum_k p_k * expert_k(norm(x)).
+        ``tokens`` (<= tokens_local, the same on every rank) rows take part; ``weights`` selects the layer."""
         fab, rank = self.fab, self.fab.rank
-        a = self._ep_args(x, gamma, ids, probs)
+        w = weights or self.w
+        T = self.T if tokens is None else tokens
+        if not 0 < T <= self.T:
+            raise ValueError(f"{T} rows exceed the exchange buffers sized for {self.T}")
+        a = self._ep_args(x, gamma, ids, probs, T)
         K.ep_count(a, pdl=pdl)
         K.ep_dispatch(a, pdl=pdl)
         st = fab.status.data_ptr()
@@ -103,29 +118,29 @@ class EPMoE:
         g.n_total, g.k_total, g.rows, g.out_scale = self.I, self.H, 16, 1.0
         g.n_active, g.active_ids, g.max_slots = self.n_items.data_ptr(), self.item_expert.data_ptr(), self.max_items
         g.row_offsets = self.item_row.data_ptr()
-        g.w_scale0, g.w_scale1, g.a_scale = self.gate_s.data_ptr(), self.up_s.data_ptr(), self.recvs[rank]
+        g.w_scale0, g.w_scale1, g.a_scale = w.gate_s.data_ptr(), w.up_s.data_ptr(), self.recvs[rank]
         g.out_q, g.out_qscale = self.y8.data_ptr(), self.ys.data_ptr()
         g.fab = fab.fabric_args(0, self.H)
         g.fab.ag_call, g.fab.ag_flags = CALL_DISPATCH, self.flags[rank]
         g.status = st
-        K.gemm(K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM), self.map_gate, self.map_up, self.map_recv, g,
+        K.gemm(K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM), w.map_gate, w.map_up, self.map_recv, g,
                self.I // 128, self.max_items, pdl=pdl)
         d = K.GemmArgs()
         d.n_total, d.k_total, d.rows, d.out_scale = self.H, self.I, 16, 1.0
         d.n_active, d.active_ids, d.max_slots = self.n_items.data_ptr(), self.item_expert.data_ptr(), self.max_items
         d.row_offsets = self.item_row.data_ptr()
-        d.w_scale0, d.a_scale = self.down_s.data_ptr(), self.ys.data_ptr()
+        d.w_scale0, d.a_scale = w.down_s.data_ptr(), self.ys.data_ptr()
         d.fab = fab.fabric_args(0, self.H)
         d.status = st
         d.ep_meta, d.ep_top_k = self.meta[rank], self.K
         for i in range(K.K_MAX_PEERS):
             d.ep_combine[i] = self.combine[i]
         d.ep_dispatch_call, d.ep_return_call = CALL_DISPATCH, CALL_RETURN
-        K.gemm(K.gemm_variant(True, False, K.EPI_RETURN, K.GROUP_ITEM), self.map_down, None, self.map_y, d,
+        K.gemm(K.gemm_variant(True, False, K.EPI_RETURN, K.GROUP_ITEM), w.map_down, None, self.map_y, d,
                self.H // 128, self.max_items, pdl=pdl)
         c = K.EpCombineArgs()
         c.slots, c.topk_p, c.resid, c.out = self.combine[rank], probs.data_ptr(), resid.data_ptr(), out.data_ptr()
         c.epoch, c.status = fab.epoch.data_ptr(), st
-        c.tokens, c.top_k, c.hidden, c.call, c.timeout_ns = self.T, self.K, self.H, CALL_RETURN, fab.timeout_ns
+        c.tokens, c.top_k, c.hidden, c.call, c.timeout_ns = T, self.K, self.H, CALL_RETURN, fab.timeout_ns
         K.ep_combine(c, pdl=pdl)
         K.epoch_advance(fab.epoch, pdl=pdl)

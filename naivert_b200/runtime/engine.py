@@ -45,16 +45,22 @@ class GenerationResult:
 
 
 class Engine:
-    def __init__(self, spec: ModelSpec, fabric: Fabric, target: TargetRuntime, rnd: SpeculativeRound):
+    def __init__(self, spec: ModelSpec, fabric: Fabric, target: TargetRuntime, rnd: SpeculativeRound, prefill=None):
         self.spec, self.fabric, self.target, self.round = spec, fabric, target, rnd
         self.tp, self.rank = fabric.tp, fabric.rank
+        self.prefill = prefill                       # NativePrefill (chunked prompt ingestion) or None: replay only
+        self.native_min_rows = 64                    # shorter prompts are replayed eight rows at a time
+        self.last_prefill = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def build(cls, spec: ModelSpec, rank: int = 0, tp: int = 1, group=None, capacity: int = 16384, seed: int = 0,
               target_ckpt: Optional[str] = None, draft_ckpt: Optional[str] = None, device=None,
               weights: Optional[dict] = None, draft_weights: Optional[dict] = None, pdl: Optional[bool] = None,
-              shape_tp: int = 0, device_chain: Optional[bool] = None) -> "Engine":
+              shape_tp: int = 0, device_chain: Optional[bool] = None, prefill_chunk: int = 0,
+              ep_weights: Optional[list] = None) -> "Engine":
+        """``prefill_chunk`` > 0 adds the chunked native prefill (rows per chunk); ``ep_weights`` (whole experts of
+        this rank per layer, ``models.weights.shard_expert_weights``) selects its expert-parallel MoE path."""
         device = device or torch.device("cuda", torch.cuda.current_device())
         if pdl is None:
             # Programmatic dependent launch is available on every kernel (NAIVERT_PDL=1).  Measured on
@@ -85,18 +91,38 @@ class Engine:
                 from ..models.device_init import init_draft_rank_weights_device
                 draft_weights = init_draft_rank_weights_device(spec, rank, tp, seed=seed + 1, device=device)
         target = TargetRuntime(spec, weights, fabric, rows=spec.draft.rows, capacity=capacity, device=device, pdl=pdl,
-                               shape_tp=shape_tp)
+                               shape_tp=shape_tp, prefill_chunk=prefill_chunk)
         del weights
         if device_chain is None:
             import os
             device_chain = os.environ.get("NAIVERT_DEVICE_CHAIN", "0") == "1"
         rnd = SpeculativeRound(spec, target, draft_weights, capacity, pdl=pdl, device_chain=device_chain)
-        return cls(spec, fabric, target, rnd)
+        prefill = None
+        if prefill_chunk:
+            from ..prefill.native import NativePrefill
+            prefill = NativePrefill(spec, target, rnd.draft, chunk=prefill_chunk, ep_weights=ep_weights, group=group)
+        return cls(spec, fabric, target, rnd, prefill)
 
     # ------------------------------------------------------------------ one request
+    def prefill_native(self, prompt: torch.Tensor, start: int = 0) -> int:
+        """Ingest prompt context rows [start, n - 1) in whole chunks where that pays; returns the position from
+        which the eight-row replay has to continue."""
+        n = int(prompt.numel())
+        self.last_prefill = {"path": "replay", "native_rows": 0}
+        if self.prefill is None or n - 1 - start < max(self.native_min_rows, self.prefill.quantum):
+            return start
+        if n > self.target.capacity:
+            raise RuntimeContractError(f"prompt {n} exceeds the cache capacity {self.target.capacity}")
+        with torch.cuda.stream(self.round.stream):
+            pos = self.prefill.run(prompt, start, n - 1)
+        self.last_prefill = {"path": "native", "native_rows": pos - start, "executor_ms": round(self.prefill.executor_ms(), 3)}
+        self.prefill.check()
+        return pos
+
     def open(self, prompt: torch.Tensor, max_tokens: int, sampling: Optional[SamplingParams] = None,
              use_graphs: bool = True) -> None:
-        self.round.initialize(prompt, max_tokens, sampling or SamplingParams(), use_graphs=use_graphs)
+        start = self.prefill_native(prompt)
+        self.round.initialize(prompt, max_tokens, sampling or SamplingParams(), use_graphs=use_graphs, start_pos=start)
 
     def stream_rounds(self, ahead: int = 4, timeout_s: float = 120.0) -> Iterator[RoundRecord]:
         """Launch rounds ``ahead`` of the host and yield each round's record as it is published."""
@@ -136,5 +162,7 @@ class Engine:
         return self.target.kv_bytes() + self.round.draft.kv_bytes()
 
     def close(self) -> None:
+        if self.prefill is not None:
+            self.prefill.close()
         self.round.close()
         self.fabric.close()

@@ -198,9 +198,13 @@ class SessionEngine:
             if prefill_estimate(n - 1, "replay") - prefill_estimate(new_after, "replay") > gb * RESTORE_MS_PER_GB:
                 start = self.store.restore(choice)
         t1 = time.perf_counter()
-        path = prefill_path(n - 1 - start, self.resume_policy, native_ready=False)
+        path = prefill_path(n - 1 - start, self.resume_policy, native_ready=self.engine.prefill is not None)
         prompt = torch.tensor(tokens, dtype=torch.int32)
-        self.engine.round.initialize(prompt, max_decode, sampling or SamplingParams(), use_graphs=use_graphs, start_pos=start)
+        replay_from = start
+        if path == "native":
+            replay_from = self.engine.prefill_native(prompt, start)
+        self.engine.round.initialize(prompt, max_decode, sampling or SamplingParams(), use_graphs=use_graphs,
+                                     start_pos=replay_from)
         t2 = time.perf_counter()
         key = session_id or "anon"
         if n - 1 >= 16:

@@ -49,12 +49,15 @@ class _Linear8:
 
 class TargetRuntime:
     def __init__(self, spec: ModelSpec, rank_weights: dict, fabric, rows: int = 8, capacity: int = 16384,
-                 device="cuda", pdl: bool = True, shape_tp: int = 0):
+                 device="cuda", pdl: bool = True, shape_tp: int = 0, prefill_chunk: int = 0):
         if spec.weight_dtype != "fp8":
             raise ValueError("the CUDA runtime implements the W8A8 recipe only")
         if spec.routing.shared_expert_count:
             raise ValueError("shared experts are only supported by the torch oracle")
         self.spec, self.fab, self.rows, self.capacity, self.dev, self.pdl = spec, fabric, rows, capacity, device, pdl
+        # a chunked prefill appends `prefill_chunk` rows to a sliding-window ring in one launch: the ring must hold
+        # the window of the chunk's first row and the whole chunk at once
+        self.prefill_chunk = prefill_chunk
         # shape_tp > 1 with a single-rank fabric runs one rank's share of a tp-way model without peers
         # (kernel profiling of the per-rank shapes; the results are not a model output)
         self.tp, self.rank = (shape_tp, 0) if shape_tp else (fabric.tp, fabric.rank)
@@ -139,7 +142,7 @@ class TargetRuntime:
                 d["iks"] = torch.ones(capacity, dtype=f32, device=dev)
                 d["ring"] = 0
             else:
-                ring = a.sliding_window + PAD_ROWS
+                ring = a.sliding_window + max(PAD_ROWS, prefill_chunk)
                 d["k"] = torch.zeros(ring, nkv, a.head_dim, dtype=bf, device=dev)
                 d["v"] = torch.zeros(ring, nkv, a.v_head_dim, dtype=bf, device=dev)
                 d["ring"] = ring

@@ -50,3 +50,21 @@ def test_expert_parallel_all_to_all(n):
     assert r["status"] == 0 and r["repeat_identical"], r
     assert r.get("worst_err", r["max_rel_err"]) < 0.02, r
     assert r.get("total_rows", r["rows"]) == 96 * 4 * n
+
+
+@pytest.mark.parametrize("n", [1, 2])
+def test_native_prefill_matches_replay(n):
+    """Chunked prefill (TP attention; EP experts at n > 1) leaves the caches the eight-row replay leaves."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    r = _run_worker(n, "mp_prefill_worker.py")
+    assert r["status"] == 0 and r["repeat_identical"], r
+    assert r["prefill"]["path"] == "native" and r["prefill"]["native_rows"] >= 672, r
+    if n == 1:
+        # same arithmetic up to the first MoE output: attention-side kernels and the dense MLP are exact
+        for k in ("L0.k", "L0.v", "L0.ik", "L0.iks", "L1.k", "L1.v"):
+            assert k in r["bitwise"], r
+    else:
+        assert r["lockstep"], r
+    assert r["worst"] < 0.1, r
+    assert r["token_prefix_agreement"] >= 1, r

@@ -56,3 +56,15 @@ def test_build_manifest_digest_tracks_sources(tmp_path, monkeypatch):
     assert "gemm.cu" in inv and "ptx.cuh" in inv and all(not p.startswith("/") for p in inv)
     monkeypatch.setattr(build, "NVCC_FLAGS", build.NVCC_FLAGS + ["-DX"])
     assert build.source_digest() != d1
+
+
+def test_prefill_chunk_plan():
+    from naivert_b200.prefill.native import plan_chunks
+    cs = plan_chunks(0, 699, 256, 16)
+    assert [(c.pos0, c.rows) for c in cs] == [(0, 256), (256, 256), (512, 176)]
+    assert plan_chunks(100, 110, 256, 16) == []
+    cs = plan_chunks(64, 64 + 4096 * 2 + 40, 4096, 128)
+    assert sum(c.rows for c in cs) == 4096 * 2 and all(c.rows % 128 == 0 for c in cs)
+    import pytest
+    with pytest.raises(ValueError):
+        plan_chunks(0, 100, 250, 16)
