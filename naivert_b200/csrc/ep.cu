@@ -40,7 +40,7 @@ struct EpArgs {
   int* slot_of;               // [tokens*top_k] destination row of each pair
   int* n_items;               // grouped-GEMM work list of this rank's experts
   int* item_expert;           // [max_items] local expert id
-  int* item_row;              // [max_items] first row of the 16-row group
+  int* item_row;              // [max_items] first row of the item's row group
   int* seg_rows;              // [experts_local] rows received per local expert (unpadded)
   int max_items;
   int cap_rows;               // receive buffer capacity in rows
@@ -54,6 +54,7 @@ struct EpArgs {
   uint64_t* flags[kXchgPeers];   // [tp] dispatch-complete words
   unsigned int* ticket;
   int call;                      // tag call index of this layer's dispatch
+  int item_rows;                 // rows per grouped-GEMM work item and segment padding (16 or 64; 0 = 16)
   XchgArgs x_args;
 };
 
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
   griddep_wait();
   const int tp = a.x_args.tp, rank = a.x_args.rank;
   const int n = a.tokens * a.top_k;
+  const int ir = a.item_rows > 0 ? a.item_rows : 16;
   for (int i = threadIdx.x; i < a.experts; i += 1024) hist[i] = 0u;
   for (int i = threadIdx.x; i < tp * a.experts; i += 1024) xv[i] = 0ull;
   __syncthreads();
@@ -83,7 +85,7 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
       int rows = 0;
       for (int s = 0; s < tp; ++s) rows += (int)xv[s * a.experts + e];
       seg_base[e] = base;
-      base += (rows + 15) & ~15;
+      base += (rows + ir - 1) / ir * ir;
     }
   }
   __syncthreads();
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
       int rows = 0;
       for (int s = 0; s < tp; ++s) rows += (int)xv[s * a.experts + e];
       a.seg_rows[el] = rows;
-      for (int r0 = 0; r0 < rows; r0 += 16) {
+      for (int r0 = 0; r0 < rows; r0 += ir) {
         if (items < a.max_items) { a.item_expert[items] = el; a.item_row[items] = seg_base[e] + r0; }
         ++items;
       }

@@ -139,13 +139,14 @@ def weight_tmap(w: torch.Tensor) -> TensorMap:
     return TensorMap(w, (k, n, e), (k * es, n * k * es), (128 // es, 128, 1), code)
 
 
-def act_tmap(x: torch.Tensor) -> TensorMap:
-    """[rows (multiple of 16), K] activations -> 2-D map with 16-row x 128-byte boxes."""
-    assert x.dim() == 2 and x.stride(1) == 1 and x.shape[0] % K_TOK == 0
+def act_tmap(x: torch.Tensor, box_rows: int = K_TOK) -> TensorMap:
+    """[rows (multiple of ``box_rows``), K] activations -> 2-D map with ``box_rows`` x 128-byte boxes
+    (16 rows for the step engine, 64 for the chunk GEMM)."""
+    assert x.dim() == 2 and x.stride(1) == 1 and x.shape[0] % box_rows == 0
     r, k = x.shape
     es = x.element_size()
     assert (x.stride(0) * es) % 16 == 0 and x.data_ptr() % 16 == 0
-    return TensorMap(x, (k, r), (x.stride(0) * es,), (128 // es, K_TOK), 0 if es == 1 else 1)
+    return TensorMap(x, (k, r), (x.stride(0) * es,), (128 // es, box_rows), 0 if es == 1 else 1)
 
 
 _SPLIT_MIN_KB = int(__import__("os").environ.get("NAIVERT_SPLIT_MIN_KB", "1"))
@@ -166,6 +167,18 @@ def gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: TensorMap, arg
          grid_y: int = 1, pdl: bool = True) -> None:
     check(lib().nrt_gemm_launch(variant, C.byref(a0.buf), C.byref(a1.buf) if a1 is not None else None,
                                 C.byref(b.buf), C.byref(args), grid_x, grid_y, VP(_stream()), int(pdl)), "gemm launch")
+
+
+WIDE_TOK = 64
+
+
+def wide_gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: TensorMap, args: GemmArgs, n_tiles: int,
+              items: int, pdl: bool = False, items_fastest: bool = False) -> None:
+    """Chunk GEMM (64 token rows per item, item mode only); ``b`` must be a 64-row-box token map.
+    ``items_fastest``: consecutive CTAs share a weight tile (one large weight matrix) instead of a token tile."""
+    check(lib().nrt_wide_gemm_launch(variant, C.byref(a0.buf), C.byref(a1.buf) if a1 is not None else None,
+                                     C.byref(b.buf), C.byref(args), n_tiles, items, int(items_fastest), VP(_stream()),
+                                     int(pdl)), "wide gemm launch")
 
 
 def embed_rows(tokens, table, x, rows, pdl=True):
@@ -189,6 +202,14 @@ def attn_post(args: AttnPostArgs, pdl=True):
 
 def attn_rows(args: AttnArgs, splits: int = 1, pdl=True):
     check(lib().nrt_attn_rows(C.byref(args), splits, VP(_stream()), int(pdl)), "attn_rows")
+
+
+def attn_group(args: AttnArgs, pdl=True):
+    """Row attention with the query heads of each KV head handled by one CTA (prefill chunks)."""
+    L = lib()
+    if L.nrt_attn_group_args_size() != C.sizeof(AttnArgs):
+        raise RuntimeError("AttnArgs layout drift")
+    check(L.nrt_attn_group(C.byref(args), VP(_stream()), int(pdl)), "attn_group")
 
 
 class SweepArgs(C.Structure):
@@ -337,7 +358,7 @@ class EpArgs(C.Structure):
                 ("hidden", I32), ("slot_of", VP), ("n_items", VP), ("item_expert", VP), ("item_row", VP), ("seg_rows", VP),
                 ("max_items", I32), ("cap_rows", I32), ("x", VP), ("gamma", VP), ("eps", F32),
                 ("recv8", VP * K_MAX_PEERS), ("recvs", VP * K_MAX_PEERS), ("meta", VP * K_MAX_PEERS), ("flags", VP * K_MAX_PEERS),
-                ("ticket", VP), ("call", I32), ("x_args", XchgArgs)]
+                ("ticket", VP), ("call", I32), ("item_rows", I32), ("x_args", XchgArgs)]
 
 
 class EpCombineArgs(C.Structure):

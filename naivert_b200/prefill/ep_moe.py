@@ -26,13 +26,13 @@ from ..parallel.fabric import Fabric
 CALL_DISPATCH, CALL_RETURN = 900, 901
 
 
-def _raw_map(ptr: int, rows: int, cols_bytes: int) -> K.TensorMap:
-    """Tensor map over a fabric allocation viewed as [rows, cols_bytes] bytes (16-row x 128-byte boxes)."""
+def _raw_map(ptr: int, rows: int, cols_bytes: int, box_rows: int = 16) -> K.TensorMap:
+    """Tensor map over a fabric allocation viewed as [rows, cols_bytes] bytes (``box_rows`` x 128-byte boxes)."""
     m = K.TensorMap.__new__(K.TensorMap)
     m.tensor, m.buf = None, (C.c_ubyte * 128)()
     d = (C.c_uint64 * 5)(cols_bytes, rows)
     st = (C.c_uint64 * 5)(cols_bytes)
-    bx = (C.c_uint32 * 5)(128, 16)
+    bx = (C.c_uint32 * 5)(128, box_rows)
     K.check(K.lib().nrt_tmap_encode(C.byref(m.buf), 0, 2, d, st, bx, 3, C.c_void_p(ptr)), "tensor map")
     return m
 
@@ -52,14 +52,19 @@ class EPWeights:
 
 class EPMoE:
     def __init__(self, fabric: Fabric, hidden: int, inter: int, experts: int, top_k: int, tokens_local: int,
-                 gate: Optional[dict] = None, up: Optional[dict] = None, down: Optional[dict] = None, eps: float = 1e-5):
+                 gate: Optional[dict] = None, up: Optional[dict] = None, down: Optional[dict] = None, eps: float = 1e-5,
+                 item_rows: int = 16):
         """Exchange buffers for up to ``tokens_local`` rows per rank; the experts of a layer are passed to
-        ``run`` (``EPWeights``) or, for a single layer, given here."""
+        ``run`` (``EPWeights``) or, for a single layer, given here.  ``item_rows`` = 64 pads expert segments to
+        64 rows and runs the grouped GEMMs on the 64-column chunk engine (16: the step engine's tile)."""
+        if item_rows not in (16, K.WIDE_TOK):
+            raise ValueError("item_rows must be 16 or 64")
         self.fab, self.H, self.I, self.E, self.K, self.T, self.eps = fabric, hidden, inter, experts, top_k, tokens_local, eps
+        self.item_rows = item_rows
         tp, dev = fabric.tp, fabric.device
         self.El = experts // tp
-        self.cap_rows = tokens_local * tp * top_k + 16 * self.El          # worst case + segment padding
-        self.max_items = self.cap_rows // 16 + self.El
+        self.cap_rows = -(-(tokens_local * tp * top_k) // item_rows) * item_rows + item_rows * self.El    # worst case + segment padding
+        self.max_items = self.cap_rows // item_rows + self.El
         i32, f32 = torch.int32, torch.float32
         self._keep: List[torch.Tensor] = []          # single-rank buffers (no fabric allocation needed)
         self.slot_of = torch.zeros(tokens_local * top_k, dtype=i32, device=dev)
@@ -78,8 +83,9 @@ class EPMoE:
         self.y8 = torch.zeros(self.cap_rows, inter, dtype=torch.uint8, device=dev)
         self.ys = torch.ones(self.cap_rows, inter // 128, dtype=f32, device=dev)
         self.w = EPWeights(gate, up, down) if gate is not None else None
-        self.map_recv = _raw_map(self.recv8[fabric.rank], self.cap_rows, hidden)
-        self.map_y = K.act_tmap(self.y8)
+        self.stage = None                              # optional context-manager factory: per-kernel timing
+        self.map_recv = _raw_map(self.recv8[fabric.rank], self.cap_rows, hidden, item_rows)
+        self.map_y = K.act_tmap(self.y8, item_rows)
 
     def _local(self, nbytes: int) -> List[int]:
         t = torch.zeros(nbytes, dtype=torch.uint8, device=self.fab.device)
@@ -96,7 +102,7 @@ class EPMoE:
         a.x, a.gamma, a.eps = x.data_ptr(), None if gamma is None else gamma.data_ptr(), self.eps
         for i in range(K.K_MAX_PEERS):
             a.recv8[i], a.recvs[i], a.meta[i], a.flags[i] = self.recv8[i], self.recvs[i], self.meta[i], self.flags[i]
-        a.ticket, a.call = self.ticket.data_ptr(), CALL_DISPATCH
+        a.ticket, a.call, a.item_rows = self.ticket.data_ptr(), CALL_DISPATCH, self.item_rows
         a.x_args = self.fab.xchg_args()
         return a
 
@@ -110,12 +116,16 @@ class EPMoE:
         T = self.T if tokens is None else tokens
         if not 0 < T <= self.T:
             raise ValueError(f"{T} rows exceed the exchange buffers sized for {self.T}")
+        from contextlib import nullcontext
+        stage = self.stage or (lambda name: nullcontext())
         a = self._ep_args(x, gamma, ids, probs, T)
-        K.ep_count(a, pdl=pdl)
-        K.ep_dispatch(a, pdl=pdl)
+        with stage("moe.count"):
+            K.ep_count(a, pdl=pdl)
+        with stage("moe.dispatch"):
+            K.ep_dispatch(a, pdl=pdl)
         st = fab.status.data_ptr()
         g = K.GemmArgs()
-        g.n_total, g.k_total, g.rows, g.out_scale = self.I, self.H, 16, 1.0
+        g.n_total, g.k_total, g.rows, g.out_scale = self.I, self.H, self.item_rows, 1.0
         g.n_active, g.active_ids, g.max_slots = self.n_items.data_ptr(), self.item_expert.data_ptr(), self.max_items
         g.row_offsets = self.item_row.data_ptr()
         g.w_scale0, g.w_scale1, g.a_scale = w.gate_s.data_ptr(), w.up_s.data_ptr(), self.recvs[rank]
@@ -123,10 +133,12 @@ class EPMoE:
         g.fab = fab.fabric_args(0, self.H)
         g.fab.ag_call, g.fab.ag_flags = CALL_DISPATCH, self.flags[rank]
         g.status = st
-        K.gemm(K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM), w.map_gate, w.map_up, self.map_recv, g,
-               self.I // 128, self.max_items, pdl=pdl)
+        launch = K.wide_gemm if self.item_rows == K.WIDE_TOK else K.gemm
+        with stage("moe.gate_up"):
+            launch(K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM), w.map_gate, w.map_up, self.map_recv, g,
+                   self.I // 128, self.max_items, pdl=pdl)
         d = K.GemmArgs()
-        d.n_total, d.k_total, d.rows, d.out_scale = self.H, self.I, 16, 1.0
+        d.n_total, d.k_total, d.rows, d.out_scale = self.H, self.I, self.item_rows, 1.0
         d.n_active, d.active_ids, d.max_slots = self.n_items.data_ptr(), self.item_expert.data_ptr(), self.max_items
         d.row_offsets = self.item_row.data_ptr()
         d.w_scale0, d.a_scale = w.down_s.data_ptr(), self.ys.data_ptr()
@@ -136,11 +148,13 @@ class EPMoE:
         for i in range(K.K_MAX_PEERS):
             d.ep_combine[i] = self.combine[i]
         d.ep_dispatch_call, d.ep_return_call = CALL_DISPATCH, CALL_RETURN
-        K.gemm(K.gemm_variant(True, False, K.EPI_RETURN, K.GROUP_ITEM), w.map_down, None, self.map_y, d,
-               self.H // 128, self.max_items, pdl=pdl)
+        with stage("moe.down_return"):
+            launch(K.gemm_variant(True, False, K.EPI_RETURN, K.GROUP_ITEM), w.map_down, None, self.map_y, d,
+                   self.H // 128, self.max_items, pdl=pdl)
         c = K.EpCombineArgs()
         c.slots, c.topk_p, c.resid, c.out = self.combine[rank], probs.data_ptr(), resid.data_ptr(), out.data_ptr()
         c.epoch, c.status = fab.epoch.data_ptr(), st
         c.tokens, c.top_k, c.hidden, c.call, c.timeout_ns = T, self.K, self.H, CALL_RETURN, fab.timeout_ns
-        K.ep_combine(c, pdl=pdl)
-        K.epoch_advance(fab.epoch, pdl=pdl)
+        with stage("moe.combine"):
+            K.ep_combine(c, pdl=pdl)
+            K.epoch_advance(fab.epoch, pdl=pdl)

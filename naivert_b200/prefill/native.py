@@ -27,8 +27,10 @@ Parity: ``NativePrefill`` (naivert/prefill/native/executor.py: chunk body :479-5
 """
 from __future__ import annotations
 
+import os
+from contextlib import contextmanager
 from dataclasses import dataclass
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -83,27 +85,32 @@ class NativePrefill:
         if FULL_DSA in spec.layer_kinds and not t.use_sweep:
             raise ValueError("the chunked indexer needs the tcgen05 sweep geometry (16 heads x 128)")
         self.C = C = chunk
+        # 64-column chunk GEMM (a weight tile feeds 64 rows) unless NAIVERT_PREFILL_WIDE=0 or the chunk is not a
+        # multiple of 64 rows; otherwise the step engine's 16-column tiles in item mode
+        self.wide = os.environ.get("NAIVERT_PREFILL_WIDE", "1") == "1" and chunk % K.WIDE_TOK == 0
+        self.step = K.WIDE_TOK if self.wide else ROWS
+        # plain projections share one weight matrix over all items: let consecutive CTAs share weight tiles
+        self._gemm = (lambda *a, **k: K.wide_gemm(*a, items_fastest=True, **k)) if self.wide else K.gemm
         s, dev = spec, self.dev
         H = s.hidden
         bf, f32, i32, u8 = torch.bfloat16, torch.float32, torch.int32, torch.uint8
         self.pos = torch.zeros(4, dtype=i32, device=dev)                 # [0] = position of the chunk's row 0
-        self.pos_host = torch.zeros(4, dtype=i32).pin_memory()
         self.tokens = torch.zeros(C, dtype=i32, device=dev)
         self.x = torch.zeros(C, H, dtype=bf, device=dev)
         self.xn = torch.zeros(C, H, dtype=bf, device=dev)
         self.x8 = torch.zeros(C, H, dtype=u8, device=dev)
         self.xs = torch.ones(C, H // 128, dtype=f32, device=dev)
         self.part = torch.zeros(C, H, dtype=bf, device=dev)
-        self.map_xn, self.map_x8 = K.act_tmap(self.xn), K.act_tmap(self.x8)
+        self.map_xn, self.map_x8 = K.act_tmap(self.xn, self.step), K.act_tmap(self.x8, self.step)
         self.qkv = torch.zeros(C, t.qkv.shape[1], dtype=f32, device=dev)
         self.q = torch.zeros(C, t.q.shape[1], t.q.shape[2], dtype=bf, device=dev)
         self.o8 = torch.zeros(C, t.o8.shape[1], dtype=u8, device=dev)
         self.os = torch.ones(C, t.os.shape[1], dtype=f32, device=dev)
-        self.map_o8 = K.act_tmap(self.o8)
+        self.map_o8 = K.act_tmap(self.o8, self.step)
         self.rope = {k: torch.zeros(C, v.shape[1], 2, dtype=f32, device=dev) for k, v in t.rope.items()}
         self.idx_rope = torch.zeros(C, t.idx_rope.shape[1], 2, dtype=f32, device=dev)
-        self.items = C // ROWS
-        self.row_offsets = (torch.arange(self.items, dtype=i32, device=dev) * ROWS).contiguous()
+        self.items = C // self.step
+        self.row_offsets = (torch.arange(self.items, dtype=i32, device=dev) * self.step).contiguous()
         self.zero_ids = torch.zeros(self.items, dtype=i32, device=dev)
         self.n_items = torch.zeros(1, dtype=i32, device=dev)
         ix = s.indexer
@@ -117,7 +124,7 @@ class NativePrefill:
             Id = s.dense_inter_local(self.tp)
             self.yd8 = torch.zeros(C, Id, dtype=u8, device=dev)
             self.yds = torch.ones(C, Id // 128, dtype=f32, device=dev)
-            self.map_yd8 = K.act_tmap(self.yd8)
+            self.map_yd8 = K.act_tmap(self.yd8, self.step)
         # ---- MoE
         rt = s.routing
         self.T = C // self.tp if self.ep else C                            # rows a rank routes
@@ -134,7 +141,7 @@ class NativePrefill:
         self.moe_w: List[Optional[EPWeights]] = []
         if has_moe:
             inter = rt.intermediate if self.ep else s.expert_inter_local(self.tp)
-            self.moe = EPMoE(self.moe_fab, H, inter, rt.expert_count, rt.top_k, self.T, eps=s.norm_eps)
+            self.moe = EPMoE(self.moe_fab, H, inter, rt.expert_count, rt.top_k, self.T, eps=s.norm_eps, item_rows=self.step)
             for L, d in enumerate(t.layers):
                 if "gate" not in d:
                     self.moe_w.append(None)
@@ -148,19 +155,24 @@ class NativePrefill:
             taps = len(s.draft.target_layer_ids)
             Hd = s.draft.hidden
             self.feats = torch.zeros(C, max(1, taps) * H, dtype=bf, device=dev)
-            self.map_feats = K.act_tmap(self.feats[:, self.rank * draft.kf:(self.rank + 1) * draft.kf])
+            self.map_feats = K.act_tmap(self.feats[:, self.rank * draft.kf:(self.rank + 1) * draft.kf], self.step)
             self.dh = torch.zeros(C, Hd, dtype=bf, device=dev)
             self.dxn = torch.zeros(C, Hd, dtype=bf, device=dev)
-            self.map_dxn = K.act_tmap(self.dxn)
+            self.map_dxn = K.act_tmap(self.dxn, self.step)
             self.draw = torch.zeros(C, draft.wkv.shape[0], dtype=f32, device=dev)
             self.drope = torch.zeros(C, s.draft.head_dim // 2, 2, dtype=f32, device=dev)
         self.phases: dict = {}
+        # grouped-head attention kernel; NAIVERT_PREFILL_GROUP_ATTN=0 keeps the per-head row kernel of the step
+        # path (bitwise-comparable with replay)
+        self.group_attn = os.environ.get("NAIVERT_PREFILL_GROUP_ATTN", "1") == "1"
+        self.profile = False                         # per-stage CUDA-event timing (adds an event pair per stage)
+        self._timed: Dict[str, list] = {}
         self._build_args()
 
     # ------------------------------------------------------------------ argument blocks
     def _item_args(self, n, k) -> K.GemmArgs:
         g = K.GemmArgs()
-        g.n_total, g.k_total, g.rows, g.a_group, g.out_scale = n, k, ROWS, 0, 1.0
+        g.n_total, g.k_total, g.rows, g.a_group, g.out_scale = n, k, self.step, 0, 1.0
         g.n_active, g.active_ids, g.max_slots = self.n_items.data_ptr(), self.zero_ids.data_ptr(), self.items
         g.row_offsets = self.row_offsets.data_ptr()
         g.status = self.t.fab.status.data_ptr()
@@ -193,6 +205,8 @@ class NativePrefill:
             if d["kind"] == FULL_DSA:
                 q.sel = self.sel.data_ptr()
             e["attn"] = q
+            # one CTA per (KV head, row) shares every gathered key among the group's query heads
+            e["group_attn"] = self.group_attn and a.head_dim == 192 and a.v_head_dim == 128 and nh // nkv <= 16
             g = self._item_args(H, d["wo"].k)
             g.w_scale0, g.a_scale = d["wo"].s.data_ptr(), self.os.data_ptr()
             g.out_bf16, g.ld_out = self.part.data_ptr(), H
@@ -231,6 +245,24 @@ class NativePrefill:
                 p.qkv, p.ld, p.pos0, p.rope = self.draw.data_ptr(), self.draw.shape[1], pos0, self.drope.data_ptr()
                 self.args_ingest.append(p)
 
+    @contextmanager
+    def _stage(self, name: str):
+        if not self.profile:
+            yield
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        yield
+        b.record()
+        self._timed.setdefault(name, []).append((a, b))
+
+    def stage_ms(self) -> Dict[str, float]:
+        """Device milliseconds per stage since the last call (``profile`` must be on); waits for the stream."""
+        torch.cuda.current_stream().synchronize()
+        out = {k: round(sum(a.elapsed_time(b) for a, b in v), 3) for k, v in self._timed.items()}
+        self._timed = {}
+        return out
+
     # ------------------------------------------------------------------ collectives (NCCL on the current stream)
     def _all_reduce(self, buf: torch.Tensor) -> None:
         if self.tp > 1:
@@ -240,9 +272,8 @@ class NativePrefill:
     def _chunk(self, pos0: int, R: int) -> None:
         s, t, tp = self.spec, self.t, self.tp
         H, pdl = s.hidden, False
-        items = R // ROWS
-        self.pos_host[0] = pos0
-        self.pos.copy_(self.pos_host, non_blocking=True)
+        items = -(-R // self.step)
+        self.pos.fill_(pos0)
         self.n_items.fill_(items)
         x, xn, part = self.x, self.xn, self.part
         K.embed_rows(self.tokens, t.embed, x, R, pdl=pdl)
@@ -255,66 +286,84 @@ class NativePrefill:
         xl = x[self.rank * T:(self.rank + 1) * T] if self.ep else x[:R]
         for L, (d, e) in enumerate(zip(t.layers, self.L)):
             # ---- attention (tensor parallel)
-            K.prep_norm(x, d["g_in"], R, s.norm_eps, xn=xn, pdl=pdl)
-            K.gemm(self.V_BF16_F32, d["map_qkv"], None, self.map_xn, e["qkv"], d["wqkv"].shape[0] // 128, items, pdl=pdl)
+            with self._stage("norm"):
+                K.prep_norm(x, d["g_in"], R, s.norm_eps, xn=xn, pdl=pdl)
+            with self._stage("qkv_gemm"):
+                self._gemm(self.V_BF16_F32, d["map_qkv"], None, self.map_xn, e["qkv"], d["wqkv"].shape[0] // 128, items, pdl=pdl)
             e["post"].rows = R
-            K.attn_post(e["post"], pdl=pdl)
+            with self._stage("attn_post"):
+                K.attn_post(e["post"], pdl=pdl)
             if d["kind"] == FULL_DSA and pos0 + R > s.indexer.top_k:
                 e["sweep"].rows = R
                 tiles = -(-(pos0 + R) // 128)
-                K.index_sweep(*e["sweep_maps"], e["sweep"], max(1, min(tiles, 592 // items)), pdl=pdl)
-                if t.topk_grid:
-                    K.topk_rows_grid(self.idx_logits, self.pos, R, s.indexer.top_k, self.sel, self.topk_state, 16, pdl=pdl)
-                else:
-                    K.topk_rows(self.idx_logits, self.pos, R, s.indexer.top_k, self.sel, pdl=pdl)
+                with self._stage("index_sweep"):
+                    K.index_sweep(*e["sweep_maps"], e["sweep"], max(1, min(tiles, 592 // (R // ROWS))), pdl=pdl)
+                with self._stage("topk"):
+                    if t.topk_grid:
+                        K.topk_rows_grid(self.idx_logits, self.pos, R, s.indexer.top_k, self.sel, self.topk_state, 16, pdl=pdl)
+                    else:
+                        K.topk_rows(self.idx_logits, self.pos, R, s.indexer.top_k, self.sel, pdl=pdl)
             e["attn"].rows = R
-            K.attn_rows(e["attn"], 1, pdl=pdl)
-            K.gemm(self.V_FP8_BF16, d["wo"].map, None, self.map_o8, e["o"], H // 128, items, pdl=pdl)
+            with self._stage("attn_dsa" if d["kind"] == FULL_DSA else "attn_swa"):
+                if e["group_attn"]:
+                    K.attn_group(e["attn"], pdl=pdl)
+                else:
+                    K.attn_rows(e["attn"], 1, pdl=pdl)
+            with self._stage("o_gemm"):
+                self._gemm(self.V_FP8_BF16, d["wo"].map, None, self.map_o8, e["o"], H // 128, items, pdl=pdl)
             moe = "dense" not in d
-            if self.ep and moe:
-                # sequence parallel from here to the end of the layer: this rank keeps rows [rank*T, (rank+1)*T)
-                dist.reduce_scatter_tensor(self.rs[:T], part[:R], group=self.group)
-                torch.add(xl, self.rs[:T], out=self.xl[:T])
-            else:
-                self._all_reduce(part[:R])
-                torch.add(x[:R], part[:R], out=x[:R])
+            with self._stage("tp_reduce"):
+                if self.ep and moe:
+                    # sequence parallel from here to the end of the layer: this rank keeps rows [rank*T, (rank+1)*T)
+                    dist.reduce_scatter_tensor(self.rs[:T], part[:R], group=self.group)
+                    torch.add(xl, self.rs[:T], out=self.xl[:T])
+                else:
+                    self._all_reduce(part[:R])
+                    torch.add(x[:R], part[:R], out=x[:R])
             # ---- MLP
             if not moe:
                 dn = d["dense"]
-                K.prep_norm(x, d["g_post"], R, s.norm_eps, x8=self.x8, xs=self.xs, pdl=pdl)
-                K.gemm(self.V_FP8_GU, dn["gate"].map, dn["up"].map, self.map_x8, e["gu"], dn["gate"].n // 128, items, pdl=pdl)
-                K.gemm(self.V_FP8_BF16, dn["down"].map, None, self.map_yd8, e["down"], H // 128, items, pdl=pdl)
-                self._all_reduce(part[:R])
-                torch.add(x[:R], part[:R], out=x[:R])
-            else:
-                src = self.xl if self.ep else x
-                K.prep_norm(src, d["g_post"], T, s.norm_eps, xn=xn, pdl=pdl)
-                e["router"].rows = T
-                K.router(e["router"], pdl=pdl)
-                if self.ep:
-                    self.moe.run(src, d["g_post"], self.topk_ids, self.topk_p, src, src, weights=self.moe_w[L], tokens=T)
-                    dist.all_gather_into_tensor(x[:R], src[:T], group=self.group)
-                elif tp == 1:
-                    self.moe.run(src, d["g_post"], self.topk_ids, self.topk_p, src, src, weights=self.moe_w[L], tokens=T)
-                else:
-                    self.moe.run(src, d["g_post"], self.topk_ids, self.topk_p, self.zeros, part, weights=self.moe_w[L], tokens=T)
+                with self._stage("dense_mlp"):
+                    K.prep_norm(x, d["g_post"], R, s.norm_eps, x8=self.x8, xs=self.xs, pdl=pdl)
+                    self._gemm(self.V_FP8_GU, dn["gate"].map, dn["up"].map, self.map_x8, e["gu"], dn["gate"].n // 128, items, pdl=pdl)
+                    self._gemm(self.V_FP8_BF16, dn["down"].map, None, self.map_yd8, e["down"], H // 128, items, pdl=pdl)
+                with self._stage("tp_reduce"):
                     self._all_reduce(part[:R])
                     torch.add(x[:R], part[:R], out=x[:R])
+            else:
+                src = self.xl if self.ep else x
+                with self._stage("router"):
+                    K.prep_norm(src, d["g_post"], T, s.norm_eps, xn=xn, pdl=pdl)
+                    e["router"].rows = T
+                    K.router(e["router"], pdl=pdl)
+                self.moe.stage = self._stage if self.profile else None
+                with self._stage("moe"):
+                    if self.ep or tp == 1:
+                        self.moe.run(src, d["g_post"], self.topk_ids, self.topk_p, src, src, weights=self.moe_w[L], tokens=T)
+                    else:
+                        self.moe.run(src, d["g_post"], self.topk_ids, self.topk_p, self.zeros, part, weights=self.moe_w[L], tokens=T)
+                with self._stage("tp_reduce"):
+                    if self.ep:
+                        dist.all_gather_into_tensor(x[:R], src[:T], group=self.group)
+                    elif tp > 1:
+                        self._all_reduce(part[:R])
+                        torch.add(x[:R], part[:R], out=x[:R])
             tap = t.tap_of_layer.get(L)
             if tap is not None and self.draft is not None:
                 self.feats[:R, tap * H:(tap + 1) * H].copy_(x[:R])
         if self.draft is not None:
-            self._ingest(R, items)
+            with self._stage("draft_ingest"):
+                self._ingest(R, items)
 
     def _ingest(self, R: int, items: int) -> None:
         """Draft context for the chunk's rows: fc over this rank's feature taps (reduced over the ranks),
         RMSNorm, every draft layer's k/v projection in one GEMM, k-norm + RoPE + append."""
         dr, dd, pdl = self.draft, self.spec.draft, False
         K.rope_table(self.pos, R, dd.head_dim, dd.rope_theta, self.drope, pdl=pdl)
-        K.gemm(self.V_BF16_BF16, dr.map_fc, None, self.map_feats, self.args_fc, dd.hidden // 128, items, pdl=pdl)
+        self._gemm(self.V_BF16_BF16, dr.map_fc, None, self.map_feats, self.args_fc, dd.hidden // 128, items, pdl=pdl)
         self._all_reduce(self.dh[:R])
         K.prep_norm(self.dh, dr.hidden_norm, R, dd.norm_eps, xn=self.dxn, pdl=pdl)
-        K.gemm(self.V_BF16_F32, dr.map_kv, None, self.map_dxn, self.args_kv, dr.wkv.shape[0] // 128, items, pdl=pdl)
+        self._gemm(self.V_BF16_F32, dr.map_kv, None, self.map_dxn, self.args_kv, dr.wkv.shape[0] // 128, items, pdl=pdl)
         for p in self.args_ingest:
             p.rows = R
             K.attn_post(p, pdl=pdl)

@@ -34,6 +34,9 @@ def main():
     sl = slice(rank * El, (rank + 1) * El)
     fab = Fabric(rank, world, H, group=dist.group.WORLD if world > 1 else None, device=dev)
     moe = EPMoE(fab, H, I, E, Kk, T, {"w": g8[sl], "s": gs[sl]}, {"w": u8[sl], "s": us[sl]}, {"w": d8[sl], "s": ds[sl]})
+    # the same layer on the 64-column chunk engine (segments padded to 64 rows)
+    moe64 = EPMoE(fab, H, I, E, Kk, T, {"w": g8[sl], "s": gs[sl]}, {"w": u8[sl], "s": us[sl]}, {"w": d8[sl], "s": ds[sl]},
+                  item_rows=64)
     x, ids, probs = x_all[rank].contiguous(), ids_all[rank].int().contiguous(), p_all[rank].contiguous()
     out = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
     outs = []
@@ -42,6 +45,10 @@ def main():
         moe.run(x, gamma, ids, probs, x, out)
         torch.cuda.synchronize()
         outs.append(out.clone())
+    out.zero_()
+    moe64.run(x, gamma, ids, probs, x, out)
+    torch.cuda.synchronize()
+    out64 = out.clone()
     fab.check()
     # torch reference of this rank's tokens
     xf = x.float()
@@ -60,11 +67,14 @@ def main():
     dd = (outs[0].float() - outs[1].float()).abs()
     res = {"world": world, "max_rel_err": err, "first_err": err0, "diff_rows": dd.amax(-1).nonzero().flatten().tolist()[:12],
            "diff_max": dd.max().item(), "repeat_identical": bool(torch.equal(outs[0], outs[1])),
-           "items": int(moe.n_items), "rows": int(moe.seg_rows.sum()), "status": int(fab.status[0])}
+           "items": int(moe.n_items), "rows": int(moe.seg_rows.sum()), "status": int(fab.status[0]),
+           "wide_identical": bool(torch.equal(out64, outs[1])), "wide_items": int(moe64.n_items),
+           "wide_err": ((out64.float() - ref).abs().max() / ref.abs().max()).item()}
     if world > 1:
         allr = [None] * world
         dist.all_gather_object(allr, res)
-        res["worst_err"] = max(r["max_rel_err"] for r in allr)
+        res["worst_err"] = max(max(r["max_rel_err"], r["wide_err"]) for r in allr)
+        res["wide_identical"] = all(r["wide_identical"] for r in allr)
         res["total_rows"] = sum(r["rows"] for r in allr)
     if rank == 0:
         print("RESULT " + json.dumps(res), flush=True)

@@ -123,6 +123,50 @@ def test_attention_rows_match_torch():
                 assert (got - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3, (mode, r, h)
 
 
+def test_grouped_head_attention_matches_row_attention():
+    """The prefill attention kernel (all query heads of a KV head in one CTA, tensor-core tiles) against the
+    per-head row kernel: sliding window with sink, dense prefix, and selection lists; 40 rows."""
+    from naivert_b200.ops import kernels as K
+    K.lib()
+    g = torch.Generator(device="cuda").manual_seed(4)
+    hd, vd, rows, window = 192, 128, 40, 128
+    for heads, kvh in ((32, 2), (8, 4), (8, 8)):
+        for mode, pos0, top_k in ((0, 700, 0), (1, 100, 4096), (1, 900, 256)):
+            cap, ring = 1024, window + 48
+            q = torch.randn(rows, heads, hd, device="cuda", generator=g).bfloat16()
+            kc = torch.randn(cap, kvh, hd, device="cuda", generator=g).bfloat16()
+            vc = torch.randn(cap, kvh, vd, device="cuda", generator=g).bfloat16()
+            sink = torch.randn(heads, device="cuda", generator=g).bfloat16()
+            p = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+            sel = torch.stack([torch.sort(torch.randperm(pos0 + r + 1, device="cuda", generator=g)[:max(1, top_k)])[0]
+                               for r in range(rows)]).int().contiguous() if top_k == 256 else None
+            outs = []
+            for fn in ("rows", "group"):
+                o = torch.zeros(rows, heads * vd, device="cuda", dtype=torch.bfloat16)
+                o8 = torch.zeros(rows, heads * vd, device="cuda", dtype=torch.uint8)
+                osc = torch.zeros(rows, heads, device="cuda")
+                a = K.AttnArgs()
+                a.q, a.pos0, a.rows, a.heads, a.kv_heads, a.head_dim, a.v_dim = q.data_ptr(), p.data_ptr(), rows, heads, kvh, hd, vd
+                a.scale, a.mode, a.o_bf16, a.o8, a.o_scale = hd ** -0.5, mode, o.data_ptr(), o8.data_ptr(), osc.data_ptr()
+                if mode == 0:
+                    kr = torch.zeros(ring, kvh, hd, device="cuda", dtype=torch.bfloat16)
+                    vr = torch.zeros(ring, kvh, vd, device="cuda", dtype=torch.bfloat16)
+                    for t in range(pos0 + rows - ring, pos0 + rows):
+                        kr[t % ring], vr[t % ring] = kc[t], vc[t]
+                    a.k_cache, a.v_cache, a.window, a.ring, a.sink = kr.data_ptr(), vr.data_ptr(), window, ring, sink.data_ptr()
+                else:
+                    a.k_cache, a.v_cache, a.top_k = kc.data_ptr(), vc.data_ptr(), top_k
+                    if sel is not None:
+                        a.sel = sel.data_ptr()
+                (K.attn_rows if fn == "rows" else K.attn_group)(a, pdl=False)
+                torch.cuda.synchronize()
+                outs.append((o.float(), o8.view(torch.float8_e4m3fn).float() * osc.repeat_interleave(vd, 1)))
+            (ref, ref8), (got, got8) = outs
+            tol = 0.02 * ref.abs().max().item()
+            assert (got - ref).abs().max().item() <= tol, (heads, kvh, mode, pos0)
+            assert (got8 - ref8).abs().max().item() <= 0.08 * ref.abs().max().item(), (heads, kvh, mode, pos0)
+
+
 def test_tcgen05_index_sweep_matches_cuda_core_form():
     from naivert_b200.ops import kernels as K
     spec, rt, _ = _build(layers=1, capacity=2048)
