@@ -79,6 +79,8 @@ def main() -> int:
     ap.add_argument("--pdl", action="store_true", help="chain kernels with programmatic dependent launch (default: plain stream order, measured faster)")
     ap.add_argument("--device-chain", action="store_true", help="the round graph relaunches itself from the device")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
+    ap.add_argument("--prefill-chunk", type=int, default=2048,
+                    help="rows per chunk of the native prompt ingestion (0: eight-row replay only); outside the timed rounds")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -113,7 +115,7 @@ def main() -> int:
     capacity = -(-capacity // 128) * 128
     t_build = time.perf_counter()
     eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=capacity, seed=0, device=dev, pdl=a.pdl, shape_tp=a.shape_tp,
-                       device_chain=a.device_chain)
+                       device_chain=a.device_chain, prefill_chunk=0 if a.shape_tp else a.prefill_chunk)
     build_s = time.perf_counter() - t_build
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
 
@@ -221,7 +223,7 @@ def main() -> int:
             "gpu_launches": int(r.kernels_per_round * a.steps),
             "kernels_per_round": int(r.kernels_per_round),
             "diagnostic_shape_tp": a.shape_tp or None,
-            "build_s": round(build_s, 2), "prefill_s": round(prefill_s, 3),
+            "build_s": round(build_s, 2), "prefill_s": round(prefill_s, 3), "prefill": eng.last_prefill,
             "kv_bytes_per_gpu": eng.kv_bytes(),
         }
         print(json.dumps(out))

@@ -40,7 +40,8 @@ def main():
     dw = prepare_draft_weights(spec, init_draft_state_dict(spec, seed=1, device=dev))
     eng = Engine.build(spec, rank=rank, tp=world, group=dist.group.WORLD if world > 1 else None, capacity=2048, device=dev,
                        weights=shard_weights(spec, w, rank, world), draft_weights=shard_draft_weights(spec, dw, rank, world),
-                       prefill_chunk=256, ep_weights=shard_expert_weights(spec, w, rank, world) if world > 1 else None)
+                       prefill_chunk=256,
+                       ep_weights=shard_expert_weights(spec, w, rank, world) if (world > 1 and os.environ.get("PREFILL_MOE", "ep") == "ep") else None)
     if world == 1:
         eng.target.attn_splits = 1
     g = torch.Generator().manual_seed(3)
@@ -91,7 +92,7 @@ def main():
     info = dict(eng.last_prefill)
     got2, got2_toks = run(True)
     errs = {k: rel(got[k], ref[k]) for k in ref}
-    out = {"world": world, "prefill": info, "errs": {k: round(v, 5) for k, v in errs.items()},
+    out = {"world": world, "prefill": info, "moe": "ep" if eng.prefill.ep else ("local" if world == 1 else "tp"), "errs": {k: round(v, 5) for k, v in errs.items()},
            "bitwise": sorted(k for k in ref if torch.equal(got[k], ref[k])),
            "repeat_identical": all(torch.equal(got[k], got2[k]) for k in got) and got_toks == got2_toks,
            "worst": max(errs.values()), "tokens_ref": ref_toks[:12], "tokens_native": got_toks[:12],

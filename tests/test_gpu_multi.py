@@ -70,3 +70,13 @@ def test_native_prefill_matches_replay(n, exact):
         assert r["lockstep"], r
     assert r["worst"] < 0.1, r
     assert r["token_prefix_agreement"] >= 1, r
+
+
+def test_native_prefill_tensor_parallel_experts():
+    """Without expert-parallel weight copies every rank runs all rows through its slice of every expert and the
+    partial sums are all-reduced (the path bench.py uses for its prompt)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _run_worker(2, "mp_prefill_worker.py", PREFILL_MOE="tp")
+    assert r["moe"] == "tp" and r["status"] == 0 and r["repeat_identical"] and r["lockstep"], r
+    assert r["prefill"]["path"] == "native" and r["worst"] < 0.1 and r["token_prefix_agreement"] >= 1, r
