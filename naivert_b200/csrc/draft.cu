@@ -7,6 +7,7 @@
 // (W2_shard is 9.7 MB per rank at tp = 8 and stays L2 resident across the seven steps).
 // Reference math: naivert/body/dspark_head_markov/markov_body.cuh:6-27,
 // naivert/body/dspark_sampling/random.cuh:17-20 (Gumbel-max over (logits + bias) / T).
+#include "contract.h"
 #include "fabric.cuh"
 #include "launch.hpp"
 
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
   __syncthreads();
   const float inv_t = a.params[6];
   const unsigned long long seed = *a.seed;
-  const uint32_t ctr = (uint32_t)a.ctrl[8] * 8u + (uint32_t)step;
+  const uint32_t ctr = (uint32_t)a.ctrl[NRT_CTRL_ROUND] * 8u + (uint32_t)step;
   unsigned long long best = 0ull;
   // 8 lanes cooperate on one token row (rank_dim bf16 = 64 bytes per lane at rank 256), 4 rows per warp
   // at a time: every 16-byte load of a warp is part of a fully used 128-byte line.

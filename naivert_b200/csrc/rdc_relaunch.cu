@@ -6,6 +6,7 @@
 // (does not relaunch) when it is a ring length ahead, and the host restarts it with an ordinary launch.
 // Reference counterpart: naivert/entry/dspark_tail_entry.cu:16-23
 // (cudaGraphLaunch(cudaGetCurrentGraphExec(), cudaStreamGraphTailLaunch)).
+#include "contract.h"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -14,12 +15,12 @@ namespace {
 // ctrl[4] stopped, ctrl[5] reason, ctrl[8] round counter, ctrl[12] relaunch failures, ctrl[13] paused
 __global__ void relaunch_kernel(int* ctrl, const volatile int* host_consumed, int ring_size) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  if (ctrl[4]) return;
-  const int ahead = ctrl[8] - *host_consumed;
-  if (ahead >= ring_size - 8) { ctrl[13] = 1; return; }          // let the host catch up
-  ctrl[13] = 0;
+  if (ctrl[NRT_CTRL_STOPPED]) return;
+  const int ahead = ctrl[NRT_CTRL_ROUND] - *host_consumed;
+  if (ahead >= ring_size - 8) { ctrl[NRT_CTRL_PAUSED] = 1; return; }          // let the host catch up
+  ctrl[NRT_CTRL_PAUSED] = 0;
   const cudaError_t e = cudaGraphLaunch(cudaGetCurrentGraphExec(), cudaStreamGraphTailLaunch);
-  if (e != cudaSuccess) { ctrl[12] += 1; ctrl[4] = 1; ctrl[5] = 6; }   // fail closed: chain launch failed
+  if (e != cudaSuccess) { ctrl[NRT_CTRL_RELAUNCH_FAIL] += 1; ctrl[NRT_CTRL_STOPPED] = 1; ctrl[NRT_CTRL_REASON] = NRT_STOP_RELAUNCH_FAILED; }   // fail closed: chain launch failed
 }
 
 }  // namespace

@@ -17,6 +17,7 @@
 // Rows 0..7 are the target distributions, rows 8..14 the draft distributions.
 // Reference: naivert/body/dspark_sampling/{sharded,persistent,parallel}.cuh (math),
 // random.cuh (Philox domains), naivert/body/dspark_tail/{body,commit}.cuh (accept prefix, commit).
+#include "contract.h"
 #include "fabric.cuh"
 #include "launch.hpp"
 
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
   xchg_reduce_u64<kXSum>(xv, 8, a.x, 6);
   if (threadIdx.x == 0) {
     const unsigned long long seed = *a.seed;
-    const uint32_t round = (uint32_t)a.ctrl[8];
+    const uint32_t round = (uint32_t)a.ctrl[NRT_CTRL_ROUND];
     const float forced = a.params[5];
     int m = 0;
     for (; m < a.n_rows_q; ++m) {
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a
   const int xo = from_p ? 8 : 0, mo = from_p ? 128 : 0;
   total = 0ull;
   for (int r = 0; r < a.x.tp; ++r) { if (r < a.x.rank) before += xv[xo + r]; total += xv[xo + r]; }
-  const double u = (double)philox_uniform(*a.seed, (uint32_t)domain, (uint32_t)a.ctrl[8], (uint32_t)m);
+  const double u = (double)philox_uniform(*a.seed, (uint32_t)domain, (uint32_t)a.ctrl[NRT_CTRL_ROUND], (uint32_t)m);
   unsigned long long target = (unsigned long long)(u * (double)total);
   if (total > 0ull && target >= total) target = total - 1ull;
   const bool mine = total > 0ull && target >= before && target < before + xv[xo + a.x.rank];
@@ -435,32 +436,32 @@ __global__ void tail_commit_kernel(const TailArgs a) {
   const bool cancel_any = xv[0] != 0ull, failed_any = xv[1] != 0ull;
   if (threadIdx.x != 0) return;
   int* c = a.ctrl;
-  const int round = c[8];
-  if (c[4]) {                                  // already stopped: keep the fabric epoch moving, publish nothing
+  const int round = c[NRT_CTRL_ROUND];
+  if (c[NRT_CTRL_STOPPED]) {                                  // already stopped: keep the fabric epoch moving, publish nothing
     // The round that just ran completed the draft context of the last committed rows; any further
     // round must not overwrite it with features of rows that were never committed.
-    c[2] = c[0];
+    c[NRT_CTRL_INGEST_POS] = c[NRT_CTRL_POS];
     *a.epoch += 1u;
-    c[8] = round + 1;
+    c[NRT_CTRL_ROUND] = round + 1;
     return;
   }
   const int m = a.st->accepted;
-  const int pos0 = c[0];
+  const int pos0 = c[NRT_CTRL_POS];
   int reason = 0, n = 0;
   int out[8];
-  if (failed_any) reason = 5;
-  else if (cancel_any) reason = 4;
+  if (failed_any) reason = NRT_STOP_DEVICE_WAIT_FAILED;
+  else if (cancel_any) reason = NRT_STOP_CANCELLED;
   for (int j = 0; j <= m && reason == 0; ++j) {
     const int tok = j < m ? a.block_ids[j + 1] : a.st->extra_token;
     out[n++] = tok;
-    c[6] += 1;
+    c[NRT_CTRL_GENERATED] += 1;
     const int local = tok - a.vbase;
     if (a.counts && local >= 0 && local < a.vlocal && a.counts[local] < 65535) a.counts[local] += 1;
     for (int s = 0; s < a.n_stop; ++s)
-      if (tok == a.stop_ids[s]) reason = 1;
-    if (reason == 0 && c[6] >= c[7]) reason = 2;
+      if (tok == a.stop_ids[s]) reason = NRT_STOP_EOS;
+    if (reason == 0 && c[NRT_CTRL_GENERATED] >= c[NRT_CTRL_MAX_TOKENS]) reason = NRT_STOP_MAX_TOKENS;
   }
-  if (reason == 0 && pos0 + n + 16 >= c[9]) reason = 3;
+  if (reason == 0 && pos0 + n + 16 >= c[NRT_CTRL_CAPACITY]) reason = NRT_STOP_CAPACITY;
   RingRecord* rec = a.ring + (round % a.ring_size);
   rec->count = n;
   for (int j = 0; j < 8; ++j) rec->tokens[j] = j < n ? out[j] : -1;
@@ -472,13 +473,13 @@ __global__ void tail_commit_kernel(const TailArgs a) {
   *reinterpret_cast<volatile unsigned int*>(&rec->generation) = (unsigned int)round + 1u;
   // next round: rows 0..n-1 of this verify are committed context
   if (n > 0) {
-    c[2] = pos0;
-    c[1] = n;
-    c[0] = pos0 + n;
+    c[NRT_CTRL_INGEST_POS] = pos0;
+    c[NRT_CTRL_COMMITTED] = n;
+    c[NRT_CTRL_POS] = pos0 + n;
     a.block_ids[0] = out[n - 1];
   }
-  if (reason) { c[4] = 1; c[5] = reason; }
-  c[8] = round + 1;
+  if (reason) { c[NRT_CTRL_STOPPED] = 1; c[NRT_CTRL_REASON] = reason; }
+  c[NRT_CTRL_ROUND] = round + 1;
   *a.epoch += 1u;
 }
 
@@ -487,14 +488,14 @@ __global__ void tail_commit_kernel(const TailArgs a) {
 __global__ void prefill_cursor_kernel(const int* __restrict__ prompt, int n_prompt, int rows, int* ctrl, int* tokens) {
   griddep_launch();
   griddep_wait();
-  const int cur = ctrl[10];
-  if (n_prompt < 0) n_prompt = ctrl[11];          // length kept in the control block (graph replays)
+  const int cur = ctrl[NRT_CTRL_CURSOR];
+  if (n_prompt < 0) n_prompt = ctrl[NRT_CTRL_PROMPT_CTX];          // length kept in the control block (graph replays)
   if (threadIdx.x < 16) {
     const int t = cur + (int)threadIdx.x;
     tokens[threadIdx.x] = ((int)threadIdx.x < rows && t < n_prompt) ? prompt[t] : 0;
   }
   __syncthreads();
-  if (threadIdx.x == 0) { ctrl[0] = cur; ctrl[2] = cur; ctrl[10] = cur + rows; }
+  if (threadIdx.x == 0) { ctrl[NRT_CTRL_POS] = cur; ctrl[NRT_CTRL_INGEST_POS] = cur; ctrl[NRT_CTRL_CURSOR] = cur + rows; }
 }
 
 // advance the fabric epoch (eager steps outside a round)

@@ -92,3 +92,42 @@ def w8a8_linear_ref(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
         part = xa[:, b] @ wa[:, b].T                           # exact products, fp32 accumulate
         out = out + part * (xs[:, b, None] * ws[None, :, b])
     return out
+
+
+# --------------------------------------------------------------------------- power-of-two (UE8M0) scale variants
+def ue8m0_round_up(scale: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= scale (the exponent-only 'UE8M0' scale format); zeros map to one."""
+    s = scale.float()
+    m, e = torch.frexp(s)                       # s = m * 2^e, m in [0.5, 1)
+    e = torch.where(m == 0.5, e - 1, e)
+    out = torch.ldexp(torch.ones_like(s), e)
+    return torch.where(s > 0, out, torch.ones_like(s))
+
+
+def requant_block_ue8m0(w8: torch.Tensor, scale_inv: torch.Tensor, block: int = BLOCK):
+    """Re-express block-scaled e4m3 weights with power-of-two block scales: dequantise, round every block
+    scale up to a power of two, quantise again.  Values change by at most one e4m3 rounding.
+    Parity: the UE8M0 re-quantisation of expert weights in naivert/kernels/naive_n0p5/prefill.py."""
+    w = dequant_block(w8, scale_inv, block)
+    s2 = ue8m0_round_up(scale_inv)
+    n, k = w.shape[-2], w.shape[-1]
+    sf = s2.repeat_interleave(block, -2)[..., :n, :].repeat_interleave(block, -1)[..., :k]
+    return (w / sf).clamp(-448, 448).to(torch.float8_e4m3fn), s2
+
+
+def quantize_mxfp8(x: torch.Tensor, group: int = 32):
+    """MX-style e4m3: one power-of-two scale per ``group`` consecutive elements of the last dimension.
+    Returns (e4m3 tensor, scales [..., K / group]).  Parity: the mxfp8 packers of naivert/kernels/packing.py."""
+    xf = x.float()
+    k = xf.shape[-1]
+    if k % group:
+        raise ValueError(f"last dimension {k} is not a multiple of {group}")
+    g = xf.reshape(*xf.shape[:-1], k // group, group)
+    s = pow2_scale(g.abs().amax(-1))
+    q = (g / s.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q.reshape(xf.shape), s
+
+
+def dequant_mxfp8(q: torch.Tensor, s: torch.Tensor, group: int = 32) -> torch.Tensor:
+    k = q.shape[-1]
+    return (q.float().reshape(*q.shape[:-1], k // group, group) * s.unsqueeze(-1)).reshape(q.shape)

@@ -23,10 +23,10 @@ import torch
 
 from ..models.spec import ModelSpec, SamplingParams
 from ..ops import kernels as K
+from .contract import (CTRL_CAPACITY, CTRL_CURSOR, CTRL_MAX_TOKENS, CTRL_PROMPT_CTX, STOP_REASONS)
 from .draft import DraftRuntime
 from .target import PAD_ROWS, TargetRuntime
 
-STOP_REASONS = {0: None, 1: "eos", 2: "output_limit", 3: "position_limit", 4: "cancelled", 5: "device_wait_failed"}
 RING_SIZE = 1024
 
 
@@ -190,7 +190,7 @@ class SpeculativeRound:
         ctrl = torch.zeros(16, dtype=torch.int32)
         if not 0 <= start_pos <= n - 1:
             raise RuntimeContractError(f"resume position {start_pos} outside the prompt context 0..{n - 1}")
-        ctrl[7], ctrl[9], ctrl[10], ctrl[11] = max_tokens, self.capacity, start_pos, n - 1
+        ctrl[CTRL_MAX_TOKENS], ctrl[CTRL_CAPACITY], ctrl[CTRL_CURSOR], ctrl[CTRL_PROMPT_CTX] = max_tokens, self.capacity, start_pos, n - 1
         self.t.ctrl.copy_(ctrl)
         self.counts.zero_()
         self.fab.status.zero_()

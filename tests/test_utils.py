@@ -68,3 +68,85 @@ def test_prefill_chunk_plan():
     import pytest
     with pytest.raises(ValueError):
         plan_chunks(0, 100, 250, 16)
+
+
+def test_contract_header_matches_python():
+    from naivert_b200.runtime import contract as C
+    h = C.parse_header()
+    for name, value in h.items():
+        if name.startswith("NRT_CTRL_") and name != "NRT_CTRL_RESERVED3":
+            assert getattr(C, name[4:]) == value, name
+    stops = {v: k for k, v in h.items() if k.startswith("NRT_STOP_")}
+    assert set(stops) == set(C.STOP_REASONS), (stops, C.STOP_REASONS)
+    assert h["NRT_CTRL_WORDS"] == 16
+
+
+def test_power_of_two_scale_variants():
+    import torch
+    from naivert_b200.ops import quant as Q
+    g = torch.Generator().manual_seed(0)
+    s = torch.tensor([0.0, 0.25, 0.3, 1.0, 1.5, 3.9e-5])
+    assert Q.ue8m0_round_up(s).tolist() == [1.0, 0.25, 0.5, 1.0, 2.0, 2.0 ** -14]
+    w = torch.randn(256, 384, generator=g) * 0.02
+    w8, si = Q.quantize_fp8_block(w)
+    q2, s2 = Q.requant_block_ue8m0(w8, si)
+    assert torch.all(torch.log2(s2) == torch.log2(s2).round())
+    back = Q.dequant_block(q2, s2)
+    assert (back - w).abs().max() <= 0.13 * w.abs().max()      # two e4m3 roundings
+    x = torch.randn(4, 128, generator=g)
+    q, sc = Q.quantize_mxfp8(x)
+    assert sc.shape == (4, 4) and torch.all(torch.log2(sc) == torch.log2(sc).round())
+    assert (Q.dequant_mxfp8(q, sc) - x).abs().max() <= 0.07 * x.abs().max()
+
+
+def test_moe_math_pieces():
+    import torch
+    from naivert_b200.models import moe_math as M
+    from naivert_b200.models.spec import MoeRoutingSpec
+    g = torch.Generator().manual_seed(1)
+    rt = MoeRoutingSpec(score_func="sigmoid", expert_count=8, top_k=2, intermediate=128, shared_expert_count=0,
+                        route_scale=1.0, normalize_top_k=True)
+    x = torch.randn(5, 64, generator=g).bfloat16()
+    xn = M.rmsnorm(x, torch.ones(64), 1e-5)
+    assert abs(xn.pow(2).mean().item() - 1.0) < 0.05
+    w, b = torch.randn(8, 64, generator=g) * 0.1, torch.zeros(8)
+    b[3] = 10.0                                           # the bias forces expert 3 into every selection ...
+    ids, p = M.route(xn, w, b, rt)
+    assert (ids == 3).any(-1).all() and torch.allclose(p.sum(-1), torch.ones(5), atol=1e-6)
+    score = torch.sigmoid(xn @ w.t())
+    sel3 = (ids == 3).float()
+    # ... but its weight is the unbiased score
+    assert torch.allclose((p * sel3).sum(-1), score[:, 3] / torch.gather(score, 1, ids.long()).sum(-1), atol=1e-5)
+    outs = [torch.randn(5, 64, generator=g).bfloat16() for _ in range(8)]
+    y = M.combine(x, outs, ids, p)
+    r0 = x[0].float() + sum(pp * outs[e][0].float() for e, pp in sorted(zip(ids[0].tolist(), p[0].tolist())))
+    assert torch.equal(y[0], r0.to(torch.bfloat16))
+    parts = [torch.randn(5, 64, generator=g) for _ in range(4)]
+    z = M.combine_tp_partials(x, parts)
+    assert torch.equal(z, (x.float() + sum(pp.to(torch.bfloat16).float() for pp in parts)).to(torch.bfloat16)) or \
+        (z.float() - (x.float() + sum(parts))).abs().max() < 0.1
+    q = M.quantize_down_activation(torch.randn(3, 256, generator=g))
+    assert q.shape == (3, 256)
+
+
+def test_audit_prefix_capture(tmp_path):
+    import json
+    from naivert_b200.serve.tools.audit_prefix_capture import audit
+    sys_p = [{"type": "text", "text": "be brief", "cache_control": {"type": "ephemeral"}}]
+    r1 = {"system": sys_p, "messages": [{"role": "user", "content": "hi"}]}
+    r2 = {"system": "be brief" and [{"type": "text", "text": "be brief"}],
+          "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]},
+                       {"role": "assistant", "content": [{"type": "thinking", "thinking": "x"}, {"type": "text", "text": "yo"}]},
+                       {"role": "user", "content": "more"}]}
+    r3 = {"system": sys_p, "messages": [{"role": "user", "content": "changed"}, {"role": "user", "content": "more"}]}
+    cap = tmp_path / "cap.jsonl"
+    rows = [{"rid": "a", "body": json.dumps(r1)}, {"rid": "b", "body": json.dumps(r2)}, {"rid": "c", "body": json.dumps(r3)},
+            {"rid": "b", "response": True, "usage": {"input_tokens": 7, "cache_read_input_tokens": 5}}]
+    cap.write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    rep = audit(cap, [["a", "b"], ["a", "c"], ["a", "zzz"]])
+    ab, ac, az = rep["pairs"]
+    assert ab["messages_prefix_equal"] and ab["system_equal"] and ab["added_roles"] == ["assistant", "user"]
+    assert ab["added_assistant_block_types"] == [["thinking", "text"]] and ab["later_usage"]["cache_read_input_tokens"] == 5
+    assert not ac["messages_prefix_equal"] and ac["first_changed_message"] == 0
+    assert "error" in az and len(rep["capture_sha256"]) == 64
+    assert "hi" not in json.dumps(rep)
