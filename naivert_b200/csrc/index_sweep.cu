@@ -34,6 +34,7 @@ struct SweepArgs {
   float* logits;         // [16][ld]
   int ld;
   uint32_t* status;
+  int group0, ngroups;   // row groups [group0, group0 + ngroups) are swept (ngroups == 0: all); query-row sharding
 };
 
 struct SweepTail {
@@ -54,7 +55,7 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   SweepTail* tail = reinterpret_cast<SweepTail*>(qsm + 256 * 128);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // grid.y row groups (prefill chunks): group g holds rows g*16.. with queries at row g*256 of the query map
-  const int rg = blockIdx.y;
+  const int rg = blockIdx.y + p.group0;
   const int grows = min(16, p.rows - rg * 16);
   const int ncol = grows * p.heads;                                        // UMMA N (<= 256)
 
@@ -155,8 +156,11 @@ extern "C" int nrt_index_sweep(const void* tmK, const void* tmQ, const void* arg
   memcpy(&q, tmQ, sizeof(q));
   SweepArgs a;
   memcpy(&a, args, sizeof(a));
-  const int groups = (a.rows + 15) / 16;
+  int groups = (a.rows + 15) / 16;
   if (a.heads != 16 && groups > 1) return -3;           // row groups assume 256 query rows per group
+  if (a.group0 < 0 || a.group0 + a.ngroups > groups) return -3;
+  if (a.ngroups > 0) groups = a.ngroups;
+  else if (a.group0 > 0) return -3;
   const int ncol = (a.rows > 16 ? 16 : a.rows) * a.heads;
   if (a.heads % 16 || ncol > 256 || ncol % 16) return -3;
   constexpr int smem = kSweepStages * kATileBytes + 256 * 128 + 2048 + 1024;

@@ -214,7 +214,7 @@ def attn_group(args: AttnArgs, pdl=True):
 
 class SweepArgs(C.Structure):
     _fields_ = [("ihw", VP), ("iks", VP), ("pos0", VP), ("rows", I32), ("heads", I32), ("top_k", I32),
-                ("logits", VP), ("ld", I32), ("status", VP)]
+                ("logits", VP), ("ld", I32), ("status", VP), ("group0", I32), ("ngroups", I32)]
 
 
 def sweep_maps(ik_cache: torch.Tensor, iq8: torch.Tensor):

@@ -119,6 +119,10 @@ class NativePrefill:
             self.ihw = torch.zeros(C, ix.head_count, dtype=f32, device=dev)
             self.idx_logits = torch.zeros(C, t.capacity, dtype=f32, device=dev)
             self.sel = torch.zeros(C, ix.top_k, dtype=i32, device=dev)
+            # the indexer is replicated, so ranks split the query rows of a chunk for the sweep and the top-k and
+            # all-gather the selection lists (NAIVERT_PREFILL_SHARD_INDEX=0: every rank selects for every row)
+            self.shard_index = self.tp > 1 and os.environ.get("NAIVERT_PREFILL_SHARD_INDEX", "1") == "1"
+            self.sel_local = torch.zeros(C // self.tp, ix.top_k, dtype=i32, device=dev) if self.shard_index else None
             self.topk_state = torch.zeros(C * K.topk_grid_state_bytes() // 4, dtype=i32, device=dev) if t.topk_grid else None
         if s.dense_layer_count:
             Id = s.dense_inter_local(self.tp)
@@ -274,6 +278,8 @@ class NativePrefill:
         H, pdl = s.hidden, False
         items = -(-R // self.step)
         self.pos.fill_(pos0)
+        if getattr(self, "shard_index", False) and R % (ROWS * tp) == 0:
+            self.pos[1:2].fill_(pos0 + self.rank * (R // tp))
         self.n_items.fill_(items)
         x, xn, part = self.x, self.xn, self.part
         K.embed_rows(self.tokens, t.embed, x, R, pdl=pdl)
@@ -294,15 +300,24 @@ class NativePrefill:
             with self._stage("attn_post"):
                 K.attn_post(e["post"], pdl=pdl)
             if d["kind"] == FULL_DSA and pos0 + R > s.indexer.top_k:
-                e["sweep"].rows = R
+                sw = e["sweep"]
+                sw.rows = R
+                shard = self.shard_index and R % (ROWS * tp) == 0
+                Rl = R // tp if shard else R                         # rows this rank selects for
+                row0 = self.rank * Rl if shard else 0
+                sw.group0, sw.ngroups = row0 // ROWS, Rl // ROWS
                 tiles = -(-(pos0 + R) // 128)
                 with self._stage("index_sweep"):
-                    K.index_sweep(*e["sweep_maps"], e["sweep"], max(1, min(tiles, 592 // (R // ROWS))), pdl=pdl)
+                    K.index_sweep(*e["sweep_maps"], sw, max(1, min(tiles, 592 // (Rl // ROWS))), pdl=pdl)
                 with self._stage("topk"):
+                    logits, pos_l = self.idx_logits[row0:row0 + Rl], self.pos[1:]          # pos[1] = pos0 + row0
+                    sel = self.sel_local if shard else self.sel
                     if t.topk_grid:
-                        K.topk_rows_grid(self.idx_logits, self.pos, R, s.indexer.top_k, self.sel, self.topk_state, 16, pdl=pdl)
+                        K.topk_rows_grid(logits, pos_l, Rl, s.indexer.top_k, sel, self.topk_state, 16, pdl=pdl)
                     else:
-                        K.topk_rows(self.idx_logits, self.pos, R, s.indexer.top_k, self.sel, pdl=pdl)
+                        K.topk_rows(logits, pos_l, Rl, s.indexer.top_k, sel, pdl=pdl)
+                    if shard:
+                        dist.all_gather_into_tensor(self.sel[:R], self.sel_local[:Rl], group=self.group)
             e["attn"].rows = R
             with self._stage("attn_dsa" if d["kind"] == FULL_DSA else "attn_swa"):
                 if e["group_attn"]:

@@ -133,9 +133,9 @@ def test_audit_prefix_capture(tmp_path):
     import json
     from naivert_b200.serve.tools.audit_prefix_capture import audit
     sys_p = [{"type": "text", "text": "be brief", "cache_control": {"type": "ephemeral"}}]
-    r1 = {"system": sys_p, "messages": [{"role": "user", "content": "hi"}]}
+    r1 = {"system": sys_p, "messages": [{"role": "user", "content": "zqxj-secret"}]}
     r2 = {"system": "be brief" and [{"type": "text", "text": "be brief"}],
-          "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]},
+          "messages": [{"role": "user", "content": [{"type": "text", "text": "zqxj-secret"}]},
                        {"role": "assistant", "content": [{"type": "thinking", "thinking": "x"}, {"type": "text", "text": "yo"}]},
                        {"role": "user", "content": "more"}]}
     r3 = {"system": sys_p, "messages": [{"role": "user", "content": "changed"}, {"role": "user", "content": "more"}]}
@@ -149,4 +149,4 @@ def test_audit_prefix_capture(tmp_path):
     assert ab["added_assistant_block_types"] == [["thinking", "text"]] and ab["later_usage"]["cache_read_input_tokens"] == 5
     assert not ac["messages_prefix_equal"] and ac["first_changed_message"] == 0
     assert "error" in az and len(rep["capture_sha256"]) == 64
-    assert "hi" not in json.dumps(rep)
+    assert "zqxj-secret" not in json.dumps(rep)
