@@ -66,7 +66,7 @@ def test_native_prefill_matches_replay(n, exact):
         # same arithmetic up to the first MoE output: attention-side kernels and the dense MLP are exact
         for k in ("L0.k", "L0.v", "L0.ik", "L0.iks", "L1.k", "L1.v"):
             assert k in r["bitwise"], r
-    else:
+    if n > 1:
         assert r["lockstep"], r
     assert r["worst"] < 0.1, r
     assert r["token_prefix_agreement"] >= 1, r
