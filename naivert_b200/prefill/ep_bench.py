@@ -35,6 +35,7 @@ def main() -> int:
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--iters", type=int, default=12)
+    ap.add_argument("--item-rows", type=int, default=64, help="64: chunk GEMM engine, 16: step engine tiles")
     a = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -51,7 +52,7 @@ def main() -> int:
         s = torch.full((shape[0], shape[1] // 128, shape[2] // 128), 0.02 / 96, device=dev)
         return {"w": w, "s": s}
 
-    moe = EPMoE(fab, H, I, E, Kk, T, q8(El, I, H), q8(El, I, H), q8(El, H, I))
+    moe = EPMoE(fab, H, I, E, Kk, T, q8(El, I, H), q8(El, I, H), q8(El, H, I), item_rows=a.item_rows)
     x = torch.randn(T, H, device=dev, generator=g).bfloat16()
     gamma = torch.ones(H, device=dev, dtype=torch.bfloat16)
     ids = torch.stack([torch.randperm(E, device=dev, generator=g)[:Kk] for _ in range(T)]).int().contiguous()
@@ -86,7 +87,7 @@ def main() -> int:
 
     # parts: count + dispatch only (then let the epoch move so tags stay unique)
     def disp_only():
-        ea = moe._ep_args(x, gamma, ids, probs)
+        ea = moe._ep_args(x, gamma, ids, probs, T)
         K.ep_count(ea, pdl=False)
         K.ep_dispatch(ea, pdl=False)
         K.epoch_advance(fab.epoch, pdl=False)
@@ -114,7 +115,18 @@ def main() -> int:
     nv_bytes = T * Kk * remote * (H + H // 128 * 4 + 16) + T * Kk * remote * H * 4      # e4m3 out; tagged bf16 words back
     roof = nv_bytes / (NVLINK_GBS * 1e9) * 1e6
     flops = 2.0 * T * Kk * 3 * H * I
-    res = {"tp": world, "tokens": a.tokens, "hidden": H, "inter": I, "experts": E, "top_k": Kk,
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
+    gemm_us = flops / (bf16_peak * 1e12) * 1e6            # expert math at the measured cuBLAS bf16 rate (no e4m3 figure is measured)
+    hbm_us = El * 3.0 * H * I / (float(peaks.get("hbm_gbs", 6650.0)) * 1e9) * 1e6   # every local expert's e4m3 weights once
+    target = max(roof, gemm_us, hbm_us)
+    res = {"tp": world, "tokens": a.tokens, "item_rows": a.item_rows, "gemm_term_us_at_measured_bf16_peak": round(gemm_us, 1),
+           "hbm_weight_term_us_at_measured_copy_rate": round(hbm_us, 1),
+           "roofline_target_us": round(target, 1), "fraction_of_roofline": round(target / max(fused, 1e-9), 4), "hidden": H, "inter": I, "experts": E, "top_k": Kk,
            "fused_layer_us": round(fused, 1), "count_dispatch_us": round(dispatch_us, 1),
            "nccl_all_to_all_both_ways_us": None if base is None else round(base, 1),
            "nvlink_roofline_us": round(roof, 1), "dispatch_combine_fraction_of_roofline": round(roof / max(fused, 1e-9), 4),
