@@ -25,8 +25,8 @@ struct AgPushArgs {
 
 // grid = tp CTAs: CTA p serves destination rank (rank + p) % tp.
 __global__ void __launch_bounds__(256) ag_push_kernel(const AgPushArgs a) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int dst = (a.rank + blockIdx.x) % a.tp;
   const int vec = a.slice_bytes / 16;
   uint8_t* base = a.gather[dst] + (size_t)a.rank * a.slice_bytes;

@@ -22,8 +22,8 @@ namespace {
 __global__ void draft_block_input_kernel(const int* __restrict__ block_ids, const __nv_bfloat16* __restrict__ embed,
                                          const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ x, int hidden,
                                          int rows, int vocab) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.x;
   uint4* dst = reinterpret_cast<uint4*>(x + (size_t)r * hidden);
   const uint4* src = nullptr;
@@ -59,8 +59,8 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
   __shared__ unsigned long long sbest;
   __shared__ bool s_last;
   __shared__ uint64_t xv[16];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   int prev = a.block_ids[step];
   prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
   for (int i = threadIdx.x; i < a.rank_dim; i += 256) w1s[i] = __bfloat162float(a.w1[(size_t)prev * a.rank_dim + i]);

@@ -63,8 +63,8 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
   __shared__ unsigned int hist[kEpMaxExperts];
   __shared__ uint64_t xv[kXchgMaxWords];          // [tp][experts]
   __shared__ int seg_base[kEpMaxExperts + 1];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int tp = a.x_args.tp, rank = a.x_args.rank;
   const int n = a.tokens * a.top_k;
   const int ir = a.item_rows > 0 ? a.item_rows : 16;
@@ -142,8 +142,8 @@ __device__ __forceinline__ uint8_t e4m3_of(float v) {
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpArgs a) {
   __shared__ float red[8];
   __shared__ bool s_last;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int t = blockIdx.x;
   const int per = a.hidden / 8;
   const int tp = a.x_args.tp, rank = a.x_args.rank;
@@ -236,8 +236,8 @@ struct EpCombineArgs {
 };
 
 __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineArgs a) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int t = blockIdx.x;
   const uint32_t tag = (*a.epoch) * 1024u + (uint32_t)a.call + 1u;
   const int words = a.hidden / 2;

@@ -165,10 +165,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
 
-  // Dependent kernels may start their own preamble now.  Weights never depend on earlier
-  // kernels, so (ungrouped) the producer streams the first weight tiles *before* waiting for
-  // the upstream grid; token tiles, scales, residuals and expert lists are read after the wait.
-  griddep_launch();
+  // Weights never depend on earlier kernels, so (ungrouped) the producer streams the first weight
+  // tiles *before* waiting for the upstream grid; token tiles, scales, residuals and expert lists are
+  // read after the wait.  The dependent kernel is released only after this kernel's own wait, so at
+  // most one successor is resident early (a chain of waiting grids clogs the CTA scheduler).
   // stages whose weight tile is issued before the wait
   const int early = GROUP == kGroupNone ? min(kb_count, Cfg::kStages) : 0;
   if (GROUP == kGroupNone) {
@@ -183,6 +183,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
     }
   }
   griddep_wait();
+  griddep_launch();
 
   int n_groups = 1, g_first = 0, g_step = 1;
   if (GROUP == kGroupItem) {

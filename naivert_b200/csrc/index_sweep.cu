@@ -72,8 +72,8 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
 
   const int p0 = *p.pos0 + rg * 16;
   const int total = p0 + grows;                        // positions visible to the last row of this group

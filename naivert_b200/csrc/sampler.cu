@@ -105,8 +105,8 @@ __device__ __forceinline__ bool last_block(unsigned int* ticket) {
 __global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a) {
   __shared__ unsigned int smax;
   __shared__ uint64_t xv[16];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int d = blockIdx.y;
   if (threadIdx.x == 0) smax = 0u;
   __syncthreads();
@@ -144,8 +144,8 @@ __global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a)
 __global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a) {
   __shared__ unsigned long long ssum;
   __shared__ uint64_t xv[16];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int d = blockIdx.y;
   if (threadIdx.x == 0) ssum = 0ull;
   __syncthreads();
@@ -184,8 +184,8 @@ __global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a)
 __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a, int pass) {
   __shared__ unsigned long long sh[256];
   __shared__ uint64_t xv[kDist * 256];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int d = blockIdx.y;
   const int shift = 24 - 8 * pass;
   const unsigned int mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
@@ -246,8 +246,8 @@ __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a
 // One CTA.  Gathers e_p(d_j), e_q(d_j) from the owning ranks, decides acceptance.
 __global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
   __shared__ uint64_t xv[16];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int j = threadIdx.x;                  // proposal j+1 is judged by target row j / draft row j
   if (j < 16) xv[j] = 0ull;
   __syncthreads();
@@ -298,8 +298,8 @@ __device__ __forceinline__ unsigned long long resample_mass(const SamplerArgs& a
 // ---------------------------------------------------------------- resample: per-tile masses
 __global__ void __launch_bounds__(kThreads) samp_tile_mass_kernel(const SamplerArgs a) {
   __shared__ unsigned long long ssum;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   if (threadIdx.x == 0) ssum = 0ull;
   __syncthreads();
   const int m = a.st->accepted;
@@ -323,8 +323,8 @@ __global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a
   __shared__ uint64_t xv[16];
   __shared__ unsigned long long part[kThreads];
   __shared__ int s_tok;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int m = a.st->accepted;
   if (threadIdx.x < 16) xv[threadIdx.x] = 0ull;
   __syncthreads();
@@ -424,8 +424,8 @@ struct TailArgs {
 
 __global__ void tail_commit_kernel(const TailArgs a) {
   __shared__ uint64_t xv[16];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   // Every rank must take the same stop decision in the same round: the host cancel word (set on one
   // rank only) and a failed device wait on any rank are max-reduced over the ranks first.
   if (threadIdx.x < 16)
@@ -486,8 +486,8 @@ __global__ void tail_commit_kernel(const TailArgs a) {
 // Prompt replay cursor: loads the next `rows` prompt tokens into the step's token buffer, points
 // the step (ctrl[0]) and the draft ingest (ctrl[2]) at their position and advances ctrl[10].
 __global__ void prefill_cursor_kernel(const int* __restrict__ prompt, int n_prompt, int rows, int* ctrl, int* tokens) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int cur = ctrl[NRT_CTRL_CURSOR];
   if (n_prompt < 0) n_prompt = ctrl[NRT_CTRL_PROMPT_CTX];          // length kept in the control block (graph replays)
   if (threadIdx.x < 16) {
@@ -500,8 +500,8 @@ __global__ void prefill_cursor_kernel(const int* __restrict__ prompt, int n_prom
 
 // advance the fabric epoch (eager steps outside a round)
 __global__ void epoch_advance_kernel(uint32_t* epoch) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   if (threadIdx.x == 0) *epoch += 1u;
 }
 

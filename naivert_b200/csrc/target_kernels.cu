@@ -63,8 +63,8 @@ __device__ __forceinline__ float from_e4m3(uint8_t b) {
 // ----------------------------------------------------------------------------- embedding gather
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
                                   __nv_bfloat16* __restrict__ x, int hidden, int rows, int vocab) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.x;
   if (r >= rows) return;
   int t = tokens[r];
@@ -77,8 +77,8 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const __nv_bfl
 // ----------------------------------------------------------------------------- RoPE tables for this step
 // table[r][i] = (cos, sin)(pos_r * theta^(-2i/dim)), evaluated in fp64 and rounded to fp32.
 __global__ void rope_table_kernel(const int* __restrict__ pos0, int rows, int dim, double theta, float2* __restrict__ out) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.x, i = threadIdx.x;
   if (r >= rows || i >= dim / 2) return;
   const double inv = pow(theta, -2.0 * (double)i / (double)dim);
@@ -94,8 +94,8 @@ __global__ void __launch_bounds__(256)
 prep_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, int hidden, int rows,
                  float eps, __nv_bfloat16* __restrict__ xn, uint8_t* __restrict__ x8, float* __restrict__ xs) {
   __shared__ float red[8];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.x;
   const int per = hidden / 8;              // 8-element vectors per row
   if (r >= rows) {
@@ -194,8 +194,8 @@ __device__ __forceinline__ void rope_pair(float& a, float& b, float2 cs) {
 __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
   __shared__ float red[8];
   __shared__ float kbuf[256];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.x;
   if (r >= a.rows) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -334,8 +334,8 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(const AttnArgs a) {
   __shared__ float sc[kAttnChunk];
   __shared__ float red[4];
   __shared__ int kid[kAttnChunk];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int h = blockIdx.x, r = blockIdx.y;
   if (r >= a.rows) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -472,8 +472,8 @@ struct IndexArgs {
 
 __global__ void __launch_bounds__(256) index_logits_simple_kernel(const IndexArgs a) {
   extern __shared__ float qf[];                    // [rows*heads][dim] as float
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int p0 = *a.pos0;
   if (p0 + a.rows <= a.top_k) return;              // every row is still dense
   const int total = p0 + a.rows;
@@ -522,8 +522,8 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
   __shared__ uint32_t s_prefix, s_need;
   __shared__ uint32_t wsum_gt[32], wsum_eq[32];
   __shared__ uint32_t base_out, base_eq;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.x;
   if (r >= rows) return;
   const int n = *pos0 + r + 1;
@@ -607,8 +607,8 @@ __global__ void __launch_bounds__(1024) topk_grid_hist_kernel(const float* __res
                                                                int rows, int top_k, TopkGridState* st, int pass) {
   __shared__ unsigned int sh[256];
   __shared__ bool s_last;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.y;
   const int n = *pos0 + r + 1;
   if (r >= rows || n <= top_k) return;
@@ -655,8 +655,8 @@ __global__ void __launch_bounds__(1024) topk_grid_hist_kernel(const float* __res
 __global__ void __launch_bounds__(1024) topk_grid_count_kernel(const float* __restrict__ logits, int ld, const int* pos0,
                                                                 int rows, int top_k, TopkGridState* st) {
   __shared__ unsigned int s_gt, s_eq;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.y;
   const int n = *pos0 + r + 1;
   if (r >= rows || n <= top_k) return;
@@ -683,8 +683,8 @@ __global__ void __launch_bounds__(1024) topk_grid_write_kernel(const float* __re
                                                                 int rows, int top_k, TopkGridState* st, int* __restrict__ sel) {
   __shared__ uint32_t wsum_gt[32], wsum_eq[32];
   __shared__ uint32_t base_out, base_eq;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int r = blockIdx.y;
   const int n = *pos0 + r + 1;
   if (r >= rows || n <= top_k) return;
@@ -770,8 +770,8 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   __shared__ bool last;
   __shared__ unsigned int used[8];                  // bitmap over <= 256 experts
   __shared__ int slot_of[256];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 2;
   extern __shared__ uint4 router_smem[];
@@ -843,6 +843,40 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   for (int j = 0; j < 2; ++j)
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) acc[j][r] = 0.f;
+  if (a.hidden == 4096) {
+    // Every load of the thread is issued before the first FMA (one HBM + one L2 round trip instead of one per
+    // K step): the two experts' weights for the thread's four K positions, then eight rows of activations at a
+    // time (rows beyond a.rows are predicated off, not read).
+    float4 w0[4], w1[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = tid * 4 + 1024 * i;
+      w0[i] = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * 4096 + k);
+      w1[i] = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * 4096 + k) : make_float4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (half * 8 < a.rows) {
+        uint2 xv[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            xv[i][r] = (half * 8 + r < a.rows)
+                           ? *reinterpret_cast<const uint2*>(xsrc + (size_t)(half * 8 + r) * xld + tid * 4 + 1024 * i)
+                           : make_uint2(0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].x));
+            const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].y));
+            acc[0][half * 8 + r] += x01.x * w0[i].x + x01.y * w0[i].y + x23.x * w0[i].z + x23.y * w0[i].w;
+            acc[1][half * 8 + r] += x01.x * w1[i].x + x01.y * w1[i].y + x23.x * w1[i].z + x23.y * w1[i].w;
+          }
+      }
+    }
+  } else {
 #pragma unroll 4
   for (int k = tid * 4; k < a.hidden; k += 1024) {
     float4 w0 = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k);
@@ -858,6 +892,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
         acc[1][r] += x01.x * w1.x + x01.y * w1.y + x23.x * w1.z + x23.y * w1.w;
       }
     }
+  }
   }
 #pragma unroll
   for (int j = 0; j < 2; ++j)
@@ -890,20 +925,27 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   // one warp per row: iterative arg-max with lowest-index ties
   for (int r = warp; r < a.rows; r += 8) {
     float sc[8], ch[8];                             // experts lane, lane+32, ... (<= 256 experts)
+    // all sixteen loads (scores from L2, selection bias) are issued before anything depends on them
+    float raw[8], bv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = min(lane + 32 * j, a.experts - 1);
+      raw[j] = __ldcg(a.scores + r * a.experts + e);
+      bv[j] = a.bias ? __ldg(a.bias + e) : 0.f;
+    }
     float mx = -FLT_MAX;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int e = lane + 32 * j;
-      const float v = e < a.experts ? __ldcg(a.scores + r * a.experts + e) : -FLT_MAX;
-      sc[j] = v;
-      mx = fmaxf(mx, v);
+      const bool in = lane + 32 * j < a.experts;
+      sc[j] = in ? raw[j] : -FLT_MAX;
+      mx = fmaxf(mx, sc[j]);
     }
     if (a.sigmoid) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int e = lane + 32 * j;
-        if (e < a.experts) { sc[j] = 1.f / (1.f + __expf(-sc[j])); ch[j] = sc[j] + (a.bias ? a.bias[e] : 0.f); }
-        else ch[j] = -FLT_MAX;
+        const bool in = lane + 32 * j < a.experts;
+        sc[j] = in ? 1.f / (1.f + __expf(-sc[j])) : 0.f;
+        ch[j] = in ? sc[j] + bv[j] : -FLT_MAX;
       }
     } else {
       mx = warp_max(mx);
@@ -918,26 +960,29 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) { sc[j] /= sum; ch[j] = (lane + 32 * j) < a.experts ? sc[j] : -FLT_MAX; }
     }
+    uint32_t kk[8];                                 // order-preserving keys; 0 once taken
+#pragma unroll
+    for (int j = 0; j < 8; ++j) kk[j] = order_key(ch[j]);
     float psum = 0.f;
     float my_p = 0.f;
     int my_id = -1;
     for (int t = 0; t < a.top_k; ++t) {
-      float best = -FLT_MAX;
-      int bi = 1 << 30;
+      // arg-max over the warp with two hardware reductions: the largest key, then the lowest expert index
+      // among the lanes that hold it
+      uint32_t bk = 0u;
+      int bj = 0;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (ch[j] > best) { best = ch[j]; bi = lane + 32 * j; }     // ascending j keeps the lowest index on ties
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-      }
+        if (kk[j] > bk) { bk = kk[j]; bj = j; }                     // ascending j keeps the lowest index on ties
+      const uint32_t best = __reduce_max_sync(0xffffffffu, bk);
+      const int bi = (int)__reduce_min_sync(0xffffffffu, bk == best ? (unsigned)(lane + 32 * bj) : 0xffffffffu);
       float pv = 0.f;
+      if ((bi & 31) == lane) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (lane + 32 * j == bi) { pv = sc[j]; ch[j] = -FLT_MAX; }
-      pv = warp_sum(pv);                              // only the owner lane holds a non-zero value
+        for (int j = 0; j < 8; ++j)
+          if (j == (bi >> 5)) { pv = sc[j]; kk[j] = 0u; }
+      }
+      pv = __shfl_sync(0xffffffffu, pv, bi & 31);
       psum += pv;
       if (lane == t) { my_p = pv; my_id = bi; }
     }

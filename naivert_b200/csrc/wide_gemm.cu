@@ -86,8 +86,8 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
 
   const int na = min(*p.n_active, p.max_slots);
   const bool live_item = item < na;
