@@ -251,6 +251,19 @@ class XchgArgs(C.Structure):
                 ("timeout_ns", U64)]
 
 
+class ArgmaxArgs(C.Structure):
+    _fields_ = [("logits", VP), ("ld", I32), ("rows", I32), ("vlocal", I32), ("vbase", I32), ("tokens", VP), ("keys", VP),
+                ("ticket", VP), ("call", I32), ("x", XchgArgs)]
+
+
+def argmax_rows(args: ArgmaxArgs, pdl=True):
+    """Greedy arg-max over the vocabulary shards of all ranks (lowest id on ties)."""
+    L = aux_lib()
+    if L.nrt_argmax_args_size() != C.sizeof(ArgmaxArgs):
+        raise RuntimeError("ArgmaxArgs layout drift")
+    check(L.nrt_argmax_rows(C.byref(args), VP(_stream()), int(pdl)), "argmax_rows")
+
+
 class SamplerArgs(C.Structure):
     _fields_ = [("zp", VP), ("ldp", I32), ("zq", VP), ("ldq", I32), ("vlocal", I32), ("vbase", I32), ("e", VP),
                 ("counts", VP), ("params", VP), ("seed", VP), ("ctrl", VP), ("block_ids", VP),

@@ -175,6 +175,10 @@ class TargetRuntime:
         self.attn_splits = 4
         self.attn_part = torch.zeros(PAD_ROWS * nh_max * self.attn_splits * (a0.v_head_dim + 2), dtype=f32, device=dev)
         self.attn_tickets = torch.zeros(PAD_ROWS * nh_max, dtype=i32, device=dev)
+        # greedy arg-max over all ranks' vocabulary shards (seq-1 greedy decoding, sampler cross-check)
+        self.greedy = torch.zeros(PAD_ROWS, dtype=i32, device=dev)
+        self._argmax_keys = torch.zeros(PAD_ROWS, dtype=torch.int64, device=dev)
+        self._argmax_ticket = torch.zeros(1, dtype=i32, device=dev)
         self._build_args()
 
     # ------------------------------------------------------------------ argument blocks (built once)
@@ -343,6 +347,19 @@ class TargetRuntime:
         if head:
             K.prep_norm(self.x, self.g_final, R, s.norm_eps, xn=self.xn, pdl=pdl)
             K.gemm(self.V_BF16_STORE, self.map_lm, None, self.map_xn, self.args_head, -(-self.lm_head.shape[0] // 128), pdl=pdl)
+
+    ARGMAX_CALL = 60                                  # small-exchange call index (unique inside one epoch)
+
+    def greedy_argmax(self) -> torch.Tensor:
+        """Enqueue the tensor-parallel arg-max of the current logits rows; returns the device tensor that will hold
+        the global token ids (identical on every rank).  Capturable; one exchange per epoch."""
+        a = K.ArgmaxArgs()
+        V = self.logits.shape[1]
+        a.logits, a.ld, a.rows, a.vlocal, a.vbase = self.logits.data_ptr(), V, self.rows, V, self.rank * V
+        a.tokens, a.keys, a.ticket = self.greedy.data_ptr(), self._argmax_keys.data_ptr(), self._argmax_ticket.data_ptr()
+        a.call, a.x = self.ARGMAX_CALL, self.fab.xchg_args()
+        K.argmax_rows(a, pdl=self.pdl)
+        return self.greedy
 
     # ------------------------------------------------------------------ host helpers (not on the hot path)
     def set_inputs(self, tokens, pos0: int) -> None:

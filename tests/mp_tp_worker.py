@@ -53,6 +53,13 @@ def main():
         errs.append(((got - wl).abs().mean() / wl.abs().mean()).item())
     eng.fabric.check()
     out["verify_mean_rel"] = max(errs)
+    # tensor-parallel arg-max of the last step's logits vs the gathered full-vocabulary logits
+    tok = t.greedy_argmax()
+    K.epoch_advance(eng.fabric.epoch, pdl=False)
+    torch.cuda.synchronize()
+    full = [torch.zeros_like(t.logits[:8]) for _ in range(world)]
+    dist.all_gather(full, t.logits[:8].contiguous())
+    out["argmax_ok"] = tok[:8].tolist() == torch.cat(full, dim=1).argmax(-1).tolist()
     # residual stream must be bitwise identical on all ranks (same partials, same order)
     xs = [torch.zeros_like(t.x) for _ in range(world)]
     dist.all_gather(xs, t.x)

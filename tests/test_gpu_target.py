@@ -218,6 +218,20 @@ def test_split_attention_matches_single():
     assert (outs[0] - outs[1]).abs().max().item() <= 0.02 * outs[0].abs().max().item()
 
 
+def test_greedy_argmax_rows():
+    """Tensor-parallel arg-max kernel at tp = 1: lowest token id on ties, every row."""
+    spec, rt, _ = _build(layers=1, capacity=128)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rt.logits.copy_(torch.randn(rt.logits.shape, device="cuda", generator=g))
+    rt.logits[3, 100] = rt.logits[3, 4000] = 50.0                 # a tie: the lower id wins
+    got = rt.greedy_argmax()
+    torch.cuda.synchronize()
+    want = rt.logits[: rt.rows].argmax(-1)
+    want[3] = 100
+    assert got[: rt.rows].tolist() == want.tolist()
+    rt.fab.check()
+
+
 def test_step_is_bitwise_repeatable():
     spec, rt, _ = _build(layers=2, capacity=128)
     toks = torch.arange(8) * 37 % spec.vocab
