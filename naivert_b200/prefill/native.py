@@ -89,8 +89,7 @@ class NativePrefill:
         # multiple of 64 rows; otherwise the step engine's 16-column tiles in item mode
         self.wide = os.environ.get("NAIVERT_PREFILL_WIDE", "1") == "1" and chunk % K.WIDE_TOK == 0
         self.step = K.WIDE_TOK if self.wide else ROWS
-        # plain projections share one weight matrix over all items: let consecutive CTAs share weight tiles
-        self._gemm = (lambda *a, **k: K.wide_gemm(*a, items_fastest=True, **k)) if self.wide else K.gemm
+        self._gemm = self._wide_gemm if self.wide else K.gemm
         s, dev = spec, self.dev
         H = s.hidden
         bf, f32, i32, u8 = torch.bfloat16, torch.float32, torch.int32, torch.uint8
@@ -172,6 +171,14 @@ class NativePrefill:
         self.profile = False                         # per-stage CUDA-event timing (adds an event pair per stage)
         self._timed: Dict[str, list] = {}
         self._build_args()
+
+    @staticmethod
+    def _wide_gemm(variant, a0, a1, b, args, n_tiles, items, pdl=False):
+        """Plain projections share one weight matrix over all items.  A matrix that fits the L2 (126 MB) stays
+        resident while feature tiles vary fastest (tokens stream once); a larger one is walked item-fastest so
+        that each weight tile is fetched from HBM once and the (smaller) token operand stays resident instead."""
+        wbytes = a0.tensor.numel() * a0.tensor.element_size() * (2 if a1 is not None else 1)
+        K.wide_gemm(variant, a0, a1, b, args, n_tiles, items, pdl=pdl, items_fastest=wbytes > (96 << 20))
 
     # ------------------------------------------------------------------ argument blocks
     def _item_args(self, n, k) -> K.GemmArgs:
