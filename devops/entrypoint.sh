@@ -18,6 +18,8 @@ ARGS=(--host "${NAIVERT_HOST:-0.0.0.0}" --port "${NAIVERT_PORT:-8080}" --model "
 [[ -n "${NAIVERT_TOP_P:-}" ]] && ARGS+=(--top-p "$NAIVERT_TOP_P")
 [[ -n "${NAIVERT_CORS_ORIGIN:-}" ]] && ARGS+=(--cors-origin "$NAIVERT_CORS_ORIGIN")
 [[ -n "${NAIVERT_RESUME_POLICY:-}" ]] && ARGS+=(--resume-policy "$NAIVERT_RESUME_POLICY")
+[[ -n "${NAIVERT_PREFILL:-}" ]] && ARGS+=(--prefill "$NAIVERT_PREFILL")
+[[ -n "${NAIVERT_PREFILL_CHUNK:-}" ]] && ARGS+=(--prefill-chunk "$NAIVERT_PREFILL_CHUNK")
 if [[ "${NAIVERT_DRY_RUN:-0}" == "1" ]]; then
   echo "gpus=$GPUS" "${ARGS[@]}"
   exit 0

@@ -41,7 +41,11 @@ def parse_args(argv=None):
     ap.add_argument("--store-gb", type=float, default=8.0, help="parked-prefix budget per rank")
     ap.add_argument("--queue-depth", type=int, default=8)
     ap.add_argument("--resume-policy", choices=("cost", "replay", "native"), default="cost")
-    ap.add_argument("--prefill", choices=("verify8", "native"), default="verify8")
+    ap.add_argument("--prefill", choices=("verify8", "native"), default="verify8",
+                    help="native: long prompts are ingested in chunks (tensor-parallel attention, experts per --prefill-experts)")
+    ap.add_argument("--prefill-chunk", type=int, default=4096, help="rows per native prefill chunk")
+    ap.add_argument("--prefill-experts", choices=("tp", "ep"), default="tp",
+                    help="ep: a second, expert-parallel copy of the experts (random-init only; doubles expert memory)")
     ap.add_argument("--thinking", action="store_true", help="enable thinking by default in the chat template")
     ap.add_argument("--log-level", default="info")
     return ap.parse_args(argv)
@@ -82,8 +86,15 @@ def main(argv=None) -> int:
         target, draft = resolve_checkpoint(a.target), resolve_checkpoint(a.draft, "NAIVERT_DRAFT_ROOTS")
 
     def build_engine() -> SessionEngine:
+        ep_w = None
+        if a.prefill == "native" and a.prefill_experts == "ep" and world > 1:
+            if not a.random_init:
+                raise SystemExit("--prefill-experts ep needs --random-init (checkpoints are loaded in the tensor-parallel layout)")
+            from naivert_b200.models.device_init import init_expert_rank_weights_device
+            ep_w = init_expert_rank_weights_device(spec, rank, world, seed=a.seed, device=dev)
         eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=a.capacity, seed=a.seed, target_ckpt=target,
-                           draft_ckpt=draft, device=dev)
+                           draft_ckpt=draft, device=dev, prefill_chunk=a.prefill_chunk if a.prefill == "native" else 0,
+                           ep_weights=ep_w)
         return SessionEngine(eng, store_gb=a.store_gb, max_output_tokens=a.max_decode_tokens, resume_policy=a.resume_policy)
 
     if rank != 0:

@@ -24,9 +24,10 @@ from .prefix_store import PrefixStore, common_prefix, park_name, select_resume
 from .round import RuntimeContractError
 
 # Measured on B200 (ms); inputs of the resume / prefill-path policy.
-REPLAY_MS_PER_TOKEN = 1.2            # 8-row verify replay per prompt token (tp8, 48 layers)
-NATIVE_FIRST_CHUNK_MS = 62.0
-NATIVE_NEXT_CHUNK_MS = 60.0
+REPLAY_MS_PER_TOKEN = 1.2            # 8-row verify replay per prompt token (tp8, 48 layers: 9.6 ms per 8 rows)
+NATIVE_FIXED_MS = 30.0               # chunked native prefill: launches + collectives of one (partial) chunk ...
+NATIVE_MS_PER_TOKEN = 0.035          # ... plus per-row work at short context (tp8: 8192 tokens in 0.48 s with 2048-row chunks)
+NATIVE_MS_PER_TOKEN_PER_64K_CONTEXT = 0.008  # indexer sweep + top-k grow with the context (131072 tokens: 6.6 s)
 NATIVE_CHUNK = 4096
 RESTORE_MS_PER_GB = 2.0
 
@@ -38,7 +39,8 @@ def prefill_estimate(new_tokens: int, path: str) -> float:
     if path == "replay":
         return new_tokens * REPLAY_MS_PER_TOKEN
     chunks = -(-new_tokens // NATIVE_CHUNK)
-    return NATIVE_FIRST_CHUNK_MS + (chunks - 1) * NATIVE_NEXT_CHUNK_MS
+    context_term = NATIVE_MS_PER_TOKEN_PER_64K_CONTEXT * new_tokens * (new_tokens / 2.0) / 65536.0
+    return chunks * NATIVE_FIXED_MS + new_tokens * NATIVE_MS_PER_TOKEN + context_term
 
 
 def prefill_path(new_tokens: int, policy: str = "cost", native_ready: bool = False) -> str:
