@@ -190,3 +190,69 @@ def test_prep_norm_packet():
     assert torch.equal(xs[:rows], s)
     assert torch.equal(x8[:rows], q.view(torch.uint8))
     assert int(xn[rows:].abs().sum()) == 0 and int(x8[rows:].sum()) == 0
+
+
+def _items(n_items, step=64):
+    off = (torch.arange(n_items, dtype=torch.int32, device="cuda") * step).contiguous()
+    ids = torch.zeros(n_items, dtype=torch.int32, device="cuda")
+    cnt = torch.tensor([n_items], dtype=torch.int32, device="cuda")
+    return off, ids, cnt
+
+
+@pytest.mark.parametrize("order", [False, True])
+def test_chunk_gemm_bf16_matches_torch(order):
+    """64-column persistent chunk GEMM (bf16, fp32 store) against torch on 320 rows x 640 features x K 1024."""
+    K = _setup()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rows, n, k = 320, 640, 1024
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+    x = torch.randn(rows, k, device="cuda", generator=g).bfloat16()
+    out = torch.zeros(rows, n, device="cuda")
+    st = _status()
+    off, ids, cnt = _items(rows // 64)
+    a = K.GemmArgs()
+    a.n_total, a.k_total, a.rows, a.out_scale = n, k, 64, 1.0
+    a.n_active, a.active_ids, a.max_slots, a.row_offsets = cnt.data_ptr(), ids.data_ptr(), rows // 64, off.data_ptr()
+    a.out_f32, a.ld_out, a.status = out.data_ptr(), n, st.data_ptr()
+    K.wide_gemm(K.gemm_variant(False, False, K.EPI_STORE_F32, K.GROUP_ITEM), K.weight_tmap(w), None, K.act_tmap(x, 64), a,
+                n // 128, rows // 64, items_fastest=order)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    ref = x.float() @ w.float().T
+    assert (out - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+
+
+def test_chunk_gemm_fp8_gate_up_matches_torch():
+    """e4m3 block-scaled gate/up with SiLU and e4m3 re-quantisation on the chunk engine vs the torch recipe."""
+    K = _setup()
+    from naivert_b200.ops.quant import dequant_act, quantize_act_pow2, quantize_fp8_block, w8a8_linear_ref
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rows, n, k = 192, 256, 1024
+    wg = torch.randn(n, k, device="cuda", generator=g) * 0.05
+    wu = torch.randn(n, k, device="cuda", generator=g) * 0.05
+    x = torch.randn(rows, k, device="cuda", generator=g).bfloat16().float()
+    g8, gs = quantize_fp8_block(wg)
+    u8, us = quantize_fp8_block(wu)
+    xq, xs = quantize_act_pow2(x)
+    x8 = xq.view(torch.uint8).contiguous()
+    xs = xs.float().contiguous()
+    y8 = torch.zeros(rows, n, dtype=torch.uint8, device="cuda")
+    ys = torch.zeros(rows, n // 128, device="cuda")
+    st = _status()
+    off, ids, cnt = _items(rows // 64)
+    a = K.GemmArgs()
+    a.n_total, a.k_total, a.rows, a.out_scale = n, k, 64, 1.0
+    a.n_active, a.active_ids, a.max_slots, a.row_offsets = cnt.data_ptr(), ids.data_ptr(), rows // 64, off.data_ptr()
+    a.w_scale0, a.w_scale1, a.a_scale = gs.data_ptr(), us.data_ptr(), xs.data_ptr()
+    a.out_q, a.out_qscale, a.status = y8.data_ptr(), ys.data_ptr(), st.data_ptr()
+    K.wide_gemm(K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM), K.weight_tmap(g8.view(torch.uint8)),
+                K.weight_tmap(u8.view(torch.uint8)), K.act_tmap(x8, 64), a, n // 128, rows // 64)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    gg, uu = w8a8_linear_ref(x, g8, gs), w8a8_linear_ref(x, u8, us)
+    want = torch.nn.functional.silu(gg) * uu
+    got = dequant_act(y8.view(torch.float8_e4m3fn), ys)
+    # one e4m3 rounding of the reference value (relative step 2^-3, half of it as error) plus accumulation noise
+    assert (got - want).abs().max().item() <= 0.07 * want.abs().max().item()
+    wq, wsc = quantize_act_pow2(want)
+    assert torch.equal(ys, wsc.float()) or (ys - wsc.float()).abs().max().item() <= ys.max().item()
