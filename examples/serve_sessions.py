@@ -46,6 +46,8 @@ def parse_args(argv=None):
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="rows per native prefill chunk")
     ap.add_argument("--prefill-experts", choices=("tp", "ep"), default="tp",
                     help="ep: a second, expert-parallel copy of the experts (random-init only; doubles expert memory)")
+    ap.add_argument("--prefill-warm-chunks", action="store_true", help="run every native chunk size once before serving")
+    ap.add_argument("--dump-tokens", default=None, help="append the output token ids of every request to this JSONL file")
     ap.add_argument("--thinking", action="store_true", help="enable thinking by default in the chat template")
     ap.add_argument("--log-level", default="info")
     return ap.parse_args(argv)
@@ -95,6 +97,9 @@ def main(argv=None) -> int:
         eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=a.capacity, seed=a.seed, target_ckpt=target,
                            draft_ckpt=draft, device=dev, prefill_chunk=a.prefill_chunk if a.prefill == "native" else 0,
                            ep_weights=ep_w)
+        if eng.prefill is not None and a.prefill_warm_chunks:
+            with torch.cuda.stream(eng.round.stream):
+                eng.prefill.warm_chunks()
         return SessionEngine(eng, store_gb=a.store_gb, max_output_tokens=a.max_decode_tokens, resume_policy=a.resume_policy)
 
     if rank != 0:
@@ -111,7 +116,7 @@ def main(argv=None) -> int:
         engine = LeaderEngine(se, Commands(cpu_group)) if world > 1 else se
         return ServerContext(engine, ChatFormatter.from_path(target, enable_thinking=a.thinking))
 
-    app = build_app(factory, defaults, queue_depth=a.queue_depth, cors_origin=a.cors_origin, cors_credentials=a.cors_credentials)
+    app = build_app(factory, defaults, queue_depth=a.queue_depth, cors_origin=a.cors_origin, cors_credentials=a.cors_credentials, dump_tokens=a.dump_tokens)
     run_app(app, a.host, a.port, a.log_level)
     return 0
 

@@ -83,6 +83,15 @@ def segment_stats(tokens: Sequence[int], round_sizes: Sequence[int], round_ns: S
     return out
 
 
+def acceptance_histogram(accepted: Sequence[int], block: int = 7) -> List[int]:
+    """Rounds by accepted draft prefix length 0..block (the reference keeps this as a device counter array,
+    ``verify_counts``; here it is derived from the ring records the host already reads)."""
+    hist = [0] * (block + 1)
+    for a in accepted:
+        hist[min(max(int(a), 0), block)] += 1
+    return hist
+
+
 class Session:
     def __init__(self, owner: "SessionEngine", tokens: List[int], cached: int, session_id: Optional[str], info: dict):
         self.owner, self.prompt, self.cached_tokens, self.session_id = owner, tokens, cached, session_id
@@ -148,6 +157,7 @@ class Session:
         stats = {"prefill_path": self.prefill_info.get("path"), "initialize_ms": self.prefill_info.get("init_ms"),
                  "segments": segment_stats(self.out, self.round_sizes, self.round_ns, self.owner.config.think_end_token_id,
                                            self.accepted)}
+        stats["accepted_prefix_histogram"] = acceptance_histogram(self.accepted)
         tot = stats["segments"].get("total")
         if tot:
             stats["decode_tok_s_device"] = tot["device_tok_s"]
@@ -212,7 +222,10 @@ class SessionEngine:
         if n - 1 >= 16:
             self.store.checkpoint(key, n - 1)            # ring state at prompt end, for later rewinds
         info = {"path": path, "restore_ms": round((t1 - t0) * 1e3, 3), "init_ms": round((t2 - t1) * 1e3, 3),
-                "resumed_from": choice.key if start else None, "estimate_ms": round(prefill_estimate(n - 1 - start, path), 2)}
+                "resumed_from": choice.key if start else None, "estimate_ms": round(prefill_estimate(n - 1 - start, path), 2),
+                "phases": {"restore_ms": round((t1 - t0) * 1e3, 3), "executor_ms": self.engine.last_prefill.get("executor_ms", 0.0),
+                           "native_rows": self.engine.last_prefill.get("native_rows", 0), "replay_rows": n - 1 - replay_from,
+                           "init_ms": round((t2 - t1) * 1e3, 3)}}
         self.active = Session(self, tokens, start, session_id, info)
         return self.active
 

@@ -51,8 +51,9 @@ class Job:
 class Worker:
     """Single owner thread of the engine.  Status: loading -> ok -> shutting_down | error."""
 
-    def __init__(self, ctx_factory: Callable[[], ServerContext], queue_depth: int = 8):
+    def __init__(self, ctx_factory: Callable[[], ServerContext], queue_depth: int = 8, dump_tokens: Optional[str] = None):
         self.ctx_factory = ctx_factory
+        self.dump_tokens = dump_tokens               # JSONL path: one line of output token ids per finished request
         self.jobs: "queue.Queue[Optional[Job]]" = queue.Queue(maxsize=max(1, queue_depth))
         self.status = "loading"
         self.ctx: Optional[ServerContext] = None
@@ -141,6 +142,13 @@ class Worker:
             elif isinstance(item, Final):
                 final = item
             job.out.put(item)
+        if final is not None and self.dump_tokens:
+            try:
+                with open(self.dump_tokens, "a") as f:
+                    f.write(json.dumps({"t": time.time(), "stop_reason": final.stop_reason, "output_tokens": final.output_tokens,
+                                        "tokens": list(final.tokens)}) + "\n")
+            except OSError as e:
+                log.warning("token dump failed: %s", e)
         if final is not None:
             seg = final.timings.get("segments", {}).get("total", {})
             log.info("request done prompt_n=%s cache=%s prefill_ms=%s predicted_n=%s stop=%s device_tok_s=%s wall_ms=%.1f",
@@ -154,11 +162,12 @@ def _error_response(e: ApiError):
 
 
 def build_app(ctx_factory: Callable[[], ServerContext], defaults: Optional[ServerDefaults] = None, queue_depth: int = 8,
-              cors_origin: Optional[str] = None, cors_credentials: bool = False, display_name: Optional[str] = None):
+              cors_origin: Optional[str] = None, cors_credentials: bool = False, display_name: Optional[str] = None,
+              dump_tokens: Optional[str] = None):
     from contextlib import asynccontextmanager
 
     defaults = defaults or ServerDefaults()
-    worker = Worker(ctx_factory, queue_depth)
+    worker = Worker(ctx_factory, queue_depth, dump_tokens=dump_tokens)
     replay = AssistantReplay()
 
     @asynccontextmanager

@@ -82,11 +82,12 @@ class FakeEngine:
 
 
 @pytest.fixture()
-def server():
+def server(tmp_path_factory):
     import uvicorn
     eng = FakeEngine()
+    eng.dump_path = str(tmp_path_factory.mktemp("dump") / "tokens.jsonl")
     app = build_app(lambda: ServerContext(eng, ChatFormatter(eng.tok)), ServerDefaults(served_model="naive-n0.5", max_output_tokens=4000),
-                    queue_depth=2)
+                    queue_depth=2, dump_tokens=eng.dump_path)
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     srv = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))
     t = threading.Thread(target=srv.run, daemon=True)
@@ -138,6 +139,20 @@ def test_json_reply_usage_and_models(server):
     assert h == {"status": "ok", "slot": "IDLE", "queued": 0}
     n = httpx.post(base + "/v1/messages/count_tokens", json={"model": "naive-n0.5", "messages": [{"role": "user", "content": "hi"}]}).json()
     assert n["input_tokens"] == eng.opened[0][1]
+
+
+def test_token_dump_lines(server):
+    base, eng = server
+    r = httpx.post(base + "/v1/messages", json=_body(), timeout=30)
+    assert r.status_code == 200
+    deadline = time.time() + 5
+    rows = []
+    while time.time() < deadline and not rows:
+        try:
+            rows = [json.loads(l) for l in open(eng.dump_path)]
+        except FileNotFoundError:
+            time.sleep(0.05)
+    assert rows and rows[-1]["output_tokens"] == r.json()["usage"]["output_tokens"] and isinstance(rows[-1]["tokens"], list)
 
 
 def test_sse_event_order(server):

@@ -150,3 +150,9 @@ def test_audit_prefix_capture(tmp_path):
     assert not ac["messages_prefix_equal"] and ac["first_changed_message"] == 0
     assert "error" in az and len(rep["capture_sha256"]) == 64
     assert "zqxj-secret" not in json.dumps(rep)
+
+
+def test_acceptance_histogram():
+    from naivert_b200.runtime.session_engine import acceptance_histogram
+    assert acceptance_histogram([0, 7, 7, 3, 9, -1]) == [2, 0, 0, 1, 0, 0, 0, 3]
+    assert acceptance_histogram([]) == [0] * 8
