@@ -7,8 +7,8 @@ a status word and make every later wait return at once - so the failure paths th
 provoked on a GPU of the shared pool (a rank that never publishes, a rank that leaves between
 steps) are exercised here.
 
-Parity: naivert/common/tp8_mailbox.cuh:122-195 (bounded waits + watchdog word) and the fault
-plan of the survey (CPU-rank simulator with one withheld publish).
+Parity: naivert/common/tp8_mailbox.cuh:122-195 (bounded waits + watchdog word); failures are injected on
+the host only (a simulated rank withholds one publish).
 """
 from __future__ import annotations
 
