@@ -3,9 +3,9 @@
 // One CTA (8 warps) per (KV head, query row): the up to 16 query heads that share the KV head form the
 // M = 16 side of bf16 tensor-core tiles, so every gathered key/value row is read once per KV head instead of
 // once per query head (grouped-query attention: 16 heads per KV head in the sparse layers at tp = 1, 8 at
-// tp = 8).  Keys come in chunks of 128 (the row's sliding window, its dense prefix, or its top-k selection
-// list), are staged in shared memory with independent 16-byte loads, scored with m16n8k16 MMAs
-// (S = Q K^T, 16 heads x 128 keys), soft-maxed online per head, and accumulated with a second set of MMAs
+// tp = 8).  Keys come in chunks of 64 (the row's sliding window, its dense prefix, or its top-k selection
+// list), are staged in shared memory with cp.async (two buffers: the next chunk's gather overlaps the current
+// chunk's math), scored with m16n8k16 MMAs (S = Q K^T, 16 heads x 64 keys), soft-maxed online per head, and accumulated with a second set of MMAs
 // (O += P V, V fragments through ldmatrix.trans).  The work per CTA is a gather of ~1.3 MB at top-k 2048, so
 // the kernel is bound by L2/HBM gather bandwidth, not by tensor throughput; with M = 16 live rows there is no
 // 128-lane UMMA shape to fill, which is why this kernel uses warp-level MMAs rather than tcgen05.
@@ -51,21 +51,30 @@ struct AttnArgs {               // must match target_kernels.cu
   unsigned int* tickets;
 };
 
-constexpr int kHd = 192, kVd = 128, kChunk = 128, kM = 16;
+constexpr int kHd = 192, kVd = 128, kChunk = 64, kM = 16, kStagesKV = 2;
 constexpr int kQStride = kHd + 8;        // bf16 elements; 400-byte rows: fragment loads hit 32 distinct banks
 constexpr int kVStride = kVd + 8;        // 272-byte rows: ldmatrix rows fall into distinct 16-byte bank groups
-constexpr int kSStride = kChunk + 4;     // fp32
+constexpr int kSStride = kVd + 4;        // fp32; also carries the 128 output channels at the end
 constexpr int kPStride = kChunk + 8;     // bf16
 
 struct Smem {
   __nv_bfloat16 q[kM][kQStride];
-  __nv_bfloat16 k[kChunk][kQStride];
-  __nv_bfloat16 v[kChunk][kVStride];
+  __nv_bfloat16 k[kStagesKV][kChunk][kQStride];
+  __nv_bfloat16 v[kStagesKV][kChunk][kVStride];
   float s[kM][kSStride];
   __nv_bfloat16 p[kM][kPStride];
   float m[kM], l[kM], corr[kM];
-  int kid[kChunk];
 };
+
+// 16-byte asynchronous copy global -> shared; `valid` false writes zeros (nothing is read)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void mma16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -126,45 +135,44 @@ __global__ void __launch_bounds__(256, 2) attn_group_kernel(const AttnArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) oc[t][j] = 0.f;
 
-  for (int c0 = 0; c0 < count; c0 += kChunk) {
-    const int n = min(kChunk, count - c0);
-    __syncthreads();                                          // previous chunk fully consumed
-    if (tid < kChunk) {
-      const int j = c0 + tid;
-      sm.kid[tid] = tid < n ? (a.mode == 1 ? (use_sel ? a.sel[(size_t)r * a.top_k + j] : j) : lo + j) : -1;
-    }
-    __syncthreads();
-    // ---- gather K and V rows (dead rows zero: a zero probability must not meet a NaN)
+  // Key chunks of 64 are staged with cp.async into two buffers: the gather of chunk c + 1 is in flight while
+  // chunk c is scored, so a CTA covers its own gather latency (two CTAs per SM cover the rest).
+  auto issue = [&](int c0, int stage) {
     for (int i = tid; i < kChunk * (kHd / 8); i += 256) {
       const int t = i / (kHd / 8), c = i - t * (kHd / 8);
-      const int id = sm.kid[t];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (id >= 0) {
-        const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
-        v = reinterpret_cast<const uint4*>(a.k_cache + (slot * a.kv_heads + g) * kHd)[c];
-      }
-      *reinterpret_cast<uint4*>(&sm.k[t][c * 8]) = v;
+      const int j = c0 + t;
+      const bool valid = j < count;
+      const int id = !valid ? 0 : (a.mode == 1 ? (use_sel ? a.sel[(size_t)r * a.top_k + j] : j) : lo + j);
+      const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
+      cp_async16(&sm.k[stage][t][c * 8], a.k_cache + (slot * a.kv_heads + g) * kHd + c * 8, valid);
     }
     for (int i = tid; i < kChunk * (kVd / 8); i += 256) {
       const int t = i / (kVd / 8), c = i - t * (kVd / 8);
-      const int id = sm.kid[t];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (id >= 0) {
-        const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
-        v = reinterpret_cast<const uint4*>(a.v_cache + (slot * a.kv_heads + g) * kVd)[c];
-      }
-      *reinterpret_cast<uint4*>(&sm.v[t][c * 8]) = v;
+      const int j = c0 + t;
+      const bool valid = j < count;
+      const int id = !valid ? 0 : (a.mode == 1 ? (use_sel ? a.sel[(size_t)r * a.top_k + j] : j) : lo + j);
+      const size_t slot = a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id;
+      cp_async16(&sm.v[stage][t][c * 8], a.v_cache + (slot * a.kv_heads + g) * kVd + c * 8, valid);
     }
-    __syncthreads();
-    // ---- S = Q K^T: warp w scores keys [16w, 16w + 16) for all heads
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int key0 = warp * 16 + t * 8;
+  };
+  const int nchunks = (count + kChunk - 1) / kChunk;
+  issue(0, 0);
+  cp_async_commit();
+  for (int ci = 0; ci < nchunks; ++ci) {
+    const int c0 = ci * kChunk, st = ci & 1;
+    const int n = min(kChunk, count - c0);
+    if (ci + 1 < nchunks) issue(c0 + kChunk, st ^ 1);
+    cp_async_commit();                                        // (possibly empty) group of chunk ci + 1
+    cp_async_wait<1>();                                       // this thread's copies of chunk ci have landed
+    __syncthreads();                                          // ... and everybody else's
+    // ---- S = Q K^T: warp w scores keys [8w, 8w + 8) for all heads
+    {
+      const int key0 = warp * 8;
       float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < kHd / 16; ++ks) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.k[key0 + qr][ks * 16 + qc]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.k[key0 + qr][ks * 16 + qc + 8]);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.k[st][key0 + qr][ks * 16 + qc]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.k[st][key0 + qr][ks * 16 + qc + 8]);
         mma16816(c, qa[ks], b0, b1);
       }
       const int kc = key0 + qc;
@@ -178,16 +186,16 @@ __global__ void __launch_bounds__(256, 2) attn_group_kernel(const AttnArgs a) {
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
       const int h = warp * 2 + t;
-      float v[4];
+      float v[kChunk / 32];
       float mx = -FLT_MAX;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { v[j] = sm.s[h][lane + 32 * j]; mx = fmaxf(mx, v[j]); }
+      for (int j = 0; j < kChunk / 32; ++j) { v[j] = sm.s[h][lane + 32 * j]; mx = fmaxf(mx, v[j]); }
       mx = wmax(mx);
       const float m_old = sm.m[h];
       const float m_new = fmaxf(m_old, mx);
       float sum = 0.f;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < kChunk / 32; ++j) {
         const int kc = lane + 32 * j;
         const float p = kc < n ? rbf16(__expf(v[j] - m_new)) : 0.f;
         sm.p[h][kc] = __float2bfloat16_rn(p);
@@ -217,12 +225,14 @@ __global__ void __launch_bounds__(256, 2) attn_group_kernel(const AttnArgs a) {
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           uint32_t b0, b1;
-          ldmatrix_x2_trans(b0, b1, &sm.v[kk * 16 + (lane & 15)][warp * 16 + t * 8]);
+          ldmatrix_x2_trans(b0, b1, &sm.v[st][kk * 16 + (lane & 15)][warp * 16 + t * 8]);
           mma16816(oc[t], pa, b0, b1);
         }
       }
     }
+    __syncthreads();                                          // stage st is free for chunk ci + 2
   }
+  cp_async_wait<0>();
   __syncthreads();
   // ---- sink column (no value), normalisation, bf16 rounding; o goes through shared memory for the packet
   if (tid < kM) {
