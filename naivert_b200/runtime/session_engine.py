@@ -25,9 +25,9 @@ from .round import RuntimeContractError
 
 # Measured on B200 (ms); inputs of the resume / prefill-path policy.
 REPLAY_MS_PER_TOKEN = 1.2            # 8-row verify replay per prompt token (tp8, 48 layers: 9.6 ms per 8 rows)
-NATIVE_FIXED_MS = 30.0               # chunked native prefill: launches + collectives of one (partial) chunk ...
-NATIVE_MS_PER_TOKEN = 0.035          # ... plus per-row work at short context (tp8: 8192 tokens in 0.48 s with 2048-row chunks)
-NATIVE_MS_PER_TOKEN_PER_64K_CONTEXT = 0.008  # indexer sweep + top-k grow with the context (131072 tokens: 6.6 s)
+NATIVE_FIXED_MS = 90.0               # chunked native prefill at tp8, 48 layers: a chunk is bound by per-layer latencies
+NATIVE_MS_PER_TOKEN = 0.003          # ... (launches, NCCL and peer exchanges: ~2 ms per layer), rows add little on top
+NATIVE_MS_PER_TOKEN_PER_64K_CONTEXT = 0.001  # sweep + top-k grow with the context (131072 tokens: 3.2 s measured)
 NATIVE_CHUNK = 4096
 RESTORE_MS_PER_GB = 2.0
 
