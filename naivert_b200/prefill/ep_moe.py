@@ -158,3 +158,42 @@ class EPMoE:
         with stage("moe.combine"):
             K.ep_combine(c, pdl=pdl)
             K.epoch_advance(fab.epoch, pdl=pdl)
+
+
+def ep_layout_reference(ids_per_rank: List[torch.Tensor], experts: int, item_rows: int = 16):
+    """Host restatement of the layout ``ep_count`` computes on the device (for tests and debugging).
+
+    ``ids_per_rank[s]`` are source rank s's routing choices [tokens, top_k] (global expert ids).  Returns, for every
+    destination rank d: ``seg_base[d][el]`` (first receive-buffer row of local expert el, segments padded to
+    ``item_rows``), ``seg_rows[d][el]`` (rows received), the work list ``items[d]`` = [(local expert, first row)], and
+    ``slot[s]`` = destination row of every (token, k) pair of source s: segment base + rows of lower source ranks +
+    the pair's rank among the source's pairs of that expert in (token, k) order."""
+    tp = len(ids_per_rank)
+    if experts % tp:
+        raise ValueError("experts must divide over the ranks")
+    el_n = experts // tp
+    counts = torch.stack([torch.bincount(i.flatten().long(), minlength=experts) for i in ids_per_rank])   # [tp, E]
+    seg_base, seg_rows, items = [], [], []
+    for d in range(tp):
+        base, bases, rows_d, work = 0, [], [], []
+        for el in range(el_n):
+            e = d * el_n + el
+            rows = int(counts[:, e].sum())
+            bases.append(base)
+            rows_d.append(rows)
+            work += [(el, base + r0) for r0 in range(0, rows, item_rows)]
+            base += -(-rows // item_rows) * item_rows
+        seg_base.append(bases); seg_rows.append(rows_d); items.append(work)
+    slots = []
+    for s, ids in enumerate(ids_per_rank):
+        flat = ids.flatten().long()
+        cursor = {}
+        out = torch.empty_like(flat)
+        for i, e in enumerate(flat.tolist()):
+            d, el = divmod(e, el_n)
+            start = seg_base[d][el] + int(counts[:s, e].sum())
+            k = cursor.get(e, 0)
+            out[i] = start + k
+            cursor[e] = k + 1
+        slots.append(out.reshape(ids.shape))
+    return {"seg_base": seg_base, "seg_rows": seg_rows, "items": items, "slot": slots}

@@ -156,3 +156,27 @@ def test_acceptance_histogram():
     from naivert_b200.runtime.session_engine import acceptance_histogram
     assert acceptance_histogram([0, 7, 7, 3, 9, -1]) == [2, 0, 0, 1, 0, 0, 0, 3]
     assert acceptance_histogram([]) == [0] * 8
+
+
+def test_ep_layout_reference_invariants():
+    import torch
+    from naivert_b200.prefill.ep_moe import ep_layout_reference
+    g = torch.Generator().manual_seed(2)
+    tp, E, T, k = 2, 16, 40, 4
+    ids = [torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]) for _ in range(tp)]
+    for item_rows in (16, 64):
+        lay = ep_layout_reference(ids, E, item_rows)
+        for d in range(tp):
+            taken = {}
+            for s in range(tp):
+                for e, row in zip(ids[s].flatten().tolist(), lay["slot"][s].flatten().tolist()):
+                    if e // (E // tp) == d:
+                        assert row not in taken                     # every pair has its own row
+                        taken[row] = e
+            for el, (base, rows) in enumerate(zip(lay["seg_base"][d], lay["seg_rows"][d])):
+                assert base % item_rows == 0
+                got = sorted(r for r, e in taken.items() if e == d * (E // tp) + el)
+                assert got == list(range(base, base + rows))        # a segment is dense and starts at its base
+            covered = sum(min(item_rows, lay["seg_rows"][d][el] - (r0 - lay["seg_base"][d][el])) for el, r0 in lay["items"][d])
+            assert covered == sum(lay["seg_rows"][d])               # the work list covers every received row once
+        assert sum(sum(r) for r in lay["seg_rows"]) == tp * T * k
