@@ -17,7 +17,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     from naivert_b200.ops.quant import quantize_act_pow2, quantize_fp8_block, w8a8_linear_ref
     from naivert_b200.parallel.fabric import Fabric
-    from naivert_b200.prefill.ep_moe import EPMoE
+    from naivert_b200.prefill.ep_moe import EPMoE, ep_layout_reference
     H, I, E, Kk, T = 1024, 512, 16, 4, 96
     El = E // world
     g = torch.Generator(device=dev).manual_seed(5)          # same on every rank: the full model
@@ -50,6 +50,12 @@ def main():
     torch.cuda.synchronize()
     out64 = out.clone()
     fab.check()
+    # device layout (segments, work list, destination rows) against its host restatement
+    lay = ep_layout_reference([ids_all[s].int().cpu() for s in range(world)], E, 16)
+    n_it = int(moe.n_items)
+    layout_ok = (moe.seg_rows.tolist() == lay["seg_rows"][rank]
+                 and list(zip(moe.item_expert[:n_it].tolist(), moe.item_row[:n_it].tolist())) == lay["items"][rank]
+                 and moe.slot_of.tolist() == lay["slot"][rank].flatten().tolist())
     # torch reference of this rank's tokens
     xf = x.float()
     xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()).bfloat16().float()
@@ -68,13 +74,14 @@ def main():
     res = {"world": world, "max_rel_err": err, "first_err": err0, "diff_rows": dd.amax(-1).nonzero().flatten().tolist()[:12],
            "diff_max": dd.max().item(), "repeat_identical": bool(torch.equal(outs[0], outs[1])),
            "items": int(moe.n_items), "rows": int(moe.seg_rows.sum()), "status": int(fab.status[0]),
-           "wide_identical": bool(torch.equal(out64, outs[1])), "wide_items": int(moe64.n_items),
+           "layout_ok": bool(layout_ok), "wide_identical": bool(torch.equal(out64, outs[1])), "wide_items": int(moe64.n_items),
            "wide_err": ((out64.float() - ref).abs().max() / ref.abs().max()).item()}
     if world > 1:
         allr = [None] * world
         dist.all_gather_object(allr, res)
         res["worst_err"] = max(max(r["max_rel_err"], r["wide_err"]) for r in allr)
         res["wide_identical"] = all(r["wide_identical"] for r in allr)
+        res["layout_ok"] = all(r["layout_ok"] for r in allr)
         res["total_rows"] = sum(r["rows"] for r in allr)
     if rank == 0:
         print("RESULT " + json.dumps(res), flush=True)

@@ -50,6 +50,7 @@ def test_expert_parallel_all_to_all(n):
     assert r["status"] == 0 and r["repeat_identical"], r
     assert r.get("worst_err", r["max_rel_err"]) < 0.02 and r["wide_err"] < 0.02, r
     assert r["wide_identical"], r                       # the 64-column chunk engine adds in the same order
+    assert r["layout_ok"], r                            # segments / work list / rows as the host restatement predicts
     assert r.get("total_rows", r["rows"]) == 96 * 4 * n
 
 
