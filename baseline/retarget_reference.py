@@ -1,0 +1,67 @@
+"""Prepare the reference tree for the same-box comparison arm of ``bench.py``.
+
+The reference is not pip-installable (no ``setup.py`` / ``pyproject.toml``), so it is copied as a
+source tree into ``baseline/_ref``.  Its kernel builders hard-code the B300 architecture
+(``compute_103a``), for which this CUDA toolkit cannot generate code that runs on a B200; the only
+edit made to the copy is that architecture string (``compute_103a`` -> ``compute_100a``,
+``sm_103a`` -> ``sm_100a``, arch list ``10.3a`` -> ``10.0a``).  Every edited line is listed in
+``baseline/RETARGET.txt``; nothing else of the copy differs from the source.
+
+    python baseline/retarget_reference.py [--source /path/to/reference]
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+DEST = os.path.join(HERE, "_ref")
+SUBS = (("compute_103a", "compute_100a"), ("sm_103a", "sm_100a"), ("'10.3a'", "'10.0a'"))
+SUFFIXES = (".py", ".sh")
+
+
+def retarget(source: str) -> list:
+    if os.path.isdir(DEST):
+        shutil.rmtree(DEST)
+    shutil.copytree(source, DEST, symlinks=True)
+    edits = []
+    for root, _, files in os.walk(DEST):
+        for name in sorted(files):
+            if not name.endswith(SUFFIXES) and name != "Dockerfile":
+                continue
+            path = os.path.join(root, name)
+            try:
+                text = open(path, encoding="utf-8").read()
+            except UnicodeDecodeError:
+                continue
+            if not any(a in text for a, _ in SUBS):
+                continue
+            lines = text.split("\n")
+            for i, line in enumerate(lines):
+                new = line
+                for a, b in SUBS:
+                    new = new.replace(a, b)
+                if new != line:
+                    edits.append((os.path.relpath(path, DEST), i + 1, line.strip(), new.strip()))
+                    lines[i] = new
+            with open(path, "w", encoding="utf-8") as f:
+                f.write("\n".join(lines))
+    return edits
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--source", default="/root/reference")
+    a = ap.parse_args()
+    edits = retarget(a.source)
+    with open(os.path.join(HERE, "RETARGET.txt"), "w") as f:
+        f.write("# lines of the reference copy that differ from the source (architecture string only)\n")
+        for rel, ln, old, new in edits:
+            f.write(f"{rel}:{ln}\n  - {old}\n  + {new}\n")
+    print(f"{len(edits)} lines edited in {DEST}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

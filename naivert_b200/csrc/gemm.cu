@@ -21,24 +21,41 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-template <bool FP8, bool DUAL, int EPI, int GROUP>
+template <bool FP8, bool DUAL, int EPI, int GROUP, int BSRC = kBTma>
 int launch_variant(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmArgs& args, int gx,
                    int gy, cudaStream_t stream, int pdl) {
-  using Cfg = GemmCfg<FP8, DUAL>;
-  auto* kern = skinny_gemm_kernel<FP8, DUAL, EPI, GROUP>;
+  using Cfg = GemmCfg<FP8, DUAL, BSRC>;
+  auto* kern = skinny_gemm_kernel<FP8, DUAL, EPI, GROUP, BSRC>;
+  constexpr int kMaxSmem = 227 * 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         BSRC == kBTma ? Cfg::kSmemBytes : kMaxSmem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   if ((EPI == kEpiAllReduce || (GROUP != kGroupItem && gy > 1)) && args.rows > kArRows) return -5;
-  if (GROUP != kGroupItem && gy > 1) {
-    if (gy > kMaxSplit) return -4;
-    return launch_cluster(kern, dim3(gx, gy, 1), dim3(192, 1, 1), dim3(1, gy, 1), Cfg::kSmemBytes, stream, pdl != 0, a0,
-                          a1, b, args);
+  const bool clustered = GROUP != kGroupItem && gy > 1;
+  if (clustered && gy > kMaxSplit) return -4;
+  int smem = Cfg::kSmemBytes;
+  if (BSRC != kBTma) {
+    if (!args.nx || !args.ngamma || !args.nssq || args.k_total % 128) return -6;
+    const int kb_total = args.k_total / (FP8 ? 128 : 64);
+    const int split = GROUP == kGroupNone && clustered ? gy : 1;
+    if (kb_total % split) return -6;
+    smem = Cfg::smem_bytes(kb_total / split);
+    if (smem > kMaxSmem) return -7;
   }
-  return launch_pdl(kern, dim3(gx, gy, 1), dim3(192, 1, 1), Cfg::kSmemBytes, stream, pdl != 0, a0, a1, b, args);
+  if (EPI == kEpiQkvPost) {
+    const AttnPostArgs& q = args.post;
+    // reductions over a head / the indexer key run over the 128 threads of one tile
+    if (q.idx_heads > 0 && (q.idx_dim != kTileN || q.col_iq % kTileN || q.col_ik % kTileN || !q.iq_scale)) return -8;
+    if ((q.q_norm || q.k_norm) && (q.head_dim != kTileN || q.col_q % kTileN || q.col_k % kTileN)) return -8;
+    if ((q.col_q | q.col_k | q.col_v | q.head_dim | q.rope_dim) & 1) return -8;
+  }
+  if (clustered)
+    return launch_cluster(kern, dim3(gx, gy, 1), dim3(192, 1, 1), dim3(1, gy, 1), smem, stream, pdl != 0, a0, a1, b, args);
+  return launch_pdl(kern, dim3(gx, gy, 1), dim3(192, 1, 1), smem, stream, pdl != 0, a0, a1, b, args);
 }
 
 }  // namespace
@@ -71,19 +88,22 @@ extern "C" int nrt_tmap_encode(void* out128, int dtype, int rank, const uint64_t
 
 extern "C" int nrt_gemm_args_size() { return (int)sizeof(GemmArgs); }
 
-// variant = fp8 | dual<<1 | epi<<2 | group<<5
+// variant = fp8 | dual<<1 | epi<<2 | group<<5 | bsrc<<7
 extern "C" int nrt_gemm_launch(int variant, const void* tmA0, const void* tmA1, const void* tmB, const void* args,
                                int grid_x, int grid_y, void* stream, int pdl) {
   CUtensorMap a0, a1, b;
   memcpy(&a0, tmA0, sizeof(a0));
   memcpy(&a1, tmA1 ? tmA1 : tmA0, sizeof(a1));
-  memcpy(&b, tmB, sizeof(b));
+  memcpy(&b, tmB ? tmB : tmA0, sizeof(b));
   GemmArgs g;
   memcpy(&g, args, sizeof(g));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define NRT_CASE(FP8, DUAL, EPI, GROUP)                                             \
   case ((FP8) | ((DUAL) << 1) | ((EPI) << 2) | ((GROUP) << 5)):                      \
     return launch_variant<(FP8) != 0, (DUAL) != 0, EPI, GROUP>(a0, a1, b, g, grid_x, grid_y, s, pdl);
+#define NRT_CASE_NORM(FP8, DUAL, EPI, GROUP)                                        \
+  case ((FP8) | ((DUAL) << 1) | ((EPI) << 2) | ((GROUP) << 5) | (kBNorm << 7)):      \
+    return launch_variant<(FP8) != 0, (DUAL) != 0, EPI, GROUP, kBNorm>(a0, a1, b, g, grid_x, grid_y, s, pdl);
   switch (variant) {
     NRT_CASE(1, 0, kEpiStoreF32, kGroupNone)
     NRT_CASE(1, 0, kEpiAllReduce, kGroupNone)
@@ -98,8 +118,15 @@ extern "C" int nrt_gemm_launch(int variant, const void* tmA0, const void* tmA1, 
     NRT_CASE(0, 0, kEpiStoreBF16, kGroupNone)
     NRT_CASE(0, 0, kEpiAllReduce, kGroupNone)
     NRT_CASE(0, 1, kEpiSiluBF16, kGroupNone)
+    // token operand normalised inside the kernel (fused RMSNorm)
+    NRT_CASE_NORM(0, 0, kEpiQkvPost, kGroupNone)
+    NRT_CASE_NORM(0, 0, kEpiStoreF32, kGroupNone)
+    NRT_CASE_NORM(0, 1, kEpiSiluBF16, kGroupNone)
+    NRT_CASE_NORM(1, 1, kEpiSiluQuant, kGroupNone)
+    NRT_CASE_NORM(1, 1, kEpiSiluQuant, kGroupItem)
     default:
       return -2;
   }
 #undef NRT_CASE
+#undef NRT_CASE_NORM
 }

@@ -39,7 +39,50 @@ constexpr int kMailboxSlabs = 4;
 constexpr int kMaxSplit = 4;                    // CTAs of one cluster that share an output tile (split K / split experts)
 
 enum GroupMode : int { kGroupNone = 0, kGroupItem = 1, kGroupLoop = 2 };
-enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4, kEpiReturn = 5 };
+enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4, kEpiReturn = 5,
+                      kEpiQkvPost = 6 };
+// Where the token (B) operand comes from: a TMA load of a prepared tensor, or rows the CTA normalises itself
+// (RMSNorm fused into the operand build: no separate normalisation launch, no normalised copy in global memory).
+enum BSource : int { kBTma = 0, kBNorm = 1 };
+
+// q/k/v(/indexer) post-processing: per-head RMS norm (draft), RoPE on adjacent pairs, KV-cache append, value
+// scaling, indexer query / key quantisation.  Used by attn_post_kernel on stored projections and by the
+// kEpiQkvPost epilogue straight from the accumulators.
+struct AttnPostArgs {
+  const float* qkv;          // [rows][ld] fp32 projection outputs: q | k | v | iq | ik | iw   (attn_post_kernel only)
+  int ld;
+  int rows;
+  const int* pos0;
+  int heads, kv_heads, head_dim, v_dim, rope_dim;
+  float value_scale;
+  const float2* rope;        // [rows][rope_dim/2]
+  __nv_bfloat16* q_out;      // [rows][heads][head_dim]
+  __nv_bfloat16* k_cache;    // [cap][kv_heads][head_dim]
+  __nv_bfloat16* v_cache;    // [cap][kv_heads][v_dim]
+  int ring;                  // > 0: position p is stored at p % ring; < 0: row r is stored at r (block buffers)
+  // optional per-head RMS norms (draft q_norm / k_norm), applied before RoPE
+  const __nv_bfloat16* q_norm;
+  const __nv_bfloat16* k_norm;
+  float norm_eps;
+  // indexer (idx_heads == 0: none)
+  int idx_heads, idx_dim, idx_rope;
+  const float2* idx_rope_tab;   // [rows][idx_rope/2]
+  const __nv_bfloat16* ik_w;
+  const __nv_bfloat16* ik_b;
+  float ln_eps, idx_weight_scale;
+  uint8_t* iq8;              // [16*idx_heads][idx_dim] e4m3 (row r, head h at r*idx_heads + h)
+  float* ihw;                // [16][idx_heads] head weight (x query scale when iq_scale is null)
+  uint8_t* ik_cache;         // [cap][idx_dim]
+  float* ik_scale;           // [cap]
+  int col_q, col_k, col_v, col_iq, col_ik, col_iw;
+  float* iq_scale;           // [16][idx_heads] query quantisation scale kept apart from the head weight (epilogue form)
+  // epilogue form, several layers' k | v projections in one GEMM (draft context ingest): the columns repeat every
+  // group_cols features; group g appends to k_cache + g * k_group_stride (elements) with k_norm + g * norm_group_stride
+  int group_cols;            // 0: one group
+  int norm_group_stride;
+  long long k_group_stride;
+  long long v_group_stride;
+};
 
 struct FabricArgs {
   uint64_t* mailbox[kMaxPeers];   // mailbox[p] = base of rank p's mailbox (peer-mapped); mailbox[rank] is local
@@ -65,6 +108,7 @@ struct GemmArgs {
   const int* active_ids;          // [slots] expert id per slot (ascending)
   const float* probs;             // [slots][16] routing probability of token r for slot
   int max_slots;
+  int n_experts;                  // kGroupLoop: total experts; a cluster splits the list by expert-id range
   // block scales (fp8 only)
   const float* w_scale0;          // [groups][n_total/128][k_total/128]
   const float* w_scale1;          // second matrix in dual mode
@@ -88,19 +132,37 @@ struct GemmArgs {
   int ep_top_k;
   int ep_dispatch_call;           // tag call index the metadata rows must carry
   int ep_return_call;             // tag call index of the returned words
+  // fused RMSNorm of the token operand (kBNorm): xn = bf16(nx * rsqrt(sum(nssq) / k_total + neps) * ngamma)
+  const __nv_bfloat16* nx;        // [16][k_total] un-normalised rows
+  const __nv_bfloat16* ngamma;    // [k_total]
+  const float* nssq;              // [k_total/128][16] sums of squares of nx per 128-feature tile (written by nx's producer)
+  float neps;
+  // kEpiAllReduce: sums of squares of the result rows per 128-feature tile, [n_total/128][16] (null: none)
+  float* ssq_out;
+  AttnPostArgs post;              // kEpiQkvPost
 };
 
-template <bool FP8, bool DUAL>
+template <bool FP8, bool DUAL, int BSRC = kBTma>
 struct GemmCfg {
-  static constexpr int kStageBytes = (DUAL ? 2 : 1) * kATileBytes + kBTileBytes;
+  static constexpr int kABytes = (DUAL ? 2 : 1) * kATileBytes;
+  // kBNorm keeps the whole token operand of the CTA beside the ring, so a stage carries weights only
+  static constexpr int kStageBytes = kABytes + (BSRC == kBTma ? kBTileBytes : 0);
   // single-matrix tiles keep the footprint near 100 KiB so two CTAs (typically of consecutive kernels,
   // overlapped by programmatic dependent launch) share an SM
-  static constexpr int kStages = 5;
+  static constexpr int kStages = (DUAL && BSRC != kBTma) ? 4 : 5;
   static constexpr int kAccCols = DUAL ? 2 * kTok : kTok;          // TMEM columns per accumulator buffer
   static constexpr int kAccBufs = FP8 ? (DUAL ? 4 : 8) : 1;
   static constexpr int kTmemCols = (kAccCols * kAccBufs < 32) ? 32 : kAccCols * kAccBufs;
-  static constexpr int kPartBytes = (kMaxSplit - 1) * kArRows * kTileN * 4;   // split partials of the cluster peers
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers + scratch*/ + kPartBytes;
+  static constexpr int kPartBytes = (DUAL ? 2 : 1) * (kMaxSplit - 1) * kArRows * kTileN * 4;   // split partials of the cluster peers
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  // token operand built in shared memory: one 2 KiB swizzled chunk per K block (+ activation scales for e4m3)
+  __host__ __device__ static constexpr int operand_bytes(int kb_count) {
+    return BSRC == kBTma ? 0 : kb_count * kBTileBytes + (FP8 ? ((kb_count * kTok * 4 + 1023) & ~1023) : 0);
+  }
+  __host__ __device__ static constexpr int smem_bytes(int kb_count) {
+    return kRingBytes + operand_bytes(kb_count) + 1024 /*align*/ + 1024 /*barriers + scratch*/ + kPartBytes;
+  }
+  static constexpr int kSmemBytes = kRingBytes + 1024 + 1024 + kPartBytes;     // kBTma
 };
 
 struct GemmSmemTail {
@@ -109,9 +171,11 @@ struct GemmSmemTail {
   uint64_t acc_full[8];
   uint64_t acc_empty[8];
   uint64_t split_bar;          // leader: arrivals of the cluster peers' partials
+  uint64_t b_ready;            // kBNorm: the token operand is complete in shared memory
   uint32_t tmem_base;
   uint32_t pad;
   float red[4][kTok];
+  float rs[kTok];              // kBNorm: 1 / rms of each row
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
@@ -126,14 +190,318 @@ __device__ __forceinline__ float pow2_scale(float amax) {
   return ldexpf(1.0f, e);
 }
 
-template <bool FP8, bool DUAL, int EPI, int GROUP>
-__global__ void __launch_bounds__(192, DUAL ? 1 : 2)
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Reduction of 16 per-thread values over the 128 epilogue threads of a CTA (fixed order: warp butterfly,
+// then the four warps in order).  `red` is [4][16] shared floats; SUM = false takes the maximum.
+template <bool SUM>
+__device__ __forceinline__ void epi_reduce16(float (&v)[kTok], int rows, float (*red)[kTok], int quad, int lane) {
+#pragma unroll
+  for (int r = 0; r < kTok; ++r)
+    if (r < rows) {
+      const float t = SUM ? warp_sum_f(v[r]) : warp_max_f(v[r]);
+      if (lane == 0) red[quad][r] = t;
+    }
+  epi_bar();
+#pragma unroll
+  for (int r = 0; r < kTok; ++r)
+    if (r < rows)
+      v[r] = SUM ? ((red[0][r] + red[1][r]) + (red[2][r] + red[3][r]))
+                 : fmaxf(fmaxf(red[0][r], red[1][r]), fmaxf(red[2][r], red[3][r]));
+  epi_bar();
+}
+
+__device__ __forceinline__ void rope_pair(float& a, float& b, float2 cs) {
+  const float re = a * cs.x - b * cs.y;
+  const float im = a * cs.y + b * cs.x;
+  a = re;
+  b = im;
+}
+// RoPE of the element a thread holds when its pair partner sits in the neighbouring lane (feature index
+// parity = lane parity): both lanes evaluate the same pair and keep their own half.
+__device__ __forceinline__ float rope_lane(float x, float other, bool odd, float2 cs) {
+  float a = odd ? other : x, b = odd ? x : other;
+  rope_pair(a, b, cs);
+  return odd ? b : a;
+}
+__device__ __forceinline__ uint8_t e4m3_bits(float v) {
+  const __nv_fp8_e4m3 q(v);
+  return *reinterpret_cast<const uint8_t*>(&q);
+}
+
+// ----------------------------------------------------------------------------- fused RMSNorm operand build
+// Called by the 128 epilogue threads (et = 0..127).  Writes the CTA's K blocks [kb_first, kb_first + kb_count)
+// of the normalised rows into `ball` in the layout a 128-byte-swizzled TMA box {128 B, 16 rows} would produce:
+// chunk c at c * 2 KiB, row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte unit j at ((j ^ (r % 8)) * 16).
+// bf16: 64 elements per chunk; e4m3: 128 elements per chunk with one power-of-two scale per (row, chunk)
+// stored in bscale[r * kb_count + c].  Rows >= p.rows are zero.
+template <bool FP8>
+__device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* ball, float* bscale, float* rs_s,
+                                                   int kb_first, int kb_count, int et) {
+  const int warp = et >> 5, lane = et & 31;
+  const int rows = p.rows;
+  const int tiles = p.k_total / 128;
+  // dead rows: zero (finite inputs for the unused MMA columns); stores only, nothing waits on them
+  {
+    const int dead = kTok - rows;
+    const int units = kb_count * dead * 8;
+    for (int u = et; u < units; u += 128) {
+      const int j = u & 7, rr = (u >> 3) % dead, c = (u >> 3) / dead;
+      const int r = rows + rr;
+      *reinterpret_cast<uint4*>(ball + c * kBTileBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) =
+          make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  // A unit is 16 bytes of operand: 8 bf16 elements, or 16 e4m3 elements (two 16-byte loads of x).  Every load of a
+  // batch is issued before anything waits (one L2 round trip per batch), the per-tile sums of squares included.
+  constexpr int kBatch = FP8 ? 4 : 8;
+  constexpr int kLoads = FP8 ? 2 : 1;
+  const int total = kb_count * rows * 8;
+  bool have_rs = false;
+  for (int u0 = et; u0 - et < total; u0 += 128 * kBatch) {          // uniform trip count over the 128 threads
+    uint4 xv[kBatch][kLoads], gv[kBatch][kLoads];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int u = u0 + b * 128;
+      if (u < total) {
+        const int j = u & 7, r = (u >> 3) % rows, c = (u >> 3) / rows;
+        const int k = (kb_first + c) * (FP8 ? 128 : 64) + j * (FP8 ? 16 : 8);
+#pragma unroll
+        for (int l = 0; l < kLoads; ++l) {
+          xv[b][l] = *reinterpret_cast<const uint4*>(p.nx + (size_t)r * p.k_total + k + 8 * l);
+          gv[b][l] = __ldg(reinterpret_cast<const uint4*>(p.ngamma + k + 8 * l));
+        }
+      }
+    }
+    if (!have_rs) {
+      for (int r = warp; r < rows; r += 4) {
+        float s = 0.f;
+        for (int t = lane; t < tiles; t += 32) s += __ldcg(p.nssq + t * kTok + r);
+        s = warp_sum_f(s);
+        if (lane == 0) rs_s[r] = rsqrtf(s / (float)p.k_total + p.neps);
+      }
+      epi_bar();
+      have_rs = true;
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int u = u0 + b * 128;
+      const bool on = u < total;
+      const int j = u & 7, r = on ? (u >> 3) % rows : 0, c = on ? (u >> 3) / rows : 0;
+      const float rs = rs_s[r];
+      float o[8 * kLoads];
+      float am = 0.f;
+      if (on) {
+#pragma unroll
+        for (int l = 0; l < kLoads; ++l) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xv[b][l]);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv[b][l]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
+            o[8 * l + 2 * q] = round_bf16(f.x * rs * g.x);
+            o[8 * l + 2 * q + 1] = round_bf16(f.y * rs * g.y);
+          }
+        }
+      }
+      uint4 w;
+      if (!FP8) {
+        __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) wh[q] = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
+      } else {
+        // the 8 units of a (row, chunk) sit in 8 consecutive lanes
+        if (on) {
+#pragma unroll
+          for (int q = 0; q < 8 * kLoads; ++q) am = fmaxf(am, fabsf(o[q]));
+        }
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+        const float sc = pow2_scale(am);
+        uint8_t* wb = reinterpret_cast<uint8_t*>(&w);
+#pragma unroll
+        for (int q = 0; q < 8 * kLoads; ++q) wb[q] = e4m3_bits(o[q] / sc);
+        if (on && j == 0) bscale[r * kb_count + c] = sc;
+      }
+      if (on)
+        *reinterpret_cast<uint4*>(ball + c * kBTileBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = w;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- q/k/v post-processing epilogue
+// Thread = one feature `n` of the fused q | k | v | iq | ik | iw projection, v[r] = its fp32 accumulators for
+// the token rows.  Tiles of indexer heads, the indexer key and per-head-normed heads (head_dim == 128) must be
+// 128-aligned: their reductions run over the 128 threads of the tile.
+struct PostCtx {             // what the epilogue reads from global memory, fetched while the MMAs still run
+  int p0;
+  float2 cs[kTok];            // RoPE (cos, sin) of this thread's pair for every row (identity where no RoPE applies)
+  float w, b;                 // per-feature norm weight / LayerNorm weight and bias
+};
+
+__device__ __forceinline__ void post_group(AttnPostArgs& a, int& n0, int& n) {
+  if (a.group_cols > 0) {
+    const int g = n0 / a.group_cols;
+    n0 -= g * a.group_cols;
+    n -= g * a.group_cols;
+    a.k_cache += (size_t)g * a.k_group_stride;
+    a.v_cache += (size_t)g * a.v_group_stride;
+    if (a.k_norm) a.k_norm += (size_t)g * a.norm_group_stride;
+  }
+}
+
+__device__ __forceinline__ PostCtx qkv_post_prepare(const AttnPostArgs& a_in, int n0, int n, int rows) {
+  AttnPostArgs a = a_in;
+  post_group(a, n0, n);
+  PostCtx c;
+  c.p0 = *a.pos0;
+  c.w = 1.f;
+  c.b = 0.f;
+  const int q_end = a.col_q + a.heads * a.head_dim;
+  const int k_end = a.col_k + a.kv_heads * a.head_dim;
+  const bool t_iq = a.idx_heads > 0 && n0 >= a.col_iq && n0 < a.col_iq + a.idx_heads * a.idx_dim;
+  const bool t_ik = a.idx_heads > 0 && n0 == a.col_ik;
+  const float2* tab = nullptr;
+  int half = 0, pair = 0;
+  if (t_iq || t_ik) {
+    const int d = n - n0;
+    if (d < a.idx_rope) { tab = a.idx_rope_tab; half = a.idx_rope / 2; pair = d >> 1; }
+    if (t_ik && d < a.idx_dim) { c.w = __bfloat162float(a.ik_w[d]); c.b = __bfloat162float(a.ik_b[d]); }
+  } else {
+    const bool is_q = n >= a.col_q && n < q_end;
+    const bool is_k = n >= a.col_k && n < k_end;
+    if (is_q || is_k) {
+      const int off = is_q ? n - a.col_q : n - a.col_k;
+      const int d = off % a.head_dim;
+      if (d < a.rope_dim) { tab = a.rope; half = a.rope_dim / 2; pair = d >> 1; }
+      const __nv_bfloat16* nw = is_q ? a.q_norm : a.k_norm;
+      if (nw) c.w = __bfloat162float(nw[d]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kTok; ++r) c.cs[r] = (tab != nullptr && r < rows) ? tab[r * half + pair] : make_float2(1.f, 0.f);
+  return c;
+}
+
+__device__ __forceinline__ void qkv_post_epilogue(const AttnPostArgs& a_in, const PostCtx& c, int n0, int n, int quad, int lane,
+                                                  float (&v)[kTok], int rows, float (*red)[kTok], bool live) {
+  AttnPostArgs a = a_in;
+  post_group(a, n0, n);
+  const int p0 = c.p0;
+  const bool odd = (n & 1) != 0;
+  const int q_end = a.col_q + a.heads * a.head_dim;
+  const int k_end = a.col_k + a.kv_heads * a.head_dim;
+  const int v_end = a.col_v + a.kv_heads * a.v_dim;
+  const bool t_iq = a.idx_heads > 0 && n0 >= a.col_iq && n0 < a.col_iq + a.idx_heads * a.idx_dim;
+  const bool t_ik = a.idx_heads > 0 && n0 == a.col_ik;
+  if (t_iq) {
+    // indexer query head: bf16 -> RoPE -> bf16 -> e4m3 with a per-(row, head) scale
+    const int h = (n0 - a.col_iq) / a.idx_dim, d = n - n0;
+    float x[kTok], am[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) {
+      x[r] = round_bf16(v[r]);
+      const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
+      if (r < rows && d < a.idx_rope) x[r] = round_bf16(rope_lane(x[r], other, odd, c.cs[r]));
+      am[r] = fabsf(x[r]);
+    }
+    epi_reduce16<false>(am, rows, red, quad, lane);
+#pragma unroll
+    for (int r = 0; r < kTok; ++r)
+      if (r < rows && live) {
+        const float s = am[r] > 0.f ? am[r] / 448.f : 1.f;
+        a.iq8[((size_t)r * a.idx_heads + h) * a.idx_dim + d] = e4m3_bits(x[r] / s);
+        if (d == 0) a.iq_scale[r * a.idx_heads + h] = s;
+      }
+    return;
+  }
+  if (t_ik) {
+    // indexer key: LayerNorm (fp32) -> bf16 -> RoPE -> bf16 -> e4m3 with a per-row scale amax / 448
+    const int d = n - n0;
+    const bool in = d < a.idx_dim;
+    float t[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) t[r] = in ? v[r] : 0.f;
+    epi_reduce16<true>(t, rows, red, quad, lane);
+    float dv[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) { dv[r] = in ? v[r] - t[r] / (float)a.idx_dim : 0.f; t[r] = dv[r] * dv[r]; }
+    epi_reduce16<true>(t, rows, red, quad, lane);
+    float x[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) {
+      x[r] = in ? round_bf16(dv[r] * rsqrtf(t[r] / (float)a.idx_dim + a.ln_eps) * c.w + c.b) : 0.f;
+      const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
+      if (r < rows && d < a.idx_rope) x[r] = round_bf16(rope_lane(x[r], other, odd, c.cs[r]));
+      t[r] = fabsf(x[r]);
+    }
+    epi_reduce16<false>(t, rows, red, quad, lane);
+#pragma unroll
+    for (int r = 0; r < kTok; ++r)
+      if (r < rows && live && in) {
+        const float s = t[r] > 0.f ? t[r] / 448.f : 1.f;
+        const size_t pos = (size_t)(p0 + r);
+        a.ik_cache[pos * a.idx_dim + d] = e4m3_bits(x[r] / s);
+        if (d == 0) a.ik_scale[pos] = s;
+      }
+    return;
+  }
+  const bool is_q = n >= a.col_q && n < q_end;
+  const bool is_k = n >= a.col_k && n < k_end;
+  const bool is_v = n >= a.col_v && n < v_end;
+  const bool is_w = a.idx_heads > 0 && n >= a.col_iw && n < a.col_iw + a.idx_heads;
+  const int hq = is_q ? (n - a.col_q) / a.head_dim : (is_k ? (n - a.col_k) / a.head_dim : 0);
+  const int d = is_q ? (n - a.col_q) - hq * a.head_dim : (is_k ? (n - a.col_k) - hq * a.head_dim : 0);
+  float x[kTok];
+#pragma unroll
+  for (int r = 0; r < kTok; ++r) x[r] = round_bf16(v[r]);
+  // per-head RMS norm (heads are whole tiles): uniform over the tile
+  const bool t_qn = a.q_norm != nullptr && n0 >= a.col_q && n0 < q_end;
+  const bool t_kn = a.k_norm != nullptr && n0 >= a.col_k && n0 < k_end;
+  if (t_qn || t_kn) {
+    float ss[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) ss[r] = x[r] * x[r];
+    epi_reduce16<true>(ss, rows, red, quad, lane);
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) x[r] = round_bf16(x[r] * rsqrtf(ss[r] / (float)a.head_dim + a.norm_eps) * c.w);
+  }
+#pragma unroll
+  for (int r = 0; r < kTok; ++r) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
+    if (r >= rows || !live) continue;
+    const int pos = p0 + r;
+    const size_t slot = a.ring > 0 ? (size_t)(pos % a.ring) : (a.ring < 0 ? (size_t)r : (size_t)pos);
+    if (is_q || is_k) {
+      float o = x[r];
+      if (d < a.rope_dim) o = rope_lane(x[r], other, odd, c.cs[r]);
+      if (is_q) a.q_out[((size_t)r * a.heads + hq) * a.head_dim + d] = __float2bfloat16_rn(o);
+      else a.k_cache[(slot * a.kv_heads + hq) * a.head_dim + d] = __float2bfloat16_rn(o);
+    } else if (is_v) {
+      a.v_cache[slot * a.kv_heads * a.v_dim + (n - a.col_v)] = __float2bfloat16_rn(v[r] * a.value_scale);
+    } else if (is_w) {
+      a.ihw[r * a.idx_heads + (n - a.col_iw)] = v[r] * a.idx_weight_scale;
+    }
+  }
+}
+
+template <bool FP8, bool DUAL, int EPI, int GROUP, int BSRC = kBTma>
+__global__ void __launch_bounds__(192, (DUAL || BSRC != kBTma) ? 1 : 2)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                    const __grid_constant__ CUtensorMap tmB, const GemmArgs p) {
-  using Cfg = GemmCfg<FP8, DUAL>;
+  using Cfg = GemmCfg<FP8, DUAL, BSRC>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(smem + Cfg::kStages * Cfg::kStageBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -147,15 +515,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   const int crank = split > 1 ? (int)cluster_ctarank() : 0;
   const int kb_count = GROUP == kGroupNone ? kb_total / split : kb_total;   // K blocks this CTA walks per group
   const int kb_first = GROUP == kGroupNone ? crank * kb_count : 0;
-  float* part = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + 1024);
+  uint8_t* ball = smem + Cfg::kRingBytes;                                    // kBNorm: the CTA's token operand
+  float* bscale = reinterpret_cast<float*>(ball + kb_count * kBTileBytes);   // kBNorm e4m3: [16][kb_count]
+  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(smem + Cfg::kRingBytes + Cfg::operand_bytes(kb_count));
+  float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + 1024);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
     for (int i = 0; i < Cfg::kAccBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
     mbar_init(&tail->split_bar, 128 * (split > 1 ? split - 1 : 1));
+    mbar_init(&tail->b_ready, 128);
     mbar_fence_init();
     tma_prefetch_desc(&tmA0);
-    tma_prefetch_desc(&tmB);
+    if (BSRC == kBTma) tma_prefetch_desc(&tmB);
     if (DUAL) tma_prefetch_desc(&tmA1);
   }
   if (warp == 1) { tmem_alloc(&tail->tmem_base, Cfg::kTmemCols); tmem_relinquish(); }
@@ -191,10 +563,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
     n_groups = (int)blockIdx.y < na ? 1 : 0;
     g_first = blockIdx.y;
   } else if (GROUP == kGroupLoop) {
+    // CTA y of the cluster takes the active experts whose id lies in the y-th range of the expert ids (the list is
+    // ascending, so that is one contiguous run of slots).  A token's experts are then always added in the same
+    // grouping and order, whatever other tokens share the step: a row's result does not depend on its batch.
     const int na = min(*p.n_active, p.max_slots);
-    g_first = blockIdx.y;
-    g_step = gridDim.y;
-    n_groups = na > g_first ? (na - g_first + g_step - 1) / g_step : 0;
+    const int per = (p.n_experts + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int id_lo = (int)blockIdx.y * per, id_hi = id_lo + per;
+    int lo = 0;
+    while (lo < na && p.active_ids[lo] < id_lo) ++lo;
+    int hi = lo;
+    while (hi < na && p.active_ids[hi] < id_hi) ++hi;
+    g_first = lo;
+    g_step = 1;
+    n_groups = hi - lo;
   }
   const int units = n_groups * kb_count;
 
@@ -216,6 +597,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           tma_load_3d(sa, &tmA0, &tail->full[st], kx, n0, z);
           if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
         }
+        if (BSRC != kBTma) continue;
         const int brow = (GROUP == kGroupLoop) ? slot * kTok : ((GROUP == kGroupItem && p.row_offsets) ? p.row_offsets[slot] : 0);
         if (GROUP == kGroupItem && p.fab.ag_call >= 0 && p.fab.tp > 1 && ag_seen < 0) {
           // expert-parallel dispatch: rows of every source rank must have landed before the first token tile
@@ -243,14 +625,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
             ag_seen = src;
           }
         }
-        tma_load_2d(sa + (DUAL ? 2 : 1) * kATileBytes, &tmB, &tail->full[st], kx, brow);
+        tma_load_2d(sa + Cfg::kABytes, &tmB, &tail->full[st], kx, brow);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc(FP8 ? 0u : 1u, kTileN, kTok);
-      for (int u = 0; u < units; ++u) {
+      bool ok = true;
+      if (BSRC != kBTma && units > 0) ok = mbar_wait(&tail->b_ready, 0, p.status, kSiteTmaFull | 0x40);
+      for (int u = 0; u < units && ok; ++u) {
         const int st = u % Cfg::kStages;
         const int kb = u % kb_count;
         const int buf = FP8 ? (u % Cfg::kAccBufs) : 0;
@@ -261,7 +645,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         const uint32_t sa = smem_u32(smem + st * Cfg::kStageBytes);
         const uint64_t da0 = umma_desc_sw128(sa);
         const uint64_t da1 = umma_desc_sw128(sa + kATileBytes);
-        const uint64_t db = umma_desc_sw128(sa + (DUAL ? 2 : 1) * kATileBytes);
+        const uint64_t db = umma_desc_sw128(BSRC == kBTma ? sa + Cfg::kABytes : smem_u32(ball + kb * kBTileBytes));
         const uint32_t d0 = tmem + buf * Cfg::kAccCols;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {          // 4 x 32 bytes of K per 128-byte swizzle atom
@@ -285,6 +669,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
     const int n = n0 + row;
     const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
     const int nt_count = p.n_total / kTileN;
+    if (BSRC != kBTma) {
+      // the epilogue warps are idle until the first accumulator completes: they normalise (and quantise)
+      // the CTA's token rows into shared memory while the weight tiles stream in
+      if (units > 0) build_norm_operand<FP8>(p, ball, bscale, tail->rs, kb_first, kb_count, (int)threadIdx.x - 64);
+      fence_proxy_async_smem();
+      mbar_arrive(&tail->b_ready);
+      epi_bar();                                     // bscale of every thread is visible to the epilogue
+    }
+    PostCtx post_ctx;
+    if (EPI == kEpiQkvPost) post_ctx = qkv_post_prepare(p.post, n0, n, p.rows);
     float mix0[kTok];
 #pragma unroll
     for (int r = 0; r < kTok; ++r) mix0[r] = 0.f;
@@ -302,15 +696,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       if (FP8) {
         const size_t in_row = GROUP == kGroupLoop ? (size_t)slot * kTok
                                                    : ((GROUP == kGroupItem && p.row_offsets) ? (size_t)p.row_offsets[slot] : 0);
-        const float* as = p.a_scale + in_row * kb_total + kb_first;
+        const float* as = BSRC == kBTma ? p.a_scale + in_row * kb_total + kb_first : nullptr;
         const float* ws0 = p.w_scale0 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first;
         const float* ws1 = DUAL ? p.w_scale1 + ((size_t)z * nt_count + n_tile) * kb_total + kb_first : nullptr;
         for (int kb = 0; kb < kb_count; ++kb, ++u) {
           const int buf = u % Cfg::kAccBufs;
           // scales are fetched before the wait so their latency hides behind the MMA of this block
           float sc[kTok];
-          const bool gathered = GROUP != kGroupLoop && p.fab.ag_call >= 0 && p.fab.tp > 1;
-          if (!gathered) {
+          const bool gathered = BSRC == kBTma && GROUP != kGroupLoop && p.fab.ag_call >= 0 && p.fab.tp > 1;
+          if (BSRC != kBTma) {
+#pragma unroll
+            for (int r = 0; r < kTok; ++r) sc[r] = r < p.rows ? bscale[r * kb_count + kb] : 0.f;
+          } else if (!gathered) {
 #pragma unroll
             for (int r = 0; r < kTok; ++r) sc[r] = __ldg(as + r * kb_total + kb);
           }
@@ -359,14 +756,20 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         leader = false;
         const uint32_t dst = mapa_shared(smem_u32(part), 0);
 #pragma unroll
-        for (int r = 0; r < kArRows; ++r)
+        for (int r = 0; r < kArRows; ++r) {
           st_cluster_f32(dst + (uint32_t)((((crank - 1) * kArRows + r) * kTileN + row) * 4), mix0[r]);
+          if (DUAL)
+            st_cluster_f32(dst + (uint32_t)(((((kMaxSplit - 1) + crank - 1) * kArRows + r) * kTileN + row) * 4), mix1[r]);
+        }
         mbar_arrive_cluster(mapa_shared(smem_u32(&tail->split_bar), 0));
       } else {
         if (mbar_wait_cluster(&tail->split_bar, 0, p.status, kSiteCluster)) {
           for (int y = 1; y < split; ++y)
 #pragma unroll
-            for (int r = 0; r < kArRows; ++r) mix0[r] += part[((y - 1) * kArRows + r) * kTileN + row];
+            for (int r = 0; r < kArRows; ++r) {
+              mix0[r] += part[((y - 1) * kArRows + r) * kTileN + row];
+              if (DUAL) mix1[r] += part[(((kMaxSplit - 1) + y - 1) * kArRows + r) * kTileN + row];
+            }
         }
       }
     }
@@ -387,6 +790,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
       for (int r = 0; r < kTok; ++r)
         if (live && r < p.rows) p.out_bf16[(size_t)r * p.ld_out + n] = __float2bfloat16_rn(silu(mix0[r]) * mix1[r]);
+    } else if (EPI == kEpiQkvPost) {
+      if (leader) qkv_post_epilogue(p.post, post_ctx, n0, n, quad, lane, mix0, p.rows, tail->red, live);
     } else if (EPI == kEpiSiluQuant) {
       if (n_groups > 0) {
         // y = silu(gate) * up in fp32; one power-of-two scale per (token, this 128-feature tile)
@@ -406,8 +811,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           const float am = fmaxf(fmaxf(tail->red[0][r], tail->red[1][r]), fmaxf(tail->red[2][r], tail->red[3][r]));
           const float s = pow2_scale(am);
           const __nv_fp8_e4m3 q(y[r] / s);
-          p.out_q[(qrow + r) * p.n_total + n] = *reinterpret_cast<const uint8_t*>(&q);
-          if (row == 0) p.out_qscale[(qrow + r) * nt_count + n_tile] = s;
+          if (leader) {                          // K split over a cluster: only the leader holds the full sums
+            p.out_q[(qrow + r) * p.n_total + n] = *reinterpret_cast<const uint8_t*>(&q);
+            if (row == 0) p.out_qscale[(qrow + r) * nt_count + n_tile] = s;
+          }
         }
       }
     } else if (EPI == kEpiReturn) {
@@ -493,13 +900,30 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
         for (int r = 0; r < kArRows; ++r) sum[r] += round_bf16(mix0[r]);
       }
+      float sq[kArRows];
 #pragma unroll
-      for (int r = 0; r < kArRows; ++r)
+      for (int r = 0; r < kArRows; ++r) {
+        sq[r] = 0.f;
         if (r < p.rows && col_ok && mine) {
           const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
           p.out_bf16[(size_t)r * p.ld_out + n] = o;
           if (p.out_copy) p.out_copy[(size_t)r * p.ld_copy + n] = o;
+          const float of = __bfloat162float(o);
+          sq[r] = of * of;
         }
+      }
+      if (p.ssq_out != nullptr) {
+        // sums of squares of this tile's result rows: the next RMSNorm adds the tiles' partials in tile order
+#pragma unroll
+        for (int r = 0; r < kArRows; ++r) {
+          const float t = warp_sum_f(sq[r]);
+          if (lane == 0) tail->red[quad][r] = t;
+        }
+        epi_bar();
+        if (leader && row < kTok)
+          p.ssq_out[n_tile * kTok + row] =
+              row < kArRows ? ((tail->red[0][row] + tail->red[1][row]) + (tail->red[2][row] + tail->red[3][row])) : 0.f;
+      }
     }
     (void)ok;
   }

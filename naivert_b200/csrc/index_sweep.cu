@@ -35,6 +35,7 @@ struct SweepArgs {
   int ld;
   uint32_t* status;
   int group0, ngroups;   // row groups [group0, group0 + ngroups) are swept (ngroups == 0: all); query-row sharding
+  const float* iq_scale; // [16][heads] query quantisation scales kept apart from ihw (null: already folded into ihw)
 };
 
 struct SweepTail {
@@ -114,7 +115,7 @@ index_sweep_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   } else {
     const int quad = warp & 3;
     const int e = threadIdx.x - 64;                     // 0..127
-    for (int i = e; i < 256; i += 128) tail->hw[i] = i < ncol ? p.ihw[(size_t)rg * 16 * p.heads + i] : 0.f;
+    for (int i = e; i < 256; i += 128) tail->hw[i] = i < ncol ? p.ihw[(size_t)rg * 16 * p.heads + i] * (p.iq_scale ? p.iq_scale[(size_t)rg * 16 * p.heads + i] : 1.f) : 0.f;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
     int u = 0;

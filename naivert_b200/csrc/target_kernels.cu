@@ -86,6 +86,66 @@ __global__ void rope_table_kernel(const int* __restrict__ pos0, int rows, int di
   out[r * (dim / 2) + i] = make_float2((float)cos(ang), (float)sin(ang));
 }
 
+// ----------------------------------------------------------------------------- step prologue
+// One launch for everything a step needs before its first projection: the input rows (embedding gather, or the
+// draft block: anchor embedding + mask embeddings), the per-128-feature sums of squares of those rows (the first
+// RMSNorm is fused into the projection that follows and only needs these partials) and the RoPE tables of the
+// step's positions.  CTAs 0..15 take one row each, CTA 16 + t fills table t.
+struct PrologueArgs {
+  const int* tokens;               // mode 0: [rows] token ids; mode 1: [0] is the anchor token
+  const __nv_bfloat16* table;      // [vocab][hidden]
+  const __nv_bfloat16* mask;       // mode 1: [hidden] mask embedding of rows 1..rows-1
+  __nv_bfloat16* x;                // [16][hidden]
+  float* ssq;                      // [hidden/128][16]
+  int hidden, rows, vocab, mode;
+  int n_tabs;
+  const int* tab_pos0[4];
+  int tab_dim[4];
+  double tab_theta[4];
+  float2* tab_out[4];              // [rows][dim/2]
+};
+
+__global__ void __launch_bounds__(128) step_prologue_kernel(const PrologueArgs a) {
+  griddep_wait();
+  griddep_launch();
+  if (blockIdx.x >= kMaxRows) {
+    const int t = blockIdx.x - kMaxRows;
+    const int half = a.tab_dim[t] / 2;
+    const int p0 = *a.tab_pos0[t];
+    for (int i = threadIdx.x; i < a.rows * half; i += 128) {
+      const int r = i / half, c = i - r * half;
+      const double inv = pow(a.tab_theta[t], -2.0 * (double)c / (double)a.tab_dim[t]);
+      const double ang = (double)(p0 + r) * inv;
+      a.tab_out[t][i] = make_float2((float)cos(ang), (float)sin(ang));
+    }
+    return;
+  }
+  const int r = blockIdx.x;
+  const uint4* src = nullptr;
+  if (r < a.rows) {
+    if (a.mode == 0 || r == 0) {
+      int t = a.tokens[r];
+      t = t < 0 ? 0 : (t >= a.vocab ? a.vocab - 1 : t);
+      src = reinterpret_cast<const uint4*>(a.table + (size_t)t * a.hidden);
+    } else {
+      src = reinterpret_cast<const uint4*>(a.mask);
+    }
+  }
+  uint4* dst = reinterpret_cast<uint4*>(a.x + (size_t)r * a.hidden);
+  // 16 consecutive threads cover one 128-feature tile
+  for (int i = threadIdx.x; i < a.hidden / 8; i += 128) {
+    const uint4 v = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+    dst[i] = v;
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); ss += f.x * f.x + f.y * f.y; }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((i & 15) == 0) a.ssq[(i >> 4) * kMaxRows + r] = ss;
+  }
+}
+
 // ----------------------------------------------------------------------------- RMSNorm (+ e4m3 packet)
 // One CTA per row (16 CTAs; rows >= `rows` are zero-filled so the padded GEMM operand is clean).
 // xn = bf16(x * rsqrt(mean(x^2) + eps) * g); optional packet: e4m3(xn / s) with one power-of-two
@@ -154,42 +214,6 @@ prep_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
 }
 
 // ----------------------------------------------------------------------------- q/k/v post-processing
-struct AttnPostArgs {
-  const float* qkv;          // [rows][ld] fp32 projection outputs: q | k | v | iq | ik | iw
-  int ld;
-  int rows;
-  const int* pos0;
-  int heads, kv_heads, head_dim, v_dim, rope_dim;
-  float value_scale;
-  const float2* rope;        // [rows][rope_dim/2]
-  __nv_bfloat16* q_out;      // [rows][heads][head_dim]
-  __nv_bfloat16* k_cache;    // [cap][kv_heads][head_dim]
-  __nv_bfloat16* v_cache;    // [cap][kv_heads][v_dim]
-  int ring;                  // > 0: position p is stored at p % ring; < 0: row r is stored at r (block buffers)
-  // optional per-head RMS norms (draft q_norm / k_norm), applied before RoPE
-  const __nv_bfloat16* q_norm;
-  const __nv_bfloat16* k_norm;
-  float norm_eps;
-  // indexer (idx_heads == 0: none)
-  int idx_heads, idx_dim, idx_rope;
-  const float2* idx_rope_tab;   // [rows][idx_rope/2]
-  const __nv_bfloat16* ik_w;
-  const __nv_bfloat16* ik_b;
-  float ln_eps, idx_weight_scale;
-  uint8_t* iq8;              // [16*idx_heads][idx_dim] e4m3 (row r, head h at r*idx_heads + h)
-  float* ihw;                // [16][idx_heads] head weight * query scale
-  uint8_t* ik_cache;         // [cap][idx_dim]
-  float* ik_scale;           // [cap]
-  int col_q, col_k, col_v, col_iq, col_ik, col_iw;
-};
-
-__device__ __forceinline__ void rope_pair(float& a, float& b, float2 cs) {
-  const float re = a * cs.x - b * cs.y;
-  const float im = a * cs.y + b * cs.x;
-  a = re;
-  b = im;
-}
-
 // One CTA per row; warps take whole heads.
 __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
   __shared__ float red[8];
@@ -264,7 +288,10 @@ __global__ void __launch_bounds__(256) attn_post_kernel(const AttnPostArgs a) {
       const int i = lane + 32 * t;
       if (i < pairs) { dst[2 * i] = to_e4m3(v[2 * t] / s); dst[2 * i + 1] = to_e4m3(v[2 * t + 1] / s); }
     }
-    if (lane == 0) a.ihw[r * a.idx_heads + h] = src[a.col_iw + h] * a.idx_weight_scale * s;
+    if (lane == 0) {
+      if (a.iq_scale) { a.ihw[r * a.idx_heads + h] = src[a.col_iw + h] * a.idx_weight_scale; a.iq_scale[r * a.idx_heads + h] = s; }
+      else a.ihw[r * a.idx_heads + h] = src[a.col_iw + h] * a.idx_weight_scale * s;
+    }
   }
   // indexer key: LayerNorm (fp32) -> bf16 -> RoPE -> bf16 -> e4m3 with a per-row scale amax/448
   if (part == 0) {
@@ -468,6 +495,7 @@ struct IndexArgs {
   int rows, heads, dim, top_k;
   float* logits;        // [16][ld]
   int ld;
+  const float* iq_scale;   // [16][heads] or null (scale already folded into ihw)
 };
 
 __global__ void __launch_bounds__(256) index_logits_simple_kernel(const IndexArgs a) {
@@ -500,7 +528,7 @@ __global__ void __launch_bounds__(256) index_logits_simple_kernel(const IndexArg
         float d = 0.f;
 #pragma unroll 16
         for (int j = 0; j < a.dim; ++j) d += q[j] * kf[j];
-        lg += fmaxf(d, 0.f) * a.ihw[r * a.heads + h];
+        lg += fmaxf(d, 0.f) * (a.ihw[r * a.heads + h] * (a.iq_scale ? a.iq_scale[r * a.heads + h] : 1.f));
       }
       a.logits[(size_t)r * a.ld + t] = lg * ks;
     }
@@ -730,12 +758,12 @@ __global__ void __launch_bounds__(1024) topk_grid_write_kernel(const float* __re
 
 // ----------------------------------------------------------------------------- MoE router
 struct RouterArgs {
-  const __nv_bfloat16* xn;   // [16][hidden] normed activations (plain router) or null (fused form)
-  const __nv_bfloat16* x;    // fused form: residual rows [16][hidden]
+  const __nv_bfloat16* xn;   // [16][hidden] normed activations (plain router) or null (inline-norm form)
+  const __nv_bfloat16* x;    // inline-norm form: residual rows [16][hidden], normalised while they are read
   const __nv_bfloat16* gamma;
   float eps;
-  uint8_t* x8;               // fused form: e4m3 packet [16][hidden] + scales [16][hidden/128] for the expert GEMMs
-  float* xs;
+  const float* ssq;          // inline-norm form: [hidden/128][16] sums of squares of x per 128-feature tile
+  float* xs;                 // inline-norm form: scales [16][hidden/128] of the e4m3 packet below (null: no packet)
   const float* w;            // [experts][hidden] fp32
   const float* bias;         // [experts] or null
   int hidden, experts, rows, top_k;
@@ -750,6 +778,8 @@ struct RouterArgs {
   int* topk_ids;             // [16][top_k]
   float* topk_p;             // [16][top_k]
   int max_slots;
+  uint8_t* x8;               // inline-norm form: e4m3 packet [16][hidden] of the normalised rows for the expert GEMMs;
+                             // each CTA quantises a few (row, 128-channel block) pairs, so nobody repeats the work
 };
 
 // grid = experts / 2 CTAs; each warp-pair of a CTA... one CTA computes 2 experts x 16 rows; the last CTA
@@ -770,90 +800,94 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   __shared__ bool last;
   __shared__ unsigned int used[8];                  // bitmap over <= 256 experts
   __shared__ int slot_of[256];
-  griddep_wait();
-  griddep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e0 = blockIdx.x * 2;
-  extern __shared__ uint4 router_smem[];
-  const __nv_bfloat16* xsrc = a.xn;
-  int xld = a.hidden;
-  if (a.x) {
-    // Fused RMSNorm: every CTA normalises all rows into shared memory (64 KiB read from L2); the CTA
-    // whose index equals a row also writes that row's e4m3 packet for the expert GEMMs.
-    __nv_bfloat16* xn_s = reinterpret_cast<__nv_bfloat16*>(router_smem);
-    const int per = a.hidden / 8;
-    for (int r = warp; r < kMaxRows; r += 8) {
-      const bool live = r < a.rows;
-      const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)r * a.hidden);
-      float ss = 0.f;
-      if (live)
-        for (int i = lane; i < per; i += 32) {
-          const uint4 v = src[i];
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  __shared__ float rs_s[kMaxRows];
+  const bool inline_norm = a.x != nullptr;
+  const bool fast = a.hidden == 4096;
+  // The two experts' weights and the norm weights never depend on earlier kernels: their loads are issued before
+  // this kernel waits for its predecessor, so the HBM round trip overlaps the predecessor's tail.
+  float4 w0[4], w1[4], gm[4];
+  if (fast) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); ss += f.x * f.x + f.y * f.y; }
-        }
-      ss = warp_sum(ss);
-      const float rs = rsqrtf(ss / (float)a.hidden + a.eps);
-      const bool packet = (int)blockIdx.x == r && a.x8 != nullptr;
-      for (int i = lane; i < per; i += 32) {
-        float o[8];
-        float am = 0.f;
-        if (live) {
-          const uint4 v = src[i];
-          const uint4 gv = reinterpret_cast<const uint4*>(a.gamma)[i];
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h[j]), g = __bfloat1622float2(gh[j]);
-            o[2 * j] = round_bf16(f.x * rs * g.x);
-            o[2 * j + 1] = round_bf16(f.y * rs * g.y);
-            am = fmaxf(am, fmaxf(fabsf(o[2 * j]), fabsf(o[2 * j + 1])));
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = 0.f;
-        }
-        if (r < a.rows) {
-          uint4 w;
-          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) wh[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
-          reinterpret_cast<uint4*>(xn_s + (size_t)r * a.hidden)[i] = w;
-        }
-        if (packet) {
-#pragma unroll
-          for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-          const float sc = live ? pow2_scale(am) : 1.f;
-          uint2 q;
-          uint8_t* qb = reinterpret_cast<uint8_t*>(&q);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) qb[j] = to_e4m3(o[j] / sc);
-          reinterpret_cast<uint2*>(a.x8 + (size_t)r * a.hidden)[i] = q;
-          if ((i & 15) == 0) a.xs[(size_t)r * (a.hidden / 128) + (i >> 4)] = sc;
-        }
+    for (int i = 0; i < 4; ++i) {
+      const int k = tid * 4 + 1024 * i;
+      gm[i] = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (inline_norm) {
+        const uint2 gv = __ldg(reinterpret_cast<const uint2*>(a.gamma + k));
+        const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
+        const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
+        gm[i] = make_float4(g01.x, g01.y, g23.x, g23.y);
       }
+      w0[i] = __ldg(reinterpret_cast<const float4*>(a.w + (size_t)e0 * 4096 + k));
+      w1[i] = (e0 + 1 < a.experts) ? __ldg(reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * 4096 + k)) : make_float4(0, 0, 0, 0);
     }
-    __syncthreads();
-    xsrc = xn_s;
+  }
+  griddep_wait();
+  griddep_launch();
+  const __nv_bfloat16* xsrc = inline_norm ? a.x : a.xn;
+  const int xld = a.hidden;
+  // e4m3 packet of the normalised rows: pair (row, 128-channel block) number blockIdx.x + gridDim.x * g goes to the
+  // g-th group of 16 threads of this CTA
+  const int blocks = a.hidden / 128;
+  const int pairs = (inline_norm && a.x8 != nullptr) ? a.rows * blocks : 0;
+  const int my_pair = (int)blockIdx.x + (int)gridDim.x * (tid >> 4);
+  const bool pk_on = my_pair < pairs;
+  const int pk_r = pk_on ? my_pair % a.rows : 0, pk_b = pk_on ? my_pair / a.rows : 0;
+  uint4 pk_x = make_uint4(0u, 0u, 0u, 0u), pk_g = pk_x;
+  if (pk_on) {
+    const int k = pk_b * 128 + (tid & 15) * 8;
+    pk_x = *reinterpret_cast<const uint4*>(a.x + (size_t)pk_r * a.hidden + k);
+    pk_g = __ldg(reinterpret_cast<const uint4*>(a.gamma + k));
   }
   float acc[2][kMaxRows];
 #pragma unroll
   for (int j = 0; j < 2; ++j)
 #pragma unroll
     for (int r = 0; r < kMaxRows; ++r) acc[j][r] = 0.f;
-  if (a.hidden == 4096) {
-    // Every load of the thread is issued before the first FMA (one HBM + one L2 round trip instead of one per
-    // K step): the two experts' weights for the thread's four K positions, then eight rows of activations at a
-    // time (rows beyond a.rows are predicated off, not read).
-    float4 w0[4], w1[4];
+  bool have_rs = false;
+  auto compute_rs = [&]() {
+    // 1/rms per row from the per-tile sums of squares left behind by the producer of x
+    if (inline_norm) {
+      for (int r = warp; r < a.rows; r += 8) {
+        float ss = 0.f;
+        for (int t = lane; t < blocks; t += 32) ss += __ldcg(a.ssq + t * kMaxRows + r);
+        ss = warp_sum(ss);
+        if (lane == 0) rs_s[r] = rsqrtf(ss / (float)a.hidden + a.eps);
+      }
+      __syncthreads();
+      if (pairs > 0) {                               // uniform over the CTA
+        const float rs = rs_s[pk_r];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk_x);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&pk_g);
+        float o[8];
+        float am = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int k = tid * 4 + 1024 * i;
-      w0[i] = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * 4096 + k);
-      w1[i] = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * 4096 + k) : make_float4(0, 0, 0, 0);
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
+          o[2 * q] = round_bf16(f.x * rs * g.x);
+          o[2 * q + 1] = round_bf16(f.y * rs * g.y);
+          am = fmaxf(am, fmaxf(fabsf(o[2 * q]), fabsf(o[2 * q + 1])));
+        }
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+        const float sc = pow2_scale(am);
+        uint2 q8;
+        uint8_t* qb = reinterpret_cast<uint8_t*>(&q8);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) qb[q] = to_e4m3(o[q] / sc);
+        if (pk_on) {
+          *reinterpret_cast<uint2*>(a.x8 + (size_t)pk_r * a.hidden + pk_b * 128 + (tid & 15) * 8) = q8;
+          if ((tid & 15) == 0) a.xs[(size_t)pk_r * blocks + pk_b] = sc;
+        }
+      }
     }
+    have_rs = true;
+  };
+  if (fast) {
+    // Every load of the thread is issued before the first FMA (one round trip instead of one per K step): eight rows
+    // of activations at a time (rows beyond a.rows are predicated off, not read); the sums of squares are fetched
+    // while those loads are in flight.
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       if (half * 8 < a.rows) {
@@ -865,18 +899,25 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
             xv[i][r] = (half * 8 + r < a.rows)
                            ? *reinterpret_cast<const uint2*>(xsrc + (size_t)(half * 8 + r) * xld + tid * 4 + 1024 * i)
                            : make_uint2(0u, 0u);
+        if (!have_rs) compute_rs();
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
-            const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].x));
-            const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].y));
+            float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].x));
+            float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].y));
+            if (inline_norm) {
+              const float rs = rs_s[half * 8 + r];
+              x01.x = round_bf16(x01.x * rs * gm[i].x); x01.y = round_bf16(x01.y * rs * gm[i].y);
+              x23.x = round_bf16(x23.x * rs * gm[i].z); x23.y = round_bf16(x23.y * rs * gm[i].w);
+            }
             acc[0][half * 8 + r] += x01.x * w0[i].x + x01.y * w0[i].y + x23.x * w0[i].z + x23.y * w0[i].w;
             acc[1][half * 8 + r] += x01.x * w1[i].x + x01.y * w1[i].y + x23.x * w1[i].z + x23.y * w1[i].w;
           }
       }
     }
   } else {
+  compute_rs();
 #pragma unroll 4
   for (int k = tid * 4; k < a.hidden; k += 1024) {
     float4 w0 = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k);
@@ -886,8 +927,16 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
     for (int r = 0; r < kMaxRows; ++r) {
       if (r < a.rows) {
         const uint2 xv = *reinterpret_cast<const uint2*>(xsrc + (size_t)r * xld + k);
-        const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
-        const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+        float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+        float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+        if (inline_norm) {
+          const uint2 gv = *reinterpret_cast<const uint2*>(a.gamma + k);
+          const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
+          const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
+          const float rs = rs_s[r];
+          x01.x = round_bf16(x01.x * rs * g01.x); x01.y = round_bf16(x01.y * rs * g01.y);
+          x23.x = round_bf16(x23.x * rs * g23.x); x23.y = round_bf16(x23.y * rs * g23.y);
+        }
         acc[0][r] += x01.x * w0.x + x01.y * w0.y + x23.x * w0.z + x23.y * w0.w;
         acc[1][r] += x01.x * w1.x + x01.y * w1.y + x23.x * w1.z + x23.y * w1.w;
       }
@@ -1029,6 +1078,13 @@ extern "C" int nrt_embed_rows(const int* tokens, const void* table, void* x, int
   return launch_pdl(embed_rows_kernel, dim3(rows > kMaxRows ? rows : kMaxRows), dim3(128), 0, S(stream), pdl != 0, tokens,
                     (const __nv_bfloat16*)table, (__nv_bfloat16*)x, hidden, rows, vocab);
 }
+extern "C" int nrt_prologue_args_size() { return (int)sizeof(PrologueArgs); }
+extern "C" int nrt_step_prologue(const void* args, void* stream, int pdl) {
+  PrologueArgs a;
+  memcpy(&a, args, sizeof(a));
+  if (a.hidden % 128 || a.n_tabs < 0 || a.n_tabs > 4 || a.rows < 1 || a.rows > kMaxRows) return -3;
+  return launch_pdl(step_prologue_kernel, dim3(kMaxRows + a.n_tabs), dim3(128), 0, S(stream), pdl != 0, a);
+}
 extern "C" int nrt_rope_table(const int* pos0, int rows, int dim, double theta, void* out, void* stream, int pdl) {
   return launch_pdl(rope_table_kernel, dim3(rows), dim3(dim / 2 < 32 ? 32 : dim / 2), 0, S(stream), pdl != 0, pos0, rows,
                     dim, theta, (float2*)out);
@@ -1099,17 +1155,10 @@ extern "C" int nrt_router_args_size() { return (int)sizeof(RouterArgs); }
 extern "C" int nrt_router(const void* args, void* stream, int pdl) {
   RouterArgs a;
   memcpy(&a, args, sizeof(a));
-  size_t smem = 0;
-  if (a.x) {
-    if ((a.experts + 1) / 2 < kMaxRows && a.x8) return -3;          // one CTA per packet row is required
-    smem = (size_t)kMaxRows * a.hidden * 2;
-    static bool configured = false;
-    if (!configured) {
-      cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      configured = true;
-    }
-    if (smem > 200 * 1024 || a.hidden % 256) return -3;
-  }
+  const size_t smem = 0;
+  if (a.x && (!a.ssq || !a.gamma || a.hidden % 128)) return -3;
+  // the packet's (row, block) pairs are spread over the CTAs, 16 groups of 16 threads each
+  if (a.x && a.x8 && (!a.xs || a.rows * (a.hidden / 128) > 16 * ((a.experts + 1) / 2))) return -3;
   const int groups = a.rows > kMaxRows ? (a.rows + kMaxRows - 1) / kMaxRows : 1;
   if (groups > 1 && (a.x || a.probs)) return -3;                      // row groups: plain routing of normed rows only
   return launch_pdl(router_kernel, dim3((a.experts + 1) / 2, groups), dim3(256), smem, S(stream), pdl != 0, a);

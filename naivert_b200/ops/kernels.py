@@ -21,30 +21,20 @@ K_MAX_PEERS = 8
 K_ROW_PAIRS = 8
 K_MAILBOX_SLABS = 4
 
-# GEMM variants: fp8 | dual<<1 | epi<<2 | group<<5
-EPI_STORE_F32, EPI_STORE_BF16, EPI_SILU_QUANT, EPI_ALLREDUCE, EPI_SILU_BF16, EPI_RETURN = 0, 1, 2, 3, 4, 5
+# GEMM variants: fp8 | dual<<1 | epi<<2 | group<<5 | bsrc<<7
+EPI_STORE_F32, EPI_STORE_BF16, EPI_SILU_QUANT, EPI_ALLREDUCE, EPI_SILU_BF16, EPI_RETURN, EPI_QKV_POST = 0, 1, 2, 3, 4, 5, 6
+B_TMA, B_NORM = 0, 1
 GROUP_NONE, GROUP_ITEM, GROUP_LOOP = 0, 1, 2
 
 
-def gemm_variant(fp8: bool, dual: bool, epi: int, group: int) -> int:
-    return int(fp8) | (int(dual) << 1) | (epi << 2) | (group << 5)
+def gemm_variant(fp8: bool, dual: bool, epi: int, group: int, bsrc: int = 0) -> int:
+    return int(fp8) | (int(dual) << 1) | (epi << 2) | (group << 5) | (bsrc << 7)
 
 
 class FabricArgs(C.Structure):
     _fields_ = [("mailbox", VP * K_MAX_PEERS), ("epoch", VP), ("status", VP), ("tp", I32), ("rank", I32),
                 ("call_idx", I32), ("features", I32), ("timeout_ns", U64), ("mode", I32), ("ag_call", I32),
                 ("ag_flags", VP)]
-
-
-class GemmArgs(C.Structure):
-    _fields_ = [("n_total", I32), ("k_total", I32), ("rows", I32), ("a_group", I32),
-                ("n_active", VP), ("active_ids", VP), ("probs", VP), ("max_slots", I32),
-                ("w_scale0", VP), ("w_scale1", VP), ("a_scale", VP),
-                ("out_f32", VP), ("out_bf16", VP), ("ld_out", I32), ("out_scale", F32),
-                ("out_q", VP), ("out_qscale", VP), ("resid", VP), ("out_copy", VP), ("ld_copy", I32),
-                ("fab", FabricArgs), ("status", VP),
-                ("row_offsets", VP), ("ep_meta", VP), ("ep_combine", VP * K_MAX_PEERS), ("ep_top_k", I32),
-                ("ep_dispatch_call", I32), ("ep_return_call", I32)]
 
 
 class AttnPostArgs(C.Structure):
@@ -55,7 +45,21 @@ class AttnPostArgs(C.Structure):
                 ("idx_heads", I32), ("idx_dim", I32), ("idx_rope", I32), ("idx_rope_tab", VP),
                 ("ik_w", VP), ("ik_b", VP), ("ln_eps", F32), ("idx_weight_scale", F32),
                 ("iq8", VP), ("ihw", VP), ("ik_cache", VP), ("ik_scale", VP),
-                ("col_q", I32), ("col_k", I32), ("col_v", I32), ("col_iq", I32), ("col_ik", I32), ("col_iw", I32)]
+                ("col_q", I32), ("col_k", I32), ("col_v", I32), ("col_iq", I32), ("col_ik", I32), ("col_iw", I32),
+                ("iq_scale", VP), ("group_cols", I32), ("norm_group_stride", I32), ("k_group_stride", C.c_longlong),
+                ("v_group_stride", C.c_longlong)]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [("n_total", I32), ("k_total", I32), ("rows", I32), ("a_group", I32),
+                ("n_active", VP), ("active_ids", VP), ("probs", VP), ("max_slots", I32), ("n_experts", I32),
+                ("w_scale0", VP), ("w_scale1", VP), ("a_scale", VP),
+                ("out_f32", VP), ("out_bf16", VP), ("ld_out", I32), ("out_scale", F32),
+                ("out_q", VP), ("out_qscale", VP), ("resid", VP), ("out_copy", VP), ("ld_copy", I32),
+                ("fab", FabricArgs), ("status", VP),
+                ("row_offsets", VP), ("ep_meta", VP), ("ep_combine", VP * K_MAX_PEERS), ("ep_top_k", I32),
+                ("ep_dispatch_call", I32), ("ep_return_call", I32),
+                ("nx", VP), ("ngamma", VP), ("nssq", VP), ("neps", F32), ("ssq_out", VP), ("post", AttnPostArgs)]
 
 
 class AttnArgs(C.Structure):
@@ -68,15 +72,15 @@ class AttnArgs(C.Structure):
 
 class IndexArgs(C.Structure):
     _fields_ = [("iq8", VP), ("ihw", VP), ("ik", VP), ("iks", VP), ("pos0", VP),
-                ("rows", I32), ("heads", I32), ("dim", I32), ("top_k", I32), ("logits", VP), ("ld", I32)]
+                ("rows", I32), ("heads", I32), ("dim", I32), ("top_k", I32), ("logits", VP), ("ld", I32), ("iq_scale", VP)]
 
 
 class RouterArgs(C.Structure):
-    _fields_ = [("xn", VP), ("x", VP), ("gamma", VP), ("eps", F32), ("x8", VP), ("xs", VP),
+    _fields_ = [("xn", VP), ("x", VP), ("gamma", VP), ("eps", F32), ("ssq", VP), ("xs", VP),
                 ("w", VP), ("bias", VP), ("hidden", I32), ("experts", I32), ("rows", I32),
                 ("top_k", I32), ("sigmoid", I32), ("normalize", I32), ("route_scale", F32),
                 ("scores", VP), ("ticket", VP), ("n_active", VP), ("active_ids", VP), ("probs", VP),
-                ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32)]
+                ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32), ("x8", VP)]
 
 
 _lib = None
@@ -163,10 +167,11 @@ def pick_split(n_tiles: int, k_blocks: int, max_ctas: int = 160) -> int:
 
 
 # ----------------------------------------------------------------------------- launches
-def gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: TensorMap, args: GemmArgs, grid_x: int,
+def gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: Optional[TensorMap], args: GemmArgs, grid_x: int,
          grid_y: int = 1, pdl: bool = True) -> None:
     check(lib().nrt_gemm_launch(variant, C.byref(a0.buf), C.byref(a1.buf) if a1 is not None else None,
-                                C.byref(b.buf), C.byref(args), grid_x, grid_y, VP(_stream()), int(pdl)), "gemm launch")
+                                C.byref(b.buf) if b is not None else None, C.byref(args), grid_x, grid_y, VP(_stream()),
+                                int(pdl)), "gemm launch")
 
 
 WIDE_TOK = 64
@@ -184,6 +189,20 @@ def wide_gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: TensorMap
 def embed_rows(tokens, table, x, rows, pdl=True):
     check(lib().nrt_embed_rows(VP(ptr(tokens)), VP(ptr(table)), VP(ptr(x)), table.shape[1], rows, table.shape[0],
                                VP(_stream()), int(pdl)), "embed_rows")
+
+
+class PrologueArgs(C.Structure):
+    _fields_ = [("tokens", VP), ("table", VP), ("mask", VP), ("x", VP), ("ssq", VP),
+                ("hidden", I32), ("rows", I32), ("vocab", I32), ("mode", I32), ("n_tabs", I32),
+                ("tab_pos0", VP * 4), ("tab_dim", I32 * 4), ("tab_theta", C.c_double * 4), ("tab_out", VP * 4)]
+
+
+def step_prologue(args: PrologueArgs, pdl=True):
+    """Input rows (embedding gather or draft block), their per-tile sums of squares, and the step's RoPE tables."""
+    L = lib()
+    if L.nrt_prologue_args_size() != C.sizeof(PrologueArgs):
+        raise RuntimeError("PrologueArgs layout drift")
+    check(L.nrt_step_prologue(C.byref(args), VP(_stream()), int(pdl)), "step_prologue")
 
 
 def rope_table(pos0, rows, dim, theta, out, pdl=True):
@@ -214,7 +233,7 @@ def attn_group(args: AttnArgs, pdl=True):
 
 class SweepArgs(C.Structure):
     _fields_ = [("ihw", VP), ("iks", VP), ("pos0", VP), ("rows", I32), ("heads", I32), ("top_k", I32),
-                ("logits", VP), ("ld", I32), ("status", VP), ("group0", I32), ("ngroups", I32)]
+                ("logits", VP), ("ld", I32), ("status", VP), ("group0", I32), ("ngroups", I32), ("iq_scale", VP)]
 
 
 def sweep_maps(ik_cache: torch.Tensor, iq8: torch.Tensor):

@@ -50,6 +50,11 @@ class DraftRuntime:
         self.w1, self.w2 = dv(w["markov_w1"]), dv(w["markov_w2"])
         kv_rows = self.nkv * hd * 2
         wkv = torch.zeros(_pad128(d.layer_count * kv_rows), Hd, dtype=bf, device=dev)
+        self.fused = target.fused
+        # draft KV of all layers in one allocation: the context ingest appends every layer's rows from one GEMM epilogue
+        self.kc = torch.zeros(d.layer_count, capacity, self.nkv, hd, dtype=bf, device=dev)
+        self.vc = torch.zeros(d.layer_count, capacity, self.nkv, hd, dtype=bf, device=dev)
+        self.k_norms = torch.stack([dv(lw["k_norm"]) for lw in w["layers"]]).contiguous()
         self.layers: List[dict] = []
         for l, lw in enumerate(w["layers"]):
             wkv[l * kv_rows:(l + 1) * kv_rows] = torch.cat([dv(lw["wk"]), dv(lw["wv"])])
@@ -59,8 +64,7 @@ class DraftRuntime:
             L = {"wqkv": wqkv, "map_qkv": K.weight_tmap(wqkv), "g_in": dv(lw["g_in"]), "g_post": dv(lw["g_post"]),
                  "q_norm": dv(lw["q_norm"]), "k_norm": dv(lw["k_norm"]),
                  "wo": dv(lw["wo"]), "gate": dv(lw["gate"]), "up": dv(lw["up"]), "down": dv(lw["down"]),
-                 "k": torch.zeros(capacity, self.nkv, hd, dtype=bf, device=dev),
-                 "v": torch.zeros(capacity, self.nkv, hd, dtype=bf, device=dev)}
+                 "k": self.kc[l], "v": self.vc[l]}
             for nme in ("wo", "gate", "up", "down"):
                 L["map_" + nme] = K.weight_tmap(L[nme])
             self.layers.append(L)
@@ -92,6 +96,9 @@ class DraftRuntime:
         self.best = torch.zeros(2, dtype=torch.int64, device=dev)
         self.ticket = torch.zeros(1, dtype=i32, device=dev)
         self.seed_buf, self.params_buf = seed_buf, params_buf
+        # per-tile sums of squares of h (fc output) and of the block residual xd for the fused RMSNorms
+        self.ssq_h = torch.zeros(Hd // 128, PAD_ROWS, dtype=f32, device=dev)
+        self.ssq_x = torch.zeros(Hd // 128, PAD_ROWS, dtype=f32, device=dev)
         self._build_args()
 
     def _g(self, n, k, rows):
@@ -107,11 +114,25 @@ class DraftRuntime:
         g = self._g(Hd, self.kf, R)
         g.out_bf16, g.ld_out = self.h.data_ptr(), Hd
         g.fab = self.fab.fabric_args(DRAFT_CALL_BASE, Hd)
+        g.ssq_out = self.ssq_h.data_ptr() if self.fused else None
         self.args_fc = g
         g = self._g(self.wkv.shape[0], Hd, R)
         g.out_f32, g.ld_out = self.raw.data_ptr(), self.raw.shape[1]
-        self.args_kv = g
         kv_rows = self.nkv * hd * 2
+        if self.fused:
+            # RMSNorm(h) in the operand build; k-norm + RoPE + append of every layer in the epilogue
+            g.n_total = d.layer_count * kv_rows
+            g.nx, g.ngamma, g.nssq, g.neps = self.h.data_ptr(), self.hidden_norm.data_ptr(), self.ssq_h.data_ptr(), d.norm_eps
+            p = g.post
+            p.rows, p.pos0 = R, self.ctrl_ingest_pos.data_ptr()
+            p.heads, p.kv_heads, p.head_dim, p.v_dim, p.rope_dim = 0, self.nkv, hd, hd, hd
+            p.value_scale, p.rope = 1.0, self.rope_ing.data_ptr()
+            p.k_cache, p.v_cache, p.ring = self.kc.data_ptr(), self.vc.data_ptr(), 0
+            p.k_norm, p.norm_eps = self.k_norms.data_ptr(), d.norm_eps
+            p.col_q, p.col_k, p.col_v = 0, 0, self.nkv * hd
+            p.group_cols, p.norm_group_stride = kv_rows, hd
+            p.k_group_stride = p.v_group_stride = self.capacity * self.nkv * hd
+        self.args_kv = g
         for l, L in enumerate(self.layers):
             p = K.AttnPostArgs()
             p.qkv, p.ld, p.rows, p.pos0 = self.raw.data_ptr(), self.raw.shape[1], R, self.ctrl_ingest_pos.data_ptr()
@@ -125,7 +146,9 @@ class DraftRuntime:
             g = self._g(L["wqkv"].shape[0], Hd, R)
             g.out_f32, g.ld_out = self.raw.data_ptr(), self.raw.shape[1]
             L["args_qkv"] = g
-            p = K.AttnPostArgs()
+            p = g.post if self.fused else K.AttnPostArgs()
+            if self.fused:
+                g.nx, g.ngamma, g.nssq, g.neps = self.xd.data_ptr(), L["g_in"].data_ptr(), self.ssq_x.data_ptr(), d.norm_eps
             p.qkv, p.ld, p.rows, p.pos0 = self.raw.data_ptr(), self.raw.shape[1], R, self.ctrl.data_ptr()
             p.heads, p.kv_heads, p.head_dim, p.v_dim, p.rope_dim = self.nh, self.nkv, hd, hd, hd
             p.value_scale, p.rope = 1.0, self.rope_blk.data_ptr()
@@ -143,13 +166,17 @@ class DraftRuntime:
             g = self._g(Hd, self.nh * hd, R)
             g.out_bf16, g.ld_out, g.resid = self.xd.data_ptr(), Hd, self.xd.data_ptr()
             g.fab = self.fab.fabric_args(DRAFT_CALL_BASE + 1 + 2 * l, Hd)
+            g.ssq_out = self.ssq_x.data_ptr() if self.fused else None
             L["args_o"] = g
             g = self._g(self.I, Hd, R)
             g.out_bf16, g.ld_out = self.y.data_ptr(), self.I
+            if self.fused:
+                g.nx, g.ngamma, g.nssq, g.neps = self.xd.data_ptr(), L["g_post"].data_ptr(), self.ssq_x.data_ptr(), d.norm_eps
             L["args_gu"] = g
             g = self._g(Hd, self.I, R)
             g.out_bf16, g.ld_out, g.resid = self.xd.data_ptr(), Hd, self.xd.data_ptr()
             g.fab = self.fab.fabric_args(DRAFT_CALL_BASE + 2 + 2 * l, Hd)
+            g.ssq_out = self.ssq_x.data_ptr() if self.fused else None
             L["args_down"] = g
         g = self._g(self.t.lm_head.shape[0], Hd, R)
         g.out_f32, g.ld_out = self.dlogits.data_ptr(), self.dlogits.shape[1]
@@ -164,15 +191,34 @@ class DraftRuntime:
         m.best, m.ticket = self.best.data_ptr(), self.ticket.data_ptr()
         m.x = self.fab.xchg_args()
         self.args_markov = m
+        pa = K.PrologueArgs()
+        pa.tokens, pa.table, pa.mask = self.block_ids.data_ptr(), self.t.embed.data_ptr(), self.mask.data_ptr()
+        pa.x, pa.ssq = self.xd.data_ptr(), self.ssq_x.data_ptr()
+        pa.hidden, pa.rows, pa.vocab, pa.mode, pa.n_tabs = Hd, R, self.t.embed.shape[0], 1, 2
+        pa.tab_pos0[0], pa.tab_dim[0], pa.tab_theta[0], pa.tab_out[0] = (self.ctrl_ingest_pos.data_ptr(), hd, d.rope_theta,
+                                                                         self.rope_ing.data_ptr())
+        pa.tab_pos0[1], pa.tab_dim[1], pa.tab_theta[1], pa.tab_out[1] = self.ctrl.data_ptr(), hd, d.rope_theta, self.rope_blk.data_ptr()
+        self.args_prologue = pa
 
     V_STORE = K.gemm_variant(False, False, K.EPI_STORE_F32, K.GROUP_NONE)
     V_AR = K.gemm_variant(False, False, K.EPI_ALLREDUCE, K.GROUP_NONE)
     V_GU = K.gemm_variant(False, True, K.EPI_SILU_BF16, K.GROUP_NONE)
+    V_QKV_POST = K.gemm_variant(False, False, K.EPI_QKV_POST, K.GROUP_NONE, K.B_NORM)
+    V_GU_NORM = K.gemm_variant(False, True, K.EPI_SILU_BF16, K.GROUP_NONE, K.B_NORM)
 
     def ingest(self) -> None:
         """Draft KV for the (up to 8) feature rows the last target step produced, at positions
         ctrl[2].. ; rows beyond the committed count land beyond the context and are rewritten later."""
         d, R, pdl = self.d, self.rows, self.pdl
+        if self.fused:
+            # prologue: block input rows + both RoPE tables (the block that follows in a round reuses them; the
+            # control words they depend on do not change before the round's tail)
+            K.step_prologue(self.args_prologue, pdl=pdl)
+            K.gemm(self.V_AR, self.map_fc, None, self.map_feats, self.args_fc, d.hidden // 128,
+                   K.pick_split(d.hidden // 128, self.kf // 64), pdl=pdl)
+            nt = self.wkv.shape[0] // 128
+            K.gemm(self.V_QKV_POST, self.map_kv, None, None, self.args_kv, nt, K.pick_split(nt, d.hidden // 64), pdl=pdl)
+            return
         K.rope_table(self.ctrl_ingest_pos, R, d.head_dim, d.rope_theta, self.rope_ing, pdl=pdl)
         K.gemm(self.V_AR, self.map_fc, None, self.map_feats, self.args_fc, d.hidden // 128,
                K.pick_split(d.hidden // 128, self.kf // 64), pdl=pdl)
@@ -182,8 +228,22 @@ class DraftRuntime:
         for L in self.layers:
             K.attn_post(L["args_ingest_post"], pdl=pdl)
 
-    def block(self) -> None:
+    def block(self, prologue: bool = False) -> None:
         d, R, pdl = self.d, self.rows, self.pdl
+        if self.fused:
+            if prologue:                   # standalone use (no ingest before it)
+                K.step_prologue(self.args_prologue, pdl=pdl)
+            for L in self.layers:
+                nt = L["wqkv"].shape[0] // 128
+                K.gemm(self.V_QKV_POST, L["map_qkv"], None, None, L["args_qkv"], nt, K.pick_split(nt, d.hidden // 64), pdl=pdl)
+                K.attn_rows(L["args_attn"], self.attn_splits, pdl=pdl)
+                K.gemm(self.V_AR, L["map_wo"], None, self.map_o, L["args_o"], d.hidden // 128,
+                       K.pick_split(d.hidden // 128, self.nh * d.head_dim // 64), pdl=pdl)
+                K.gemm(self.V_GU_NORM, L["map_gate"], L["map_up"], None, L["args_gu"], self.I // 128,
+                       K.pick_split(self.I // 128, d.hidden // 64), pdl=pdl)
+                K.gemm(self.V_AR, L["map_down"], None, self.map_y, L["args_down"], d.hidden // 128,
+                       K.pick_split(d.hidden // 128, self.I // 64), pdl=pdl)
+            return
         K.draft_block_input(self.block_ids, self.t.embed, self.mask, self.xd, R, pdl=pdl)
         K.rope_table(self.ctrl, R, d.head_dim, d.rope_theta, self.rope_blk, pdl=pdl)
         for L in self.layers:

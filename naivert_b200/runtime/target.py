@@ -64,6 +64,10 @@ class TargetRuntime:
         # the router can normalise its own input (one launch fewer per MoE layer); measured slower on B200
         # (every CTA re-normalises all rows), so the separate RMSNorm kernel stays the default
         self.fuse_router_norm = False
+        # fused step (default): RMSNorm inside the projections' operand build, q/k/v post-processing inside the
+        # projection epilogue, one prologue launch.  NAIVERT_LEGACY_STEP=1 keeps the separate kernels (A/B timing).
+        import os
+        self.fused = os.environ.get("NAIVERT_LEGACY_STEP", "0") != "1"
         s = spec
         H = s.hidden
         dev = device
@@ -122,6 +126,12 @@ class TargetRuntime:
             cols = {"q": 0, "k": nh * a.head_dim, "v": nh * a.head_dim + nkv * a.head_dim}
             n = cols["v"] + nkv * a.v_head_dim
             if lw["kind"] == FULL_DSA:
+                # indexer heads and the indexer key start on 128-feature tiles: the projection epilogue reduces
+                # over one tile (quantisation scale, LayerNorm)
+                pad = _pad128(n) - n
+                if pad:
+                    parts.append(torch.zeros(pad, H, dtype=bf, device=dev))
+                n += pad
                 cols["iq"], cols["ik"] = n, n + ix.head_count * ix.head_dim
                 cols["iw"] = cols["ik"] + ix.head_dim
                 parts += [lw["iwq"], lw["iwk"], lw["iww"]]
@@ -154,6 +164,9 @@ class TargetRuntime:
                 d["gate"], d["up"], d["down"] = (_Linear8(lw[n_], dev) for n_ in ("gate", "up", "down"))
             self.layers.append(d)
         self.qkv = torch.zeros(PAD_ROWS, max_qkv, dtype=f32, device=dev)
+        # sums of squares of the residual rows per 128-feature tile, left behind by whoever wrote the rows
+        # (prologue, o_proj / down epilogues) for the RMSNorm fused into the next projection
+        self.ssq = torch.zeros(H // 128, PAD_ROWS, dtype=f32, device=dev)
         a0 = s.attention[s.layer_kinds[0]]
         nh_max = max(s.attention[k].local_heads(self.tp) for k in set(s.layer_kinds))
         self.q = torch.zeros(PAD_ROWS, nh_max, a0.head_dim, dtype=bf, device=dev)
@@ -166,6 +179,7 @@ class TargetRuntime:
         if FULL_DSA in s.layer_kinds:
             self.iq8 = torch.zeros(PAD_ROWS * ix.head_count, ix.head_dim, dtype=u8, device=dev)
             self.ihw = torch.zeros(PAD_ROWS, ix.head_count, dtype=f32, device=dev)
+            self.iq_scale = torch.ones(PAD_ROWS, ix.head_count, dtype=f32, device=dev)
             self.idx_logits = torch.zeros(PAD_ROWS, capacity, dtype=f32, device=dev)
             self.sel = torch.zeros(PAD_ROWS, ix.top_k, dtype=i32, device=dev)
             # long contexts select with many CTAs per row (six launches); short ones with one CTA per row
@@ -199,7 +213,9 @@ class TargetRuntime:
             g = self._gemm_args(d["wqkv"].shape[0], H, R)
             g.out_f32, g.ld_out = self.qkv.data_ptr(), self.qkv.shape[1]
             d["args_qkv"] = g
-            p = K.AttnPostArgs()
+            p = g.post if self.fused else K.AttnPostArgs()
+            if self.fused:
+                g.nx, g.ngamma, g.nssq, g.neps = self.x.data_ptr(), d["g_in"].data_ptr(), self.ssq.data_ptr(), s.norm_eps
             p.qkv, p.ld, p.rows, p.pos0 = self.qkv.data_ptr(), self.qkv.shape[1], R, pos0
             p.heads, p.kv_heads, p.head_dim, p.v_dim, p.rope_dim = nh, nkv, a.head_dim, a.v_head_dim, a.rope_dim
             p.value_scale = a.value_scale
@@ -215,7 +231,9 @@ class TargetRuntime:
                 p.iq8, p.ihw = self.iq8.data_ptr(), self.ihw.data_ptr()
                 p.ik_cache, p.ik_scale = d["ik"].data_ptr(), d["iks"].data_ptr()
                 p.col_iq, p.col_ik, p.col_iw = cols["iq"], cols["ik"], cols["iw"]
+                p.iq_scale = self.iq_scale.data_ptr() if self.fused else None
                 ia = K.IndexArgs()
+                ia.iq_scale = p.iq_scale
                 ia.iq8, ia.ihw, ia.ik, ia.iks, ia.pos0 = (self.iq8.data_ptr(), self.ihw.data_ptr(), d["ik"].data_ptr(),
                                                           d["iks"].data_ptr(), pos0)
                 ia.rows, ia.heads, ia.dim, ia.top_k = R, ix.head_count, ix.head_dim, ix.top_k
@@ -227,6 +245,7 @@ class TargetRuntime:
                     sw.ihw, sw.iks, sw.pos0 = self.ihw.data_ptr(), d["iks"].data_ptr(), pos0
                     sw.rows, sw.heads, sw.top_k = R, ix.head_count, ix.top_k
                     sw.logits, sw.ld, sw.status = self.idx_logits.data_ptr(), self.idx_logits.shape[1], self.fab.status.data_ptr()
+                    sw.iq_scale = p.iq_scale
                     d["args_sweep"] = sw
             d["args_post"] = p
             t = K.AttnArgs()
@@ -246,6 +265,7 @@ class TargetRuntime:
             g.w_scale0, g.a_scale = d["wo"].s.data_ptr(), self.os.data_ptr()
             g.out_bf16, g.ld_out, g.resid = self.x.data_ptr(), H, self.x.data_ptr()
             g.fab = self.fab.fabric_args(2 * L, H)
+            g.ssq_out = self.ssq.data_ptr() if self.fused else None
             d["args_o"] = g
             tap = self.tap_of_layer.get(L)
             copy_ptr = None if tap is None else self.feats.data_ptr() + tap * H * 2
@@ -254,20 +274,24 @@ class TargetRuntime:
                 g = self._gemm_args(dn["gate"].n, H, R)
                 g.w_scale0, g.w_scale1, g.a_scale = dn["gate"].s.data_ptr(), dn["up"].s.data_ptr(), self.xs.data_ptr()
                 g.out_q, g.out_qscale = self.yd8.data_ptr(), self.yds.data_ptr()
+                if self.fused:
+                    g.nx, g.ngamma, g.nssq, g.neps = self.x.data_ptr(), d["g_post"].data_ptr(), self.ssq.data_ptr(), s.norm_eps
                 d["args_gu"] = g
                 g = self._gemm_args(H, dn["down"].k, R)
                 g.w_scale0, g.a_scale = dn["down"].s.data_ptr(), self.yds.data_ptr()
                 g.out_bf16, g.ld_out, g.resid = self.x.data_ptr(), H, self.x.data_ptr()
                 g.out_copy, g.ld_copy = copy_ptr, self.feats.shape[1]
                 g.fab = self.fab.fabric_args(2 * L + 1, H)
+                g.ssq_out = self.ssq.data_ptr() if self.fused else None
                 d["args_down"] = g
             else:
                 rt = s.routing
                 r = K.RouterArgs()
                 r.w, r.bias = d["router_w"].data_ptr(), d["router_b"].data_ptr()
-                if self.fuse_router_norm and rt.expert_count >= 2 * PAD_ROWS:   # fused RMSNorm + packet + router
+                if self.fused:                       # RMSNorm applied while the router reads the rows
                     r.xn, r.x, r.gamma, r.eps = None, self.x.data_ptr(), d["g_post"].data_ptr(), s.norm_eps
-                    r.x8, r.xs = self.x8.data_ptr(), self.xs.data_ptr()
+                    r.ssq = self.ssq.data_ptr()
+                    r.x8, r.xs = self.x8.data_ptr(), self.xs.data_ptr()      # the packet the expert GEMMs read
                     d["router_fused"] = True
                 else:
                     r.xn = self.xn.data_ptr()
@@ -286,14 +310,26 @@ class TargetRuntime:
                 g = self._gemm_args(H, d["down"].k, R)
                 g.n_active, g.active_ids, g.probs, g.max_slots = (self.n_active.data_ptr(), self.active_ids.data_ptr(),
                                                                  self.probs.data_ptr(), self.max_slots)
+                g.n_experts = rt.expert_count
                 g.w_scale0, g.a_scale = d["down"].s.data_ptr(), self.ys.data_ptr()
                 g.out_bf16, g.ld_out, g.resid = self.x.data_ptr(), H, self.x.data_ptr()
                 g.out_copy, g.ld_copy = copy_ptr, self.feats.shape[1]
                 g.fab = self.fab.fabric_args(2 * L + 1, H)
+                g.ssq_out = self.ssq.data_ptr() if self.fused else None
                 d["args_down"] = g
         g = self._gemm_args(self.lm_head.shape[0], H, R)
         g.out_f32, g.ld_out = self.logits.data_ptr(), self.logits.shape[1]
         self.args_head = g
+        pa = K.PrologueArgs()
+        pa.tokens, pa.table, pa.x, pa.ssq = self.tokens.data_ptr(), self.embed.data_ptr(), self.x.data_ptr(), self.ssq.data_ptr()
+        pa.hidden, pa.rows, pa.vocab, pa.mode = H, R, self.embed.shape[0], 0
+        tabs = [(s.attention[kind].rope_dim, s.attention[kind].rope_theta, tab) for kind, tab in self.rope.items()]
+        if FULL_DSA in self.rope:
+            tabs.append((ix.rope_dim, s.attention[FULL_DSA].rope_theta, self.idx_rope))
+        pa.n_tabs = len(tabs)
+        for i, (dim, theta, tab) in enumerate(tabs):
+            pa.tab_pos0[i], pa.tab_dim[i], pa.tab_theta[i], pa.tab_out[i] = pos0, dim, theta, tab.data_ptr()
+        self.args_prologue = pa
 
     # ------------------------------------------------------------------ the step
     V_FP8_STORE = K.gemm_variant(True, False, K.EPI_STORE_F32, K.GROUP_NONE)
@@ -302,8 +338,50 @@ class TargetRuntime:
     V_FP8_GU_ITEM = K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM)
     V_FP8_DOWN_LOOP = K.gemm_variant(True, False, K.EPI_ALLREDUCE, K.GROUP_LOOP)
     V_BF16_STORE = K.gemm_variant(False, False, K.EPI_STORE_F32, K.GROUP_NONE)
+    V_QKV_POST = K.gemm_variant(False, False, K.EPI_QKV_POST, K.GROUP_NONE, K.B_NORM)
+    V_FP8_GU_NORM = K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_NONE, K.B_NORM)
+    V_FP8_GU_ITEM_NORM = K.gemm_variant(True, True, K.EPI_SILU_QUANT, K.GROUP_ITEM, K.B_NORM)
 
     def step(self, head: bool = True, stop_after=None) -> None:
+        if not self.fused:
+            return self._step_legacy(head, stop_after)
+        s, R, pdl = self.spec, self.rows, self.pdl
+        K.step_prologue(self.args_prologue, pdl=pdl)
+        for L, d in enumerate(self.layers):
+            nt = d["wqkv"].shape[0] // 128
+            K.gemm(self.V_QKV_POST, d["map_qkv"], None, None, d["args_qkv"], nt, K.pick_split(nt, s.hidden // 64), pdl=pdl)
+            if d["kind"] == FULL_DSA:
+                if self.use_sweep:
+                    K.index_sweep(*d["sweep_maps"], d["args_sweep"], min(148, -(-self.capacity // 128)), pdl=pdl)
+                else:
+                    K.index_logits_simple(d["args_index"], 148, pdl=pdl)
+                if self.topk_grid:
+                    K.topk_rows_grid(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, self.topk_state, 16, pdl=pdl)
+                else:
+                    K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
+            K.attn_rows(d["args_attn"], self.attn_splits if d["kind"] == FULL_DSA else 1, pdl=pdl)
+            K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128,
+                   K.pick_split(s.hidden // 128, d["wo"].k // 128), pdl=pdl)
+            if stop_after == (L, "attn"):
+                return
+            if "dense" in d:
+                dn = d["dense"]
+                nt = dn["gate"].n // 128
+                K.gemm(self.V_FP8_GU_NORM, dn["gate"].map, dn["up"].map, None, d["args_gu"], nt,
+                       K.pick_split(nt, s.hidden // 128), pdl=pdl)
+                K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128,
+                       K.pick_split(s.hidden // 128, dn["down"].k // 128), pdl=pdl)
+            else:
+                K.router(d["args_router"], pdl=pdl)
+                K.gemm(self.V_FP8_GU_ITEM, d["gate"].map, d["up"].map, self.map_x8, d["args_gu"], d["gate"].n // 128,
+                       self.step_slots, pdl=pdl)
+                K.gemm(self.V_FP8_DOWN_LOOP, d["down"].map, None, self.map_y8, d["args_down"], s.hidden // 128,
+                       K.pick_split(s.hidden // 128, 4), pdl=pdl)
+        if head:
+            K.prep_norm(self.x, self.g_final, R, s.norm_eps, xn=self.xn, pdl=pdl)
+            K.gemm(self.V_BF16_STORE, self.map_lm, None, self.map_xn, self.args_head, -(-self.lm_head.shape[0] // 128), pdl=pdl)
+
+    def _step_legacy(self, head: bool = True, stop_after=None) -> None:
         s, R, pdl = self.spec, self.rows, self.pdl
         K.embed_rows(self.tokens, self.embed, self.x, R, pdl=pdl)
         for kind, tab in self.rope.items():

@@ -145,6 +145,7 @@ def test_moe_gate_up_down_grouped():
     b = K.GemmArgs()
     b.n_total, b.k_total, b.rows = H, I, rows
     b.n_active, b.active_ids, b.probs, b.max_slots = n_active.data_ptr(), active.data_ptr(), probs.data_ptr(), 8
+    b.n_experts = E
     b.w_scale0, b.a_scale = ds.data_ptr(), ys.data_ptr()
     b.out_bf16, b.ld_out, b.resid = out.data_ptr(), H, resid.data_ptr()
     b.fab = _fab(K, st, epoch, H)

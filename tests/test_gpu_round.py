@@ -154,6 +154,6 @@ def test_device_chain_matches_host_launched_rounds():
     assert a.tokens == b.tokens and b.stop_reason == "output_limit"
     assert chain.round.host_launches == 1 and host.round.host_launches > 10
     info = chain.round.native_graph.info
-    assert info["kernel_nodes"] == info["nodes"] and info["kernel_nodes"] > 50
+    assert info["kernel_nodes"] == info["nodes"] and info["kernel_nodes"] > 20
     c = chain.generate(prompt, 64, sp)                      # a second request restarts the chain
     assert c.tokens == a.tokens[:64]
