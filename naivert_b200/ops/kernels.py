@@ -90,6 +90,7 @@ def lib():
     global _lib
     if _lib is None:
         _lib = load_library()
+        _lib.nrt_attn_decode_part_floats.restype = C.c_longlong
         for name, st in (("nrt_gemm_args_size", GemmArgs), ("nrt_attn_post_args_size", AttnPostArgs),
                          ("nrt_attn_args_size", AttnArgs), ("nrt_index_args_size", IndexArgs),
                          ("nrt_router_args_size", RouterArgs)):
@@ -221,6 +222,24 @@ def attn_post(args: AttnPostArgs, pdl=True):
 
 def attn_rows(args: AttnArgs, splits: int = 1, pdl=True):
     check(lib().nrt_attn_rows(C.byref(args), splits, VP(_stream()), int(pdl)), "attn_rows")
+
+
+def attn_decode_ok(args: AttnArgs) -> bool:
+    """Geometry served by the tensor-core decode attention (else use ``attn_rows``)."""
+    return (args.v_dim == 128 and args.head_dim in (128, 192) and args.kv_heads >= 1 and args.heads % args.kv_heads == 0
+            and args.heads // args.kv_heads <= 16)
+
+
+def attn_decode_part_floats(rows: int, kv_heads: int, splits: int) -> int:
+    return int(lib().nrt_attn_decode_part_floats(rows, kv_heads, splits))
+
+
+def attn_decode(args: AttnArgs, splits: int = 1, pdl=True):
+    """Row attention of the step on tensor cores: the query heads of a KV head share every gathered key."""
+    L = lib()
+    if L.nrt_attn_decode_args_size() != C.sizeof(AttnArgs):
+        raise RuntimeError("AttnArgs layout drift")
+    check(L.nrt_attn_decode(C.byref(args), splits, VP(_stream()), int(pdl)), "attn_decode")
 
 
 def attn_group(args: AttnArgs, pdl=True):

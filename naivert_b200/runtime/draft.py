@@ -84,7 +84,9 @@ class DraftRuntime:
         self.y = torch.zeros(PAD_ROWS, self.I, dtype=bf, device=dev)
         self.map_y = K.act_tmap(self.y)
         self.attn_splits = 3
-        self.attn_part = torch.zeros(PAD_ROWS * self.nh * self.attn_splits * (hd + 2), dtype=f32, device=dev)
+        self.tc_splits = 8
+        self.attn_part = torch.zeros(max(PAD_ROWS * self.nh * self.attn_splits * (hd + 2),
+                                         K.attn_decode_part_floats(PAD_ROWS, self.nkv, self.tc_splits)), dtype=f32, device=dev)
         self.attn_tickets = torch.zeros(PAD_ROWS * self.nh, dtype=i32, device=dev)
         self.rope_blk = torch.zeros(PAD_ROWS, hd // 2, 2, dtype=f32, device=dev)
         self.rope_ing = torch.zeros(PAD_ROWS, hd // 2, 2, dtype=f32, device=dev)
@@ -163,6 +165,7 @@ class DraftRuntime:
             t.k_blk, t.v_blk, t.o_bf16 = self.k_blk.data_ptr(), self.v_blk.data_ptr(), self.o.data_ptr()
             t.part, t.tickets = self.attn_part.data_ptr(), self.attn_tickets.data_ptr()
             L["args_attn"] = t
+            L["attn_tc"] = self.fused and K.attn_decode_ok(t)
             g = self._g(Hd, self.nh * hd, R)
             g.out_bf16, g.ld_out, g.resid = self.xd.data_ptr(), Hd, self.xd.data_ptr()
             g.fab = self.fab.fabric_args(DRAFT_CALL_BASE + 1 + 2 * l, Hd)
@@ -236,7 +239,10 @@ class DraftRuntime:
             for L in self.layers:
                 nt = L["wqkv"].shape[0] // 128
                 K.gemm(self.V_QKV_POST, L["map_qkv"], None, None, L["args_qkv"], nt, K.pick_split(nt, d.hidden // 64), pdl=pdl)
-                K.attn_rows(L["args_attn"], self.attn_splits, pdl=pdl)
+                if L["attn_tc"]:
+                    K.attn_decode(L["args_attn"], self.tc_splits, pdl=pdl)
+                else:
+                    K.attn_rows(L["args_attn"], self.attn_splits, pdl=pdl)
                 K.gemm(self.V_AR, L["map_wo"], None, self.map_o, L["args_o"], d.hidden // 128,
                        K.pick_split(d.hidden // 128, self.nh * d.head_dim // 64), pdl=pdl)
                 K.gemm(self.V_GU_NORM, L["map_gate"], L["map_up"], None, L["args_gu"], self.I // 128,

@@ -187,7 +187,12 @@ class TargetRuntime:
             self.topk_state = torch.zeros(PAD_ROWS * K.topk_grid_state_bytes() // 4, dtype=i32, device=dev)
             self.use_sweep = ix.head_dim == 128 and ix.head_count % 16 == 0 and PAD_ROWS * ix.head_count == 256
         self.attn_splits = 4
-        self.attn_part = torch.zeros(PAD_ROWS * nh_max * self.attn_splits * (a0.v_head_dim + 2), dtype=f32, device=dev)
+        # tensor-core attention: 16 key splits for the 2048 selected keys of a full-attention row, one CTA per
+        # (KV head, row) for a sliding window
+        self.dsa_splits = 16
+        kv_max = max(s.attention[k].local_kv_heads(self.tp) for k in set(s.layer_kinds))
+        self.attn_part = torch.zeros(max(PAD_ROWS * nh_max * self.attn_splits * (a0.v_head_dim + 2),
+                                         K.attn_decode_part_floats(PAD_ROWS, kv_max, self.dsa_splits)), dtype=f32, device=dev)
         self.attn_tickets = torch.zeros(PAD_ROWS * nh_max, dtype=i32, device=dev)
         # greedy arg-max over all ranks' vocabulary shards (seq-1 greedy decoding, sampler cross-check)
         self.greedy = torch.zeros(PAD_ROWS, dtype=i32, device=dev)
@@ -260,6 +265,7 @@ class TargetRuntime:
             t.o8, t.o_scale = self.o8.data_ptr(), self.os.data_ptr()
             t.part, t.tickets = self.attn_part.data_ptr(), self.attn_tickets.data_ptr()
             d["args_attn"] = t
+            d["attn_tc"] = self.fused and K.attn_decode_ok(t)
             # o_proj + all-reduce + residual
             g = self._gemm_args(H, d["wo"].k, R)
             g.w_scale0, g.a_scale = d["wo"].s.data_ptr(), self.os.data_ptr()
@@ -359,7 +365,10 @@ class TargetRuntime:
                     K.topk_rows_grid(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, self.topk_state, 16, pdl=pdl)
                 else:
                     K.topk_rows(self.idx_logits, self.ctrl, R, s.indexer.top_k, self.sel, pdl=pdl)
-            K.attn_rows(d["args_attn"], self.attn_splits if d["kind"] == FULL_DSA else 1, pdl=pdl)
+            if d["attn_tc"]:
+                K.attn_decode(d["args_attn"], self.dsa_splits if d["kind"] == FULL_DSA else 1, pdl=pdl)
+            else:
+                K.attn_rows(d["args_attn"], self.attn_splits if d["kind"] == FULL_DSA else 1, pdl=pdl)
             K.gemm(self.V_FP8_AR, d["wo"].map, None, self.map_o8, d["args_o"], s.hidden // 128,
                    K.pick_split(s.hidden // 128, d["wo"].k // 128), pdl=pdl)
             if stop_after == (L, "attn"):

@@ -181,9 +181,12 @@ def _two_runtimes(layers=4, capacity=512):
 
 
 def test_fused_step_matches_separate_kernels():
-    """Same weights, same tokens: the fused step (norm in the operand build, post-processing in the epilogue)
-    and the step of separate kernels fill the same caches and produce the same logits up to the last-bit
-    difference of the two sums of squares (which can flip an e4m3 code or a bf16 rounding now and then)."""
+    """Same weights, same tokens: the fused step (norm in the operand build, post-processing in the epilogue,
+    tensor-core attention) against the step of separate kernels.  The first layer's caches depend only on the
+    embedding, the norm and the projection: keys and values must agree bit for bit, the indexer keys up to the
+    last bit of their per-row scale.  Deeper layers see the bf16 probabilities of the tensor-core attention and the
+    last-bit differences of the sums of squares, which can flip an e4m3 code or an expert choice now and then:
+    they are compared in the mean."""
     spec, fused, legacy = _two_runtimes()
     assert fused.fused and not legacy.fused
     g = torch.Generator().manual_seed(3)
@@ -198,14 +201,91 @@ def test_fused_step_matches_separate_kernels():
         fused.fab.check()
         a, b = fused.logits[:8].float(), legacy.logits[:8].float()
         assert torch.isfinite(a).all()
-        worst = max(worst, ((a - b).abs().max() / b.abs().max()).item())
+        worst = max(worst, ((a - b).abs().mean() / b.abs().mean()).item())
     n = steps * 8
+    first = True
     for df, dl in zip(fused.layers, legacy.layers):
-        if df["ring"] == 0:
-            kf, kl = df["k"][:n].float(), dl["k"][:n].float()
-            assert ((kf - kl).abs() > 0.02 * kl.abs().max()).float().mean().item() < 0.02
-            # indexer keys: the per-row scale amax / 448 moves with the last bit of the row maximum, so compare values
-            vf = df["ik"][:n].view(torch.float8_e4m3fn).float() * df["iks"][:n, None]
-            vl = dl["ik"][:n].view(torch.float8_e4m3fn).float() * dl["iks"][:n, None]
+        if df["ring"] != 0:
+            continue
+        kf, kl = df["k"][:n].float(), dl["k"][:n].float()
+        vf = df["ik"][:n].view(torch.float8_e4m3fn).float() * df["iks"][:n, None]
+        vl = dl["ik"][:n].view(torch.float8_e4m3fn).float() * dl["iks"][:n, None]
+        if first:
+            assert torch.equal(df["k"][:n], dl["k"][:n]) and torch.equal(df["v"][:n], dl["v"][:n])
             assert ((vf - vl).abs() > 0.07 * vl.abs().amax(-1, keepdim=True)).float().mean().item() < 0.01
-    assert worst < 0.15, worst
+            first = False
+        else:
+            assert ((kf - kl).abs().mean() / kl.abs().mean()).item() < 0.05
+            assert ((vf - vl).abs().mean() / vl.abs().mean()).item() < 0.08
+    assert worst < 0.08, worst
+
+
+def _attn_ref(q, keys, vals, scale, sink=None):
+    """fp32 softmax attention of one row: q [heads, hd], keys [n, hd], vals [n, vd]; optional sink logit per head
+    (an extra softmax column without a value)."""
+    s = (q.float() @ keys.float().T) * scale
+    if sink is not None:
+        s = torch.cat([s, sink.float()[:, None]], dim=1)
+    p = torch.softmax(s, dim=-1)
+    if sink is not None:
+        p = p[:, :-1]
+    return p @ vals.float()
+
+
+@pytest.mark.parametrize("mode,heads,kvh,hd,pos0,splits", [(0, 8, 1, 192, 1000, 1), (0, 8, 8, 192, 57, 1), (1, 8, 1, 192, 5000, 16),
+                                                           (1, 16, 4, 192, 300, 4), (2, 4, 1, 128, 1500, 8)])
+def test_tensor_core_decode_attention_matches_torch(mode, heads, kvh, hd, pos0, splits):
+    K = _K()
+    g = torch.Generator(device="cuda").manual_seed(20 + mode)
+    rows, vd, cap, top_k, window = 8, 128, 6144, 2048, 128 if mode == 0 else 1024
+    ring = window + 16 if mode == 0 else 0
+    q = torch.randn(16, heads, hd, device="cuda", generator=g).bfloat16()
+    kc = torch.randn(cap if not ring else ring, kvh, hd, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(cap if not ring else ring, kvh, vd, device="cuda", generator=g).bfloat16()
+    kb = torch.randn(16, kvh, hd, device="cuda", generator=g).bfloat16()
+    vb = torch.randn(16, kvh, vd, device="cuda", generator=g).bfloat16()
+    sink = torch.randn(heads, device="cuda", generator=g).bfloat16() if mode == 0 else None
+    sel = torch.zeros(16, top_k, dtype=torch.int32, device="cuda")
+    for r in range(rows):
+        sel[r] = torch.sort(torch.randperm(pos0 + r + 1, device="cuda", generator=g)[:top_k]).values if pos0 + r + 1 > top_k else 0
+    p = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    o = torch.zeros(16, heads * vd, device="cuda", dtype=torch.bfloat16)
+    o8 = torch.zeros(16, heads * vd, device="cuda", dtype=torch.uint8)
+    osc = torch.ones(16, heads, device="cuda")
+    part = torch.zeros(K.attn_decode_part_floats(16, kvh, max(splits, 1)), device="cuda")
+    tickets = torch.zeros(16 * kvh, dtype=torch.int32, device="cuda")
+    a = K.AttnArgs()
+    a.q, a.k_cache, a.v_cache, a.pos0 = q.data_ptr(), kc.data_ptr(), vc.data_ptr(), p.data_ptr()
+    a.rows, a.heads, a.kv_heads, a.head_dim, a.v_dim = rows, heads, kvh, hd, vd
+    a.scale, a.mode, a.window, a.ring = hd ** -0.5, mode, window, ring
+    a.sink = None if sink is None else sink.data_ptr()
+    a.sel, a.top_k = sel.data_ptr(), top_k
+    a.k_blk, a.v_blk = kb.data_ptr(), vb.data_ptr()
+    a.o_bf16, a.o8, a.o_scale = o.data_ptr(), o8.data_ptr(), osc.data_ptr()
+    a.part, a.tickets = part.data_ptr(), tickets.data_ptr()
+    for _ in range(2):                                    # the tickets reset themselves: a second launch must agree
+        K.attn_decode(a, splits, pdl=False)
+    torch.cuda.synchronize()
+    hpg = heads // kvh
+    worst = 0.0
+    for r in range(rows):
+        pos = pos0 + r
+        for gi in range(kvh):
+            if mode == 0:
+                ids = torch.arange(max(0, pos - window + 1), pos + 1, device="cuda") % ring
+                keys, vals = kc[ids, gi], vc[ids, gi]
+            elif mode == 1:
+                ids = sel[r].long() if pos + 1 > top_k else torch.arange(pos + 1, device="cuda")
+                keys, vals = kc[ids, gi], vc[ids, gi]
+            else:
+                lo = max(0, pos0 - window)
+                keys = torch.cat([kc[lo:pos0, gi], kb[:rows, gi]])
+                vals = torch.cat([vc[lo:pos0, gi], vb[:rows, gi]])
+            hs = slice(gi * hpg, (gi + 1) * hpg)
+            want = _attn_ref(q[r, hs], keys, vals, hd ** -0.5, None if sink is None else sink[hs])
+            got = o[r].view(heads, vd)[hs].float()
+            worst = max(worst, ((got - want).abs().max() / want.abs().max()).item())
+            deq = o8[r].view(heads, vd)[hs].view(torch.float8_e4m3fn).float() * osc[r, hs, None]
+            assert ((deq - want).abs() <= want.abs().amax(-1, keepdim=True) / 14 + 1e-6).all()
+    assert worst < 0.02, worst                             # bf16 probabilities and outputs
+    assert (tickets == 0).all()
