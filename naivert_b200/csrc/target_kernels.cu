@@ -544,12 +544,15 @@ __device__ __forceinline__ uint32_t order_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// One CTA per row.  Thread t owns the contiguous index segment [t * per, (t + 1) * per) (16-byte loads, the warp
+// covers a contiguous span), so the final sweep can emit winners in ascending index order from one block-wide
+// prefix sum.  Each radix pass builds a 256-bin shared histogram; warp 0 locates the threshold bin with a
+// shuffle scan (lane l owns bins 255 - 8l .. 248 - 8l).
 __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict__ logits, int ld, const int* pos0,
                                                          int rows, int top_k, int* __restrict__ sel) {
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need;
   __shared__ uint32_t wsum_gt[32], wsum_eq[32];
-  __shared__ uint32_t base_out, base_eq;
   griddep_wait();
   griddep_launch();
   const int r = blockIdx.x;
@@ -558,26 +561,49 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
   if (n <= top_k) return;                           // dense row: no selection needed
   const float* row = logits + (size_t)r * ld;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+  const int per = (((n + 1023) / 1024) + 3) & ~3;   // elements per thread, a multiple of 4
+  const int lo = tid * per, hi = min(n, lo + per);
 
   uint32_t prefix = 0, mask = 0, need = top_k;
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    for (int i = tid; i < n; i += 1024) {
-      const uint32_t k = order_key(row[i]);
-      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+    for (int i = lo; i < hi; i += 4) {
+      float v[4];
+      if (vec && i + 4 <= n) { const float4 f = *reinterpret_cast<const float4*>(row + i); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+      else { for (int c = 0; c < 4; ++c) v[c] = i + c < n ? row[i + c] : 0.f; }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (i + c < hi) {
+          const uint32_t k = order_key(v[c]);
+          if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+        }
     }
     __syncthreads();
-    if (tid == 0) {
-      uint32_t acc = 0;
-      int b = 255;
-      for (; b > 0; --b) {
-        if (acc + hist[b] >= need) break;
-        acc += hist[b];
+    if (warp == 0) {
+      uint32_t c[8], tot = 0;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) { c[b] = hist[255 - 8 * lane - b]; tot += c[b]; }
+      uint32_t incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+      const uint32_t excl = incl - tot;
+      // the first lane whose bins reach `need` (bin 0 takes the rest, as a sequential walk from bin 255 would)
+      const bool hit = incl >= need || lane == 31;
+      const int first = __ffs(__ballot_sync(0xffffffffu, hit)) - 1;
+      if (lane == first) {
+        uint32_t acc = excl;
+        int b = 0;
+        for (; b < 8; ++b) {
+          if (255 - 8 * lane - b == 0) break;
+          if (acc + c[b] >= need) break;
+          acc += c[b];
+        }
+        s_prefix = prefix | ((uint32_t)(255 - 8 * lane - b) << shift);
+        s_need = need - acc;                                     // winners still to take from inside that bin
       }
-      s_prefix = prefix | ((uint32_t)b << shift);
-      s_need = need - acc;                          // winners still to take from inside bin b
     }
     __syncthreads();
     prefix = s_prefix;
@@ -586,6 +612,47 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
   }
   // prefix = exact threshold key; `need` elements equal to it are taken, lowest index first
   const uint32_t thr = prefix;
+  unsigned long long m_gt = 0ull, m_eq = 0ull;      // winners of this thread's segment (per <= 64: rows up to 65536)
+  if (per <= 64) {
+    for (int i = lo; i < hi; i += 4) {
+      float v[4];
+      if (vec && i + 4 <= n) { const float4 f = *reinterpret_cast<const float4*>(row + i); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+      else { for (int c = 0; c < 4; ++c) v[c] = i + c < n ? row[i + c] : 0.f; }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (i + c < hi) {
+          const uint32_t k = order_key(v[c]);
+          if (k > thr) m_gt |= 1ull << (i + c - lo);
+          else if (k == thr) m_eq |= 1ull << (i + c - lo);
+        }
+    }
+  }
+  if (per <= 64) {
+    const uint32_t my_gt = __popcll(m_gt), my_eq = __popcll(m_eq);
+    uint32_t ig = my_gt, ie = my_eq;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t tg = __shfl_up_sync(0xffffffffu, ig, o), te = __shfl_up_sync(0xffffffffu, ie, o);
+      if (lane >= o) { ig += tg; ie += te; }
+    }
+    if (lane == 31) { wsum_gt[warp] = ig; wsum_eq[warp] = ie; }
+    __syncthreads();
+    uint32_t bg = 0, be = 0;
+    for (int w = 0; w < warp; ++w) { bg += wsum_gt[w]; be += wsum_eq[w]; }
+    uint32_t gt_before = bg + ig - my_gt, eq_before = be + ie - my_eq;
+    uint32_t out = gt_before + min(eq_before, need);
+    for (int i = lo; i < hi; ++i) {
+      const unsigned long long bit = 1ull << (i - lo);
+      if (m_gt & bit) { if (out < (uint32_t)top_k) sel[r * top_k + out] = i; ++out; }
+      else if (m_eq & bit) {
+        if (eq_before < need) { if (out < (uint32_t)top_k) sel[r * top_k + out] = i; ++out; }
+        ++eq_before;
+      }
+    }
+    return;
+  }
+  // rows longer than 65536 entries: chunked ordered sweep (1024 consecutive indices at a time)
+  __shared__ uint32_t base_out, base_eq;
   if (tid == 0) { base_out = 0; base_eq = 0; }
   __syncthreads();
   for (int c0 = 0; c0 < n; c0 += 1024) {
@@ -593,20 +660,16 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
     const uint32_t k = i < n ? order_key(row[i]) : 0u;
     const bool gt = i < n && k > thr;
     const bool eq = i < n && k == thr;
-    const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
-    if (lane == 0) { wsum_gt[warp] = __popc(bg); wsum_eq[warp] = __popc(be); }
+    const uint32_t bgm = __ballot_sync(0xffffffffu, gt), bem = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) { wsum_gt[warp] = __popc(bgm); wsum_eq[warp] = __popc(bem); }
     __syncthreads();
     uint32_t eq_before = base_eq, gt_before = 0;
     for (int w = 0; w < warp; ++w) { eq_before += wsum_eq[w]; gt_before += wsum_gt[w]; }
     const uint32_t lm = (1u << lane) - 1u;
-    const uint32_t my_eq_rank = eq_before + __popc(be & lm);
-    // output position = winners before me in index order
-    // winners before me = gt before me + min(eq before me, need)
-    const uint32_t eq_in_chunk_before = my_eq_rank - base_eq;
+    const uint32_t my_eq_rank = eq_before + __popc(bem & lm);
     const uint32_t taken_eq_before = min(my_eq_rank, need) - min(base_eq, need);
-    (void)eq_in_chunk_before;
-    const uint32_t outpos = base_out + gt_before + __popc(bg & lm) + taken_eq_before;
-    if (gt || (eq && my_eq_rank < need)) sel[r * top_k + outpos] = i;
+    const uint32_t outpos = base_out + gt_before + __popc(bgm & lm) + taken_eq_before;
+    if ((gt || (eq && my_eq_rank < need)) && outpos < (uint32_t)top_k) sel[r * top_k + outpos] = i;
     __syncthreads();
     if (tid == 0) {
       uint32_t tg = 0, te = 0;

