@@ -29,23 +29,19 @@ int launch_variant(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorM
   constexpr int kMaxSmem = 227 * 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         BSRC == kBTma ? Cfg::kSmemBytes : kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   if ((EPI == kEpiAllReduce || (GROUP != kGroupItem && gy > 1)) && args.rows > kArRows) return -5;
   const bool clustered = GROUP != kGroupItem && gy > 1;
   if (clustered && gy > kMaxSplit) return -4;
-  int smem = Cfg::kSmemBytes;
-  if (BSRC != kBTma) {
-    if (!args.nx || !args.ngamma || !args.nssq || args.k_total % 128) return -6;
-    const int kb_total = args.k_total / (FP8 ? 128 : 64);
-    const int split = GROUP == kGroupNone && clustered ? gy : 1;
-    if (kb_total % split) return -6;
-    smem = Cfg::smem_bytes(kb_total / split);
-    if (smem > kMaxSmem) return -7;
-  }
+  const int kb_total = args.k_total / (FP8 ? 128 : 64);
+  const int ksplit = GROUP == kGroupNone && clustered ? gy : 1;
+  if (kb_total % ksplit) return -6;
+  if (BSRC != kBTma && (!args.nx || !args.ngamma || !args.nssq || args.k_total % 128)) return -6;
+  const int smem = Cfg::smem_bytes(kb_total / ksplit, clustered ? gy : 1);
+  if (smem > kMaxSmem) return -7;
   if (EPI == kEpiQkvPost) {
     const AttnPostArgs& q = args.post;
     // reductions over a head / the indexer key run over the 128 threads of one tile

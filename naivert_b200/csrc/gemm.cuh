@@ -36,7 +36,7 @@ constexpr int kRowPairs = kTok / 2;             // mailbox stride: tagged words 
 constexpr int kArRows = 8;                      // rows the fused all-reduce / cluster split handle (verify = 8)
 constexpr int kArPairs = kArRows / 2;
 constexpr int kMailboxSlabs = 4;
-constexpr int kMaxSplit = 4;                    // CTAs of one cluster that share an output tile (split K / split experts)
+constexpr int kMaxSplit = 8;                    // CTAs of one cluster that share an output tile (split K / split experts)
 
 enum GroupMode : int { kGroupNone = 0, kGroupItem = 1, kGroupLoop = 2 };
 enum Epilogue : int { kEpiStoreF32 = 0, kEpiStoreBF16 = 1, kEpiSiluQuant = 2, kEpiAllReduce = 3, kEpiSiluBF16 = 4, kEpiReturn = 5,
@@ -140,6 +140,12 @@ struct GemmArgs {
   // kEpiAllReduce: sums of squares of the result rows per 128-feature tile, [n_total/128][16] (null: none)
   float* ssq_out;
   AttnPostArgs post;              // kEpiQkvPost
+  // opt-in phase stamps (%globaltimer, ns): [CTA][16] words, CTA = blockIdx.y * gridDim.x + blockIdx.x.
+  // 0 entry, 1 barriers + TMEM ready, 2 upstream grid done, 3 token operand built, 4 first weight stage landed,
+  // 5 last MMA issued, 6 accumulators read, 7 cluster partials merged, 8 peer words pushed, 9 peer words arrived
+  // (word 10: polls of the local mailbox), 11 epilogue done.  Null: no stamps.
+  unsigned long long* stamps;
+  unsigned int publish_delay_ns;  // test knob: this rank delays its mailbox publish by this long (a late peer that still arrives)
 };
 
 template <bool FP8, bool DUAL, int BSRC = kBTma>
@@ -149,20 +155,23 @@ struct GemmCfg {
   static constexpr int kStageBytes = kABytes + (BSRC == kBTma ? kBTileBytes : 0);
   // single-matrix tiles keep the footprint near 100 KiB so two CTAs (typically of consecutive kernels,
   // overlapped by programmatic dependent launch) share an SM
-  static constexpr int kStages = (DUAL && BSRC != kBTma) ? 4 : 5;
+  // (kBNorm, single matrix: 8 stages, so a CTA's whole K slice of weights is in flight while it builds the operand)
+  static constexpr int kStages = BSRC != kBTma ? (DUAL ? 4 : 8) : 5;
   static constexpr int kAccCols = DUAL ? 2 * kTok : kTok;          // TMEM columns per accumulator buffer
   static constexpr int kAccBufs = FP8 ? (DUAL ? 4 : 8) : 1;
   static constexpr int kTmemCols = (kAccCols * kAccBufs < 32) ? 32 : kAccCols * kAccBufs;
-  static constexpr int kPartBytes = (DUAL ? 2 : 1) * (kMaxSplit - 1) * kArRows * kTileN * 4;   // split partials of the cluster peers
+  // split partials of the cluster peers (leader only): (split - 1) x rows x 128 floats, twice for a dual GEMM
+  __host__ __device__ static constexpr int part_bytes(int split) {
+    return split > 1 ? (DUAL ? 2 : 1) * (split - 1) * kArRows * kTileN * 4 : 0;
+  }
   static constexpr int kRingBytes = kStages * kStageBytes;
   // token operand built in shared memory: one 2 KiB swizzled chunk per K block (+ activation scales for e4m3)
   __host__ __device__ static constexpr int operand_bytes(int kb_count) {
     return BSRC == kBTma ? 0 : kb_count * kBTileBytes + (FP8 ? ((kb_count * kTok * 4 + 1023) & ~1023) : 0);
   }
-  __host__ __device__ static constexpr int smem_bytes(int kb_count) {
-    return kRingBytes + operand_bytes(kb_count) + 1024 /*align*/ + 1024 /*barriers + scratch*/ + kPartBytes;
+  __host__ __device__ static constexpr int smem_bytes(int kb_count, int split) {
+    return kRingBytes + operand_bytes(kb_count) + 1024 /*align*/ + 1024 /*barriers + scratch*/ + part_bytes(split);
   }
-  static constexpr int kSmemBytes = kRingBytes + 1024 + 1024 + kPartBytes;     // kBTma
 };
 
 struct GemmSmemTail {
@@ -248,20 +257,10 @@ __device__ __forceinline__ uint8_t e4m3_bits(float v) {
 template <bool FP8>
 __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* ball, float* bscale, float* rs_s,
                                                    int kb_first, int kb_count, int et) {
-  const int warp = et >> 5, lane = et & 31;
   const int rows = p.rows;
   const int tiles = p.k_total / 128;
-  // dead rows: zero (finite inputs for the unused MMA columns); stores only, nothing waits on them
-  {
-    const int dead = kTok - rows;
-    const int units = kb_count * dead * 8;
-    for (int u = et; u < units; u += 128) {
-      const int j = u & 7, rr = (u >> 3) % dead, c = (u >> 3) / dead;
-      const int r = rows + rr;
-      *reinterpret_cast<uint4*>(ball + c * kBTileBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) =
-          make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
+  // Rows >= p.rows are left as they are: an MMA column depends on its own token row only, and the columns of
+  // dead rows are never stored.
   // A unit is 16 bytes of operand: 8 bf16 elements, or 16 e4m3 elements (two 16-byte loads of x).  Every load of a
   // batch is issued before anything waits (one L2 round trip per batch), the per-tile sums of squares included.
   constexpr int kBatch = FP8 ? 4 : 8;
@@ -284,11 +283,15 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
       }
     }
     if (!have_rs) {
-      for (int r = warp; r < rows; r += 4) {
+      // 1 / rms of every row in one round trip: 8 threads per row, each adds the tiles t = sub, sub + 8, ...
+      {
+        const int r = et >> 3, sub = et & 7;
         float s = 0.f;
-        for (int t = lane; t < tiles; t += 32) s += __ldcg(p.nssq + t * kTok + r);
-        s = warp_sum_f(s);
-        if (lane == 0) rs_s[r] = rsqrtf(s / (float)p.k_total + p.neps);
+        if (r < rows)
+          for (int t = sub; t < tiles; t += 8) s += __ldcg(p.nssq + t * kTok + r);
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (sub == 0 && r < rows) rs_s[r] = rsqrtf(s / (float)p.k_total + p.neps);
       }
       epi_bar();
       have_rs = true;
@@ -520,7 +523,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(smem + Cfg::kRingBytes + Cfg::operand_bytes(kb_count));
   float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + 1024);
 
+  unsigned long long* stamp = p.stamps ? p.stamps + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 : nullptr;
+#define NRT_STAMP(i) do { if (stamp) stamp[i] = globaltimer(); } while (0)
   if (threadIdx.x == 0) {
+    NRT_STAMP(0);
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
     for (int i = 0; i < Cfg::kAccBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
     mbar_init(&tail->split_bar, 128 * (split > 1 ? split - 1 : 1));
@@ -536,6 +542,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   if (split > 1) cluster_sync_all();           // peers' barriers are initialised before any remote arrive
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
+  if (threadIdx.x == 0) NRT_STAMP(1);
 
   // Weights never depend on earlier kernels, so (ungrouped) the producer streams the first weight
   // tiles *before* waiting for the upstream grid; token tiles, scales, residuals and expert lists are
@@ -556,6 +563,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   }
   griddep_wait();
   griddep_launch();
+  if (threadIdx.x == 0) NRT_STAMP(2);
 
   int n_groups = 1, g_first = 0, g_step = 1;
   if (GROUP == kGroupItem) {
@@ -569,10 +577,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
     const int na = min(*p.n_active, p.max_slots);
     const int per = (p.n_experts + (int)gridDim.y - 1) / (int)gridDim.y;
     const int id_lo = (int)blockIdx.y * per, id_hi = id_lo + per;
-    int lo = 0;
-    while (lo < na && p.active_ids[lo] < id_lo) ++lo;
-    int hi = lo;
-    while (hi < na && p.active_ids[hi] < id_hi) ++hi;
+    // every warp counts the list entries below each bound with one round of loads (the list is ascending)
+    int lo = 0, hi = 0;
+    for (int i0 = 0; i0 < na; i0 += 32) {
+      const int i = i0 + lane;
+      const int id = i < na ? __ldg(p.active_ids + i) : 0x7fffffff;
+      lo += __popc(__ballot_sync(0xffffffffu, id < id_lo));
+      hi += __popc(__ballot_sync(0xffffffffu, id < id_hi));
+    }
     g_first = lo;
     g_step = 1;
     n_groups = hi - lo;
@@ -641,6 +653,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         if (FP8 && u >= Cfg::kAccBufs &&
             !mbar_wait(&tail->acc_empty[buf], ((u / Cfg::kAccBufs) & 1) ^ 1, p.status, kSiteAccEmpty | buf)) break;
         if (!mbar_wait(&tail->full[st], (u / Cfg::kStages) & 1, p.status, kSiteTmaFull | st)) break;
+        if (u == 0) NRT_STAMP(4);
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + st * Cfg::kStageBytes);
         const uint64_t da0 = umma_desc_sw128(sa);
@@ -661,6 +674,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         umma_commit(&tail->empty[st]);                                  // frees the smem stage
         if (FP8 || kb == kb_count - 1) umma_commit(&tail->acc_full[buf]);
       }
+      NRT_STAMP(5);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -676,6 +690,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       fence_proxy_async_smem();
       mbar_arrive(&tail->b_ready);
       epi_bar();                                     // bscale of every thread is visible to the epilogue
+      if (threadIdx.x == 64) NRT_STAMP(3);
     }
     PostCtx post_ctx;
     if (EPI == kEpiQkvPost) post_ctx = qkv_post_prepare(p.post, n0, n, p.rows);
@@ -749,6 +764,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
     }
 
+    if (threadIdx.x == 64) NRT_STAMP(6);
     // ---------------------------------------------------------------- cluster split: partials -> leader
     bool leader = true;
     if (split > 1) {
@@ -759,7 +775,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         for (int r = 0; r < kArRows; ++r) {
           st_cluster_f32(dst + (uint32_t)((((crank - 1) * kArRows + r) * kTileN + row) * 4), mix0[r]);
           if (DUAL)
-            st_cluster_f32(dst + (uint32_t)(((((kMaxSplit - 1) + crank - 1) * kArRows + r) * kTileN + row) * 4), mix1[r]);
+            st_cluster_f32(dst + (uint32_t)(((((split - 1) + crank - 1) * kArRows + r) * kTileN + row) * 4), mix1[r]);
         }
         mbar_arrive_cluster(mapa_shared(smem_u32(&tail->split_bar), 0));
       } else {
@@ -768,12 +784,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
 #pragma unroll
             for (int r = 0; r < kArRows; ++r) {
               mix0[r] += part[((y - 1) * kArRows + r) * kTileN + row];
-              if (DUAL) mix1[r] += part[(((kMaxSplit - 1) + y - 1) * kArRows + r) * kTileN + row];
+              if (DUAL) mix1[r] += part[(((split - 1) + y - 1) * kArRows + r) * kTileN + row];
             }
         }
       }
     }
 
+    if (threadIdx.x == 64) NRT_STAMP(7);
     // ---------------------------------------------------------------- epilogue op
     const bool live = leader && (n_groups > 0 || split > 1) && n < p.n_total;
     // group-item mode over a long row buffer: this CTA's 16 rows start at row_offsets[item]
@@ -794,25 +811,30 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       if (leader) qkv_post_epilogue(p.post, post_ctx, n0, n, quad, lane, mix0, p.rows, tail->red, live);
     } else if (EPI == kEpiSiluQuant) {
       if (n_groups > 0) {
-        // y = silu(gate) * up in fp32; one power-of-two scale per (token, this 128-feature tile)
+        // y = silu(gate) * up in fp32; one power-of-two scale per (token, this 128-feature tile).  Live rows only;
+        // the scale of a row is derived once (thread r of the tile) and applied as an exact reciprocal.
         float y[kTok];
 #pragma unroll
         for (int r = 0; r < kTok; ++r) {
-          y[r] = silu(mix0[r]) * mix1[r];
-          float m = fabsf(y[r]);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-          if (lane == 0) tail->red[quad][r] = m;
+          y[r] = 0.f;
+          if (r < p.rows) {
+            y[r] = silu(mix0[r]) * mix1[r];
+            const float m = warp_max_f(fabsf(y[r]));
+            if (lane == 0) tail->red[quad][r] = m;
+          }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        epi_bar();
+        if (row < p.rows) {
+          const float am = fmaxf(fmaxf(tail->red[0][row], tail->red[1][row]), fmaxf(tail->red[2][row], tail->red[3][row]));
+          tail->rs[row] = pow2_scale(am);
+        }
+        epi_bar();
         const size_t qrow = GROUP == kGroupNone ? 0 : (p.row_offsets ? (size_t)p.row_offsets[g_first] : (size_t)g_first * kTok);
 #pragma unroll
         for (int r = 0; r < kTok; ++r) {
-          const float am = fmaxf(fmaxf(tail->red[0][r], tail->red[1][r]), fmaxf(tail->red[2][r], tail->red[3][r]));
-          const float s = pow2_scale(am);
-          const __nv_fp8_e4m3 q(y[r] / s);
-          if (leader) {                          // K split over a cluster: only the leader holds the full sums
-            p.out_q[(qrow + r) * p.n_total + n] = *reinterpret_cast<const uint8_t*>(&q);
+          if (r < p.rows && leader) {               // K split over a cluster: only the leader holds the full sums
+            const float s = tail->rs[r];
+            p.out_q[(qrow + r) * p.n_total + n] = e4m3_bits(y[r] * (1.0f / s));
             if (row == 0) p.out_qscale[(qrow + r) * nt_count + n_tile] = s;
           }
         }
@@ -854,6 +876,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       if (f.tp > 1 && col_ok) {
         const uint32_t tag = (*f.epoch) * 1024u + (uint32_t)f.call_idx + 1u;
         const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
+        if (p.publish_delay_ns) {                    // a late peer (skew experiment): bounded, it still arrives
+          const uint64_t until = globaltimer() + p.publish_delay_ns;
+          while (globaltimer() < until) __nanosleep(200);
+        }
         for (int d = 1; d < f.tp; ++d) {
           const int peer = (f.rank + d) % f.tp;
           if (f.mode == 1 && peer != owner) continue;
@@ -863,6 +889,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
           for (int j = 0; j < kArPairs; ++j)
             if (j < pairs) st_tagged(dst + (size_t)j * f.features, tag, own[j]);
         }
+        if (threadIdx.x == 64) NRT_STAMP(8);
         // Batched poll: every missing word of every source is re-read per sweep, so the
         // loads of one sweep overlap instead of paying one fabric round trip each.
         uint64_t missing = 0;
@@ -890,7 +917,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
             if (*reinterpret_cast<volatile uint32_t*>(f.status) != 0u) break;
             if (globaltimer() > deadline) { report(f.status, kSiteMailbox | (uint32_t)__ffsll((long long)missing)); break; }
           }
+          if (missing == 0 && threadIdx.x == 64 && stamp) stamp[10] = sweep + 1;
         }
+        if (threadIdx.x == 64) NRT_STAMP(9);
 #pragma unroll
         for (int s = 0; s < kMaxPeers; ++s)
 #pragma unroll
@@ -926,7 +955,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
     }
     (void)ok;
+    if (threadIdx.x == 64) NRT_STAMP(11);
   }
+#undef NRT_STAMP
 
   drain_on_error(p.status);
   tc_fence_before();

@@ -59,7 +59,8 @@ class GemmArgs(C.Structure):
                 ("fab", FabricArgs), ("status", VP),
                 ("row_offsets", VP), ("ep_meta", VP), ("ep_combine", VP * K_MAX_PEERS), ("ep_top_k", I32),
                 ("ep_dispatch_call", I32), ("ep_return_call", I32),
-                ("nx", VP), ("ngamma", VP), ("nssq", VP), ("neps", F32), ("ssq_out", VP), ("post", AttnPostArgs)]
+                ("nx", VP), ("ngamma", VP), ("nssq", VP), ("neps", F32), ("ssq_out", VP), ("post", AttnPostArgs),
+                ("stamps", VP), ("publish_delay_ns", C.c_uint)]
 
 
 class AttnArgs(C.Structure):
@@ -157,11 +158,13 @@ def act_tmap(x: torch.Tensor, box_rows: int = K_TOK) -> TensorMap:
 _SPLIT_MIN_KB = int(__import__("os").environ.get("NAIVERT_SPLIT_MIN_KB", "1"))
 
 
-def pick_split(n_tiles: int, k_blocks: int, max_ctas: int = 160) -> int:
-    """CTAs per output tile (one cluster): the largest of 4, 2, 1 that divides the K blocks, leaves
+def pick_split(n_tiles: int, k_blocks: int, max_ctas: int = 160, max_split: int = 4) -> int:
+    """CTAs per output tile (one cluster): the largest of (8,) 4, 2, 1 that divides the K blocks, leaves
     every CTA at least ``NAIVERT_SPLIT_MIN_KB`` K blocks and keeps the grid within about one wave of
     the 148 SMs."""
-    for s in (4, 2):
+    for s in (8, 4, 2):
+        if s > max_split:
+            continue
         if k_blocks % s == 0 and n_tiles * s <= max_ctas and k_blocks // s >= _SPLIT_MIN_KB:
             return s
     return 1

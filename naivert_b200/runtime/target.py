@@ -355,7 +355,7 @@ class TargetRuntime:
         K.step_prologue(self.args_prologue, pdl=pdl)
         for L, d in enumerate(self.layers):
             nt = d["wqkv"].shape[0] // 128
-            K.gemm(self.V_QKV_POST, d["map_qkv"], None, None, d["args_qkv"], nt, K.pick_split(nt, s.hidden // 64), pdl=pdl)
+            K.gemm(self.V_QKV_POST, d["map_qkv"], None, None, d["args_qkv"], nt, K.pick_split(nt, s.hidden // 64, max_split=8), pdl=pdl)
             if d["kind"] == FULL_DSA:
                 if self.use_sweep:
                     K.index_sweep(*d["sweep_maps"], d["args_sweep"], min(148, -(-self.capacity // 128)), pdl=pdl)
