@@ -19,12 +19,18 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 SUBS = (("compute_103a", "compute_100a"), ("sm_103a", "sm_100a"), ("'10.3a'", "'10.0a'"))
 SUFFIXES = (".py", ".sh")
+# Vendored third-party sources that only the reference's prefill path uses (FlashAttention-4, FlashInfer, DeepEP) and
+# its build outputs are left out of the copy: the comparison arm drives the decode / verify kernels, and the GPU
+# runner refuses multi-GPU calls while the tree carries those sources (their TMA loads broadcast across a cluster).
+PRUNE = ("naivert/kernels/naive_n0p5/prefill_ext", "naivert/prefill/kernels", "tests/gpu/prefill_native", "tests/build")
 
 
 def retarget(source: str) -> list:
     if os.path.isdir(DEST):
         shutil.rmtree(DEST)
     shutil.copytree(source, DEST, symlinks=True)
+    for rel in PRUNE:
+        shutil.rmtree(os.path.join(DEST, rel), ignore_errors=True)
     edits = []
     for root, _, files in os.walk(DEST):
         for name in sorted(files):
