@@ -125,6 +125,101 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
   }
 }
 
+// All proposals of a block in one launch: the same per-step work as markov_step_kernel, with the hand-over of the
+// sampled token between steps done inside the grid.  Every CTA adds itself to a monotonic arrival counter after
+// folding its best candidate into best[step]; the CTA that completes a step's count runs the tensor-parallel
+// exchange, writes block_ids[step + 1] and publishes the step's generation; the others wait for that generation
+// (bounded) and go on with the next previous-token row.  The grid must be resident at once (checked at launch).
+__global__ void __launch_bounds__(256) markov_chain_kernel(const MarkovArgs a, int steps, unsigned long long* arrive,
+                                                           unsigned int* step_gen) {
+  __shared__ float w1s[512];
+  __shared__ unsigned long long sbest;
+  __shared__ unsigned int s_gen;
+  __shared__ int s_last, s_ok;
+  __shared__ uint64_t xv[16];
+  griddep_wait();
+  griddep_launch();
+  const float inv_t = a.params[6];
+  const unsigned long long seed = *a.seed;
+  const uint32_t round = (uint32_t)a.ctrl[NRT_CTRL_ROUND];
+  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+  const int per_lane = a.rank_dim / 8;
+  for (int step = 0; step < steps; ++step) {
+    int prev = step == 0 ? a.block_ids[0] : __ldcg(a.block_ids + step);
+    prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
+    for (int i = threadIdx.x; i < a.rank_dim; i += 256) w1s[i] = __bfloat162float(a.w1[(size_t)prev * a.rank_dim + i]);
+    if (threadIdx.x == 0) { sbest = 0ull; s_ok = 1; }
+    __syncthreads();
+    const uint32_t ctr = round * 8u + (uint32_t)step;
+    unsigned long long best = 0ull;
+    for (int i = 0; i < 4; ++i) {
+      const int t = blockIdx.x * 128 + i * 32 + grp;
+      float acc = 0.f;
+      if (t < a.vlocal) {
+        const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)t * a.rank_dim + sub * per_lane);
+        for (int k = 0; k < per_lane / 8; ++k) {
+          const uint4 v = wr[k];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+          const float* w = w1s + sub * per_lane + k * 8;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc += f.x * w[2 * j] + f.y * w[2 * j + 1];
+          }
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (sub == 0 && t < a.vlocal) {
+        const float z = a.logits[(size_t)step * a.ld + t] + round_bf16(acc);
+        a.zq[(size_t)step * a.ld + t] = z;
+        const float u = philox_uniform(seed, 3u, ctr, (uint32_t)(t + a.vbase));
+        const float g = -__logf(-__logf(u));
+        const float sc = z * inv_t + g;
+        const unsigned long long key = ((unsigned long long)float_order(sc) << 32) | (uint32_t)(~(uint32_t)(t + a.vbase));
+        best = key > best ? key : best;
+      }
+    }
+    atomicMax(&sbest, best);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      atomicMax(a.best + step, sbest);
+      __threadfence();
+      const unsigned long long old = atomicAdd(arrive, 1ull);
+      s_gen = (unsigned int)(old / gridDim.x + 1ull);
+      s_last = (old + 1ull) % gridDim.x == 0ull;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      if (threadIdx.x < 16) xv[threadIdx.x] = threadIdx.x == 0 ? *reinterpret_cast<volatile unsigned long long*>(a.best + step) : 0ull;
+      __syncthreads();
+      xchg_reduce_u64<kXMax>(xv, 1, a.x, 16 + step);
+      if (threadIdx.x == 0) {
+        a.block_ids[step + 1] = (int)(~(uint32_t)xv[0]);
+        a.best[step] = 0ull;
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(step_gen), "r"(s_gen) : "memory");
+      }
+    } else if (step + 1 < steps) {
+      if (threadIdx.x == 0) {
+        const uint64_t deadline = globaltimer() + kWaitLimitNs;
+        for (uint32_t i = 0;; ++i) {
+          // generations only grow: a later step's value also releases this wait
+          if ((int)(ld_acquire_gpu(step_gen) - s_gen) >= 0) break;
+          if ((i & 255u) == 255u) {
+            if (*reinterpret_cast<volatile uint32_t*>(a.x.status) != 0u) { s_ok = 0; break; }
+            if (globaltimer() > deadline) { report(a.x.status, kSiteGrid | 0x20u | (uint32_t)step); s_ok = 0; break; }
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  }
+}
+
 }  // namespace
 
 #define S(stream) reinterpret_cast<cudaStream_t>(stream)
@@ -135,6 +230,25 @@ extern "C" int nrt_draft_block_input(const int* block_ids, const void* embed, co
                     (const __nv_bfloat16*)embed, (const __nv_bfloat16*)mask, (__nv_bfloat16*)x, hidden, rows, vocab);
 }
 extern "C" int nrt_markov_args_size() { return (int)sizeof(MarkovArgs); }
+// steps proposals in one launch.  `sync`: two 64-bit words (arrival counter, step generation), zero-initialised once.
+extern "C" int nrt_markov_chain(const void* args, int steps, void* sync, void* stream, int pdl) {
+  MarkovArgs a;
+  memcpy(&a, args, sizeof(a));
+  if (a.rank_dim > 512 || a.rank_dim % 64 || steps < 1 || steps > 8 || !sync) return -3;
+  const int grid = (a.vlocal + 127) / 128;
+  static int resident = -1;
+  if (resident < 0) {
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, markov_chain_kernel, 256, 0) != cudaSuccess) return -3;
+    resident = per_sm * sms;
+  }
+  if (grid > resident) return -9;                 // the in-grid hand-over needs every CTA resident
+  unsigned long long* w = reinterpret_cast<unsigned long long*>(sync);
+  return launch_pdl(markov_chain_kernel, dim3(grid), dim3(256), 0, S(stream), pdl != 0, a, steps, w,
+                    reinterpret_cast<unsigned int*>(w + 1));
+}
 extern "C" int nrt_markov_step(const void* args, int step, void* stream, int pdl) {
   MarkovArgs a;
   memcpy(&a, args, sizeof(a));

@@ -498,6 +498,112 @@ __device__ __forceinline__ void qkv_post_epilogue(const AttnPostArgs& a_in, cons
   }
 }
 
+// ----------------------------------------------------------------------------- fused all-reduce epilogue
+// Thread = feature n of the output tile, mix0[r] = this rank's fp32 partial for token row r (leader CTA of a
+// cluster split).  The partial is rounded to bf16, pushed to every peer's mailbox as tagged words, the peers'
+// words are polled from the local mailbox and all ranks' values are added in rank order in fp32 on top of the
+// residual; the bf16 result (and optionally its per-tile sums of squares for the next RMSNorm) is stored.
+#define NRT_STAMP(i) do { if (stamp) stamp[i] = globaltimer(); } while (0)
+__device__ __forceinline__ void allreduce_epilogue(const GemmArgs& p, float (&mix0)[kTok], int n, int n_tile, int row, int lane,
+                                                   int quad, bool leader, GemmSmemTail* tail, unsigned long long* stamp) {
+  const FabricArgs& f = p.fab;
+  const int owner = f.mode == 1 ? n / (p.n_total / f.tp) : f.rank;        // reduce-scatter: one owner per feature
+  const bool col_ok = leader && n < p.n_total;
+  const bool mine = owner == f.rank;
+  // Each rank rounds its partial to bf16, pushes it to every peer as tagged words and adds
+  // the partials of all ranks in rank order in fp32 on top of the residual.
+  uint32_t w[kMaxPeers][kArPairs];
+  const int pairs = (p.rows + 1) >> 1;
+  float sum[kArRows];
+#pragma unroll
+  for (int r = 0; r < kArRows; ++r)
+    sum[r] = (p.resid && r < p.rows && col_ok) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
+  uint32_t own[kArPairs];
+#pragma unroll
+  for (int j = 0; j < kArPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
+  if (f.tp > 1 && col_ok) {
+    const uint32_t tag = (*f.epoch) * 1024u + (uint32_t)f.call_idx + 1u;
+    const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
+    if (p.publish_delay_ns) {                    // a late peer (skew experiment): bounded, it still arrives
+      const uint64_t until = globaltimer() + p.publish_delay_ns;
+      while (globaltimer() < until) __nanosleep(200);
+    }
+    for (int d = 1; d < f.tp; ++d) {
+      const int peer = (f.rank + d) % f.tp;
+      if (f.mode == 1 && peer != owner) continue;
+      // layout [slab][source][row pair][feature]: a warp's 32 stores of one pair are contiguous
+      uint64_t* dst = f.mailbox[peer] + (slab + f.rank) * kRowPairs * f.features + n;
+#pragma unroll
+      for (int j = 0; j < kArPairs; ++j)
+        if (j < pairs) st_tagged(dst + (size_t)j * f.features, tag, own[j]);
+    }
+    if (threadIdx.x == 64) NRT_STAMP(8);
+    // Batched poll: every missing word of every source is re-read per sweep, so the
+    // loads of one sweep overlap instead of paying one fabric round trip each.
+    uint64_t missing = 0;
+#pragma unroll
+    for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+      for (int j = 0; j < kArPairs; ++j) {
+        if (s == f.rank) w[s][j] = own[j];
+        else if (mine && s < f.tp && j < pairs) missing |= 1ull << (s * kArPairs + j);
+        else w[s][j] = 0u;
+      }
+    const uint64_t deadline = globaltimer() + f.timeout_ns;
+    const uint64_t* base = f.mailbox[f.rank] + slab * kRowPairs * f.features + n;
+    for (uint32_t sweep = 0; missing != 0; ++sweep) {
+#pragma unroll
+      for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+        for (int j = 0; j < kArPairs; ++j)
+          if (missing & (1ull << (s * kArPairs + j))) {
+            uint32_t t, v;
+            ld_tagged(base + ((size_t)s * kRowPairs + j) * f.features, t, v);
+            if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kArPairs + j)); }
+          }
+      if ((sweep & 255u) == 255u) {
+        if (*reinterpret_cast<volatile uint32_t*>(f.status) != 0u) break;
+        if (globaltimer() > deadline) { report(f.status, kSiteMailbox | (uint32_t)__ffsll((long long)missing)); break; }
+      }
+      if (missing == 0 && threadIdx.x == 64 && stamp) stamp[10] = sweep + 1;
+    }
+    if (threadIdx.x == 64) NRT_STAMP(9);
+#pragma unroll
+    for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+      for (int j = 0; j < kArPairs; ++j)
+        if (s < f.tp) { sum[2 * j] += bf16_lo(w[s][j]); sum[2 * j + 1] += bf16_hi(w[s][j]); }
+  } else {
+#pragma unroll
+    for (int r = 0; r < kArRows; ++r) sum[r] += round_bf16(mix0[r]);
+  }
+  float sq[kArRows];
+#pragma unroll
+  for (int r = 0; r < kArRows; ++r) {
+    sq[r] = 0.f;
+    if (r < p.rows && col_ok && mine) {
+      const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
+      p.out_bf16[(size_t)r * p.ld_out + n] = o;
+      if (p.out_copy) p.out_copy[(size_t)r * p.ld_copy + n] = o;
+      const float of = __bfloat162float(o);
+      sq[r] = of * of;
+    }
+  }
+  if (p.ssq_out != nullptr) {
+    // sums of squares of this tile's result rows: the next RMSNorm adds the tiles' partials in tile order
+#pragma unroll
+    for (int r = 0; r < kArRows; ++r) {
+      const float t = warp_sum_f(sq[r]);
+      if (lane == 0) tail->red[quad][r] = t;
+    }
+    epi_bar();
+    if (leader && row < kTok)
+      p.ssq_out[n_tile * kTok + row] =
+          row < kArRows ? ((tail->red[0][row] + tail->red[1][row]) + (tail->red[2][row] + tail->red[3][row])) : 0.f;
+  }
+}
+#undef NRT_STAMP
+
 template <bool FP8, bool DUAL, int EPI, int GROUP, int BSRC = kBTma>
 __global__ void __launch_bounds__(192, (DUAL || BSRC != kBTma) ? 1 : 2)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
@@ -858,101 +964,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         }
       }
     } else if (EPI == kEpiAllReduce) {
-      const FabricArgs& f = p.fab;
-      const int owner = f.mode == 1 ? n / (p.n_total / f.tp) : f.rank;        // reduce-scatter: one owner per feature
-      const bool col_ok = leader && n < p.n_total;
-      const bool mine = owner == f.rank;
-      // Each rank rounds its partial to bf16, pushes it to every peer as tagged words and adds
-      // the partials of all ranks in rank order in fp32 on top of the residual.
-      uint32_t w[kMaxPeers][kArPairs];
-      const int pairs = (p.rows + 1) >> 1;
-      float sum[kArRows];
-#pragma unroll
-      for (int r = 0; r < kArRows; ++r)
-        sum[r] = (p.resid && r < p.rows && col_ok) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
-      uint32_t own[kArPairs];
-#pragma unroll
-      for (int j = 0; j < kArPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
-      if (f.tp > 1 && col_ok) {
-        const uint32_t tag = (*f.epoch) * 1024u + (uint32_t)f.call_idx + 1u;
-        const size_t slab = (size_t)(f.call_idx % kMailboxSlabs) * f.tp;
-        if (p.publish_delay_ns) {                    // a late peer (skew experiment): bounded, it still arrives
-          const uint64_t until = globaltimer() + p.publish_delay_ns;
-          while (globaltimer() < until) __nanosleep(200);
-        }
-        for (int d = 1; d < f.tp; ++d) {
-          const int peer = (f.rank + d) % f.tp;
-          if (f.mode == 1 && peer != owner) continue;
-          // layout [slab][source][row pair][feature]: a warp's 32 stores of one pair are contiguous
-          uint64_t* dst = f.mailbox[peer] + (slab + f.rank) * kRowPairs * f.features + n;
-#pragma unroll
-          for (int j = 0; j < kArPairs; ++j)
-            if (j < pairs) st_tagged(dst + (size_t)j * f.features, tag, own[j]);
-        }
-        if (threadIdx.x == 64) NRT_STAMP(8);
-        // Batched poll: every missing word of every source is re-read per sweep, so the
-        // loads of one sweep overlap instead of paying one fabric round trip each.
-        uint64_t missing = 0;
-#pragma unroll
-        for (int s = 0; s < kMaxPeers; ++s)
-#pragma unroll
-          for (int j = 0; j < kArPairs; ++j) {
-            if (s == f.rank) w[s][j] = own[j];
-            else if (mine && s < f.tp && j < pairs) missing |= 1ull << (s * kArPairs + j);
-            else w[s][j] = 0u;
-          }
-        const uint64_t deadline = globaltimer() + f.timeout_ns;
-        const uint64_t* base = f.mailbox[f.rank] + slab * kRowPairs * f.features + n;
-        for (uint32_t sweep = 0; missing != 0; ++sweep) {
-#pragma unroll
-          for (int s = 0; s < kMaxPeers; ++s)
-#pragma unroll
-            for (int j = 0; j < kArPairs; ++j)
-              if (missing & (1ull << (s * kArPairs + j))) {
-                uint32_t t, v;
-                ld_tagged(base + ((size_t)s * kRowPairs + j) * f.features, t, v);
-                if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kArPairs + j)); }
-              }
-          if ((sweep & 255u) == 255u) {
-            if (*reinterpret_cast<volatile uint32_t*>(f.status) != 0u) break;
-            if (globaltimer() > deadline) { report(f.status, kSiteMailbox | (uint32_t)__ffsll((long long)missing)); break; }
-          }
-          if (missing == 0 && threadIdx.x == 64 && stamp) stamp[10] = sweep + 1;
-        }
-        if (threadIdx.x == 64) NRT_STAMP(9);
-#pragma unroll
-        for (int s = 0; s < kMaxPeers; ++s)
-#pragma unroll
-          for (int j = 0; j < kArPairs; ++j)
-            if (s < f.tp) { sum[2 * j] += bf16_lo(w[s][j]); sum[2 * j + 1] += bf16_hi(w[s][j]); }
-      } else {
-#pragma unroll
-        for (int r = 0; r < kArRows; ++r) sum[r] += round_bf16(mix0[r]);
-      }
-      float sq[kArRows];
-#pragma unroll
-      for (int r = 0; r < kArRows; ++r) {
-        sq[r] = 0.f;
-        if (r < p.rows && col_ok && mine) {
-          const __nv_bfloat16 o = __float2bfloat16_rn(sum[r]);
-          p.out_bf16[(size_t)r * p.ld_out + n] = o;
-          if (p.out_copy) p.out_copy[(size_t)r * p.ld_copy + n] = o;
-          const float of = __bfloat162float(o);
-          sq[r] = of * of;
-        }
-      }
-      if (p.ssq_out != nullptr) {
-        // sums of squares of this tile's result rows: the next RMSNorm adds the tiles' partials in tile order
-#pragma unroll
-        for (int r = 0; r < kArRows; ++r) {
-          const float t = warp_sum_f(sq[r]);
-          if (lane == 0) tail->red[quad][r] = t;
-        }
-        epi_bar();
-        if (leader && row < kTok)
-          p.ssq_out[n_tile * kTok + row] =
-              row < kArRows ? ((tail->red[0][row] + tail->red[1][row]) + (tail->red[2][row] + tail->red[3][row])) : 0.f;
-      }
+      allreduce_epilogue(p, mix0, n, n_tile, row, lane, quad, leader, tail, stamp);
     }
     (void)ok;
     if (threadIdx.x == 64) NRT_STAMP(11);

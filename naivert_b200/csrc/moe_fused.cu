@@ -1,0 +1,421 @@
+// One launch for a whole MoE block of the decode / verify step:
+//
+//   phase R  router: every CTA scores two experts for all rows (fp32 FMA, RMSNorm applied on the fly from the
+//            per-tile sums of squares the previous all-reduce left behind) and quantises a share of the e4m3
+//            activation packet; a grid-wide arrival counter separates it from the selection, which every CTA
+//            then repeats for itself (8 rows x 256 scores: cheaper than a second hand-off through memory);
+//   phase G  gate/up: work items (active expert, 128-feature tile) on the dual tcgen05 pipeline (weights by TMA,
+//            block-scaled e4m3, fresh TMEM accumulator per 128-wide K block), SiLU(gate) * up re-quantised to
+//            e4m3 and left in L2 with a per-(expert, tile) flag;
+//   phase D  down: CTA (output tile, expert-id range) streams its experts' down weights - the weight tiles are
+//            requested before the flags of their activations are checked, so HBM streaming never stops between
+//            the phases - weights each expert by the routing probability, hands its partial to the range-0 CTA
+//            of the tile (fixed order), which runs the fused tensor-parallel all-reduce + residual epilogue.
+//
+// 128 CTAs, one per SM, all resident (the launcher checks the occupancy): the arrival counter and the flags are
+// bounded waits that record a status word instead of hanging.  Nothing depends on which other rows share the
+// step, and every sum has a fixed order: results equal those of the three separate kernels
+// (router_kernel, grouped gate/up, grouped down) bit for bit.
+//
+// Reference counterparts: naivert/body/rmsnorm_expert_proj/, naivert/body/expert_select_up_gate_silu_rows8_body.cuh,
+// naivert/body/expert_down_allreduce/expert_down_w8a8.cuh (three launches there).
+#include "gemm.cuh"
+#include "launch.hpp"
+#include "router.cuh"
+
+#include <string.h>
+
+using namespace nrt;
+
+namespace {
+
+constexpr int kMoeCtas = 128, kMoeThreads = 256, kMoeStages = 5;
+constexpr int kMoeStageA = 2 * kATileBytes;                 // gate + up tile; the down phase uses the first half
+constexpr int kMoeStageBytes = kMoeStageA + kBTileBytes;    // 34 KiB
+constexpr int kSlotsMax = 128;
+constexpr int kGuBufs = 4, kGuCols = 2 * kTok;               // TMEM columns [0, 128): dual accumulators
+constexpr int kDnBufs = 8, kDnCols = kTok, kDnBase = 128;    // TMEM columns [128, 256)
+constexpr int kMoeTmemCols = 256;
+constexpr int kRanges = 4;                                    // expert-id ranges that share one output tile
+constexpr int kGuTilesMax = 16;
+
+struct MoeArgs {
+  RouterArgs r;
+  int inter;                      // local expert intermediate size
+  const float* gate_s;            // [experts][inter/128][hidden/128]
+  const float* up_s;
+  const float* down_s;            // [experts][hidden/128][inter/128]
+  uint8_t* y8;                    // [slots * 16][inter] e4m3 hand-off between the phases (stays in L2)
+  float* ys;                      // [slots * 16][inter/128]
+  unsigned long long* sync;       // grid arrival counter (monotonic over launches)
+  unsigned int* slot_flags;       // [kSlotsMax][kGuTilesMax] launch generation once (slot, tile) of y is complete
+  float* part;                    // [hidden/128][kRanges - 1][8][128] partial sums of ranges 1..3
+  unsigned int* part_flags;       // [hidden/128][kRanges - 1]
+  GemmArgs ar;                    // epilogue of the down phase: rows, n_total, out_bf16, ld_out, resid, out_copy, fab, ssq_out
+};
+
+struct MoeSmem {
+  GemmSmemTail tail;              // full / empty: weight ring; acc_full / acc_empty: down accumulators; red: reductions
+  uint64_t gu_full[kGuBufs], gu_empty[kGuBufs];
+  uint32_t gen;
+  int ok;
+  RouterSmem router;
+  float probs[kSlotsMax * kTok];
+  int active[kSlotsMax];
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded wait for a generation tag written by another CTA of this launch
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int gen, uint32_t* status, uint32_t site) {
+  const uint64_t deadline = globaltimer() + kWaitLimitNs;
+  for (uint32_t i = 0;; ++i) {
+    if (ld_acquire_gpu(p) == gen) return true;
+    if ((i & 255u) == 255u) {
+      if (status && *reinterpret_cast<volatile uint32_t*>(status) != 0u) return false;
+      if (globaltimer() > deadline) break;
+    }
+  }
+  report(status, site);
+  return false;
+}
+
+__global__ void __launch_bounds__(kMoeThreads, 1)
+moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_constant__ CUtensorMap tmUp,
+                 const __grid_constant__ CUtensorMap tmDown, const __grid_constant__ CUtensorMap tmX8,
+                 const __grid_constant__ CUtensorMap tmY8, const MoeArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  MoeSmem& sm = *reinterpret_cast<MoeSmem*>(smem + kMoeStages * kMoeStageBytes);
+  GemmSmemTail* tail = &sm.tail;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cta = blockIdx.x;
+  uint32_t* status = p.ar.status;
+  unsigned long long* stamp = p.ar.stamps ? p.ar.stamps + (size_t)cta * 16 : nullptr;
+#define NRT_STAMP(i) do { if (stamp) stamp[i] = globaltimer(); } while (0)
+
+  if (tid == 0) {
+    NRT_STAMP(0);
+    for (int i = 0; i < kMoeStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
+    for (int i = 0; i < kGuBufs; ++i) { mbar_init(&sm.gu_full[i], 1); mbar_init(&sm.gu_empty[i], 128); }
+    for (int i = 0; i < kDnBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmGate);
+    tma_prefetch_desc(&tmUp);
+    tma_prefetch_desc(&tmDown);
+    tma_prefetch_desc(&tmX8);
+    tma_prefetch_desc(&tmY8);
+    sm.ok = 1;
+  }
+  if (warp == 1) { tmem_alloc(&tail->tmem_base, kMoeTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tail->tmem_base;
+
+  // ------------------------------------------------------------------ phase R: scores + packet, arrival, selection
+  router_scores(p.r, cta, kMoeCtas, sm.router);            // waits for the upstream grid inside
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    NRT_STAMP(1);
+    const unsigned long long old = atomicAdd(p.sync, 1ull);
+    const unsigned long long target = (old / kMoeCtas + 1ull) * kMoeCtas;
+    sm.gen = (uint32_t)(old / kMoeCtas + 1ull);
+    const uint64_t deadline = globaltimer() + kWaitLimitNs;
+    for (uint32_t i = 0; ld_acquire_u64(p.sync) < target; ++i) {
+      if ((i & 63u) == 63u) {
+        if (*reinterpret_cast<volatile uint32_t*>(status) != 0u) { sm.ok = 0; break; }
+        if (globaltimer() > deadline) { report(status, kSiteGrid | 1u); sm.ok = 0; break; }
+      }
+    }
+    NRT_STAMP(2);
+  }
+  __syncthreads();
+  griddep_launch();                                         // every CTA of this grid is resident by now
+  const uint32_t gen = sm.gen;
+  router_select(p.r, sm.router, cta == 0, sm.probs, sm.active);
+  const int n_active = sm.ok ? sm.router.n_active : 0;
+  if (tid == 0) NRT_STAMP(3);
+
+  const int kbH = p.r.hidden / 128;                         // K blocks of gate/up
+  const int kbI = p.inter / 128;                            // K blocks of down = gate/up tiles per expert
+  const int gu_items = n_active * kbI;
+  int my_items = 0;
+  for (int it = cta; it < gu_items; it += kMoeCtas) ++my_items;
+  const int gu_units = my_items * kbH;
+  // down: CTA -> (output tile, expert-id range); the active list is ascending, so a range is a run of slots
+  const int tilesH = p.r.hidden / 128;
+  const bool dn_on = cta < tilesH * kRanges;
+  const int dn_tile = cta / kRanges, dn_range = cta % kRanges;
+  int dn_lo = 0, dn_hi = 0;
+  if (dn_on) {
+    const int per = (p.r.experts + kRanges - 1) / kRanges;
+    const int id_lo = dn_range * per, id_hi = id_lo + per;
+    for (int i0 = 0; i0 < n_active; i0 += 32) {             // every warp counts with one round of reads
+      const int i = i0 + lane;
+      const int id = i < n_active ? sm.active[i] : 0x7fffffff;
+      dn_lo += __popc(__ballot_sync(0xffffffffu, id < id_lo));
+      dn_hi += __popc(__ballot_sync(0xffffffffu, id < id_hi));
+    }
+  }
+  const int dn_slots = dn_hi - dn_lo;
+  const int dn_units = dn_slots * kbI;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both phases)
+    if (elect_one()) {
+      asm volatile("fence.proxy.async;" ::: "memory");       // the packet was written by other CTAs' plain stores
+      int u = 0;
+      bool ok = true;
+      for (int it = cta; it < gu_items && ok; it += kMoeCtas) {
+        const int slot = it / kbI, tile = it - slot * kbI;
+        const int z = sm.active[slot];
+        for (int kb = 0; kb < kbH; ++kb, ++u) {
+          const int st = u % kMoeStages;
+          if (u >= kMoeStages && !mbar_wait(&tail->empty[st], ((u / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = false; break; }
+          uint8_t* sa = smem + st * kMoeStageBytes;
+          mbar_expect_tx(&tail->full[st], kMoeStageBytes);
+          tma_load_3d(sa, &tmGate, &tail->full[st], kb * 128, tile * kTileN, z);
+          tma_load_3d(sa + kATileBytes, &tmUp, &tail->full[st], kb * 128, tile * kTileN, z);
+          tma_load_2d(sa + kMoeStageA, &tmX8, &tail->full[st], kb * 128, 0);
+        }
+      }
+      // down: the weight tile of a unit is requested first; its activation tile follows once the (slot, tile) flags
+      // of that expert's y are set (checked once per slot)
+      for (int s = 0; s < dn_slots && ok; ++s) {
+        const int slot = dn_lo + s;
+        const int z = sm.active[slot];
+        bool ready = false;
+        for (int kb = 0; kb < kbI; ++kb, ++u) {
+          const int st = u % kMoeStages;
+          if (u >= kMoeStages && !mbar_wait(&tail->empty[st], ((u / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = false; break; }
+          uint8_t* sa = smem + st * kMoeStageBytes;
+          mbar_expect_tx(&tail->full[st], kATileBytes + kBTileBytes);
+          tma_load_3d(sa, &tmDown, &tail->full[st], kb * 128, dn_tile * kTileN, z);
+          if (!ready) {
+            for (int t = 0; t < kbI && ok; ++t) ok = wait_flag(p.slot_flags + slot * kGuTilesMax + t, gen, status, kSiteGrid | 2u);
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");
+            ready = true;
+          }
+          tma_load_2d(sa + kMoeStageA, &tmY8, &tail->full[st], kb * 128, slot * kTok);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer (both phases)
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(0u, kTileN, kTok);
+      int u = 0;
+      bool ok = true;
+      for (int ug = 0; ug < gu_units && ok; ++ug, ++u) {
+        const int st = u % kMoeStages, buf = ug % kGuBufs;
+        if (ug >= kGuBufs && !mbar_wait(&sm.gu_empty[buf], ((ug / kGuBufs) & 1) ^ 1, status, kSiteAccEmpty | buf)) { ok = false; break; }
+        if (!mbar_wait(&tail->full[st], (u / kMoeStages) & 1, status, kSiteTmaFull | st)) { ok = false; break; }
+        if (ug == 0) NRT_STAMP(4);
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + st * kMoeStageBytes);
+        const uint64_t da0 = umma_desc_sw128(sa), da1 = umma_desc_sw128(sa + kATileBytes);
+        const uint64_t db = umma_desc_sw128(sa + kMoeStageA);
+        const uint32_t d0 = tmem + buf * kGuCols;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          umma_f8(d0, da0 + 2 * j, db + 2 * j, idesc, j > 0);
+          umma_f8(d0 + kTok, da1 + 2 * j, db + 2 * j, idesc, j > 0);
+        }
+        umma_commit(&tail->empty[st]);
+        umma_commit(&sm.gu_full[buf]);
+      }
+      NRT_STAMP(5);
+      for (int ud = 0; ud < dn_units && ok; ++ud, ++u) {
+        const int st = u % kMoeStages, buf = ud % kDnBufs;
+        if (ud >= kDnBufs && !mbar_wait(&tail->acc_empty[buf], ((ud / kDnBufs) & 1) ^ 1, status, kSiteAccEmpty | 0x10 | buf)) { ok = false; break; }
+        if (!mbar_wait(&tail->full[st], (u / kMoeStages) & 1, status, kSiteTmaFull | 0x10 | st)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + st * kMoeStageBytes);
+        const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kMoeStageA);
+        const uint32_t d0 = tmem + kDnBase + buf * kDnCols;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) umma_f8(d0, da + 2 * j, db + 2 * j, idesc, j > 0);
+        umma_commit(&tail->empty[st]);
+        umma_commit(&tail->acc_full[buf]);
+      }
+      NRT_STAMP(6);
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue warps (both phases)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
+    const int rows = p.r.rows;
+    bool ok = true;
+    // ---- gate/up items
+    int ug = 0;
+    for (int it = cta; it < gu_items && ok; it += kMoeCtas) {
+      const int slot = it / kbI, tile = it - slot * kbI;
+      const int z = sm.active[slot];
+      const int n = tile * kTileN + row;
+      float acc0[kTok], acc1[kTok];
+#pragma unroll
+      for (int r = 0; r < kTok; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+      const float* ws0 = p.gate_s + ((size_t)z * kbI + tile) * kbH;
+      const float* ws1 = p.up_s + ((size_t)z * kbI + tile) * kbH;
+      for (int kb = 0; kb < kbH; ++kb, ++ug) {
+        const int buf = ug % kGuBufs;
+        float sc[kTok];
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? __ldcg(p.r.xs + r * kbH + kb) : 0.f;
+        const float w0 = __ldg(ws0 + kb), w1 = __ldg(ws1 + kb);
+        if (!mbar_wait(&sm.gu_full[buf], (ug / kGuBufs) & 1, status, kSiteAccFull | buf)) { ok = false; break; }
+        tc_fence_after();
+        float v0[kTok], v1[kTok];
+        tmem_ld16(lane_addr + buf * kGuCols, v0);
+        tmem_ld16(lane_addr + buf * kGuCols + kTok, v1);
+        tc_fence_before();
+        mbar_arrive(&sm.gu_empty[buf]);
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) {
+          acc0[r] += v0[r] * (sc[r] * w0);
+          acc1[r] += v1[r] * (sc[r] * w1);
+        }
+      }
+      if (!ok) break;
+      // y = silu(gate) * up, one power-of-two scale per (row, this tile), e4m3
+      float y[kTok];
+#pragma unroll
+      for (int r = 0; r < kTok; ++r) {
+        y[r] = 0.f;
+        if (r < rows) {
+          y[r] = silu(acc0[r]) * acc1[r];
+          const float m = warp_max_f(fabsf(y[r]));
+          if (lane == 0) tail->red[quad][r] = m;
+        }
+      }
+      epi_bar();
+      if (row < rows) {
+        const float am = fmaxf(fmaxf(tail->red[0][row], tail->red[1][row]), fmaxf(tail->red[2][row], tail->red[3][row]));
+        tail->rs[row] = pow2_scale(am);
+      }
+      epi_bar();
+#pragma unroll
+      for (int r = 0; r < kTok; ++r)
+        if (r < rows) {
+          const float s = tail->rs[r];
+          p.y8[((size_t)slot * kTok + r) * p.inter + n] = e4m3_bits(y[r] * (1.0f / s));
+          if (row == 0) p.ys[((size_t)slot * kTok + r) * kbI + tile] = s;
+        }
+      __threadfence();
+      epi_bar();
+      if (row == 0) st_release_u32(p.slot_flags + slot * kGuTilesMax + tile, gen);
+    }
+    if (tid == 64) NRT_STAMP(7);
+    // ---- down: probability-weighted sum over this CTA's experts
+    float mix0[kTok];
+#pragma unroll
+    for (int r = 0; r < kTok; ++r) mix0[r] = 0.f;
+    const int n = dn_tile * kTileN + row;
+    int ud = 0;
+    for (int s = 0; s < dn_slots && ok; ++s) {
+      const int slot = dn_lo + s;
+      const int z = sm.active[slot];
+      float acc[kTok];
+#pragma unroll
+      for (int r = 0; r < kTok; ++r) acc[r] = 0.f;
+      const float* ws = p.down_s + ((size_t)z * tilesH + dn_tile) * kbI;
+      for (int kb = 0; kb < kbI; ++kb, ++ud) {
+        const int buf = ud % kDnBufs;
+        const float w0 = __ldg(ws + kb);
+        if (!mbar_wait(&tail->acc_full[buf], (ud / kDnBufs) & 1, status, kSiteAccFull | 0x10 | buf)) { ok = false; break; }
+        float sc[kTok];
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? __ldcg(p.ys + ((size_t)slot * kTok + r) * kbI + kb) : 0.f;
+        tc_fence_after();
+        float v[kTok];
+        tmem_ld16(lane_addr + kDnBase + buf * kDnCols, v);
+        tc_fence_before();
+        mbar_arrive(&tail->acc_empty[buf]);
+#pragma unroll
+        for (int r = 0; r < kTok; ++r) acc[r] += v[r] * (sc[r] * w0);
+      }
+      const float* pr = sm.probs + slot * kTok;
+#pragma unroll
+      for (int r = 0; r < kTok; ++r) mix0[r] += pr[r] * acc[r];
+    }
+    if (tid == 64) NRT_STAMP(8);
+    // ---- ranges 1..3 hand their partial to range 0 of the tile, which adds them in range order
+    bool leader = dn_on && dn_range == 0;
+    if (dn_on && dn_range != 0) {
+      float* dst = p.part + ((size_t)(dn_tile * (kRanges - 1) + dn_range - 1) * kArRows) * kTileN + row;
+#pragma unroll
+      for (int r = 0; r < kArRows; ++r) dst[(size_t)r * kTileN] = mix0[r];
+      __threadfence();
+      epi_bar();
+      if (row == 0) st_release_u32(p.part_flags + dn_tile * (kRanges - 1) + dn_range - 1, gen);
+    } else if (leader) {
+      for (int y = 1; y < kRanges && ok; ++y) {
+        ok = wait_flag(p.part_flags + dn_tile * (kRanges - 1) + y - 1, gen, status, kSiteGrid | 3u);
+        const float* src = p.part + ((size_t)(dn_tile * (kRanges - 1) + y - 1) * kArRows) * kTileN + row;
+#pragma unroll
+        for (int r = 0; r < kArRows; ++r) mix0[r] += __ldcg(src + (size_t)r * kTileN);
+      }
+    }
+    if (tid == 64) NRT_STAMP(9);
+    // every CTA takes part in the epilogue's barriers; only the leaders exchange and store
+    allreduce_epilogue(p.ar, mix0, n, dn_tile, row, lane, quad, leader, tail, nullptr);
+    if (tid == 64) NRT_STAMP(11);
+  }
+#undef NRT_STAMP
+
+  drain_on_error(status);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, kMoeTmemCols); }
+}
+
+}  // namespace
+
+extern "C" int nrt_moe_args_size() { return (int)sizeof(MoeArgs); }
+extern "C" int nrt_moe_slot_flag_words() { return kSlotsMax * kGuTilesMax; }
+extern "C" long long nrt_moe_part_floats(int hidden) { return (long long)(hidden / 128) * (kRanges - 1) * kArRows * kTileN; }
+
+// Returns -3 when the geometry does not fit this kernel (the caller keeps the three separate launches) and -9 when
+// the device cannot hold all 128 CTAs at once (the arrival counter needs every CTA resident).
+extern "C" int nrt_moe_layer(const void* tmGate, const void* tmUp, const void* tmDown, const void* tmX8, const void* tmY8,
+                             const void* args, void* stream, int pdl) {
+  MoeArgs a;
+  memcpy(&a, args, sizeof(a));
+  const RouterArgs& r = a.r;
+  if (!r.x || !r.ssq || !r.gamma || !r.x8 || !r.xs || !r.scores || r.hidden % 128 || a.inter % 128) return -3;
+  if (r.experts > 2 * kMoeCtas || r.experts > 256 || r.rows < 1 || r.rows > kArRows || r.top_k > 32) return -3;
+  if (r.max_slots > kSlotsMax || a.inter / 128 > kGuTilesMax || (r.hidden / 128) * kRanges > kMoeCtas) return -3;
+  if (r.rows * (r.hidden / 128) > 16 * kMoeCtas) return -3;
+  if (!a.sync || !a.slot_flags || !a.part || !a.part_flags || !a.y8 || !a.ys || !a.ar.status) return -3;
+  constexpr int smem = kMoeStages * kMoeStageBytes + 1024 + (int)sizeof(MoeSmem);
+  static int resident = -1;
+  if (resident < 0) {
+    cudaError_t e = cudaFuncSetAttribute(moe_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_layer_kernel, kMoeThreads, smem);
+    if (e != cudaSuccess) return (int)e;
+    resident = per_sm * sms;
+  }
+  if (resident < kMoeCtas) return -9;
+  CUtensorMap g, u, d, x, y;
+  memcpy(&g, tmGate, sizeof(g));
+  memcpy(&u, tmUp, sizeof(u));
+  memcpy(&d, tmDown, sizeof(d));
+  memcpy(&x, tmX8, sizeof(x));
+  memcpy(&y, tmY8, sizeof(y));
+  return launch_pdl(moe_layer_kernel, dim3(kMoeCtas), dim3(kMoeThreads), smem, reinterpret_cast<cudaStream_t>(stream), pdl != 0,
+                    g, u, d, x, y, a);
+}

@@ -84,6 +84,11 @@ class RouterArgs(C.Structure):
                 ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32), ("x8", VP)]
 
 
+class MoeArgs(C.Structure):
+    _fields_ = [("r", RouterArgs), ("inter", I32), ("gate_s", VP), ("up_s", VP), ("down_s", VP), ("y8", VP), ("ys", VP),
+                ("sync", VP), ("slot_flags", VP), ("part", VP), ("part_flags", VP), ("ar", GemmArgs)]
+
+
 _lib = None
 
 
@@ -282,6 +287,27 @@ def topk_rows(logits, pos0, rows, top_k, sel, pdl=True):
                               VP(_stream()), int(pdl)), "topk_rows")
 
 
+def moe_layer(gate: TensorMap, up: TensorMap, down: TensorMap, x8: TensorMap, y8: TensorMap, args: "MoeArgs", pdl=True) -> int:
+    """Router + grouped gate/up + grouped down + all-reduce of one MoE block in a single launch.  Returns the
+    library's code without raising for -3 / -9 (geometry or occupancy does not fit: use the separate kernels)."""
+    L = lib()
+    if L.nrt_moe_args_size() != C.sizeof(MoeArgs):
+        raise RuntimeError("MoeArgs layout drift")
+    code = L.nrt_moe_layer(C.byref(gate.buf), C.byref(up.buf), C.byref(down.buf), C.byref(x8.buf), C.byref(y8.buf),
+                           C.byref(args), VP(_stream()), int(pdl))
+    if code in (-3, -9):
+        return code
+    check(code, "moe_layer")
+    return 0
+
+
+def moe_scratch_sizes(hidden: int):
+    """(slot flag words, partial floats) of the fused MoE kernel's hand-off buffers."""
+    L = lib()
+    L.nrt_moe_part_floats.restype = C.c_longlong
+    return int(L.nrt_moe_slot_flag_words()), int(L.nrt_moe_part_floats(hidden))
+
+
 def router(args: RouterArgs, pdl=True):
     check(lib().nrt_router(C.byref(args), VP(_stream()), int(pdl)), "router")
 
@@ -369,6 +395,15 @@ def draft_block_input(block_ids, embed, mask, x, rows, pdl=True):
 
 def markov_step(args: MarkovArgs, step: int, pdl=True):
     check(aux_lib().nrt_markov_step(C.byref(args), step, VP(_stream()), int(pdl)), "markov_step")
+
+
+def markov_chain(args: MarkovArgs, steps: int, sync, pdl=True) -> int:
+    """All ``steps`` proposals in one launch; returns -3 / -9 without raising when the launch form does not fit."""
+    code = aux_lib().nrt_markov_chain(C.byref(args), steps, VP(ptr(sync)), VP(_stream()), int(pdl))
+    if code in (-3, -9):
+        return code
+    check(code, "markov_chain")
+    return 0
 
 
 def philox_uniform(seed: int, domain: int, a: int, b: int) -> float:

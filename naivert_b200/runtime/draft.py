@@ -95,7 +95,10 @@ class DraftRuntime:
         V = spec.vocab_shard(self.tp)
         self.dlogits = torch.zeros(PAD_ROWS, V, dtype=f32, device=dev)
         self.zq = torch.zeros(8, V, dtype=f32, device=dev)
-        self.best = torch.zeros(2, dtype=torch.int64, device=dev)
+        self.best = torch.zeros(8, dtype=torch.int64, device=dev)
+        self.markov_sync = torch.zeros(2, dtype=torch.int64, device=dev)
+        import os
+        self.markov_chain = target.fused and os.environ.get("NAIVERT_MARKOV_CHAIN", "1") == "1"
         self.ticket = torch.zeros(1, dtype=i32, device=dev)
         self.seed_buf, self.params_buf = seed_buf, params_buf
         # per-tile sums of squares of h (fc output) and of the block residual xd for the fused RMSNorms
@@ -270,6 +273,9 @@ class DraftRuntime:
         d, R, pdl = self.d, self.rows, self.pdl
         K.prep_norm(self.xd, self.g_final, R, d.norm_eps, xn=self.xn, pdl=pdl)
         K.gemm(self.V_STORE, self.t.map_lm, None, self.map_xn, self.args_head, -(-self.t.lm_head.shape[0] // 128), pdl=pdl)
+        if self.markov_chain and K.markov_chain(self.args_markov, d.block_size, self.markov_sync, pdl=pdl) == 0:
+            return
+        self.markov_chain = False
         for step in range(d.block_size):
             K.markov_step(self.args_markov, step, pdl=pdl)
 

@@ -115,19 +115,23 @@ class PrefixStore:
     def bytes(self) -> int:
         return sum(e.nbytes() for e in self.entries.values())
 
-    def checkpoint(self, key: str, position: int) -> None:
-        """Ring snapshot at ``position`` attached to the (possibly future) entry ``key``."""
-        e = self.entries.get(key)
-        ck = RingCheckpoint(position, [self._keep(r) for r in self.rings])
-        if e is None:
-            e = ParkedPrefix(key, [], 0, [], [], [ck], time.monotonic())
-            self.entries[key] = e
-        else:
-            e.checkpoints = [c for c in e.checkpoints if c.position != position][-3:] + [ck]
+    def make_checkpoint(self, position: int) -> RingCheckpoint:
+        """Snapshot of the rings at ``position``, owned by the caller (a session keeps the one taken at its prompt
+        end and hands it to ``save`` together with the tokens it belongs to)."""
+        return RingCheckpoint(position, [self._keep(r) for r in self.rings])
 
-    def save(self, key: str, tokens: Sequence[int], position: int) -> ParkedPrefix:
+    def save(self, key: str, tokens: Sequence[int], position: int,
+             checkpoints: Optional[Sequence[RingCheckpoint]] = None) -> ParkedPrefix:
+        """Park ``tokens[:position]``.  A checkpoint must belong to the saved prefix: those handed in were taken
+        while this very sequence was in the caches; those of the entry being replaced are kept only inside the
+        token prefix the old and the new sequence share."""
         old = self.entries.get(key)
-        cks = [c for c in (old.checkpoints if old else []) if c.position <= position]
+        shared = min(position, common_prefix(old.tokens, tokens)) if old else 0
+        cks = [c for c in (old.checkpoints if old else []) if c.position <= shared]
+        for c in checkpoints or ():
+            if c is not None and c.position <= position:
+                cks = [k for k in cks if k.position != c.position] + [c]
+        cks = sorted(cks, key=lambda c: c.position)[-4:]
         e = ParkedPrefix(key, list(tokens), position, [self._keep(t[:position]) for t in self.full],
                          [self._keep(r) for r in self.rings], cks, time.monotonic())
         self.entries[key] = e

@@ -218,15 +218,16 @@ class SessionEngine:
         self.engine.round.initialize(prompt, max_decode, sampling or SamplingParams(), use_graphs=use_graphs,
                                      start_pos=replay_from)
         t2 = time.perf_counter()
-        key = session_id or "anon"
-        if n - 1 >= 16:
-            self.store.checkpoint(key, n - 1)            # ring state at prompt end, for later rewinds
+        # ring state at prompt end, for later rewinds; it stays with this session until the sequence it belongs to
+        # is parked (a checkpoint filed under the bare session key could end up beside another branch's tokens)
+        ring_ck = self.store.make_checkpoint(n - 1) if n - 1 >= 16 else None
         info = {"path": path, "restore_ms": round((t1 - t0) * 1e3, 3), "init_ms": round((t2 - t1) * 1e3, 3),
                 "resumed_from": choice.key if start else None, "estimate_ms": round(prefill_estimate(n - 1 - start, path), 2),
                 "phases": {"restore_ms": round((t1 - t0) * 1e3, 3), "executor_ms": self.engine.last_prefill.get("executor_ms", 0.0),
                            "native_rows": self.engine.last_prefill.get("native_rows", 0), "replay_rows": n - 1 - replay_from,
                            "init_ms": round((t2 - t1) * 1e3, 3)}}
         self.active = Session(self, tokens, start, session_id, info)
+        self.active.ring_checkpoint = ring_ck
         return self.active
 
     def _park(self, s: Session) -> None:
@@ -236,7 +237,8 @@ class SessionEngine:
         if position < 16 or position > len(seq):
             return
         name = park_name(self.store.entries, s.session_id, seq)
-        self.store.save(name, seq, position)
+        ck = getattr(s, "ring_checkpoint", None)
+        self.store.save(name, seq, position, checkpoints=[ck] if ck is not None else None)
 
     def close(self) -> None:
         self.store.clear()

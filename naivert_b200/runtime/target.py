@@ -167,6 +167,14 @@ class TargetRuntime:
         # sums of squares of the residual rows per 128-feature tile, left behind by whoever wrote the rows
         # (prologue, o_proj / down epilogues) for the RMSNorm fused into the next projection
         self.ssq = torch.zeros(H // 128, PAD_ROWS, dtype=f32, device=dev)
+        # fused MoE block (router + gate/up + down + all-reduce in one launch): hand-off buffers shared by all layers
+        import os as _os
+        self.moe_fused = self.fused and _os.environ.get("NAIVERT_MOE_FUSED", "1") == "1" and rows <= 8
+        flag_words, part_floats = K.moe_scratch_sizes(H)
+        self.moe_sync = torch.zeros(2, dtype=torch.int64, device=dev)
+        self.moe_slot_flags = torch.zeros(flag_words, dtype=i32, device=dev)
+        self.moe_part = torch.zeros(part_floats, dtype=f32, device=dev)
+        self.moe_part_flags = torch.zeros(H // 128 * 4, dtype=i32, device=dev)
         a0 = s.attention[s.layer_kinds[0]]
         nh_max = max(s.attention[k].local_heads(self.tp) for k in set(s.layer_kinds))
         self.q = torch.zeros(PAD_ROWS, nh_max, a0.head_dim, dtype=bf, device=dev)
@@ -323,6 +331,16 @@ class TargetRuntime:
                 g.fab = self.fab.fabric_args(2 * L + 1, H)
                 g.ssq_out = self.ssq.data_ptr() if self.fused else None
                 d["args_down"] = g
+                if self.moe_fused:
+                    m = K.MoeArgs()
+                    m.r = d["args_router"]
+                    m.inter = d["gate"].n
+                    m.gate_s, m.up_s, m.down_s = d["gate"].s.data_ptr(), d["up"].s.data_ptr(), d["down"].s.data_ptr()
+                    m.y8, m.ys = self.y8.data_ptr(), self.ys.data_ptr()
+                    m.sync, m.slot_flags = self.moe_sync.data_ptr(), self.moe_slot_flags.data_ptr()
+                    m.part, m.part_flags = self.moe_part.data_ptr(), self.moe_part_flags.data_ptr()
+                    m.ar = d["args_down"]
+                    d["args_moe"] = m
         g = self._gemm_args(self.lm_head.shape[0], H, R)
         g.out_f32, g.ld_out = self.logits.data_ptr(), self.logits.shape[1]
         self.args_head = g
@@ -380,7 +398,11 @@ class TargetRuntime:
                        K.pick_split(nt, s.hidden // 128), pdl=pdl)
                 K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128,
                        K.pick_split(s.hidden // 128, dn["down"].k // 128), pdl=pdl)
+            elif self.moe_fused and K.moe_layer(d["gate"].map, d["up"].map, d["down"].map, self.map_x8, self.map_y8,
+                                                d["args_moe"], pdl=pdl) == 0:
+                pass
             else:
+                self.moe_fused = False           # geometry or occupancy does not fit the fused kernel: separate launches
                 K.router(d["args_router"], pdl=pdl)
                 K.gemm(self.V_FP8_GU_ITEM, d["gate"].map, d["up"].map, self.map_x8, d["args_gu"], d["gate"].n // 128,
                        self.step_slots, pdl=pdl)

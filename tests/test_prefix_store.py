@@ -15,9 +15,9 @@ def test_save_restore_roundtrip_and_rewind():
     for t in full:
         t.copy_(torch.arange(t.numel(), dtype=torch.float32).reshape(t.shape))
     rings[0].fill_(1.0)
-    st.checkpoint("a", 10)                       # ring state at prompt end
+    ck = st.make_checkpoint(10)                  # ring state at prompt end, kept by the session
     rings[0].fill_(2.0)
-    st.save("a", list(range(30)), 29)
+    st.save("a", list(range(30)), 29, checkpoints=[ck])
     saved = [t.clone() for t in full]
     for t in full:
         t.zero_()
@@ -32,6 +32,38 @@ def test_save_restore_roundtrip_and_rewind():
     assert ch.position == 10 and ch.checkpoint == 0
     st.restore(ch)
     assert float(rings[0][0, 0]) == 1.0
+
+
+def test_branch_then_rewind_never_takes_the_other_branch_rings():
+    """Conversation A is parked under its session key; a branch of the same session is parked as ``key#1`` with its
+    own prompt-end checkpoint.  A later rewind inside A must get rings taken while A was in the caches."""
+    full, rings, st = _store()
+    a_prompt = list(range(100, 140))                                    # 40 tokens
+    rings[0].fill_(1.0)
+    ck_a = st.make_checkpoint(39)
+    rings[0].fill_(2.0)
+    a_seq = a_prompt + list(range(500, 520))
+    st.save(park_name(st.entries, "S", a_seq), a_seq, 59, checkpoints=[ck_a])
+    # a branch that shares 20 tokens with A, 120 tokens long, same session id
+    b_seq = a_prompt[:20] + list(range(900, 1000))
+    rings[0].fill_(7.0)
+    ck_b = st.make_checkpoint(119)
+    rings[0].fill_(8.0)
+    name_b = park_name(st.entries, "S", b_seq)
+    assert name_b == "S#1"
+    st.save(name_b, b_seq, 119, checkpoints=[ck_b])
+    # rewind inside A: shares 50 tokens with A (beyond A's prompt end at 39), 20 with the branch
+    req = a_seq[:50] + [1, 2, 3]
+    ch = select_resume(st.entries, req, "S", min_gain=4)
+    assert ch.key == "S" and ch.position == 39 and ch.checkpoint is not None
+    st.restore(ch)
+    assert float(rings[0][0, 0]) == 1.0                                 # A's rings at its prompt end, not the branch's
+    # no entry carries a checkpoint beyond its own tokens
+    for e in st.entries.values():
+        assert all(c.position <= e.position for c in e.checkpoints)
+    # replacing A by a sequence that diverges at 30 drops A's checkpoint at 39
+    st.save("S", a_seq[:30] + [4] * 40, 69)
+    assert all(c.position <= 30 for c in st.entries["S"].checkpoints)
 
 
 def test_selection_prefers_longest_then_own_key():
