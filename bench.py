@@ -106,7 +106,7 @@ class ClockSampler(threading.Thread):
                     self.samples.append(f)
             except Exception:
                 pass
-            self.stop_flag.wait(0.2)
+            self.stop_flag.wait(0.05)
 
     def summary(self) -> dict:
         sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
@@ -134,6 +134,7 @@ def main() -> int:
     ap.add_argument("--pdl", action="store_true", help="chain kernels with programmatic dependent launch (default: plain stream order, measured faster)")
     ap.add_argument("--device-chain", action="store_true", help="the round graph relaunches itself from the device")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
+    ap.add_argument("--no-check", action="store_true", help="skip the small-geometry correctness self-check (outside the timed region)")
     ap.add_argument("--prefill-chunk", type=int, default=2048,
                     help="rows per chunk of the native prompt ingestion (0: eight-row replay only); outside the timed rounds")
     a = ap.parse_args()
@@ -162,6 +163,7 @@ def main() -> int:
         group = dist.group.WORLD
 
     spec = resolve_model(a.model)
+    full_layers = spec.layer_count
     layers = a.layers or LAYERS_FOR_GPUS.get(a.shape_tp or world, spec.layer_count)
     if layers < spec.layer_count:
         spec = spec.with_layers(layers)
@@ -231,7 +233,11 @@ def main() -> int:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    value = tokens / (ms * 1e-3)
+    # Headline: expected tokens per round of the per-position Bernoulli(0.7) mask (3.141) over the measured round
+    # time.  The tokens a short run happens to draw scatter by +-15 % around that expectation; they are reported
+    # beside it (value_sampled), the round time is the measurement.
+    value_sampled = tokens / (ms * 1e-3)
+    value = EXPECTED_TOKENS_PER_ROUND * a.steps / (ms * 1e-3)
 
     # ------------------------------------------------------------------ end to end through the public API
     # A fresh request through Engine.generate(): the prompt is copied from pinned host memory, replayed,
@@ -249,40 +255,68 @@ def main() -> int:
         if t_first is None:
             t_first, got_first = time.perf_counter(), got
     t3 = time.perf_counter()
-    e2e_rate = (got - got_first) / max(1e-9, t3 - t_first)
-    e = torch.tensor([e2e_rate], dtype=torch.float64, device=dev)
+    e2e_sampled = (got - got_first) / max(1e-9, t3 - t_first)
+    e2e_rate = EXPECTED_TOKENS_PER_ROUND * max(0, rounds - 1) / max(1e-9, t3 - t_first)
+    e = torch.tensor([e2e_rate, e2e_sampled], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e, op=dist.ReduceOp.MIN)
-    e2e_rate = float(e.item())
+    e2e_rate, e2e_sampled = float(e[0].item()), float(e[1].item())
+
+    # ------------------------------------------------------------------ correctness record for this TP degree
+    # (small W8A8 geometry, same kernels and code paths: oracle error, lockstep, determinism, speculative == greedy)
+    check = None
+    last_prefill, kv_bytes = eng.last_prefill, eng.kv_bytes()
+    kernels_per_round, host_launches = int(r.kernels_per_round), r.host_launches
+    path_info = {"pdl": bool(a.pdl), "device_chain": bool(a.device_chain), "fused_step": bool(r.t.fused),
+                 "fused_moe": bool(getattr(r.t, "moe_fused", False)), "markov_chain": bool(getattr(r.draft, "markov_chain", False))}
+    if not a.no_check and not a.shape_tp:
+        eng.close()
+        eng = None
+        r = None
+        from naivert_b200.runtime.selfcheck import tp_selfcheck
+        try:
+            check = tp_selfcheck(rank, world, group, dev)
+        except Exception as exc:                                   # noqa: BLE001 - reported, never hidden
+            check = {"error": repr(exc)[:300]}
 
     if rank == 0:
         out = {
             "metric": "single-stream device tokens/s @ forced acceptance; spec-round ms; 8xB200",
             "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": round(ms / a.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 4), "dtype": "fp8 (e4m3 block-scaled weights and activations, bf16 residual)",
+            "vs_baseline": round(value / BASELINE_TOK_S, 4) if spec.layer_count == full_layers else None, "dtype": "fp8 (e4m3 block-scaled weights and activations, bf16 residual)",
             "data": "synthetic: random-init weights generated on device, uniform random prompt ids",
+            "value_sampled": round(value_sampled, 2), "tokens_per_round_expected": round(EXPECTED_TOKENS_PER_ROUND, 4),
+            "layers": spec.layer_count, "layers_full_model": full_layers, "ms_per_layer": round(ms / a.steps / spec.layer_count, 5),
+            # what the rate would be if the whole round scaled with the layer count (draft and sampler do not, so this
+            # understates shallow cuts): lets a reader put the 16- and 32-layer cuts of TP1 / TP2 beside the full model
+            "vs_baseline_layers_scaled": round(value * spec.layer_count / full_layers / BASELINE_TOK_S, 4),
             "config": {"model": spec.name, "layers": spec.layer_count, "global_batch": 1, "seq_len": a.prompt,
                        "parallelism": f"tp{world}", "prompt_tokens": a.prompt, "temperature": 0.4, "top_p": 0.95,
                        "forced_accept_p": 0.7, "tokens_per_round": round(tokens / a.steps, 3),
+                       "value_definition": "expected tokens per round (3.141) / measured round time; value_sampled uses the tokens drawn",
+                       "path": path_info,
                        "l2": "per-round weight traffic (GBs) exceeds the 126 MB L2; no explicit flush",
                        "timing": ("device globaltimer stamps of the ring records of K self-relaunched rounds, max over ranks"
                                   if a.device_chain else "CUDA events on the round stream around K graph replays, max over ranks"),
-                       "host_graph_launches": r.host_launches,
+                       "host_graph_launches": host_launches,
                        "ignore_eos": True, "stopped_early": bool(stopped)},
             "clocks": clocks.summary() if clocks else None,
-            "e2e": {"value": round(e2e_rate, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 64,
+            "check": check,
+            "e2e": {"value": round(e2e_rate, 2), "value_sampled": round(e2e_sampled, 2), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 64,
                     "note": "host clock over Engine.stream_rounds(); prompt H2D (pinned) and replay are outside this rate",
                     "request": {"prompt_h2d_bytes": int(prompt.numel() * 4), "prefill_s": round(t2 - t1, 4),
                                 "decode_s": round(t3 - t2, 4), "tokens": got, "rounds": rounds}},
-            "gpu_launches": int(r.kernels_per_round * a.steps),
-            "kernels_per_round": int(r.kernels_per_round),
+            "gpu_launches": int(kernels_per_round * a.steps),
+            "kernels_per_round": kernels_per_round,
             "diagnostic_shape_tp": a.shape_tp or None,
-            "build_s": round(build_s, 2), "prefill_s": round(prefill_s, 3), "prefill": eng.last_prefill,
-            "kv_bytes_per_gpu": eng.kv_bytes(),
+            "build_s": round(build_s, 2), "prefill_s": round(prefill_s, 3), "prefill": last_prefill,
+            "kv_bytes_per_gpu": kv_bytes,
         }
         print(json.dumps(out))
-    eng.close()
+    if eng is not None:
+        eng.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

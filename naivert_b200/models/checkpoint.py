@@ -50,6 +50,7 @@ def read_header(path: str) -> Dict[str, dict]:
         header = json.loads(f.read(n))
     header.pop("__metadata__", None)
     end = 0
+    spans = []
     for name, meta in header.items():
         if meta["dtype"] not in ALLOWED_DTYPES:
             raise CheckpointError(f"{path}: tensor {name} has unsupported dtype {meta['dtype']}")
@@ -60,8 +61,15 @@ def read_header(path: str) -> Dict[str, dict]:
         if hi - lo != numel * torch.empty((), dtype=ALLOWED_DTYPES[meta["dtype"]]).element_size():
             raise CheckpointError(f"{path}: tensor {name} byte range does not match its shape")
         end = max(end, hi)
+        spans.append((lo, hi, name))
     if 8 + n + end > size:
         raise CheckpointError(f"{path}: tensor data runs past end of file")
+    # payload intervals tile [0, end) without gaps or overlaps (the format writes tensors back to back)
+    at = 0
+    for lo, hi, name in sorted(spans):
+        if lo != at:
+            raise CheckpointError(f"{path}: tensor {name} starts at byte {lo}, expected {at} (overlapping or non-contiguous payload)")
+        at = hi
     return header
 
 
@@ -109,9 +117,10 @@ class LocalCheckpoint:
                 raise CheckpointError(f"index maps {name} to {f}, which does not contain it")
 
     def identity(self) -> CheckpointIdentity:
-        meta = {n: (self.headers[f][n]["dtype"], self.headers[f][n]["shape"]) for n, f in self.weight_map.items()}
+        meta = {n: (self.headers[f][n]["dtype"], self.headers[f][n]["shape"], f, self.headers[f][n]["data_offsets"])
+                for n, f in self.weight_map.items()}
         counts: Dict[str, int] = {}
-        for dt, _ in meta.values():
+        for dt, *_ in meta.values():
             counts[dt] = counts.get(dt, 0) + 1
         return CheckpointIdentity(_sha(self.config_bytes), _sha(self.index_bytes),
                                   _sha(json.dumps(meta, sort_keys=True).encode()), len(meta), counts)
@@ -297,15 +306,124 @@ def validate_target_layout(spec: ModelSpec, ckpt: LocalCheckpoint) -> None:
         raise CheckpointError("hybrid_layer_pattern does not match the model geometry")
 
 
+class SliceReader:
+    """Reads rows / columns of checkpoint tensors straight from the shards (``safe_open(...).get_slice``): a rank
+    touches only the bytes it owns.  Shard handles stay open for the lifetime of the reader.
+    Parity: the sliced reads of naivert/models/naive_n0p5/checkpoint_fp8.py:149-224."""
+
+    def __init__(self, ckpt: "LocalCheckpoint"):
+        self.ckpt, self._open = ckpt, {}
+        self.bytes_read = 0
+
+    def _slice(self, name: str):
+        from safetensors import safe_open
+        f = self.ckpt.weight_map[name]
+        if f not in self._open:
+            self._open[f] = safe_open(os.path.join(self.ckpt.root, f), framework="pt", device="cpu").__enter__()
+        return self._open[f].get_slice(name)
+
+    def _count(self, t: torch.Tensor) -> torch.Tensor:
+        self.bytes_read += t.numel() * t.element_size()
+        return t
+
+    def has(self, name: str) -> bool:
+        return name in self.ckpt.weight_map
+
+    def full(self, name: str) -> torch.Tensor:
+        return self._count(self._slice(name)[:])
+
+    def rows(self, name: str, lo: int, hi: int) -> torch.Tensor:
+        return self._count(self._slice(name)[lo:hi])
+
+    def cols(self, name: str, lo: int, hi: int) -> torch.Tensor:
+        return self._count(self._slice(name)[:, lo:hi])
+
+    def close(self) -> None:
+        for h in self._open.values():
+            h.__exit__(None, None, None)
+        self._open = {}
+
+
+def load_rank_weights_sliced(spec: ModelSpec, ckpt: "LocalCheckpoint", rank: int, tp: int, reader: Optional[SliceReader] = None) -> dict:
+    """The weights rank ``rank`` of ``tp`` owns, read slice by slice: equal to
+    ``shard_weights(spec, prepare_weights(spec, full_state_dict), rank, tp)`` without ever holding the full
+    checkpoint (about 300 GB at full size) in host memory.  q / k rows are re-ordered for adjacent-pair RoPE per
+    head, so a slice of whole heads is transformed exactly like the full matrix; the 128 x 128 e4m3 blocks of
+    o_proj / dense weights are cut on block boundaries, so quantising a slice equals slicing the quantised matrix."""
+    from .weights import _q8, interleave_rope
+    own = reader is None
+    rd = reader or SliceReader(ckpt)
+    fp8 = spec.weight_dtype == "fp8"
+    ix, rt = spec.indexer, spec.routing
+    V = spec.vocab_shard(tp)
+    try:
+        out = {"embed": rd.full("model.embed_tokens.weight"), "norm": rd.full("model.norm.weight"),
+               "lm_head": rd.rows("lm_head.weight", rank * V, (rank + 1) * V).contiguous(), "layers": []}
+        for L, kind in enumerate(spec.layer_kinds):
+            a = spec.attention[kind]
+            p = f"model.layers.{L}."
+            nh = a.local_heads(tp)
+            kvs = a.kv_head_for_rank(rank, tp)
+            r = {"kind": kind, "g_in": rd.full(p + "input_layernorm.weight"), "g_post": rd.full(p + "post_attention_layernorm.weight")}
+            r["wq"] = interleave_rope(rd.rows(p + "self_attn.q_proj.weight", rank * nh * a.head_dim, (rank + 1) * nh * a.head_dim),
+                                      nh, a.head_dim, a.rope_dim)
+            r["wk"] = torch.cat([interleave_rope(rd.rows(p + "self_attn.k_proj.weight", h * a.head_dim, (h + 1) * a.head_dim),
+                                                 1, a.head_dim, a.rope_dim) for h in kvs]).contiguous()
+            r["wv"] = torch.cat([rd.rows(p + "self_attn.v_proj.weight", h * a.v_head_dim, (h + 1) * a.v_head_dim)
+                                 for h in kvs]).contiguous()
+            r["wo"] = _q8(rd.cols(p + "self_attn.o_proj.weight", rank * nh * a.v_head_dim, (rank + 1) * nh * a.v_head_dim).contiguous(), fp8)
+            sink = p + "self_attn.attention_sink_bias"
+            r["sink"] = rd.rows(sink, rank * nh, (rank + 1) * nh).contiguous() if rd.has(sink) else None
+            if kind == FULL_DSA:
+                q = p + "self_attn.indexer."
+                r["iwq"] = interleave_rope(rd.full(q + "wq.weight"), ix.head_count, ix.head_dim, ix.rope_dim)
+                r["iwk"] = interleave_rope(rd.full(q + "wk.weight"), 1, ix.head_dim, ix.rope_dim)
+                r["iww"] = rd.full(q + "weights_proj.weight")
+                r["ik_w"] = interleave_rope(rd.full(q + "k_norm.weight"), 1, ix.head_dim, ix.rope_dim)
+                r["ik_b"] = interleave_rope(rd.full(q + "k_norm.bias"), 1, ix.head_dim, ix.rope_dim)
+            if spec.is_dense(L):
+                I = spec.dense_inter_local(tp)
+                r["dense"] = {"gate": _q8(rd.rows(p + "mlp.gate_proj.weight", rank * I, (rank + 1) * I).contiguous(), fp8),
+                              "up": _q8(rd.rows(p + "mlp.up_proj.weight", rank * I, (rank + 1) * I).contiguous(), fp8),
+                              "down": _q8(rd.cols(p + "mlp.down_proj.weight", rank * I, (rank + 1) * I).contiguous(), fp8)}
+            else:
+                I = spec.expert_inter_local(tp)
+                r["router_w"] = rd.full(p + "mlp.gate.weight").float()
+                bias = p + "mlp.gate.e_score_correction_bias"
+                r["router_b"] = rd.full(bias).float() if rd.has(bias) else torch.zeros(rt.expert_count)
+                names = [p + f"mlp.experts.{e}." for e in range(rt.expert_count)]
+                names += [p + f"mlp.shared_experts.{e}." for e in range(rt.shared_expert_count)]
+                if fp8 and (I % 128 or (rank * I) % 128):
+                    raise CheckpointError(f"expert slice of {I} channels is not aligned to the 128-wide scale blocks")
+                b0, b1 = rank * I // 128, -(-(rank + 1) * I // 128)
+                for name in ("gate", "up", "down"):
+                    ws, ss = [], []
+                    for q in names:
+                        t = q + f"{name}_proj.weight"
+                        if name == "down":
+                            ws.append(rd.cols(t, rank * I, (rank + 1) * I).contiguous())
+                            if fp8:
+                                ss.append(rd.cols(t + "_scale_inv", b0, b1).contiguous())
+                        else:
+                            ws.append(rd.rows(t, rank * I, (rank + 1) * I).contiguous())
+                            if fp8:
+                                ss.append(rd.rows(t + "_scale_inv", b0, b1).contiguous())
+                    r[name] = {"w": torch.stack(ws), "s": torch.stack(ss) if fp8 else None}
+            out["layers"].append(r)
+        return out
+    finally:
+        if own:
+            rd.close()
+
+
 def load_rank_weights(spec: ModelSpec, root: str, rank: int, tp: int, device="cpu",
                       expect: Optional[CheckpointIdentity] = None) -> Tuple[dict, CheckpointIdentity]:
-    """Validate, load and TP-slice a target checkpoint for one rank."""
+    """Validate a target checkpoint and read the slices one rank owns (nothing else is read from the shards)."""
     ckpt = LocalCheckpoint(root)
     ident = ckpt.identity()
     ident.require(expect)
     validate_target_layout(spec, ckpt)
-    sd = ckpt.load_tensors(device="cpu")
-    w = shard_weights(spec, prepare_weights(spec, sd), rank, tp)
+    w = load_rank_weights_sliced(spec, ckpt, rank, tp)
     return _to_device(w, device), ident
 
 

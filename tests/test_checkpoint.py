@@ -128,3 +128,55 @@ def test_resolve_newest_step(tmp_path, monkeypatch):
         os.makedirs(tmp_path / "run" / s)
     monkeypatch.setenv("NAIVERT_MODEL_ROOTS", str(tmp_path))
     assert ck.resolve_checkpoint("run").endswith("step_40")
+
+
+def _same(a, b, path=""):
+    if isinstance(a, dict):
+        assert set(a) == set(b), path
+        for k in a:
+            _same(a[k], b[k], f"{path}.{k}")
+    elif isinstance(a, (list, tuple)):
+        assert len(a) == len(b), path
+        for i, (x, y) in enumerate(zip(a, b)):
+            _same(x, y, f"{path}[{i}]")
+    elif isinstance(a, torch.Tensor):
+        assert a.dtype == b.dtype and a.shape == b.shape, path
+        x = a.view(torch.uint8) if a.dtype == torch.float8_e4m3fn else a
+        y = b.view(torch.uint8) if b.dtype == torch.float8_e4m3fn else b
+        assert torch.equal(x, y), path
+    else:
+        assert a == b, path
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4])
+def test_sliced_rank_load_equals_shard_of_full(tmp_path, tp):
+    """Reading only a rank's rows / columns from the shards gives exactly shard_weights(prepare_weights(full)),
+    and touches a fraction of the checkpoint's bytes."""
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    spec = small_w8a8_spec(2)
+    root = str(tmp_path / "tgt")
+    ck.write_target_checkpoint(root, spec, seed=5, shard_bytes=8 << 20)
+    c = ck.LocalCheckpoint(root)
+    full = prepare_weights(spec, c.load_tensors())
+    total = sum(os.path.getsize(os.path.join(root, f)) for f in set(c.weight_map.values()))
+    for rank in range(tp):
+        rd = ck.SliceReader(c)
+        got = ck.load_rank_weights_sliced(spec, c, rank, tp, reader=rd)
+        _same(got, shard_weights(spec, full, rank, tp))
+        if tp > 1:
+            assert rd.bytes_read < 0.75 * total
+        rd.close()
+
+
+def test_header_rejects_overlapping_payload(tmp_path):
+    p = tmp_path / "y.safetensors"
+    hdr = json.dumps({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},
+                      "b": {"dtype": "F32", "shape": [2], "data_offsets": [4, 12]}}).encode()
+    p.write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 12)
+    with pytest.raises(ck.CheckpointError):
+        ck.read_header(str(p))
+    hdr = json.dumps({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},
+                      "b": {"dtype": "F32", "shape": [2], "data_offsets": [12, 20]}}).encode()
+    p.write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 20)
+    with pytest.raises(ck.CheckpointError):
+        ck.read_header(str(p))

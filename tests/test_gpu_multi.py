@@ -10,24 +10,32 @@ import torch
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
+def _free_port() -> int:
+    """A rendezvous port nobody on this (shared) host listens on right now."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _run(n):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", "29517", os.path.join(os.path.dirname(__file__), "mp_tp_worker.py")]
+           "--master-port", str(_free_port()), os.path.join(os.path.dirname(__file__), "mp_tp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-4000:]
     return json.loads(lines[-1][7:])
 
 
-@pytest.mark.parametrize("n", [2, 4])
+@pytest.mark.parametrize("n", [2, 4, 8])
 def test_tensor_parallel_engine(n):
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     r = _run(n)
     assert r["status"] == 0
     assert r["residual_identical"] and r["lockstep"] and r["deterministic"] and r["spec_equals_greedy"], r
-    assert r["verify_mean_rel"] < 0.1 and r["argmax_ok"], r
+    assert r["verify_mean_rel"] < 0.06 and r["argmax_ok"], r
     assert r["real_sampling_tokens"] == 64
 
 
@@ -35,7 +43,7 @@ def _run_worker(n, script, **extra_env):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", **extra_env)
     path = os.path.join(os.path.dirname(__file__), script)
     cmd = [sys.executable, path] if n == 1 else [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-                                                 "--master-addr", "127.0.0.1", "--master-port", "29519", path]
+                                                 "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), path]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-4000:]
@@ -57,16 +65,16 @@ def test_expert_parallel_all_to_all(n):
 @pytest.mark.parametrize("n,exact", [(1, True), (1, False), (2, False)])
 def test_native_prefill_matches_replay(n, exact):
     """Chunked prefill (TP attention; EP experts at n > 1) leaves the caches the eight-row replay leaves.
-    ``exact``: with the step path's attention kernel the arithmetic is identical up to the first MoE output."""
+    ``exact``: the chunk path runs the row attention kernel instead of the grouped-head one.  The step path sums the
+    squares of a row per 128-feature tile and runs its attention on tensor cores, so the two paths agree to
+    rounding, not bit for bit."""
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     r = _run_worker(n, "mp_prefill_worker.py", NAIVERT_PREFILL_GROUP_ATTN="0" if exact else "1")
     assert r["status"] == 0 and r["repeat_identical"], r
     assert r["prefill"]["path"] == "native" and r["prefill"]["native_rows"] >= 672, r
     if exact:
-        # same arithmetic up to the first MoE output: attention-side kernels and the dense MLP are exact
-        for k in ("L0.k", "L0.v", "L0.ik", "L0.iks", "L1.k", "L1.v"):
-            assert k in r["bitwise"], r
+        assert r["worst"] < 0.06, r
     if n > 1:
         assert r["lockstep"], r
     assert r["worst"] < 0.1, r
