@@ -113,8 +113,19 @@ def main(argv=None) -> int:
     def factory() -> ServerContext:
         torch.cuda.set_device(local)                      # the worker thread owns the device context
         se = build_engine()
+        formatter = ChatFormatter.from_path(target, enable_thinking=a.thinking)
+
+        class _Tok:                                        # decode / encode as the session engine's align_prompt wants them
+            def decode(self, ids):
+                return formatter.decode(ids)
+
+            def encode(self, text):
+                t = formatter.tok
+                return list(t.encode(text)) if not hasattr(t, "apply_chat_template") else list(t.encode(text, add_special_tokens=False))
+
+        se.tokenizer = _Tok()
         engine = LeaderEngine(se, Commands(cpu_group)) if world > 1 else se
-        return ServerContext(engine, ChatFormatter.from_path(target, enable_thinking=a.thinking))
+        return ServerContext(engine, formatter)
 
     app = build_app(factory, defaults, queue_depth=a.queue_depth, cors_origin=a.cors_origin, cors_credentials=a.cors_credentials, dump_tokens=a.dump_tokens)
     run_app(app, a.host, a.port, a.log_level)

@@ -167,8 +167,9 @@ class Session:
 
 class SessionEngine:
     def __init__(self, engine: Engine, store_gb: float = 8.0, ahead: int = 4, max_output_tokens: int = 524288,
-                 resume_policy: str = "cost", cancel_timeout_s: float = 30.0, host_store: bool = False):
+                 resume_policy: str = "cost", cancel_timeout_s: float = 30.0, host_store: bool = False, tokenizer=None):
         self.engine, self.ahead, self.resume_policy, self.cancel_timeout_s = engine, ahead, resume_policy, cancel_timeout_s
+        self.tokenizer = tokenizer                       # optional: enables incremental tokenisation in align_prompt
         spec = engine.spec
         self.config = EngineConfig(engine.round.capacity, max_output_tokens, tuple(spec.stop_token_ids), spec.think_end_token_id)
         full, rings = [], []
@@ -184,12 +185,52 @@ class SessionEngine:
         self._sampled: Dict[str, List[int]] = {}
 
     # ------------------------------------------------------------------
-    def align_prompt(self, tokens: Sequence[int], session_id: Optional[str]) -> List[int]:
-        """Re-tokenising text that the model generated may not reproduce the sampled ids.  When the
-        new prompt *decodes* like a continuation of the parked sequence, the parked (sampled) ids are
-        kept for the shared part; here ids are compared directly, so this is the identity unless a
-        formatter supplies aligned ids."""
-        return list(tokens)
+    def _entry_text(self, key: str, position: int) -> str:
+        """Decoded text of a parked sequence up to ``position`` (cached on the entry)."""
+        e = self.store.entries[key]
+        cache = e.__dict__.setdefault("_text", {})
+        if position not in cache:
+            cache[position] = self.tokenizer.decode(list(e.tokens[:position]))
+        return cache[position]
+
+    def align_prompt(self, tokens: Sequence[int], session_id: Optional[str], text: Optional[str] = None) -> List[int]:
+        """Incremental tokenisation: keep the ids the model actually wrote for a parked history.
+
+        ``tokens`` is the canonical encoding of the rendered prompt ``text``.  Re-encoding text that the model
+        generated need not reproduce the sampled ids (the sampler may have split a word differently from the
+        encoder); the token-level prefix match then stops early and the parked KV is wasted.  When no parked
+        sequence matches by ids but the decoded text of one (at its park position or at one of its ring
+        checkpoints, longest first, the session's own key first on ties) is a proper prefix of ``text``, the
+        result is the parked ids up to that position followed by the encoding of the remaining text alone.
+        Needs ``self.tokenizer`` (``decode(ids) -> str``, ``encode(str) -> ids``); without it, without ``text`` or
+        without a match the canonical ids are returned unchanged.
+        Parity: naivert/backends/naive_n0p5_session_engine.py:411-454."""
+        tokens = [int(t) for t in tokens]
+        if self.tokenizer is None or text is None or not self.store.entries:
+            return tokens
+        if select_resume(self.store.entries, tokens, session_id) is not None:
+            return tokens
+        keys = list(self.store.entries)
+        own = [k for k in keys if session_id is not None and (k == session_id or k.split("#")[0] == session_id)]
+        keys = own + [k for k in keys if k not in own]
+        points = []
+        for order, k in enumerate(keys):
+            e = self.store.entries[k]
+            for pos in {e.position, *(c.position for c in e.checkpoints)}:
+                if 0 < pos <= len(e.tokens):
+                    points.append((-pos, order, k, pos))
+        for _, _, k, pos in sorted(points):
+            parked = self._entry_text(k, pos)
+            if not parked or len(parked) >= len(text) or not text.startswith(parked):
+                continue
+            enc = self.tokenizer.encode(text[len(parked):])
+            suffix = [int(t) for t in (enc if not hasattr(enc, "input_ids") else enc.input_ids)]
+            aligned = list(self.store.entries[k].tokens[:pos]) + suffix
+            vocab = self.engine.spec.vocab
+            if not suffix or any(not 0 <= t < vocab for t in aligned):
+                return tokens
+            return aligned
+        return tokens
 
     def open_session(self, tokens: Sequence[int], max_decode: int, session_id: Optional[str],
                      sampling: Optional[SamplingParams] = None, use_graphs: bool = True) -> Session:

@@ -41,8 +41,8 @@ class LeaderEngine:
         self.inner, self.ch = engine, channel
         self.config = engine.config
 
-    def align_prompt(self, tokens: Sequence[int], session_id: Optional[str]):
-        return self.inner.align_prompt(tokens, session_id)
+    def align_prompt(self, tokens: Sequence[int], session_id: Optional[str], text: Optional[str] = None):
+        return self.inner.align_prompt(tokens, session_id, text=text)
 
     def open_session(self, tokens, max_decode, session_id, sampling: Optional[SamplingParams] = None) -> "LeaderSession":
         self.ch.send({"op": "open", "tokens": list(tokens), "max_decode": int(max_decode), "session_id": session_id,

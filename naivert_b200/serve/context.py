@@ -79,7 +79,12 @@ class ServerContext:
             self.slot.reset()
         with tl.span("Worker", "format_tokenize"):
             tokens = self.formatter.encode(p.messages, p.tools, p.thinking)
-            tokens = list(self.engine.align_prompt(tokens, p.session_id))
+            try:
+                # engines that keep sampled ids of a parked history compare decoded text, not ids
+                text = self.formatter.render(p.messages, p.tools, p.thinking)
+                tokens = list(self.engine.align_prompt(tokens, p.session_id, text=text))
+            except TypeError:
+                tokens = list(self.engine.align_prompt(tokens, p.session_id))
         ignored = list(p.ignored)
         room = cfg.capacity - 16 - len(tokens)
         if room < 1:

@@ -104,3 +104,43 @@ def test_prefill_policy_and_segment_stats():
     st = segment_stats(toks, [3, 3, 2], [1000, 4000, 8000], think_end=9, accepted=[2, 2, 1])
     assert st["think"]["tokens"] == 3 and st["answer"]["tokens"] == 5 and st["total"]["rounds"] == 2
     assert st["total"]["device_ms"] == 0.007 and st["answer"]["device_tok_s"] > 0
+
+
+def test_align_prompt_keeps_sampled_ids_of_a_parked_history():
+    """The sampler wrote "ab" as two ids; the encoder would write one.  The canonical ids of the follow-up prompt
+    therefore diverge from the parked ids inside the history, but the decoded text still extends it: the parked ids
+    are kept and only the new text is encoded."""
+    from types import SimpleNamespace
+    from naivert_b200.runtime.session_engine import SessionEngine
+
+    class Tok:                               # ids 0..25 = letters, 26 = the merged pair "ab"
+        def decode(self, ids):
+            return "".join("ab" if i == 26 else chr(97 + i) for i in ids)
+
+        def encode(self, text):
+            out, i = [], 0
+            while i < len(text):
+                if text.startswith("ab", i):
+                    out.append(26); i += 2
+                else:
+                    out.append(ord(text[i]) - 97); i += 1
+            return out
+
+    se = SessionEngine.__new__(SessionEngine)
+    full, rings, st = _store()
+    se.store, se.tokenizer = st, Tok()
+    se.engine = SimpleNamespace(spec=SimpleNamespace(vocab=27))
+    sampled = [2, 3] * 10 + [0, 1] + [4] * 10           # "cd"*10 + "a","b" (sampled split) + "e"*10
+    st.save("S", sampled, 30)                             # parks 30 ids = text "cd"*10 + "ab" + "e"*8
+    text = Tok().decode(sampled) + "xyz"
+    canonical = Tok().encode(text)
+    assert canonical[:22] != sampled[:22]                 # the encoder merges "ab"
+    assert select_resume(st.entries, canonical, "S") is None or select_resume(st.entries, canonical, "S").position < 30
+    aligned = se.align_prompt(canonical, "S", text=text)
+    assert aligned[:30] == sampled[:30] and Tok().decode(aligned) == text
+    assert select_resume(st.entries, aligned, "S").position == 30
+    # ids already match: unchanged; no tokenizer or no text: unchanged
+    assert se.align_prompt(sampled + [5], "S", text=Tok().decode(sampled + [5])) == sampled + [5]
+    assert se.align_prompt(canonical, "S") == canonical
+    se.tokenizer = None
+    assert se.align_prompt(canonical, "S", text=text) == canonical
