@@ -37,10 +37,11 @@ extern "C" {
 #define NRT_NOALLOC_E_SETUP (-12)     /* the scratch symbol could not be resolved on this device */
 
 /* Top-k expert routing of `rows` normalised token rows.
- *   xn          bf16 [16][hidden] (rows beyond `rows` are ignored)
- *   w, bias     fp32 router weight [experts][hidden], optional choice bias [experts]
+ *   xn          bf16 [16][hidden] (rows beyond `rows` are ignored); 8-byte aligned (the kernel reads 4 elements at a time)
+ *   w, bias     fp32 router weight [experts][hidden], 16-byte aligned (read as float4), optional choice bias [experts]
  *   sigmoid     1: sigmoid scores (+ bias for the choice), 0: softmax scores
- *   outputs     n_active [1], active_ids [max_slots] (ascending distinct experts), probs [max_slots][16],
+ *   outputs     n_active [1], active_ids [max_slots] (ascending distinct experts), probs [max_slots][16] - all
+ *               max_slots * 16 floats are written (zero-filled first), also when rows < 16 -,
  *               topk_ids [16][top_k], topk_p [16][top_k]
  * Returns 0, one of the codes above, or a positive cudaError_t. */
 int nrt_router_route_noalloc(const void* xn, const float* w, const float* bias, int hidden, int experts, int rows, int top_k,

@@ -96,7 +96,12 @@ class Worker:
             return
         while True:
             job = self.jobs.get()
-            if job is None or self.status == "shutting_down":
+            if job is None:
+                break
+            if self.status == "shutting_down":
+                # a real job was popped after shutdown began: its client still gets an answer
+                job.out.put(ApiError(503, "shutting_down", "server is shutting_down"))
+                job.out.put(_DONE)
                 break
             try:
                 self.complete(job)

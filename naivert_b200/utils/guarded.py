@@ -39,6 +39,10 @@ class GuardedPool:
         self._items.append((name, raw, nbytes))
         return raw[GUARD_BYTES:GUARD_BYTES + nbytes].view(dtype).reshape(*shape)
 
+    def like(self, t: torch.Tensor, name: str = "") -> torch.Tensor:
+        """A fenced, zero-filled tensor with the shape and dtype of ``t`` (contiguous)."""
+        return self.alloc(name or f"buf{len(self._items)}", tuple(t.shape), t.dtype)
+
     def verify(self) -> None:
         bad = []
         for name, raw, nbytes in self._items:

@@ -1,0 +1,93 @@
+"""Failure detection on the device without faulting it: a wait for a peer that never publishes runs out after a
+short limit, the kernel records where it gave up in the status word and returns, the context stays usable and
+the host-side check raises.  One GPU: the "peer" mailbox is a second local buffer that nothing writes."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_mailbox_wait_times_out_with_status_and_context_survives():
+    from naivert_b200.ops import kernels as K
+    from naivert_b200.ops.quant import quantize_act_pow2, quantize_fp8_block
+    K.lib()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rows, n, k = 8, 512, 256
+    w8, ws = quantize_fp8_block(torch.randn(n, k, device="cuda", generator=g) * 0.05)
+    xq, xsc = quantize_act_pow2(torch.randn(rows, k, device="cuda", generator=g).bfloat16().float())
+    x8 = torch.zeros(16, k, dtype=torch.uint8, device="cuda")
+    xs = torch.ones(16, k // 128, device="cuda")
+    x8[:rows], xs[:rows] = xq.view(torch.uint8), xsc
+    out = torch.zeros(rows, n, device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    words = K.K_MAILBOX_SLABS * 2 * n * K.K_ROW_PAIRS
+    mine = torch.zeros(words, dtype=torch.int64, device="cuda")        # nobody ever writes rank 1's lane here
+    peer = torch.zeros(words, dtype=torch.int64, device="cuda")        # stands in for rank 1's mailbox
+    a = K.GemmArgs()
+    a.n_total, a.k_total, a.rows = n, k, rows
+    a.w_scale0, a.a_scale = ws.data_ptr(), xs.data_ptr()
+    a.out_bf16, a.ld_out = out.data_ptr(), n
+    f = a.fab
+    f.mailbox[0], f.mailbox[1] = mine.data_ptr(), peer.data_ptr()
+    f.epoch, f.status, f.tp, f.rank, f.call_idx, f.features = epoch.data_ptr(), status.data_ptr(), 2, 0, 0, n
+    f.timeout_ns, f.mode, f.ag_call = 2_000_000, 0, -1                 # 2 ms
+    a.status = status.data_ptr()
+    tmA, tmB = K.weight_tmap(w8.view(torch.uint8)), K.act_tmap(x8)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    K.gemm(K.gemm_variant(True, False, K.EPI_ALLREDUCE, K.GROUP_NONE), tmA, None, tmB, a, n // 128, pdl=False)
+    ev1.record()
+    torch.cuda.synchronize()                                           # returns: the kernel gave up by itself
+    assert ev0.elapsed_time(ev1) < 500.0
+    code = int(status[0])
+    assert code != 0 and (code & 0xF00) == 0x500, hex(code)            # kSiteMailbox | missing word
+    assert int(peer.ne(0).sum()) > 0                                   # our own partial was published to the peer
+
+    from naivert_b200.parallel.fabric import Fabric
+    fab = Fabric(0, 1, n, device=torch.device("cuda"))
+    fab.status.copy_(status)
+    with pytest.raises(RuntimeError, match="gave up"):
+        fab.check()
+
+    # the context is intact: the same GEMM as a single rank gives the right numbers
+    status.zero_()
+    f.tp = 1
+    K.gemm(K.gemm_variant(True, False, K.EPI_ALLREDUCE, K.GROUP_NONE), tmA, None, tmB, a, n // 128, pdl=False)
+    torch.cuda.synchronize()
+    from naivert_b200.ops.quant import w8a8_linear_ref
+    ref = w8a8_linear_ref(xq.float() * xsc.repeat_interleave(128, dim=1), w8, ws).bfloat16().float()
+    assert int(status[0]) == 0
+    assert (out.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item()
+
+
+def test_step_outputs_stay_inside_their_buffers():
+    """Canary-fenced copies of the step's scratch and output buffers: a verify step must not touch the guard bytes
+    around any of them."""
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    from naivert_b200.models.weights import init_state_dict, prepare_weights, shard_weights
+    from naivert_b200.runtime.target import LocalFabric, TargetRuntime
+    from naivert_b200.utils.guarded import GuardedPool
+    spec = small_w8a8_spec(4)
+    w = prepare_weights(spec, init_state_dict(spec, seed=0, device="cuda"))
+    rt = TargetRuntime(spec, shard_weights(spec, w, 0, 1), LocalFabric("cuda"), rows=8, capacity=256)
+    pool = GuardedPool("cuda")
+    names = ["x", "x8", "xs", "y8", "ys", "scores", "probs", "active_ids", "topk_ids", "topk_p", "logits", "q", "o8", "os",
+             "ssq", "sel", "iq8", "ihw", "iq_scale", "feats"]
+    for nme in names:
+        old = getattr(rt, nme)
+        new = pool.like(old, nme)
+        new.copy_(old)
+        setattr(rt, nme, new)
+    # tensor maps and argument blocks hold raw pointers: rebuild them over the fenced buffers
+    from naivert_b200.ops import kernels as K
+    rt.map_x8, rt.map_y8, rt.map_o8 = K.act_tmap(rt.x8), K.act_tmap(rt.y8), K.act_tmap(rt.o8)
+    rt._build_args()
+    g = torch.Generator().manual_seed(0)
+    for i in range(40):                                  # crosses the indexer's top-k boundary
+        rt.set_inputs(torch.randint(0, spec.vocab, (8,), generator=g), i * 8)
+        rt.step()
+    torch.cuda.synchronize()
+    rt.fab.check()
+    assert torch.isfinite(rt.logits[:8]).all()
+    pool.verify()
