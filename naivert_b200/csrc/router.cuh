@@ -90,7 +90,8 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
         const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
         gm[i] = make_float4(g01.x, g01.y, g23.x, g23.y);
       }
-      w0[i] = __ldg(reinterpret_cast<const float4*>(a.w + (size_t)e0 * 4096 + k));
+      // CTAs beyond the expert list (a grid wider than experts / 2) read nothing
+      w0[i] = (e0 < a.experts) ? __ldg(reinterpret_cast<const float4*>(a.w + (size_t)e0 * 4096 + k)) : make_float4(0, 0, 0, 0);
       w1[i] = (e0 + 1 < a.experts) ? __ldg(reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * 4096 + k)) : make_float4(0, 0, 0, 0);
     }
   }
@@ -191,7 +192,7 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
   compute_rs();
 #pragma unroll 4
   for (int k = tid * 4; k < a.hidden; k += 1024) {
-    float4 w0 = *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k);
+    float4 w0 = (e0 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k) : make_float4(0, 0, 0, 0);
     float4 w1 = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * a.hidden + k)
                                      : make_float4(0, 0, 0, 0);
 #pragma unroll

@@ -101,20 +101,20 @@ __device__ __forceinline__ bool last_block(unsigned int* ticket) {
   return s_last;
 }
 
+// State written by another CTA inside one launch (persistent form) must not come from a stale L1 line.
+template <typename T>
+__device__ __forceinline__ T ldg2(const T* p) { return __ldcg(p); }
+
 // ---------------------------------------------------------------- pass A: row maxima
-__global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a) {
+__device__ __forceinline__ void work_max(const SamplerArgs& a, int bx, int d) {
   __shared__ unsigned int smax;
-  __shared__ uint64_t xv[16];
-  griddep_wait();
-  griddep_launch();
-  const int d = blockIdx.y;
   if (threadIdx.x == 0) smax = 0u;
   __syncthreads();
   if (row_active(a, d)) {
     float inv_t;
     const float* z = row_logits(a, d, inv_t);
     unsigned int best = 0u;
-    const int t0 = blockIdx.x * kTile;
+    const int t0 = bx * kTile;
     for (int i = threadIdx.x; i < kTile; i += kThreads) {
       const int t = t0 + i;
       if (t < a.vlocal) {
@@ -126,7 +126,8 @@ __global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a)
     __syncthreads();
     if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(&a.st->hist[d]), smax);   // hist[] doubles as scratch
   }
-  if (!last_block(&a.st->ticket[0])) return;
+}
+__device__ __forceinline__ void post_max(const SamplerArgs& a, uint64_t* xv) {
   if (threadIdx.x < 16) {
     const unsigned int v = threadIdx.x < kDist ? *reinterpret_cast<volatile unsigned int*>(&a.st->hist[threadIdx.x]) : 0u;
     xv[threadIdx.x] = v;
@@ -139,22 +140,26 @@ __global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a)
     a.st->total[threadIdx.x] = 0ull;
   }
 }
-
-// ---------------------------------------------------------------- pass B: integer codes + totals
-__global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a) {
-  __shared__ unsigned long long ssum;
+__global__ void __launch_bounds__(kThreads) samp_max_kernel(const SamplerArgs a) {
   __shared__ uint64_t xv[16];
   griddep_wait();
   griddep_launch();
-  const int d = blockIdx.y;
+  work_max(a, blockIdx.x, blockIdx.y);
+  if (!last_block(&a.st->ticket[0])) return;
+  post_max(a, xv);
+}
+
+// ---------------------------------------------------------------- pass B: integer codes + totals
+__device__ __forceinline__ void work_exp(const SamplerArgs& a, int bx, int d) {
+  __shared__ unsigned long long ssum;
   if (threadIdx.x == 0) ssum = 0ull;
   __syncthreads();
   if (row_active(a, d)) {
     float inv_t;
     const float* z = row_logits(a, d, inv_t);
-    const float m = a.st->rowmax[d];
+    const float m = ldg2(&a.st->rowmax[d]);
     unsigned long long acc = 0ull;
-    const int t0 = blockIdx.x * kTile;
+    const int t0 = bx * kTile;
     for (int i = threadIdx.x; i < kTile; i += kThreads) {
       const int t = t0 + i;
       if (t < a.vlocal) {
@@ -168,7 +173,8 @@ __global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a)
     __syncthreads();
     if (threadIdx.x == 0) atomicAdd(&a.st->total[d], ssum);
   }
-  if (!last_block(&a.st->ticket[1])) return;
+}
+__device__ __forceinline__ void post_exp(const SamplerArgs& a, uint64_t* xv) {
   if (threadIdx.x < 16) xv[threadIdx.x] = *reinterpret_cast<volatile unsigned long long*>(&a.st->total[threadIdx.x]);
   __syncthreads();
   xchg_reduce_u64<kXSum>(xv, 16, a.x, 1);
@@ -179,22 +185,26 @@ __global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a)
   }
   for (int i = threadIdx.x; i < kDist * 256; i += kThreads) a.st->hist[i] = 0ull;
 }
-
-// ---------------------------------------------------------------- passes C0..C3: nucleus radix select
-__global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a, int pass) {
-  __shared__ unsigned long long sh[256];
-  __shared__ uint64_t xv[kDist * 256];
+__global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a) {
+  __shared__ uint64_t xv[16];
   griddep_wait();
   griddep_launch();
-  const int d = blockIdx.y;
+  work_exp(a, blockIdx.x, blockIdx.y);
+  if (!last_block(&a.st->ticket[1])) return;
+  post_exp(a, xv);
+}
+
+// ---------------------------------------------------------------- passes C0..C3: nucleus radix select
+__device__ __forceinline__ void work_hist(const SamplerArgs& a, int bx, int d, int pass) {
+  __shared__ unsigned long long sh[256];
   const int shift = 24 - 8 * pass;
   const unsigned int mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
   for (int i = threadIdx.x; i < 256; i += kThreads) sh[i] = 0ull;
   __syncthreads();
   if (row_active(a, d)) {
-    const unsigned int prefix = a.st->prefix[d];
+    const unsigned int prefix = ldg2(&a.st->prefix[d]);
     const unsigned int* e = a.e + (size_t)d * a.vlocal;
-    const int t0 = blockIdx.x * kTile;
+    const int t0 = bx * kTile;
     // Nearly all codes of a pass fall into one bin (tiny probabilities): keep a run-length
     // accumulator per thread and touch shared memory only when the bin changes.
     unsigned int cur = 0xFFFFFFFFu;
@@ -217,7 +227,9 @@ __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a
     for (int i = threadIdx.x; i < 256; i += kThreads)
       if (sh[i]) atomicAdd(&a.st->hist[d * 256 + i], sh[i]);
   }
-  if (!last_block(&a.st->ticket[2])) return;
+}
+__device__ __forceinline__ void post_hist(const SamplerArgs& a, uint64_t* xv, int pass) {
+  const int shift = 24 - 8 * pass;
   for (int i = threadIdx.x; i < kDist * 256; i += kThreads)
     xv[i] = *reinterpret_cast<volatile unsigned long long*>(&a.st->hist[i]);
   __syncthreads();
@@ -225,8 +237,8 @@ __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a
   if (threadIdx.x < kDist && row_active(a, threadIdx.x)) {
     const int r = threadIdx.x;
     const double top_p = (double)a.params[1];
-    const unsigned long long target = (unsigned long long)ceil(top_p * (double)a.st->total[r]);
-    unsigned long long above = a.st->above[r], cum = 0ull;
+    const unsigned long long target = (unsigned long long)ceil(top_p * (double)ldg2(&a.st->total[r]));
+    unsigned long long above = ldg2(&a.st->above[r]), cum = 0ull;
     int b = 255;
     for (; b > 0; --b) {
       cum += xv[r * 256 + b];
@@ -235,29 +247,34 @@ __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a
     if (b == 0) cum += xv[r * 256];
     const unsigned long long in_bin = xv[r * 256 + b];
     a.st->above[r] = above + cum - in_bin;
-    a.st->prefix[r] |= (unsigned int)b << shift;
+    a.st->prefix[r] = ldg2(&a.st->prefix[r]) | ((unsigned int)b << shift);
     if (pass == 3) a.st->kept[r] = above + cum;      // Z: everything with e >= tau
   }
   __syncthreads();
   for (int i = threadIdx.x; i < kDist * 256; i += kThreads) a.st->hist[i] = 0ull;
 }
+__global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a, int pass) {
+  __shared__ uint64_t xv[kDist * 256];
+  griddep_wait();
+  griddep_launch();
+  work_hist(a, blockIdx.x, blockIdx.y, pass);
+  if (!last_block(&a.st->ticket[2])) return;
+  post_hist(a, xv, pass);
+}
 
 // ---------------------------------------------------------------- verify: accept prefix
 // One CTA.  Gathers e_p(d_j), e_q(d_j) from the owning ranks, decides acceptance.
-__global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
-  __shared__ uint64_t xv[16];
-  griddep_wait();
-  griddep_launch();
+__device__ __forceinline__ void do_accept(const SamplerArgs& a, uint64_t* xv) {
   const int j = threadIdx.x;                  // proposal j+1 is judged by target row j / draft row j
   if (j < 16) xv[j] = 0ull;
   __syncthreads();
   if (j < a.n_rows_q) {
     const int tok = a.block_ids[j + 1] - a.vbase;
     if (tok >= 0 && tok < a.vlocal) {
-      unsigned int ep = a.e[(size_t)j * a.vlocal + tok];
-      unsigned int eq = a.e[(size_t)(kRowsP + j) * a.vlocal + tok];
-      if (ep < a.st->prefix[j]) ep = 0u;
-      if (eq < a.st->prefix[kRowsP + j]) eq = 0u;
+      unsigned int ep = ldg2(&a.e[(size_t)j * a.vlocal + tok]);
+      unsigned int eq = ldg2(&a.e[(size_t)(kRowsP + j) * a.vlocal + tok]);
+      if (ep < ldg2(&a.st->prefix[j])) ep = 0u;
+      if (eq < ldg2(&a.st->prefix[kRowsP + j])) eq = 0u;
       xv[j] = ((uint64_t)ep << 32) | eq;
     }
   }
@@ -275,39 +292,44 @@ __global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
         acc = philox_uniform(seed, kDomForced, round, (uint32_t)m) < forced;
       } else {
         const double u = (double)philox_uniform(seed, kDomAccept, round, (uint32_t)m);
-        acc = u * eq * (double)a.st->kept[m] < ep * (double)a.st->kept[kRowsP + m];
+        acc = u * eq * (double)ldg2(&a.st->kept[m]) < ep * (double)ldg2(&a.st->kept[kRowsP + m]);
       }
       a.st->accept_flags[m] = acc ? 1 : 0;
       if (!acc) break;
     }
     a.st->accepted = m;
   }
+  __syncthreads();
+}
+__global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
+  __shared__ uint64_t xv[16];
+  griddep_wait();
+  griddep_launch();
+  do_accept(a, xv);
 }
 
 // residual / bonus mass of token t of the row being resampled (40-bit fixed point of a probability)
 __device__ __forceinline__ unsigned long long resample_mass(const SamplerArgs& a, int m, int t, bool from_p) {
-  unsigned int ep = a.e[(size_t)m * a.vlocal + t];
-  if (ep < a.st->prefix[m]) ep = 0u;
+  unsigned int ep = ldg2(&a.e[(size_t)m * a.vlocal + t]);
+  if (ep < ldg2(&a.st->prefix[m])) ep = 0u;
   if (from_p || m >= a.n_rows_q) return (unsigned long long)ep;    // bonus / anchor row / empty residual: sample from p'
-  unsigned int eq = a.e[(size_t)(kRowsP + m) * a.vlocal + t];
-  if (eq < a.st->prefix[kRowsP + m]) eq = 0u;
-  const double r = (double)ep / (double)a.st->kept[m] - (double)eq / (double)a.st->kept[kRowsP + m];
+  unsigned int eq = ldg2(&a.e[(size_t)(kRowsP + m) * a.vlocal + t]);
+  if (eq < ldg2(&a.st->prefix[kRowsP + m])) eq = 0u;
+  const double r = (double)ep / (double)ldg2(&a.st->kept[m]) - (double)eq / (double)ldg2(&a.st->kept[kRowsP + m]);
   return r > 0.0 ? (unsigned long long)(r * 1099511627776.0) : 0ull;
 }
 
 // ---------------------------------------------------------------- resample: per-tile masses
-__global__ void __launch_bounds__(kThreads) samp_tile_mass_kernel(const SamplerArgs a) {
+__device__ __forceinline__ void work_tile_mass(const SamplerArgs& a, int bx) {
   __shared__ unsigned long long ssum;
-  griddep_wait();
-  griddep_launch();
   if (threadIdx.x == 0) ssum = 0ull;
   __syncthreads();
-  const int m = a.st->accepted;
+  const int m = ldg2(&a.st->accepted);
   __shared__ unsigned long long ssum_p;
   if (threadIdx.x == 0) ssum_p = 0ull;
   __syncthreads();
   unsigned long long acc = 0ull, acc_p = 0ull;
-  const int t0 = blockIdx.x * kTile;
+  const int t0 = bx * kTile;
   for (int i = threadIdx.x; i < kTile; i += kThreads) {
     const int t = t0 + i;
     if (t < a.vlocal) { acc += resample_mass(a, m, t, false); acc_p += resample_mass(a, m, t, true); }
@@ -315,22 +337,24 @@ __global__ void __launch_bounds__(kThreads) samp_tile_mass_kernel(const SamplerA
   atomicAdd(&ssum, acc);
   atomicAdd(&ssum_p, acc_p);
   __syncthreads();
-  if (threadIdx.x == 0) { a.st->tile_mass[blockIdx.x] = ssum; a.st->tile_mass[128 + blockIdx.x] = ssum_p; }
+  if (threadIdx.x == 0) { a.st->tile_mass[bx] = ssum; a.st->tile_mass[128 + bx] = ssum_p; }
+}
+__global__ void __launch_bounds__(kThreads) samp_tile_mass_kernel(const SamplerArgs a) {
+  griddep_wait();
+  griddep_launch();
+  work_tile_mass(a, blockIdx.x);
 }
 
 // ---------------------------------------------------------------- resample: inverse CDF in vocabulary order
-__global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a, int tiles, int domain) {
-  __shared__ uint64_t xv[16];
+__device__ __forceinline__ void do_draw(const SamplerArgs& a, int tiles, int domain, uint64_t* xv) {
   __shared__ unsigned long long part[kThreads];
   __shared__ int s_tok;
-  griddep_wait();
-  griddep_launch();
-  const int m = a.st->accepted;
+  const int m = ldg2(&a.st->accepted);
   if (threadIdx.x < 16) xv[threadIdx.x] = 0ull;
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned long long tot = 0ull, tot_p = 0ull;
-    for (int i = 0; i < tiles; ++i) { tot += a.st->tile_mass[i]; tot_p += a.st->tile_mass[128 + i]; }
+    for (int i = 0; i < tiles; ++i) { tot += ldg2(&a.st->tile_mass[i]); tot_p += ldg2(&a.st->tile_mass[128 + i]); }
     xv[a.x.rank] = tot;
     xv[8 + a.x.rank] = tot_p;
     s_tok = -1;
@@ -351,7 +375,7 @@ __global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a
     unsigned long long local = target - before;       // uniform across the CTA
     int tile = 0;
     for (; tile < tiles - 1; ++tile) {
-      const unsigned long long tm = a.st->tile_mass[mo + tile];
+      const unsigned long long tm = ldg2(&a.st->tile_mass[mo + tile]);
       if (local < tm) break;
       local -= tm;
     }
@@ -391,6 +415,87 @@ __global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a
     if (tok < 0) tok = 0;                          // unreachable while the kept set is non-empty
     a.st->extra_token = tok;
   }
+}
+__global__ void __launch_bounds__(kThreads) samp_draw_kernel(const SamplerArgs a, int tiles, int domain) {
+  __shared__ uint64_t xv[16];
+  griddep_wait();
+  griddep_launch();
+  do_draw(a, tiles, domain, xv);
+}
+
+// ---------------------------------------------------------------- the whole sampler in one launch
+// Same phases, same arithmetic, same exchanges as the chain of nine kernels; the hand-over between phases happens
+// inside the grid.  After its share of a phase every CTA adds itself to a monotonic arrival counter; the CTA that
+// completes the count runs the phase's cross-rank exchange and state update and publishes the phase generation,
+// the others wait for it (bounded: a wait that gives up records a status word and the CTA leaves).  grid =
+// (vocabulary tiles, 15 distributions), all resident at once (checked at launch).
+// Reference counterpart: the persistent cooperative sampler, naivert/body/dspark_sampling/persistent.cuh:15-42,1208.
+struct PhaseSync {
+  unsigned long long* arrive;
+  unsigned int* gen;
+  uint32_t* status;
+  unsigned int n_ctas;
+};
+// true for the CTA that completed this phase's count; my_gen = generation the others wait for
+__device__ __forceinline__ bool phase_arrive(const PhaseSync& ps, unsigned int& my_gen) {
+  __shared__ unsigned int s_gen;
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned long long old = atomicAdd(ps.arrive, 1ull);
+    s_gen = (unsigned int)(old / ps.n_ctas + 1ull);
+    s_last = (old + 1ull) % ps.n_ctas == 0ull;
+  }
+  __syncthreads();
+  my_gen = s_gen;
+  __threadfence();
+  return s_last != 0;
+}
+__device__ __forceinline__ void phase_release(const PhaseSync& ps, unsigned int my_gen) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ps.gen), "r"(my_gen) : "memory");
+}
+__device__ __forceinline__ bool phase_wait(const PhaseSync& ps, unsigned int my_gen, int site) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    const uint64_t deadline = globaltimer() + kWaitLimitNs;
+    for (uint32_t i = 0;; ++i) {
+      if ((int)(ld_acquire_gpu(ps.gen) - my_gen) >= 0) break;        // generations only grow
+      if ((i & 255u) == 255u) {
+        if (*reinterpret_cast<volatile uint32_t*>(ps.status) != 0u) { s_ok = 0; break; }
+        if (globaltimer() > deadline) { report(ps.status, kSiteGrid | 0x40u | (uint32_t)site); s_ok = 0; break; }
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__global__ void __launch_bounds__(kThreads, 2) samp_persistent_kernel(const SamplerArgs a, int tiles, int domain,
+                                                                   unsigned long long* arrive, unsigned int* gen) {
+  __shared__ uint64_t xv[kDist * 256];
+  griddep_wait();
+  griddep_launch();
+  const int bx = blockIdx.x, d = blockIdx.y;
+  PhaseSync ps{arrive, gen, a.x.status, gridDim.x * gridDim.y};
+  unsigned int g;
+  work_max(a, bx, d);
+  if (phase_arrive(ps, g)) { post_max(a, xv); phase_release(ps, g); } else if (!phase_wait(ps, g, 0)) return;
+  work_exp(a, bx, d);
+  if (phase_arrive(ps, g)) { post_exp(a, xv); phase_release(ps, g); } else if (!phase_wait(ps, g, 1)) return;
+  for (int pass = 0; pass < 4; ++pass) {
+    work_hist(a, bx, d, pass);
+    if (phase_arrive(ps, g)) {
+      post_hist(a, xv, pass);
+      if (pass == 3) { __syncthreads(); do_accept(a, xv); }
+      phase_release(ps, g);
+    } else if (!phase_wait(ps, g, 2 + pass)) return;
+  }
+  if (d == 0) work_tile_mass(a, bx);
+  if (phase_arrive(ps, g)) do_draw(a, tiles, domain, xv);
 }
 
 // ---------------------------------------------------------------- tail: commit + next-round geometry
@@ -530,6 +635,27 @@ extern "C" int nrt_sampler_run(const void* args, int domain, void* stream, int p
   if ((rc = launch_pdl(samp_accept_kernel, dim3(1), dim3(64), 0, S(stream), p, a))) return rc;
   if ((rc = launch_pdl(samp_tile_mass_kernel, dim3(tiles), dim3(kThreads), 0, S(stream), p, a))) return rc;
   return launch_pdl(samp_draw_kernel, dim3(1), dim3(kThreads), 0, S(stream), p, a, tiles, domain);
+}
+
+// The same sampler in one launch.  `sync`: two 64-bit words (arrival counter, phase generation), zeroed once.
+// Returns -9 when the grid cannot be resident at once (use nrt_sampler_run).
+extern "C" int nrt_sampler_persistent(const void* args, int domain, void* sync, void* stream, int pdl) {
+  SamplerArgs a;
+  memcpy(&a, args, sizeof(a));
+  const int tiles = (a.vlocal + kTile - 1) / kTile;
+  if (tiles > 128 || !sync) return -3;
+  static int resident = -1;
+  if (resident < 0) {
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, samp_persistent_kernel, kThreads, 0) != cudaSuccess) return -3;
+    resident = per_sm * sms;
+  }
+  if (tiles * kDist > resident) return -9;
+  unsigned long long* w = reinterpret_cast<unsigned long long*>(sync);
+  return launch_pdl(samp_persistent_kernel, dim3(tiles, kDist), dim3(kThreads), 0, S(stream), pdl != 0, a, tiles, domain, w,
+                    reinterpret_cast<unsigned int*>(w + 1));
 }
 
 extern "C" int nrt_tail_commit(const void* args, void* stream, int pdl) {

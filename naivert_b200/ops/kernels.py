@@ -380,6 +380,17 @@ def sampler_run(args: SamplerArgs, domain: int = 1, pdl=True):
     check(aux_lib().nrt_sampler_run(C.byref(args), domain, VP(_stream()), int(pdl)), "sampler")
 
 
+def sampler_persistent(args: SamplerArgs, sync, domain: int = 1, pdl=True) -> int:
+    """The whole sampler in one launch; -3 / -9 are returned (not raised) when that form does not fit."""
+    code = aux_lib().nrt_sampler_persistent(C.byref(args), domain, VP(ptr(sync)), VP(_stream()), int(pdl))
+    if code in (-3, -9):
+        return code
+    LAUNCHES["count"] += 1
+    if code != 0:
+        raise RuntimeError(f"sampler failed with CUDA/driver error {code}")
+    return 0
+
+
 def tail_commit(args: TailArgs, pdl=True):
     check(aux_lib().nrt_tail_commit(C.byref(args), VP(_stream()), int(pdl)), "tail_commit")
 

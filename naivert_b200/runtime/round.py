@@ -91,6 +91,9 @@ class SpeculativeRound:
         self.counts = torch.zeros(V, dtype=torch.int16, device=dev)
         self.state = torch.zeros(K.sampler_state_bytes() // 8 + 1, dtype=torch.int64, device=dev)
         self.stop_ids = torch.tensor(list(spec.stop_token_ids) or [-1], dtype=torch.int32, device=dev)
+        import os
+        self.sampler_one_launch = target.fused and os.environ.get("NAIVERT_SAMPLER_PERSISTENT", "1") == "1"
+        self.sampler_sync = torch.zeros(2, dtype=torch.int64, device=dev)
         self.ring = HostRing()
         self.draft = DraftRuntime(spec, draft_weights, target, capacity, self.seed, self.params, self.block_ids, pdl=pdl)
         self.capacity = capacity
@@ -152,7 +155,9 @@ class SpeculativeRound:
         self.draft.block()
         self.draft.propose()
         self.t.step()
-        K.sampler_run(self.args_sampler, domain=1, pdl=self.pdl)
+        if not (self.sampler_one_launch and K.sampler_persistent(self.args_sampler, self.sampler_sync, domain=1, pdl=self.pdl) == 0):
+            self.sampler_one_launch = False
+            K.sampler_run(self.args_sampler, domain=1, pdl=self.pdl)
         K.tail_commit(self.args_tail, pdl=self.pdl)
 
     def prefill_phases(self) -> None:

@@ -70,7 +70,7 @@ def test_step_outputs_stay_inside_their_buffers():
     from naivert_b200.utils.guarded import GuardedPool
     spec = small_w8a8_spec(4)
     w = prepare_weights(spec, init_state_dict(spec, seed=0, device="cuda"))
-    rt = TargetRuntime(spec, shard_weights(spec, w, 0, 1), LocalFabric("cuda"), rows=8, capacity=256)
+    rt = TargetRuntime(spec, shard_weights(spec, w, 0, 1), LocalFabric("cuda"), rows=8, capacity=512)
     pool = GuardedPool("cuda")
     names = ["x", "x8", "xs", "y8", "ys", "scores", "probs", "active_ids", "topk_ids", "topk_p", "logits", "q", "o8", "os",
              "ssq", "sel", "iq8", "ihw", "iq_scale", "feats"]
