@@ -86,6 +86,7 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int ge
   return false;
 }
 
+template <bool ROUTE>
 __global__ void __launch_bounds__(kMoeThreads, 1)
 moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_constant__ CUtensorMap tmUp,
                  const __grid_constant__ CUtensorMap tmDown, const __grid_constant__ CUtensorMap tmX8,
@@ -119,29 +120,45 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
 
-  // ------------------------------------------------------------------ phase R: scores + packet, arrival, selection
-  router_scores(p.r, cta, kMoeCtas, sm.router);            // waits for the upstream grid inside
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    NRT_STAMP(1);
-    const unsigned long long old = atomicAdd(p.sync, 1ull);
-    const unsigned long long target = (old / kMoeCtas + 1ull) * kMoeCtas;
-    sm.gen = (uint32_t)(old / kMoeCtas + 1ull);
-    const uint64_t deadline = globaltimer() + kWaitLimitNs;
-    for (uint32_t i = 0; ld_acquire_u64(p.sync) < target; ++i) {
-      if ((i & 63u) == 63u) {
-        if (*reinterpret_cast<volatile uint32_t*>(status) != 0u) { sm.ok = 0; break; }
-        if (globaltimer() > deadline) { report(status, kSiteGrid | 1u); sm.ok = 0; break; }
+  int n_active = 0;
+  uint32_t gen = 0;
+  if (ROUTE) {
+    // ---------------------------------------------------------------- phase R: scores + packet, arrival, selection
+    router_scores(p.r, cta, kMoeCtas, sm.router, stamp);     // waits for the upstream grid inside
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      NRT_STAMP(1);
+      const unsigned long long old = atomicAdd(p.sync, 1ull);
+      const unsigned long long target = (old / kMoeCtas + 1ull) * kMoeCtas;
+      sm.gen = (uint32_t)(old / kMoeCtas + 1ull);
+      const uint64_t deadline = globaltimer() + kWaitLimitNs;
+      for (uint32_t i = 0; ld_acquire_u64(p.sync) < target; ++i) {
+        if ((i & 63u) == 63u) {
+          if (*reinterpret_cast<volatile uint32_t*>(status) != 0u) { sm.ok = 0; break; }
+          if (globaltimer() > deadline) { report(status, kSiteGrid | 1u); sm.ok = 0; break; }
+        }
       }
+      NRT_STAMP(2);
     }
-    NRT_STAMP(2);
+    __syncthreads();
+    griddep_launch();                                         // every CTA of this grid is resident by now
+    gen = sm.gen;
+    router_select(p.r, sm.router, cta == 0, sm.probs, sm.active, stamp);
+    n_active = sm.ok ? sm.router.n_active : 0;
+  } else {
+    // ---------------------------------------------------------------- routed by the preceding router kernel: its
+    // active-expert list, slot probabilities and activation packet are read from global memory.  The arrival counter
+    // only numbers this launch (the flags of a launch carry its generation); nobody waits on it.
+    griddep_wait();
+    griddep_launch();
+    if (tid == 0) sm.gen = (uint32_t)(atomicAdd(p.sync, 1ull) / kMoeCtas + 1ull);
+    n_active = min(*p.r.n_active, p.r.max_slots);
+    for (int i = tid; i < n_active; i += kMoeThreads) sm.active[i] = p.r.active_ids[i];
+    for (int i = tid; i < n_active * kTok; i += kMoeThreads) sm.probs[i] = p.r.probs[i];
+    __syncthreads();
+    gen = sm.gen;
   }
-  __syncthreads();
-  griddep_launch();                                         // every CTA of this grid is resident by now
-  const uint32_t gen = sm.gen;
-  router_select(p.r, sm.router, cta == 0, sm.probs, sm.active);
-  const int n_active = sm.ok ? sm.router.n_active : 0;
   if (tid == 0) NRT_STAMP(3);
 
   const int kbH = p.r.hidden / 128;                         // K blocks of gate/up
@@ -170,16 +187,19 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both phases)
-    if (elect_one()) {
-      asm volatile("fence.proxy.async;" ::: "memory");       // the packet was written by other CTAs' plain stores
-      int u = 0;
-      bool ok = true;
+    const bool issuer = elect_one();                          // one lane issues every copy; all lanes poll flags
+    int u = 0;
+    int ok = 1;
+    if (issuer) {
+      // the packet was written by plain stores: by other CTAs of this launch when the routing runs in here (order them
+      // before the TMA reads); by the preceding router kernel otherwise (the kernel boundary already orders them)
+      if (ROUTE) asm volatile("fence.proxy.async;" ::: "memory");
       for (int it = cta; it < gu_items && ok; it += kMoeCtas) {
         const int slot = it / kbI, tile = it - slot * kbI;
         const int z = sm.active[slot];
         for (int kb = 0; kb < kbH; ++kb, ++u) {
           const int st = u % kMoeStages;
-          if (u >= kMoeStages && !mbar_wait(&tail->empty[st], ((u / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = false; break; }
+          if (u >= kMoeStages && !mbar_wait(&tail->empty[st], ((u / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = 0; break; }
           uint8_t* sa = smem + st * kMoeStageBytes;
           mbar_expect_tx(&tail->full[st], kMoeStageBytes);
           tma_load_3d(sa, &tmGate, &tail->full[st], kb * 128, tile * kTileN, z);
@@ -187,26 +207,41 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
           tma_load_2d(sa + kMoeStageA, &tmX8, &tail->full[st], kb * 128, 0);
         }
       }
-      // down: the weight tile of a unit is requested first; its activation tile follows once the (slot, tile) flags
-      // of that expert's y are set (checked once per slot)
-      for (int s = 0; s < dn_slots && ok; ++s) {
-        const int slot = dn_lo + s;
-        const int z = sm.active[slot];
-        bool ready = false;
-        for (int kb = 0; kb < kbI; ++kb, ++u) {
-          const int st = u % kMoeStages;
-          if (u >= kMoeStages && !mbar_wait(&tail->empty[st], ((u / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = false; break; }
-          uint8_t* sa = smem + st * kMoeStageBytes;
+    }
+    // down: the weight tiles of the first ring-full of units are requested before anything waits for their
+    // activations; then every lane polls a share of the (slot, tile) flags of this CTA's experts (one round of
+    // loads for all of them), and the activation tiles follow
+    const int u0 = gu_units;                                  // == u on the issuing lane unless a wait failed
+    const int npre = min(dn_units, kMoeStages);
+    if (issuer && ok) {
+      for (int i = 0; i < npre; ++i) {
+        const int uu = u0 + i, st = uu % kMoeStages;
+        if (uu >= kMoeStages && !mbar_wait(&tail->empty[st], ((uu / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = 0; break; }
+        const int slot = dn_lo + i / kbI, kb = i % kbI;
+        mbar_expect_tx(&tail->full[st], kATileBytes + kBTileBytes);
+        tma_load_3d(smem + st * kMoeStageBytes, &tmDown, &tail->full[st], kb * 128, dn_tile * kTileN, sm.active[slot]);
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, __ffs(__ballot_sync(0xffffffffu, issuer)) - 1);
+    if (ok) {
+      for (int i = lane; i < dn_slots * kbI; i += 32) {
+        const int slot = dn_lo + i / kbI, t = i % kbI;
+        if (!wait_flag(p.slot_flags + slot * kGuTilesMax + t, gen, status, kSiteGrid | 2u)) ok = 0;
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (issuer && ok) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      for (int i = 0; i < dn_units; ++i) {
+        const int uu = u0 + i, st = uu % kMoeStages;
+        const int slot = dn_lo + i / kbI, kb = i % kbI;
+        uint8_t* sa = smem + st * kMoeStageBytes;
+        if (i >= npre) {
+          if (uu >= kMoeStages && !mbar_wait(&tail->empty[st], ((uu / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) break;
           mbar_expect_tx(&tail->full[st], kATileBytes + kBTileBytes);
-          tma_load_3d(sa, &tmDown, &tail->full[st], kb * 128, dn_tile * kTileN, z);
-          if (!ready) {
-            for (int t = 0; t < kbI && ok; ++t) ok = wait_flag(p.slot_flags + slot * kGuTilesMax + t, gen, status, kSiteGrid | 2u);
-            if (!ok) break;
-            asm volatile("fence.proxy.async;" ::: "memory");
-            ready = true;
-          }
-          tma_load_2d(sa + kMoeStageA, &tmY8, &tail->full[st], kb * 128, slot * kTok);
+          tma_load_3d(sa, &tmDown, &tail->full[st], kb * 128, dn_tile * kTileN, sm.active[slot]);
         }
+        tma_load_2d(sa + kMoeStageA, &tmY8, &tail->full[st], kb * 128, slot * kTok);
       }
     }
   } else if (warp == 1) {
@@ -271,7 +306,9 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
         const int buf = ug % kGuBufs;
         float sc[kTok];
 #pragma unroll
-        for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? __ldcg(p.r.xs + r * kbH + kb) : 0.f;
+        // written by other CTAs before the arrival counter and never read here before: a plain (L1-cached) load is
+        // coherent, and the 32 scales of a row share one line
+        for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? p.r.xs[r * kbH + kb] : 0.f;
         const float w0 = __ldg(ws0 + kb), w1 = __ldg(ws1 + kb);
         if (!mbar_wait(&sm.gu_full[buf], (ug / kGuBufs) & 1, status, kSiteAccFull | buf)) { ok = false; break; }
         tc_fence_after();
@@ -322,6 +359,10 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     for (int r = 0; r < kTok; ++r) mix0[r] = 0.f;
     const int n = dn_tile * kTileN + row;
     int ud = 0;
+    // The y scales of a slot are final once the producer has seen the slot flags, i.e. once this CTA's first down
+    // accumulator has completed (all flags are polled before the first activation tile is requested); from then on
+    // they are fetched ahead of the accumulator wait.
+    bool flags_seen = false;
     for (int s = 0; s < dn_slots && ok; ++s) {
       const int slot = dn_lo + s;
       const int z = sm.active[slot];
@@ -332,10 +373,17 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
       for (int kb = 0; kb < kbI; ++kb, ++ud) {
         const int buf = ud % kDnBufs;
         const float w0 = __ldg(ws + kb);
-        if (!mbar_wait(&tail->acc_full[buf], (ud / kDnBufs) & 1, status, kSiteAccFull | 0x10 | buf)) { ok = false; break; }
         float sc[kTok];
+        if (flags_seen) {
 #pragma unroll
-        for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? __ldcg(p.ys + ((size_t)slot * kTok + r) * kbI + kb) : 0.f;
+          for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? p.ys[((size_t)slot * kTok + r) * kbI + kb] : 0.f;
+        }
+        if (!mbar_wait(&tail->acc_full[buf], (ud / kDnBufs) & 1, status, kSiteAccFull | 0x10 | buf)) { ok = false; break; }
+        if (!flags_seen) {
+#pragma unroll
+          for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? p.ys[((size_t)slot * kTok + r) * kbI + kb] : 0.f;
+          flags_seen = true;
+        }
         tc_fence_after();
         float v[kTok];
         tmem_ld16(lane_addr + kDnBase + buf * kDnCols, v);
@@ -392,7 +440,9 @@ extern "C" int nrt_moe_layer(const void* tmGate, const void* tmUp, const void* t
   MoeArgs a;
   memcpy(&a, args, sizeof(a));
   const RouterArgs& r = a.r;
-  if (!r.x || !r.ssq || !r.gamma || !r.x8 || !r.xs || !r.scores || r.hidden % 128 || a.inter % 128) return -3;
+  if (r.hidden % 128 || a.inter % 128 || !r.x8 || !r.xs) return -3;
+  if (r.w != nullptr && (!r.x || !r.ssq || !r.gamma || !r.scores)) return -3;                 // routing inside the kernel
+  if (r.w == nullptr && (!r.n_active || !r.active_ids || !r.probs)) return -3;               // routed by nrt_router
   if (r.experts > 2 * kMoeCtas || r.experts > 256 || r.rows < 1 || r.rows > kArRows || r.top_k > 32) return -3;
   if (r.max_slots > kSlotsMax || a.inter / 128 > kGuTilesMax || (r.hidden / 128) * kRanges > kMoeCtas) return -3;
   if (r.rows * (r.hidden / 128) > 16 * kMoeCtas) return -3;
@@ -400,14 +450,21 @@ extern "C" int nrt_moe_layer(const void* tmGate, const void* tmUp, const void* t
   constexpr int smem = kMoeStages * kMoeStageBytes + 1024 + (int)sizeof(MoeSmem);
   static int resident = -1;
   if (resident < 0) {
-    cudaError_t e = cudaFuncSetAttribute(moe_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    int per_sm = 0, dev = 0, sms = 0;
+    int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_layer_kernel, kMoeThreads, smem);
-    if (e != cudaSuccess) return (int)e;
-    resident = per_sm * sms;
+    int worst = 1 << 30;
+    for (int route = 0; route < 2; ++route) {
+      const void* k = route ? (const void*)moe_layer_kernel<true> : (const void*)moe_layer_kernel<false>;
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return (int)e;
+      int per_sm = 0;
+      e = route ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_layer_kernel<true>, kMoeThreads, smem)
+                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_layer_kernel<false>, kMoeThreads, smem);
+      if (e != cudaSuccess) return (int)e;
+      worst = per_sm * sms < worst ? per_sm * sms : worst;
+    }
+    resident = worst;
   }
   if (resident < kMoeCtas) return -9;
   CUtensorMap g, u, d, x, y;
@@ -416,6 +473,9 @@ extern "C" int nrt_moe_layer(const void* tmGate, const void* tmUp, const void* t
   memcpy(&d, tmDown, sizeof(d));
   memcpy(&x, tmX8, sizeof(x));
   memcpy(&y, tmY8, sizeof(y));
-  return launch_pdl(moe_layer_kernel, dim3(kMoeCtas), dim3(kMoeThreads), smem, reinterpret_cast<cudaStream_t>(stream), pdl != 0,
-                    g, u, d, x, y, a);
+  if (r.w != nullptr)
+    return launch_pdl(moe_layer_kernel<true>, dim3(kMoeCtas), dim3(kMoeThreads), smem, reinterpret_cast<cudaStream_t>(stream),
+                      pdl != 0, g, u, d, x, y, a);
+  return launch_pdl(moe_layer_kernel<false>, dim3(kMoeCtas), dim3(kMoeThreads), smem, reinterpret_cast<cudaStream_t>(stream),
+                    pdl != 0, g, u, d, x, y, a);
 }

@@ -68,7 +68,7 @@ __device__ __forceinline__ uint32_t router_order_key(float f) {
 }
 
 // 256 threads.  Waits for the upstream grid itself (after the loads that do not depend on it).
-__device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int n_ctas, RouterSmem& sm) {
+__device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int n_ctas, RouterSmem& sm, unsigned long long* stamp = nullptr) {
   constexpr int kMaxRows = kRouterRows;
   float (*part)[2][kMaxRows] = sm.part;
   float* rs_s = sm.rs;
@@ -97,6 +97,7 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
   }
   griddep_wait();
   griddep_launch();
+  if (stamp && threadIdx.x == 0) stamp[12] = globaltimer();
   const __nv_bfloat16* xsrc = inline_norm ? a.x : a.xn;
   const int xld = a.hidden;
   // e4m3 packet of the normalised rows: pair (row, 128-channel block) number blockIdx.x + gridDim.x * g goes to the
@@ -155,6 +156,7 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
       }
     }
     have_rs = true;
+    if (stamp && threadIdx.x == 0) stamp[13] = globaltimer();
   };
   if (fast) {
     // Every load of the thread is issued before the first FMA (one round trip instead of one per K step): eight rows
@@ -215,6 +217,7 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
     }
   }
   }
+  if (stamp && threadIdx.x == 0) stamp[14] = globaltimer();
 #pragma unroll
   for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -236,7 +239,8 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
 // 256 threads; every score must be visible (the caller has synchronised the CTAs).  Results: sm.used / sm.slot_of /
 // sm.n_active, and - when `publish` - the global outputs of RouterArgs.  `probs_s` / `active_s` (shared memory,
 // may be null) receive the slot table for a consumer in the same CTA.
-__device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& sm, bool publish, float* probs_s, int* active_s) {
+__device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& sm, bool publish, float* probs_s, int* active_s,
+                                              unsigned long long* stamp = nullptr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   unsigned int* used = sm.used;
   int* slot_of = sm.slot_of;
@@ -316,6 +320,7 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
       atomicOr(&used[my_id >> 5], 1u << (my_id & 31));
     }
   }
+  if (stamp && threadIdx.x == 0) stamp[10] = globaltimer();
   __syncthreads();
   if (a.probs == nullptr && probs_s == nullptr) return;   // prefill: only the per-token choices are needed
   // ascending list of distinct experts -> slots
@@ -336,6 +341,7 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
       if (publish && a.n_active) *a.n_active = sm.n_active;
     }
   }
+  if (stamp && threadIdx.x == 0) stamp[15] = globaltimer();
   for (int i = tid; i < a.max_slots * kTok; i += 256) {
     if (publish && a.probs) a.probs[i] = 0.f;
     if (probs_s) probs_s[i] = 0.f;

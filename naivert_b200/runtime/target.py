@@ -170,6 +170,9 @@ class TargetRuntime:
         # fused MoE block (router + gate/up + down + all-reduce in one launch): hand-off buffers shared by all layers
         import os as _os
         self.moe_fused = self.fused and _os.environ.get("NAIVERT_MOE_FUSED", "1") == "1" and rows <= 8
+        # the router as its own launch in front of the fused gate/up + down kernel (measured faster than routing inside
+        # it: the selection runs once instead of in every CTA, and no grid-wide arrival is needed)
+        self.moe_split_router = _os.environ.get("NAIVERT_MOE_ROUTER_INSIDE", "0") != "1"
         flag_words, part_floats = K.moe_scratch_sizes(H)
         self.moe_sync = torch.zeros(2, dtype=torch.int64, device=dev)
         self.moe_slot_flags = torch.zeros(flag_words, dtype=i32, device=dev)
@@ -334,6 +337,8 @@ class TargetRuntime:
                 if self.moe_fused:
                     m = K.MoeArgs()
                     m.r = d["args_router"]
+                    if self.moe_split_router:          # the router kernel runs first; the fused kernel reads its lists
+                        m.r.w = None
                     m.inter = d["gate"].n
                     m.gate_s, m.up_s, m.down_s = d["gate"].s.data_ptr(), d["up"].s.data_ptr(), d["down"].s.data_ptr()
                     m.y8, m.ys = self.y8.data_ptr(), self.ys.data_ptr()
@@ -398,8 +403,7 @@ class TargetRuntime:
                        K.pick_split(nt, s.hidden // 128), pdl=pdl)
                 K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128,
                        K.pick_split(s.hidden // 128, dn["down"].k // 128), pdl=pdl)
-            elif self.moe_fused and K.moe_layer(d["gate"].map, d["up"].map, d["down"].map, self.map_x8, self.map_y8,
-                                                d["args_moe"], pdl=pdl) == 0:
+            elif self.moe_fused and self._moe_fused_layer(d, pdl):
                 pass
             else:
                 self.moe_fused = False           # geometry or occupancy does not fit the fused kernel: separate launches
@@ -411,6 +415,11 @@ class TargetRuntime:
         if head:
             K.prep_norm(self.x, self.g_final, R, s.norm_eps, xn=self.xn, pdl=pdl)
             K.gemm(self.V_BF16_STORE, self.map_lm, None, self.map_xn, self.args_head, -(-self.lm_head.shape[0] // 128), pdl=pdl)
+
+    def _moe_fused_layer(self, d, pdl) -> bool:
+        if self.moe_split_router:
+            K.router(d["args_router"], pdl=pdl)
+        return K.moe_layer(d["gate"].map, d["up"].map, d["down"].map, self.map_x8, self.map_y8, d["args_moe"], pdl=pdl) == 0
 
     def _step_legacy(self, head: bool = True, stop_after=None) -> None:
         s, R, pdl = self.spec, self.rows, self.pdl
