@@ -524,7 +524,8 @@ struct TailArgs {
   int vbase, vlocal;
   const uint32_t* status;
   int n_rows_q;
-  XchgArgs x;                    // cancel / failure consensus across ranks
+  const volatile int* host_consumed;   // mapped pinned host word: rounds the host has read (null: host-launched rounds)
+  XchgArgs x;                    // cancel / failure / pause consensus across ranks
 };
 
 __global__ void tail_commit_kernel(const TailArgs a) {
@@ -533,14 +534,23 @@ __global__ void tail_commit_kernel(const TailArgs a) {
   griddep_launch();
   // Every rank must take the same stop decision in the same round: the host cancel word (set on one
   // rank only) and a failed device wait on any rank are max-reduced over the ranks first.
-  if (threadIdx.x < 16)
-    xv[threadIdx.x] = threadIdx.x == 0 ? (uint64_t)(*a.cancel != 0) : (threadIdx.x == 1 ? (uint64_t)(*a.status != 0u) : 0ull);
+  // A self-relaunching chain pauses when the host is a ring length behind.  Each rank sees its own host's
+  // progress, so the pause is a consensus too: one rank that must wait makes every rank wait, otherwise the
+  // others would run into the next round's exchanges alone.
+  if (threadIdx.x < 16) {
+    uint64_t v = 0ull;
+    if (threadIdx.x == 0) v = (uint64_t)(*a.cancel != 0);
+    else if (threadIdx.x == 1) v = (uint64_t)(*a.status != 0u);
+    else if (threadIdx.x == 2 && a.host_consumed) v = (uint64_t)(a.ctrl[NRT_CTRL_ROUND] + 1 - *a.host_consumed >= a.ring_size - 8);
+    xv[threadIdx.x] = v;
+  }
   __syncthreads();
-  xchg_reduce_u64<kXMax>(xv, 2, a.x, 9);
+  xchg_reduce_u64<kXMax>(xv, 3, a.x, 9);
   __syncthreads();
   const bool cancel_any = xv[0] != 0ull, failed_any = xv[1] != 0ull;
   if (threadIdx.x != 0) return;
   int* c = a.ctrl;
+  c[NRT_CTRL_PAUSED] = xv[2] != 0ull ? 1 : 0;
   const int round = c[NRT_CTRL_ROUND];
   if (c[NRT_CTRL_STOPPED]) {                                  // already stopped: keep the fabric epoch moving, publish nothing
     // The round that just ran completed the draft context of the last committed rows; any further

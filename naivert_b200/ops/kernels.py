@@ -340,7 +340,7 @@ class SamplerArgs(C.Structure):
 class TailArgs(C.Structure):
     _fields_ = [("ctrl", VP), ("block_ids", VP), ("epoch", VP), ("st", VP), ("ring", VP), ("ring_size", I32),
                 ("cancel", VP), ("stop_ids", VP), ("n_stop", I32), ("counts", VP), ("vbase", I32), ("vlocal", I32),
-                ("status", VP), ("n_rows_q", I32), ("x", XchgArgs)]
+                ("status", VP), ("n_rows_q", I32), ("host_consumed", VP), ("x", XchgArgs)]
 
 
 class MarkovArgs(C.Structure):

@@ -204,6 +204,9 @@ class NativePrefill:
             p.qkv, p.ld, p.pos0, p.rope, p.q_out = self.qkv.data_ptr(), self.qkv.shape[1], pos0, self.rope[d["kind"]].data_ptr(), self.q.data_ptr()
             if d["kind"] == FULL_DSA:
                 p.idx_rope_tab, p.iq8, p.ihw = self.idx_rope.data_ptr(), self.iq8.data_ptr(), self.ihw.data_ptr()
+                # the step runtime keeps the query quantisation scale in a 16-row side buffer; a chunk has more rows,
+                # so here the scale is folded into the head weights (the kernel's form without that buffer)
+                p.iq_scale = None
                 e["sweep_maps"] = K.sweep_maps(d["ik"], self.iq8)
                 sw = K.SweepArgs()
                 sw.ihw, sw.iks, sw.pos0 = self.ihw.data_ptr(), d["iks"].data_ptr(), pos0

@@ -19,7 +19,7 @@ import torch
 
 from ..models.spec import ModelSpec, SamplingParams
 from ..parallel.fabric import Fabric
-from .round import RoundRecord, RuntimeContractError, SpeculativeRound
+from .round import RING_SIZE, RoundRecord, RuntimeContractError, SpeculativeRound
 from .target import TargetRuntime
 
 
@@ -58,7 +58,7 @@ class Engine:
               target_ckpt: Optional[str] = None, draft_ckpt: Optional[str] = None, device=None,
               weights: Optional[dict] = None, draft_weights: Optional[dict] = None, pdl: Optional[bool] = None,
               shape_tp: int = 0, device_chain: Optional[bool] = None, prefill_chunk: int = 0,
-              ep_weights: Optional[list] = None) -> "Engine":
+              ep_weights: Optional[list] = None, ring_size: int = 0) -> "Engine":
         """``prefill_chunk`` > 0 adds the chunked native prefill (rows per chunk); ``ep_weights`` (whole experts of
         this rank per layer, ``models.weights.shard_expert_weights``) selects its expert-parallel MoE path."""
         device = device or torch.device("cuda", torch.cuda.current_device())
@@ -96,7 +96,8 @@ class Engine:
         if device_chain is None:
             import os
             device_chain = os.environ.get("NAIVERT_DEVICE_CHAIN", "0") == "1"
-        rnd = SpeculativeRound(spec, target, draft_weights, capacity, pdl=pdl, device_chain=device_chain)
+        rnd = SpeculativeRound(spec, target, draft_weights, capacity, pdl=pdl, device_chain=device_chain,
+                               ring_size=ring_size or RING_SIZE)
         prefill = None
         if prefill_chunk:
             from ..prefill.native import NativePrefill

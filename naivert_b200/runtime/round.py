@@ -76,7 +76,7 @@ class HostRing:
 
 class SpeculativeRound:
     def __init__(self, spec: ModelSpec, target: TargetRuntime, draft_weights: dict, capacity: int, pdl: bool = True,
-                 device_chain: bool = False):
+                 device_chain: bool = False, ring_size: int = RING_SIZE):
         if target.rows != spec.draft.rows:
             raise RuntimeContractError("the verify runtime must run block_size + 1 rows")
         self.spec, self.t, self.fab, self.pdl = spec, target, target.fab, pdl
@@ -94,7 +94,7 @@ class SpeculativeRound:
         import os
         self.sampler_one_launch = target.fused and os.environ.get("NAIVERT_SAMPLER_PERSISTENT", "1") == "1"
         self.sampler_sync = torch.zeros(2, dtype=torch.int64, device=dev)
-        self.ring = HostRing()
+        self.ring = HostRing(ring_size)
         self.draft = DraftRuntime(spec, draft_weights, target, capacity, self.seed, self.params, self.block_ids, pdl=pdl)
         self.capacity = capacity
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -106,6 +106,7 @@ class SpeculativeRound:
         # device chain: the round graph is instantiated for device launch and relaunches itself from its
         # last kernel; the host launches once per request and polls the ring
         self.device_chain = device_chain
+        self.nudge_s = 0.5                                  # silence after which a paused chain is restarted
         self.native_graph: Optional[K.NativeGraph] = None
         self.chain_started = False
         self.host_launches = 0
@@ -130,6 +131,7 @@ class SpeculativeRound:
         t.cancel, t.stop_ids, t.n_stop = self.ring.cancel_dev, self.stop_ids.data_ptr(), len(self.spec.stop_token_ids)
         t.counts, t.vbase, t.vlocal = None, self.vbase, self.vlocal
         t.status, t.n_rows_q = self.fab.status.data_ptr(), 7
+        t.host_consumed = self.ring.consumed_dev if self.device_chain else None     # pause consensus of the chain
         t.x = self.fab.xchg_args()
         self.args_tail = t
 
@@ -155,10 +157,18 @@ class SpeculativeRound:
         self.draft.block()
         self.draft.propose()
         self.t.step()
-        if not (self.sampler_one_launch and K.sampler_persistent(self.args_sampler, self.sampler_sync, domain=1, pdl=self.pdl) == 0):
-            self.sampler_one_launch = False
-            K.sampler_run(self.args_sampler, domain=1, pdl=self.pdl)
+        self.sample()
         K.tail_commit(self.args_tail, pdl=self.pdl)
+
+    def sample(self, domain: int = 1, one_launch: Optional[bool] = None) -> None:
+        """Verify + resample on the logits in place: the single-launch sampler, or the nine-kernel chain where its
+        grid cannot be resident at once (or when ``one_launch`` is False)."""
+        want = self.sampler_one_launch if one_launch is None else one_launch
+        if want and K.sampler_persistent(self.args_sampler, self.sampler_sync, domain=domain, pdl=self.pdl) == 0:
+            return
+        if one_launch is None:
+            self.sampler_one_launch = False
+        K.sampler_run(self.args_sampler, domain=domain, pdl=self.pdl)
 
     def prefill_phases(self) -> None:
         """One 8-row prompt replay step: target rows (no head) + draft ingest of their features."""
@@ -273,7 +283,7 @@ class SpeculativeRound:
             g.begin(sid)
             try:
                 self.phases()
-                K.relaunch(self.t.ctrl, self.ring.consumed_dev, self.ring.size)
+                K.relaunch(self.t.ctrl, 0, self.ring.size)      # pause decided by the tail (rank consensus)
             finally:
                 g.end(sid)
         g.instantiate(True, sid)
@@ -319,7 +329,7 @@ class SpeculativeRound:
             rec = self.poll()
             if rec is not None:
                 return rec
-            if self.device_chain and self.use_graphs and not nudged and time.monotonic() - t0 > 0.5:
+            if self.device_chain and self.use_graphs and not nudged and time.monotonic() - t0 > self.nudge_s:
                 self.launch(force=True)                      # the chain paused for backpressure: restart it
                 nudged = True
             if time.monotonic() - t0 > timeout_s:

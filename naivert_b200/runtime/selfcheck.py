@@ -15,6 +15,39 @@ from __future__ import annotations
 import torch
 
 
+def _sampler_check(eng, spec, rank: int, world: int, device) -> bool:
+    """The sharded sampler on identical full-vocabulary logits (every rank draws the same tensors and keeps its
+    vocabulary slice) against the integer oracle, which knows nothing about shards: equal results for every TP
+    degree means the sampler is invariant under the sharding."""
+    from ..models.spec import SamplingParams
+    from ..ops import kernels as K
+    from ..ops import sampling_ref as S
+    r = eng.round
+    V, vl = spec.vocab, spec.vocab // world
+    g = torch.Generator(device=device).manual_seed(3)
+    ok = True
+    for trial, (top_p, forced, temp) in enumerate([(0.95, None, 1.0), (0.5, None, 0.4), (0.95, 0.7, 0.4)]):
+        zp = torch.randn(8, V, device=device, generator=g) * 3
+        zq = zp[:7] + torch.randn(7, V, device=device, generator=g)
+        r.t.logits[:8].copy_(zp[:, rank * vl:(rank + 1) * vl])
+        r.draft.zq[:7].copy_(zq[:, rank * vl:(rank + 1) * vl])
+        ids = [11] + [int(torch.multinomial(torch.softmax(zq[j] / temp, -1), 1, generator=g)) for j in range(7)]
+        r.block_ids[:8].copy_(torch.tensor(ids, dtype=torch.int32))
+        sp = SamplingParams(temperature=temp, top_p=top_p, seed=77 + trial, forced_accept_p=forced)
+        r.set_sampling(sp)
+        r.t.ctrl[8] = trial
+        r.sample()
+        K.epoch_advance(eng.fabric.epoch, pdl=False)
+        torch.cuda.synchronize()
+        st = r.state.view(torch.int32)
+        tail = (K.sampler_state_bytes() - 10 * 4) // 4
+        accepted, extra = int(st[tail + 0]), int(st[tail + 1])
+        m, tok, _, _ = S.verify_oracle(zp, zq, ids, 1.0 / temp, sp.clamped_top_p(), sp.seed, trial, forced=forced)
+        ok = ok and accepted == m and extra == tok
+    r.t.ctrl[8] = 0
+    return ok
+
+
 def tp_selfcheck(rank: int, world: int, group, device, layers: int = 4, generate: bool = True) -> dict:
     import torch.distributed as dist
     from ..models.naive_n0p5 import small_w8a8_spec
@@ -62,6 +95,7 @@ def tp_selfcheck(rank: int, world: int, group, device, layers: int = 4, generate
         else:
             out["argmax_ok"] = tok[:8].tolist() == t.logits[:8].argmax(-1).tolist()
             out["residual_identical"] = True
+        out["sampler_matches_oracle"] = _sampler_check(eng, spec, rank, world, device)
         if generate:
             prompt = torch.randint(0, spec.vocab - 16, (45,), generator=g)
             sp = SamplingParams(temperature=0.4, seed=5, forced_accept_p=0.7)

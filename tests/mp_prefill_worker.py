@@ -95,6 +95,7 @@ def main():
     out = {"world": world, "prefill": info, "moe": "ep" if eng.prefill.ep else ("local" if world == 1 else "tp"), "errs": {k: round(v, 5) for k, v in errs.items()},
            "bitwise": sorted(k for k in ref if torch.equal(got[k], ref[k])),
            "repeat_identical": all(torch.equal(got[k], got2[k]) for k in got) and got_toks == got2_toks,
+           "repeat_diff": sorted(k for k in got if not torch.equal(got[k], got2[k])) + ([] if got_toks == got2_toks else ["tokens"]),
            "worst": max(errs.values()), "tokens_ref": ref_toks[:12], "tokens_native": got_toks[:12],
            "status": int(eng.fabric.status[0])}
     agree = 0

@@ -22,3 +22,57 @@ def test_check_env_reports():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "devops", "warm_kernels.py"), "--check-env"], capture_output=True, text=True)
     rep = json.loads(out.stdout)
     assert "packages" in rep and rep["packages"]["fastapi"] != "" and "nvcc" in rep
+
+
+def _fake_docker(tmp_path, nogpu_exit=1):
+    """A stand-in for the docker CLI that logs its arguments and plays the container's part for every step."""
+    log = tmp_path / "docker_calls.log"
+    fake = tmp_path / "docker"
+    fake.write_text(f"""#!/usr/bin/env bash
+echo "$@" >> {log}
+case "$1" in
+  build|rm) exit 0 ;;
+  image) echo 123456789; exit 0 ;;
+  compose) exit 0 ;;
+  run)
+    if [[ "$*" == *"--name naivert-b200-tier1-"* ]]; then echo "no CUDA device"; exit {nogpu_exit}; fi
+    exit 0 ;;
+esac
+exit 64
+""")
+    fake.chmod(0o755)
+    return fake, log
+
+
+def test_tier1_passes_with_expected_exit_codes(tmp_path):
+    fake, log = _fake_docker(tmp_path)
+    out_dir = tmp_path / "out"
+    env = dict(os.environ, NAIVERT_DOCKER=str(fake), NAIVERT_VALIDATION_DIR=str(out_dir))
+    p = subprocess.run(["bash", os.path.join(ROOT, "devops", "tier1.sh"), "img:test"], env=env, capture_output=True, text=True)
+    assert p.returncode == 0 and "TIER1_OK" in p.stdout, p.stdout + p.stderr
+    calls = log.read_text()
+    assert "build -f devops/Dockerfile -t img:test ." in calls and "compose -f devops/docker-compose.yml config -q" in calls
+    assert "-m pytest tests -x -q -m not gpu" in calls
+    assert (out_dir / "nogpu.exit").read_text().strip() == "1" and (out_dir / "size_bytes").read_text().strip() == "123456789"
+
+
+def test_tier1_fails_when_gpuless_start_succeeds(tmp_path):
+    """A server that comes up without GPUs (exit 0) or hangs is a failed check, not a pass."""
+    fake, _ = _fake_docker(tmp_path, nogpu_exit=0)
+    env = dict(os.environ, NAIVERT_DOCKER=str(fake), NAIVERT_VALIDATION_DIR=str(tmp_path / "out"))
+    p = subprocess.run(["bash", os.path.join(ROOT, "devops", "tier1.sh")], env=env, capture_output=True, text=True)
+    assert p.returncode == 1 and "nogpu exited 0, expected 1" in p.stderr and "TIER1_FAILED" in p.stderr
+
+
+def test_compose_file_is_consistent_with_the_entrypoint():
+    import re
+    import yaml
+    doc = yaml.safe_load(open(os.path.join(ROOT, "devops", "docker-compose.yml")))
+    svc = doc["services"]["naivert-b200"]
+    assert svc["ipc"] == "host" and svc["build"]["dockerfile"] == "devops/Dockerfile"
+    assert svc["deploy"]["resources"]["reservations"]["devices"][0]["capabilities"] == ["gpu"]
+    entry = open(os.path.join(ROOT, "devops", "entrypoint.sh")).read()
+    known = set(re.findall(r"NAIVERT_[A-Z_]+", entry))
+    for key in svc["environment"]:
+        if key.startswith("NAIVERT_"):
+            assert key in known, f"{key} is set by compose but not read by the entrypoint"

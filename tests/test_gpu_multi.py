@@ -35,7 +35,7 @@ def test_tensor_parallel_engine(n):
     r = _run(n)
     assert r["status"] == 0
     assert r["residual_identical"] and r["lockstep"] and r["deterministic"] and r["spec_equals_greedy"], r
-    assert r["verify_mean_rel"] < 0.06 and r["argmax_ok"], r
+    assert r["verify_mean_rel"] < 0.06 and r["argmax_ok"] and r["sampler_matches_oracle"], r
     assert r["real_sampling_tokens"] == 64
 
 
@@ -48,6 +48,16 @@ def _run_worker(n, script, **extra_env):
     lines = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")]
     assert p.returncode == 0 and lines, p.stdout[-2000:] + p.stderr[-4000:]
     return json.loads(lines[-1][7:])
+
+
+def test_device_chain_pauses_by_rank_consensus():
+    """TP2 self-relaunching rounds with a 32-record ring and one lagging host: the chains pause together (the pause
+    is max-reduced over the ranks in the tail kernel), are restarted by their hosts and commit the host-launched tokens."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _run_worker(2, "mp_chain_worker.py")
+    assert r["status"] == 0 and r["tokens_match_host_rounds"] and r["lockstep"], r
+    assert min(r["host_launches"]) >= 2 and max(r["host_launches"]) < 40, r
 
 
 @pytest.mark.parametrize("n", [1, 2])
@@ -74,11 +84,20 @@ def test_native_prefill_matches_replay(n, exact):
     assert r["status"] == 0 and r["repeat_identical"], r
     assert r["prefill"]["path"] == "native" and r["prefill"]["native_rows"] >= 672, r
     if exact:
-        assert r["worst"] < 0.06, r
+        assert r["worst"] < 0.08, r
     if n > 1:
         assert r["lockstep"], r
     assert r["worst"] < 0.1, r
     assert r["token_prefix_agreement"] >= 1, r
+
+
+def test_native_prefill_is_bitwise_equal_to_the_unfused_replay():
+    """Against the step path built from separate kernels (full-row RMSNorm, row attention, no K split) the chunk
+    path with the row attention kernel reproduces the first layers' caches bit for bit: both add in the same order."""
+    r = _run_worker(1, "mp_prefill_worker.py", NAIVERT_PREFILL_GROUP_ATTN="0", NAIVERT_LEGACY_STEP="1")
+    assert r["status"] == 0 and r["repeat_identical"], r
+    assert {"L0.k", "L0.v", "L0.ik", "L0.iks", "L1.k", "L1.v"} <= set(r["bitwise"]), r
+    assert r["worst"] < 0.03 and r["token_prefix_agreement"] >= 4, r
 
 
 def test_native_prefill_tensor_parallel_experts():

@@ -12,7 +12,8 @@ def _engine(layers=2, capacity=1024, seed=0):
     return spec, Engine.build(spec, capacity=capacity, seed=seed)
 
 
-def test_sampler_matches_integer_oracle():
+@pytest.mark.parametrize("one_launch", [False, True])
+def test_sampler_matches_integer_oracle(one_launch):
     from naivert_b200.models.spec import SamplingParams
     from naivert_b200.ops import kernels as K
     from naivert_b200.ops import sampling_ref as S
@@ -30,7 +31,10 @@ def test_sampler_matches_integer_oracle():
         sp = SamplingParams(temperature=temp, top_p=top_p, seed=77 + trial, forced_accept_p=forced)
         r.set_sampling(sp)
         r.t.ctrl[8] = trial
-        K.sampler_run(r.args_sampler, domain=1, pdl=False)
+        if one_launch:
+            assert K.sampler_persistent(r.args_sampler, r.sampler_sync, domain=1, pdl=False) == 0
+        else:
+            K.sampler_run(r.args_sampler, domain=1, pdl=False)
         torch.cuda.synchronize()
         eng.fabric.check()
         st = r.state.view(torch.int32)
@@ -157,3 +161,29 @@ def test_device_chain_matches_host_launched_rounds():
     assert info["kernel_nodes"] == info["nodes"] and info["kernel_nodes"] > 20
     c = chain.generate(prompt, 64, sp)                      # a second request restarts the chain
     assert c.tokens == a.tokens[:64]
+
+
+def test_round_graph_carries_programmatic_edges():
+    """With programmatic dependent launch on, the captured round graph holds one programmatic edge per kernel-to-kernel
+    dependency (they come from the launch attribute, nothing rewrites the graph afterwards), the plain capture holds
+    none, and both commit the same tokens."""
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    from naivert_b200.models.spec import SamplingParams
+    from naivert_b200.runtime.engine import Engine
+    spec = small_w8a8_spec(2)
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, spec.vocab - 16, (41,), generator=g)
+    sp = SamplingParams(temperature=0.6, seed=3)
+    toks, infos = [], []
+    for pdl in (False, True):
+        eng = Engine.build(spec, capacity=1024, seed=0, device_chain=True, pdl=pdl)
+        try:
+            toks.append(eng.generate(prompt, 96, sp).tokens)
+            infos.append(eng.round.native_graph.info)
+        finally:
+            eng.close()
+    assert toks[0] == toks[1]
+    plain, prog = infos
+    assert plain["programmatic_edges"] == 0 and plain["kernel_nodes"] == prog["kernel_nodes"]
+    # every kernel but the first and the relaunch node (an ordinary launch) hangs on a programmatic edge
+    assert prog["programmatic_edges"] >= prog["kernel_nodes"] - 2, prog

@@ -180,3 +180,20 @@ def test_ep_layout_reference_invariants():
             covered = sum(min(item_rows, lay["seg_rows"][d][el] - (r0 - lay["seg_base"][d][el])) for el, r0 in lay["items"][d])
             assert covered == sum(lay["seg_rows"][d])               # the work list covers every received row once
         assert sum(sum(r) for r in lay["seg_rows"]) == tp * T * k
+
+
+def test_xid_delta_check(tmp_path):
+    from naivert_b200.utils import xid_check as X
+    old = "[ 10.0] NVRM: Xid (PCI:0000:1b:00): 31, pid=1, name=python, Ch 00000008\n[ 11.0] usb 1-1: new device\n"
+    new = old + "[ 99.5] NVRM: Xid (PCI:0000:1b:00): 109, pid=7, name=python, errorString CTX SWITCH TIMEOUT\n"
+    assert X.new_xid_lines(old, old) == [] and X.xid_codes(X.new_xid_lines(old, new)) == [109]
+    # the same text appearing a second time is a new event
+    assert len(X.new_xid_lines(old, old + old)) == 1
+    a, b, c = tmp_path / "a.txt", tmp_path / "b.txt", tmp_path / "c.txt"
+    src_old, src_new = tmp_path / "old.log", tmp_path / "new.log"
+    src_old.write_text(old); src_new.write_text(new)
+    assert X.main(["snapshot", str(a), "--source", str(src_old)]) == 0
+    assert X.main(["snapshot", str(b), "--source", str(src_new)]) == 0
+    assert X.main(["compare", str(a), str(a)]) == 0 and X.main(["compare", str(a), str(b)]) == 1
+    assert X.main(["snapshot", str(c), "--source", str(tmp_path / "missing.log")]) == 0
+    assert X.main(["compare", str(a), str(c)]) == 0 and X.main(["compare", str(a), str(c), "--strict"]) == 1
