@@ -39,6 +39,9 @@ struct RouterArgs {
   int max_slots;
   uint8_t* x8;               // inline-norm form: e4m3 packet [16][hidden] of the normalised rows for the expert GEMMs;
                              // each CTA quantises a few (row, 128-channel block) pairs, so nobody repeats the work
+  // opt-in phase stamps of the router kernel (%globaltimer, ns), [CTA][16]: 0 entry, 12 upstream grid done, 13 row scales
+  // ready, 14 dot products done, 1 scores published, 2 selection begins (last CTA), 10 choices made, 15 lists built, 3 end
+  unsigned long long* stamps;
 };
 
 
@@ -113,93 +116,91 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
     pk_x = *reinterpret_cast<const uint4*>(a.x + (size_t)pk_r * a.hidden + k);
     pk_g = __ldg(reinterpret_cast<const uint4*>(a.gamma + k));
   }
-  float acc[2][kMaxRows];
+  // 1 / rms per row from the per-tile sums of squares left behind by the producer of x, then this CTA's share of the
+  // e4m3 packet.  (One copy of this code: the phases below are rolled loops with small bodies on purpose - a kernel
+  // that runs once per layer executes mostly cold code, and instruction fetch is then the top stall reason.)
+  if (inline_norm) {
+#pragma unroll 1
+    for (int r = warp; r < a.rows; r += 8) {
+      float ss = 0.f;
+#pragma unroll 1
+      for (int t = lane; t < blocks; t += 32) ss += __ldcg(a.ssq + t * kMaxRows + r);
+      ss = router_warp_sum(ss);
+      if (lane == 0) rs_s[r] = rsqrtf(ss / (float)a.hidden + a.eps);
+    }
+    __syncthreads();
+    if (pairs > 0) {                               // uniform over the CTA
+      const float rs = rs_s[pk_r];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk_x);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&pk_g);
+      float o[8];
+      float am = 0.f;
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
-#pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) acc[j][r] = 0.f;
-  bool have_rs = false;
-  auto compute_rs = [&]() {
-    // 1/rms per row from the per-tile sums of squares left behind by the producer of x
-    if (inline_norm) {
-      for (int r = warp; r < a.rows; r += 8) {
-        float ss = 0.f;
-        for (int t = lane; t < blocks; t += 32) ss += __ldcg(a.ssq + t * kMaxRows + r);
-        ss = router_warp_sum(ss);
-        if (lane == 0) rs_s[r] = rsqrtf(ss / (float)a.hidden + a.eps);
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
+        o[2 * q] = round_bf16(f.x * rs * g.x);
+        o[2 * q + 1] = round_bf16(f.y * rs * g.y);
+        am = fmaxf(am, fmaxf(fabsf(o[2 * q]), fabsf(o[2 * q + 1])));
       }
-      __syncthreads();
-      if (pairs > 0) {                               // uniform over the CTA
-        const float rs = rs_s[pk_r];
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk_x);
-        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&pk_g);
-        float o[8];
-        float am = 0.f;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
-          o[2 * q] = round_bf16(f.x * rs * g.x);
-          o[2 * q + 1] = round_bf16(f.y * rs * g.y);
-          am = fmaxf(am, fmaxf(fabsf(o[2 * q]), fabsf(o[2 * q + 1])));
-        }
+      for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+      const float sc = pow2_scale(am);
+      uint2 q8;
+      uint8_t* qb = reinterpret_cast<uint8_t*>(&q8);
 #pragma unroll
-        for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-        const float sc = pow2_scale(am);
-        uint2 q8;
-        uint8_t* qb = reinterpret_cast<uint8_t*>(&q8);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) qb[q] = e4m3_bits(o[q] / sc);
-        if (pk_on) {
-          *reinterpret_cast<uint2*>(a.x8 + (size_t)pk_r * a.hidden + pk_b * 128 + (tid & 15) * 8) = q8;
-          if ((tid & 15) == 0) a.xs[(size_t)pk_r * blocks + pk_b] = sc;
-        }
+      for (int q = 0; q < 8; ++q) qb[q] = e4m3_bits(o[q] / sc);
+      if (pk_on) {
+        *reinterpret_cast<uint2*>(a.x8 + (size_t)pk_r * a.hidden + pk_b * 128 + (tid & 15) * 8) = q8;
+        if ((tid & 15) == 0) a.xs[(size_t)pk_r * blocks + pk_b] = sc;
       }
     }
-    have_rs = true;
-    if (stamp && threadIdx.x == 0) stamp[13] = globaltimer();
-  };
+  }
+  if (stamp && threadIdx.x == 0) stamp[13] = globaltimer();
   if (fast) {
-    // Every load of the thread is issued before the first FMA (one round trip instead of one per K step): eight rows
-    // of activations at a time (rows beyond a.rows are predicated off, not read); the sums of squares are fetched
-    // while those loads are in flight.
+    // four rows at a time: their sixteen loads are in flight together, then the FMAs, then the warp sums
+#pragma unroll 1
+    for (int r0 = 0; r0 < a.rows; r0 += 4) {
+      uint2 xv[4][4];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      if (half * 8 < a.rows) {
-        uint2 xv[4][8];
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int rr = 0; rr < 4; ++rr)
+          xv[i][rr] = (r0 + rr < a.rows) ? *reinterpret_cast<const uint2*>(xsrc + (size_t)(r0 + rr) * xld + tid * 4 + 1024 * i)
+                                         : make_uint2(0u, 0u);
+      float acc0[4], acc1[4];
 #pragma unroll
-          for (int r = 0; r < 8; ++r)
-            xv[i][r] = (half * 8 + r < a.rows)
-                           ? *reinterpret_cast<const uint2*>(xsrc + (size_t)(half * 8 + r) * xld + tid * 4 + 1024 * i)
-                           : make_uint2(0u, 0u);
-        if (!have_rs) compute_rs();
+      for (int rr = 0; rr < 4; ++rr) { acc0[rr] = 0.f; acc1[rr] = 0.f; }
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].x));
-            float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][r].y));
-            if (inline_norm) {
-              const float rs = rs_s[half * 8 + r];
-              x01.x = round_bf16(x01.x * rs * gm[i].x); x01.y = round_bf16(x01.y * rs * gm[i].y);
-              x23.x = round_bf16(x23.x * rs * gm[i].z); x23.y = round_bf16(x23.y * rs * gm[i].w);
-            }
-            acc[0][half * 8 + r] += x01.x * w0[i].x + x01.y * w0[i].y + x23.x * w0[i].z + x23.y * w0[i].w;
-            acc[1][half * 8 + r] += x01.x * w1[i].x + x01.y * w1[i].y + x23.x * w1[i].z + x23.y * w1[i].w;
+        for (int rr = 0; rr < 4; ++rr) {
+          float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][rr].x));
+          float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv[i][rr].y));
+          if (inline_norm) {
+            const float rs = rs_s[min(r0 + rr, kMaxRows - 1)];
+            x01.x = round_bf16(x01.x * rs * gm[i].x); x01.y = round_bf16(x01.y * rs * gm[i].y);
+            x23.x = round_bf16(x23.x * rs * gm[i].z); x23.y = round_bf16(x23.y * rs * gm[i].w);
           }
+          acc0[rr] += x01.x * w0[i].x + x01.y * w0[i].y + x23.x * w0[i].z + x23.y * w0[i].w;
+          acc1[rr] += x01.x * w1[i].x + x01.y * w1[i].y + x23.x * w1[i].z + x23.y * w1[i].w;
+        }
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr) {
+        const float v0 = router_warp_sum(acc0[rr]), v1 = router_warp_sum(acc1[rr]);
+        if (lane == 0 && r0 + rr < a.rows) { part[warp][0][r0 + rr] = v0; part[warp][1][r0 + rr] = v1; }
       }
     }
   } else {
-  compute_rs();
-#pragma unroll 4
-  for (int k = tid * 4; k < a.hidden; k += 1024) {
-    float4 w0 = (e0 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k) : make_float4(0, 0, 0, 0);
-    float4 w1 = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * a.hidden + k)
-                                     : make_float4(0, 0, 0, 0);
-#pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) {
-      if (r < a.rows) {
+    // any other width: one row at a time, the K steps of a thread in ascending order
+#pragma unroll 1
+    for (int r = 0; r < a.rows; ++r) {
+      float a0 = 0.f, a1 = 0.f;
+      const float rs = inline_norm ? rs_s[r] : 1.f;
+#pragma unroll 1
+      for (int k = tid * 4; k < a.hidden; k += 1024) {
+        const float4 v0 = (e0 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)e0 * a.hidden + k) : make_float4(0, 0, 0, 0);
+        const float4 v1 = (e0 + 1 < a.experts) ? *reinterpret_cast<const float4*>(a.w + (size_t)(e0 + 1) * a.hidden + k)
+                                               : make_float4(0, 0, 0, 0);
         const uint2 xv = *reinterpret_cast<const uint2*>(xsrc + (size_t)r * xld + k);
         float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
         float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
@@ -207,30 +208,23 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
           const uint2 gv = *reinterpret_cast<const uint2*>(a.gamma + k);
           const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
           const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
-          const float rs = rs_s[r];
           x01.x = round_bf16(x01.x * rs * g01.x); x01.y = round_bf16(x01.y * rs * g01.y);
           x23.x = round_bf16(x23.x * rs * g23.x); x23.y = round_bf16(x23.y * rs * g23.y);
         }
-        acc[0][r] += x01.x * w0.x + x01.y * w0.y + x23.x * w0.z + x23.y * w0.w;
-        acc[1][r] += x01.x * w1.x + x01.y * w1.y + x23.x * w1.z + x23.y * w1.w;
+        a0 += x01.x * v0.x + x01.y * v0.y + x23.x * v0.z + x23.y * v0.w;
+        a1 += x01.x * v1.x + x01.y * v1.y + x23.x * v1.z + x23.y * v1.w;
       }
+      a0 = router_warp_sum(a0);
+      a1 = router_warp_sum(a1);
+      if (lane == 0) { part[warp][0][r] = a0; part[warp][1][r] = a1; }
     }
-  }
   }
   if (stamp && threadIdx.x == 0) stamp[14] = globaltimer();
-#pragma unroll
-  for (int j = 0; j < 2; ++j)
-#pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) {
-      if (r < a.rows) {                              // uniform across the CTA: dead rows cost no shuffles
-        const float v = router_warp_sum(acc[j][r]);
-        if (lane == 0) part[warp][j][r] = v;
-      }
-    }
   __syncthreads();
   if (tid < 2 * kMaxRows) {
     const int j = tid / kMaxRows, r = tid % kMaxRows;
     float s = 0.f;
+#pragma unroll 1
     for (int w = 0; w < 8; ++w) s += part[w][j][r];
     if (e0 + j < a.experts && r < a.rows) a.scores[r * a.experts + e0 + j] = s;
   }
@@ -247,6 +241,7 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
   if (tid < 8) used[tid] = 0u;
   __syncthreads();
   // one warp per row: iterative arg-max with lowest-index ties
+#pragma unroll 1
   for (int r = warp; r < a.rows; r += 8) {
     float sc[8], ch[8];                             // experts lane, lane+32, ... (<= 256 experts)
     // all sixteen loads (scores from L2, selection bias) are issued before anything depends on them
@@ -264,11 +259,12 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
       sc[j] = in ? raw[j] : -FLT_MAX;
       mx = fmaxf(mx, sc[j]);
     }
+    if (stamp && threadIdx.x == 0) { stamp[4] = globaltimer(); stamp[7] = (unsigned long long)(mx != 0.f); }
     if (a.sigmoid) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const bool in = lane + 32 * j < a.experts;
-        sc[j] = in ? 1.f / (1.f + __expf(-sc[j])) : 0.f;
+        sc[j] = in ? __frcp_rn(1.f + __expf(-sc[j])) : 0.f;      // rcp.rn == 1 / y, without the division's slow path
         ch[j] = in ? sc[j] + bv[j] : -FLT_MAX;
       }
     } else {
@@ -287,9 +283,11 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
     uint32_t kk[8];                                 // order-preserving keys; 0 once taken
 #pragma unroll
     for (int j = 0; j < 8; ++j) kk[j] = router_order_key(ch[j]);
+    if (stamp && threadIdx.x == 0) stamp[5] = globaltimer() + (kk[0] == 12345u);
     float psum = 0.f;
     float my_p = 0.f;
     int my_id = -1;
+#pragma unroll 1
     for (int t = 0; t < a.top_k; ++t) {
       // arg-max over the warp with two hardware reductions: the largest key, then the lowest expert index
       // among the lanes that hold it
@@ -310,6 +308,7 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
       psum += pv;
       if (lane == t) { my_p = pv; my_id = bi; }
     }
+    if (stamp && threadIdx.x == 0) stamp[6] = globaltimer() + (psum == 12345.f);
     const float denom = a.normalize ? psum + 1e-20f : 1.f;
     if (lane < a.top_k) {
       const float p = my_p / denom * a.route_scale;
@@ -327,6 +326,7 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
   if (tid < 256) {
     const bool on = tid < a.experts && (used[tid >> 5] >> (tid & 31)) & 1u;
     int before = 0;
+#pragma unroll 1
     for (int w = 0; w < (tid >> 5); ++w) before += __popc(used[w]);
     before += __popc(used[tid >> 5] & ((1u << (tid & 31)) - 1u));
     slot_of[tid] = on ? before : -1;
@@ -336,17 +336,20 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
     }
     if (tid == 0) {
       int tot = 0;
+#pragma unroll 1
       for (int w = 0; w < 8; ++w) tot += __popc(used[w]);
       sm.n_active = min(tot, a.max_slots);
       if (publish && a.n_active) *a.n_active = sm.n_active;
     }
   }
   if (stamp && threadIdx.x == 0) stamp[15] = globaltimer();
+#pragma unroll 1
   for (int i = tid; i < a.max_slots * kTok; i += 256) {
     if (publish && a.probs) a.probs[i] = 0.f;
     if (probs_s) probs_s[i] = 0.f;
   }
   __syncthreads();
+#pragma unroll 1
   for (int i = tid; i < a.rows * a.top_k; i += 256) {
     const int r = i / a.top_k, k = i - r * a.top_k;
     const int s = slot_of[sm.tk_id[r][k]];

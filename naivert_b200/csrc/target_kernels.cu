@@ -838,18 +838,23 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   __shared__ RouterSmem sm;
   __shared__ bool last;
   const int tid = threadIdx.x;
-  router_scores(a, blockIdx.x, gridDim.x, sm);
+  unsigned long long* stamp = (a.stamps && gridDim.y == 1) ? a.stamps + (size_t)blockIdx.x * 16 : nullptr;
+  if (stamp && tid == 0) stamp[0] = globaltimer();
+  router_scores(a, blockIdx.x, gridDim.x, sm, stamp);
   __threadfence();
   __syncthreads();
   if (tid == 0) {
     const unsigned int t = atomicAdd(a.ticket, 1u);
     last = (t == gridDim.x - 1);
     if (last) *a.ticket = 0u;
+    if (stamp) stamp[1] = globaltimer();
   }
   __syncthreads();
   if (!last) return;
   __threadfence();
-  router_select(a, sm, true, nullptr, nullptr);
+  if (stamp && tid == 0) stamp[2] = globaltimer();
+  router_select(a, sm, true, nullptr, nullptr, stamp);
+  if (stamp && tid == 0) stamp[3] = globaltimer();
 }
 
 }  // namespace

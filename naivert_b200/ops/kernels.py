@@ -81,7 +81,7 @@ class RouterArgs(C.Structure):
                 ("w", VP), ("bias", VP), ("hidden", I32), ("experts", I32), ("rows", I32),
                 ("top_k", I32), ("sigmoid", I32), ("normalize", I32), ("route_scale", F32),
                 ("scores", VP), ("ticket", VP), ("n_active", VP), ("active_ids", VP), ("probs", VP),
-                ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32), ("x8", VP)]
+                ("topk_ids", VP), ("topk_p", VP), ("max_slots", I32), ("x8", VP), ("stamps", VP)]
 
 
 class MoeArgs(C.Structure):
