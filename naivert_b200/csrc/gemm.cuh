@@ -148,6 +148,8 @@ struct GemmArgs {
   unsigned int publish_delay_ns;  // test knob: this rank delays its mailbox publish by this long (a late peer that still arrives)
 };
 
+constexpr int kOutStageBytes = kTok * kTileN * 4;      // accumulators of a tile as [row][feature] for row-wise epilogues
+
 template <bool FP8, bool DUAL, int BSRC = kBTma>
 struct GemmCfg {
   static constexpr int kABytes = (DUAL ? 2 : 1) * kATileBytes;
@@ -170,7 +172,7 @@ struct GemmCfg {
     return BSRC == kBTma ? 0 : kb_count * kBTileBytes + (FP8 ? ((kb_count * kTok * 4 + 1023) & ~1023) : 0);
   }
   __host__ __device__ static constexpr int smem_bytes(int kb_count, int split) {
-    return kRingBytes + operand_bytes(kb_count) + 1024 /*align*/ + 1024 /*barriers + scratch*/ + part_bytes(split);
+    return kRingBytes + operand_bytes(kb_count) + 1024 /*align*/ + 1024 /*barriers + scratch*/ + kOutStageBytes + part_bytes(split);
   }
 };
 
@@ -343,157 +345,172 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
 }
 
 // ----------------------------------------------------------------------------- q/k/v post-processing epilogue
-// Thread = one feature `n` of the fused q | k | v | iq | ik | iw projection, v[r] = its fp32 accumulators for
-// the token rows.  Tiles of indexer heads, the indexer key and per-head-normed heads (head_dim == 128) must be
-// 128-aligned: their reductions run over the 128 threads of the tile.
-struct PostCtx {             // what the epilogue reads from global memory, fetched while the MMAs still run
+// The accumulators of a tile (thread = feature, register = token row) are staged in shared memory as
+// [row][128 features]; then every epilogue warp takes whole token rows (warp w: rows w, w + 4, ...), a lane four
+// adjacent features.  All reductions of a row (LayerNorm, per-head RMS norm, quantisation maximum) are warp
+// reductions, RoPE pairs sit in one lane, stores are 8-byte (bf16) or 4-byte (e4m3) per lane, and the per-row code
+// is one rolled loop - this epilogue runs once per launch, and a short loop body that is fetched once beats sixteen
+// unrolled copies of it.
+// Tiles of indexer heads, the indexer key and per-head-normed heads (head_dim == 128) must be 128-aligned; region
+// boundaries (q | k | v | iq | ik | iw) and head sizes are multiples of 4 features.
+enum PostKind : int { kPostNone = 0, kPostQ, kPostK, kPostV, kPostIw, kPostIq, kPostIk };
+
+struct PostCtx {             // per-lane constants, fetched while the MMAs still run
   int p0;
-  float2 cs[kTok];            // RoPE (cos, sin) of this thread's pair for every row (identity where no RoPE applies)
-  float w, b;                 // per-feature norm weight / LayerNorm weight and bias
+  int kind, h, d;            // region of the lane's four features, head index, first feature inside the head
+  bool rope, head_norm;
+  float w[4], b[4];          // per-feature norm weight / LayerNorm weight and bias
+  const float2* tab;         // RoPE table of the region, row stride `half` pairs
+  int half;
+  float4 cs0, cs1;           // (cos, sin) of the lane's two pairs for this warp's first two rows
 };
 
-__device__ __forceinline__ void post_group(AttnPostArgs& a, int& n0, int& n) {
+__device__ __forceinline__ void post_group(AttnPostArgs& a, int& n0) {
   if (a.group_cols > 0) {
     const int g = n0 / a.group_cols;
     n0 -= g * a.group_cols;
-    n -= g * a.group_cols;
     a.k_cache += (size_t)g * a.k_group_stride;
     a.v_cache += (size_t)g * a.v_group_stride;
     if (a.k_norm) a.k_norm += (size_t)g * a.norm_group_stride;
   }
 }
 
-__device__ __forceinline__ PostCtx qkv_post_prepare(const AttnPostArgs& a_in, int n0, int n, int rows) {
+__device__ __forceinline__ PostCtx qkv_post_prepare(const AttnPostArgs& a_in, int n0, int quad, int lane, int rows) {
   AttnPostArgs a = a_in;
-  post_group(a, n0, n);
+  post_group(a, n0);
   PostCtx c;
   c.p0 = *a.pos0;
-  c.w = 1.f;
-  c.b = 0.f;
-  const int q_end = a.col_q + a.heads * a.head_dim;
-  const int k_end = a.col_k + a.kv_heads * a.head_dim;
-  const bool t_iq = a.idx_heads > 0 && n0 >= a.col_iq && n0 < a.col_iq + a.idx_heads * a.idx_dim;
-  const bool t_ik = a.idx_heads > 0 && n0 == a.col_ik;
-  const float2* tab = nullptr;
-  int half = 0, pair = 0;
-  if (t_iq || t_ik) {
-    const int d = n - n0;
-    if (d < a.idx_rope) { tab = a.idx_rope_tab; half = a.idx_rope / 2; pair = d >> 1; }
-    if (t_ik && d < a.idx_dim) { c.w = __bfloat162float(a.ik_w[d]); c.b = __bfloat162float(a.ik_b[d]); }
-  } else {
-    const bool is_q = n >= a.col_q && n < q_end;
-    const bool is_k = n >= a.col_k && n < k_end;
-    if (is_q || is_k) {
-      const int off = is_q ? n - a.col_q : n - a.col_k;
-      const int d = off % a.head_dim;
-      if (d < a.rope_dim) { tab = a.rope; half = a.rope_dim / 2; pair = d >> 1; }
-      const __nv_bfloat16* nw = is_q ? a.q_norm : a.k_norm;
-      if (nw) c.w = __bfloat162float(nw[d]);
-    }
-  }
+  c.kind = kPostNone; c.h = 0; c.d = 0; c.rope = false; c.head_norm = false; c.tab = nullptr; c.half = 0;
 #pragma unroll
-  for (int r = 0; r < kTok; ++r) c.cs[r] = (tab != nullptr && r < rows) ? tab[r * half + pair] : make_float2(1.f, 0.f);
-  return c;
-}
-
-__device__ __forceinline__ void qkv_post_epilogue(const AttnPostArgs& a_in, const PostCtx& c, int n0, int n, int quad, int lane,
-                                                  float (&v)[kTok], int rows, float (*red)[kTok], bool live) {
-  AttnPostArgs a = a_in;
-  post_group(a, n0, n);
-  const int p0 = c.p0;
-  const bool odd = (n & 1) != 0;
+  for (int i = 0; i < 4; ++i) { c.w[i] = 1.f; c.b[i] = 0.f; }
+  c.cs0 = c.cs1 = make_float4(1.f, 0.f, 1.f, 0.f);
+  const int f = n0 + lane * 4;                       // first of the lane's four features
   const int q_end = a.col_q + a.heads * a.head_dim;
   const int k_end = a.col_k + a.kv_heads * a.head_dim;
   const int v_end = a.col_v + a.kv_heads * a.v_dim;
-  const bool t_iq = a.idx_heads > 0 && n0 >= a.col_iq && n0 < a.col_iq + a.idx_heads * a.idx_dim;
-  const bool t_ik = a.idx_heads > 0 && n0 == a.col_ik;
-  if (t_iq) {
-    // indexer query head: bf16 -> RoPE -> bf16 -> e4m3 with a per-(row, head) scale
-    const int h = (n0 - a.col_iq) / a.idx_dim, d = n - n0;
-    float x[kTok], am[kTok];
+  const __nv_bfloat16* nw = nullptr;
+  if (a.idx_heads > 0 && n0 >= a.col_iq && n0 < a.col_iq + a.idx_heads * a.idx_dim) {
+    c.kind = kPostIq; c.h = (n0 - a.col_iq) / a.idx_dim; c.d = f - n0;
+    if (c.d < a.idx_rope) { c.rope = true; c.tab = a.idx_rope_tab; c.half = a.idx_rope / 2; }
+  } else if (a.idx_heads > 0 && n0 == a.col_ik) {
+    c.kind = kPostIk; c.d = f - n0;
+    if (c.d < a.idx_rope) { c.rope = true; c.tab = a.idx_rope_tab; c.half = a.idx_rope / 2; }
+    if (c.d < a.idx_dim) {
 #pragma unroll
-    for (int r = 0; r < kTok; ++r) {
-      x[r] = round_bf16(v[r]);
-      const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
-      if (r < rows && d < a.idx_rope) x[r] = round_bf16(rope_lane(x[r], other, odd, c.cs[r]));
-      am[r] = fabsf(x[r]);
+      for (int i = 0; i < 4; ++i) { c.w[i] = __bfloat162float(a.ik_w[c.d + i]); c.b[i] = __bfloat162float(a.ik_b[c.d + i]); }
     }
-    epi_reduce16<false>(am, rows, red, quad, lane);
-#pragma unroll
-    for (int r = 0; r < kTok; ++r)
-      if (r < rows && live) {
-        const float s = am[r] > 0.f ? am[r] / 448.f : 1.f;
-        a.iq8[((size_t)r * a.idx_heads + h) * a.idx_dim + d] = e4m3_bits(x[r] / s);
-        if (d == 0) a.iq_scale[r * a.idx_heads + h] = s;
-      }
-    return;
+  } else if (f >= a.col_q && f < q_end) {
+    c.kind = kPostQ; c.h = (f - a.col_q) / a.head_dim; c.d = (f - a.col_q) - c.h * a.head_dim; nw = a.q_norm;
+  } else if (f >= a.col_k && f < k_end) {
+    c.kind = kPostK; c.h = (f - a.col_k) / a.head_dim; c.d = (f - a.col_k) - c.h * a.head_dim; nw = a.k_norm;
+  } else if (f >= a.col_v && f < v_end) {
+    c.kind = kPostV; c.d = f - a.col_v;
+  } else if (a.idx_heads > 0 && f >= a.col_iw && f < a.col_iw + a.idx_heads) {
+    c.kind = kPostIw; c.d = f - a.col_iw;
   }
-  if (t_ik) {
-    // indexer key: LayerNorm (fp32) -> bf16 -> RoPE -> bf16 -> e4m3 with a per-row scale amax / 448
-    const int d = n - n0;
-    const bool in = d < a.idx_dim;
-    float t[kTok];
+  if (c.kind == kPostQ || c.kind == kPostK) {
+    if (c.d < a.rope_dim) { c.rope = true; c.tab = a.rope; c.half = a.rope_dim / 2; }
+    if (nw) {
+      c.head_norm = true;
 #pragma unroll
-    for (int r = 0; r < kTok; ++r) t[r] = in ? v[r] : 0.f;
-    epi_reduce16<true>(t, rows, red, quad, lane);
-    float dv[kTok];
-#pragma unroll
-    for (int r = 0; r < kTok; ++r) { dv[r] = in ? v[r] - t[r] / (float)a.idx_dim : 0.f; t[r] = dv[r] * dv[r]; }
-    epi_reduce16<true>(t, rows, red, quad, lane);
-    float x[kTok];
-#pragma unroll
-    for (int r = 0; r < kTok; ++r) {
-      x[r] = in ? round_bf16(dv[r] * rsqrtf(t[r] / (float)a.idx_dim + a.ln_eps) * c.w + c.b) : 0.f;
-      const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
-      if (r < rows && d < a.idx_rope) x[r] = round_bf16(rope_lane(x[r], other, odd, c.cs[r]));
-      t[r] = fabsf(x[r]);
+      for (int i = 0; i < 4; ++i) c.w[i] = __bfloat162float(nw[c.d + i]);
     }
-    epi_reduce16<false>(t, rows, red, quad, lane);
+  }
+  if (c.rope) {
+    const float4* t = reinterpret_cast<const float4*>(c.tab + (c.d >> 1));      // two pairs = 16 bytes, 16-byte aligned
+    if (quad < rows) c.cs0 = __ldg(t + (size_t)quad * (c.half >> 1));
+    if (quad + 4 < rows) c.cs1 = __ldg(t + (size_t)(quad + 4) * (c.half >> 1));
+  }
+  return c;
+}
+
+// `v`: the thread's accumulators (feature n0 + quad * 32 + lane, one per token row).  `stage`: [16][128] floats of
+// shared memory owned by the epilogue warps.  Called by all 128 epilogue threads of the CTA that holds the full sums.
+__device__ __forceinline__ void qkv_post_epilogue(const AttnPostArgs& a_in, const PostCtx& c, int n0, int quad, int lane,
+                                                  const float (&v)[kTok], int rows, float* stage, bool live) {
+  AttnPostArgs a = a_in;
+  post_group(a, n0);
+  const int col = quad * 32 + lane;
 #pragma unroll
-    for (int r = 0; r < kTok; ++r)
-      if (r < rows && live && in) {
-        const float s = t[r] > 0.f ? t[r] / 448.f : 1.f;
-        const size_t pos = (size_t)(p0 + r);
-        a.ik_cache[pos * a.idx_dim + d] = e4m3_bits(x[r] / s);
-        if (d == 0) a.ik_scale[pos] = s;
+  for (int r = 0; r < kTok; ++r)
+    if (r < rows) stage[r * kTileN + col] = v[r];
+  epi_bar();
+  if (!live) return;
+  int it = 0;
+#pragma unroll 1
+  for (int r = quad; r < rows; r += 4, ++it) {
+    const float4 v4 = *reinterpret_cast<const float4*>(stage + r * kTileN + lane * 4);
+    float x[4] = {v4.x, v4.y, v4.z, v4.w};
+    const int pos = c.p0 + r;
+    float4 cs = make_float4(1.f, 0.f, 1.f, 0.f);
+    if (c.rope) cs = it == 0 ? c.cs0 : (it == 1 ? c.cs1 : __ldg(reinterpret_cast<const float4*>(c.tab + (c.d >> 1)) + (size_t)r * (c.half >> 1)));
+    if (c.kind == kPostIq || c.kind == kPostIk) {
+      // whole tile = one indexer head / the indexer key (uniform over the warp)
+      if (c.kind == kPostIk) {
+        // LayerNorm in fp32 over idx_dim features
+        const bool in = c.d < a.idx_dim;
+        float t = in ? (x[0] + x[1]) + (x[2] + x[3]) : 0.f;
+        const float mean = warp_sum_f(t) / (float)a.idx_dim;
+        float dv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dv[i] = in ? x[i] - mean : 0.f;
+        t = (dv[0] * dv[0] + dv[1] * dv[1]) + (dv[2] * dv[2] + dv[3] * dv[3]);
+        const float inv = rsqrtf(warp_sum_f(t) / (float)a.idx_dim + a.ln_eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = in ? round_bf16(dv[i] * inv * c.w[i] + c.b[i]) : 0.f;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i]);
       }
-    return;
-  }
-  const bool is_q = n >= a.col_q && n < q_end;
-  const bool is_k = n >= a.col_k && n < k_end;
-  const bool is_v = n >= a.col_v && n < v_end;
-  const bool is_w = a.idx_heads > 0 && n >= a.col_iw && n < a.col_iw + a.idx_heads;
-  const int hq = is_q ? (n - a.col_q) / a.head_dim : (is_k ? (n - a.col_k) / a.head_dim : 0);
-  const int d = is_q ? (n - a.col_q) - hq * a.head_dim : (is_k ? (n - a.col_k) - hq * a.head_dim : 0);
-  float x[kTok];
+      if (c.rope) {
+        rope_pair(x[0], x[1], make_float2(cs.x, cs.y));
+        rope_pair(x[2], x[3], make_float2(cs.z, cs.w));
 #pragma unroll
-  for (int r = 0; r < kTok; ++r) x[r] = round_bf16(v[r]);
-  // per-head RMS norm (heads are whole tiles): uniform over the tile
-  const bool t_qn = a.q_norm != nullptr && n0 >= a.col_q && n0 < q_end;
-  const bool t_kn = a.k_norm != nullptr && n0 >= a.col_k && n0 < k_end;
-  if (t_qn || t_kn) {
-    float ss[kTok];
+        for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i]);
+      }
+      const float am = warp_max_f(fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))));
+      const float sc = am > 0.f ? am / 448.f : 1.f;
+      uint32_t q4 = 0u;
 #pragma unroll
-    for (int r = 0; r < kTok; ++r) ss[r] = x[r] * x[r];
-    epi_reduce16<true>(ss, rows, red, quad, lane);
-#pragma unroll
-    for (int r = 0; r < kTok; ++r) x[r] = round_bf16(x[r] * rsqrtf(ss[r] / (float)a.head_dim + a.norm_eps) * c.w);
-  }
-#pragma unroll
-  for (int r = 0; r < kTok; ++r) {
-    const float other = __shfl_xor_sync(0xffffffffu, x[r], 1);
-    if (r >= rows || !live) continue;
-    const int pos = p0 + r;
+      for (int i = 0; i < 4; ++i) q4 |= (uint32_t)e4m3_bits(x[i] / sc) << (8 * i);
+      if (c.kind == kPostIq) {
+        *reinterpret_cast<uint32_t*>(a.iq8 + ((size_t)r * a.idx_heads + c.h) * a.idx_dim + c.d) = q4;
+        if (lane == 0) a.iq_scale[r * a.idx_heads + c.h] = sc;
+      } else if (c.d < a.idx_dim) {
+        *reinterpret_cast<uint32_t*>(a.ik_cache + (size_t)pos * a.idx_dim + c.d) = q4;
+        if (lane == 0) a.ik_scale[pos] = sc;
+      }
+      continue;
+    }
     const size_t slot = a.ring > 0 ? (size_t)(pos % a.ring) : (a.ring < 0 ? (size_t)r : (size_t)pos);
-    if (is_q || is_k) {
-      float o = x[r];
-      if (d < a.rope_dim) o = rope_lane(x[r], other, odd, c.cs[r]);
-      if (is_q) a.q_out[((size_t)r * a.heads + hq) * a.head_dim + d] = __float2bfloat16_rn(o);
-      else a.k_cache[(slot * a.kv_heads + hq) * a.head_dim + d] = __float2bfloat16_rn(o);
-    } else if (is_v) {
-      a.v_cache[slot * a.kv_heads * a.v_dim + (n - a.col_v)] = __float2bfloat16_rn(v[r] * a.value_scale);
-    } else if (is_w) {
-      a.ihw[r * a.idx_heads + (n - a.col_iw)] = v[r] * a.idx_weight_scale;
+    if (c.kind == kPostQ || c.kind == kPostK) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i]);
+      if (c.head_norm) {                               // heads are whole tiles here: uniform over the warp
+        const float ss = warp_sum_f((x[0] * x[0] + x[1] * x[1]) + (x[2] * x[2] + x[3] * x[3]));
+        const float inv = rsqrtf(ss / (float)a.head_dim + a.norm_eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = round_bf16(x[i] * inv * c.w[i]);
+      }
+      if (c.rope) {
+        rope_pair(x[0], x[1], make_float2(cs.x, cs.y));
+        rope_pair(x[2], x[3], make_float2(cs.z, cs.w));
+      }
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0], x[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2], x[3]);
+      __nv_bfloat16* dst = c.kind == kPostQ ? a.q_out + ((size_t)r * a.heads + c.h) * a.head_dim + c.d
+                                            : a.k_cache + (slot * a.kv_heads + c.h) * a.head_dim + c.d;
+      *reinterpret_cast<uint2*>(dst) = o;
+    } else if (c.kind == kPostV) {
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0] * a.value_scale, x[1] * a.value_scale);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2] * a.value_scale, x[3] * a.value_scale);
+      *reinterpret_cast<uint2*>(a.v_cache + slot * a.kv_heads * a.v_dim + c.d) = o;
+    } else if (c.kind == kPostIw) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (c.d + i < a.idx_heads) a.ihw[r * a.idx_heads + c.d + i] = x[i] * a.idx_weight_scale;
     }
   }
 }
@@ -627,7 +644,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   uint8_t* ball = smem + Cfg::kRingBytes;                                    // kBNorm: the CTA's token operand
   float* bscale = reinterpret_cast<float*>(ball + kb_count * kBTileBytes);   // kBNorm e4m3: [16][kb_count]
   GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(smem + Cfg::kRingBytes + Cfg::operand_bytes(kb_count));
-  float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + 1024);
+  float* out_stage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + 1024);      // [16][128] epilogue staging
+  float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + 1024 + kOutStageBytes);
 
   unsigned long long* stamp = p.stamps ? p.stamps + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 : nullptr;
 #define NRT_STAMP(i) do { if (stamp) stamp[i] = globaltimer(); } while (0)
@@ -799,7 +817,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       if (threadIdx.x == 64) NRT_STAMP(3);
     }
     PostCtx post_ctx;
-    if (EPI == kEpiQkvPost) post_ctx = qkv_post_prepare(p.post, n0, n, p.rows);
+    if (EPI == kEpiQkvPost) post_ctx = qkv_post_prepare(p.post, n0, quad, lane, p.rows);
     float mix0[kTok];
 #pragma unroll
     for (int r = 0; r < kTok; ++r) mix0[r] = 0.f;
@@ -914,7 +932,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       for (int r = 0; r < kTok; ++r)
         if (live && r < p.rows) p.out_bf16[(size_t)r * p.ld_out + n] = __float2bfloat16_rn(silu(mix0[r]) * mix1[r]);
     } else if (EPI == kEpiQkvPost) {
-      if (leader) qkv_post_epilogue(p.post, post_ctx, n0, n, quad, lane, mix0, p.rows, tail->red, live);
+      if (leader) qkv_post_epilogue(p.post, post_ctx, n0, quad, lane, mix0, p.rows, out_stage, leader && (n_groups > 0 || split > 1) && n0 < p.n_total);
     } else if (EPI == kEpiSiluQuant) {
       if (n_groups > 0) {
         // y = silu(gate) * up in fp32; one power-of-two scale per (token, this 128-feature tile).  Live rows only;
