@@ -263,83 +263,83 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
   const int tiles = p.k_total / 128;
   // Rows >= p.rows are left as they are: an MMA column depends on its own token row only, and the columns of
   // dead rows are never stored.
-  // A unit is 16 bytes of operand: 8 bf16 elements, or 16 e4m3 elements (two 16-byte loads of x).  Every load of a
-  // batch is issued before anything waits (one L2 round trip per batch), the per-tile sums of squares included.
-  constexpr int kBatch = FP8 ? 4 : 8;
+  // A unit is 16 bytes of operand: 8 bf16 elements, or 16 e4m3 elements (two 16-byte loads of x).  A thread owns one
+  // column unit (chunk c, unit j) - its norm weights are loaded once - and walks token rows in batches of four whose
+  // loads are all in flight together.  With fewer than 128 column units the threads form 128 / units row groups.
   constexpr int kLoads = FP8 ? 2 : 1;
-  const int total = kb_count * rows * 8;
-  bool have_rs = false;
-  for (int u0 = et; u0 - et < total; u0 += 128 * kBatch) {          // uniform trip count over the 128 threads
-    uint4 xv[kBatch][kLoads], gv[kBatch][kLoads];
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      const int u = u0 + b * 128;
-      if (u < total) {
-        const int j = u & 7, r = (u >> 3) % rows, c = (u >> 3) / rows;
-        const int k = (kb_first + c) * (FP8 ? 128 : 64) + j * (FP8 ? 16 : 8);
-#pragma unroll
-        for (int l = 0; l < kLoads; ++l) {
-          xv[b][l] = *reinterpret_cast<const uint4*>(p.nx + (size_t)r * p.k_total + k + 8 * l);
-          gv[b][l] = __ldg(reinterpret_cast<const uint4*>(p.ngamma + k + 8 * l));
-        }
-      }
-    }
-    if (!have_rs) {
-      // 1 / rms of every row in one round trip: 8 threads per row, each adds the tiles t = sub, sub + 8, ...
-      {
-        const int r = et >> 3, sub = et & 7;
-        float s = 0.f;
-        if (r < rows)
-          for (int t = sub; t < tiles; t += 8) s += __ldcg(p.nssq + t * kTok + r);
-#pragma unroll
-        for (int off = 4; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (sub == 0 && r < rows) rs_s[r] = rsqrtf(s / (float)p.k_total + p.neps);
-      }
-      epi_bar();
-      have_rs = true;
+  constexpr int kElems = FP8 ? 128 : 64;
+  const int units = kb_count * 8;
+  const int groups = units < 128 ? 128 / units : 1;
+  const int g = units < 128 ? et / units : 0;
+  // 1 / rms of every row in one round trip: 8 threads per row, each adds the tiles t = sub, sub + 8, ...
+  {
+    const int r = et >> 3, sub = et & 7;
+    float ssum = 0.f;
+    if (r < rows) {
+#pragma unroll 4
+      for (int t = sub; t < tiles; t += 8) ssum += __ldcg(p.nssq + t * kTok + r);
     }
 #pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      const int u = u0 + b * 128;
-      const bool on = u < total;
-      const int j = u & 7, r = on ? (u >> 3) % rows : 0, c = on ? (u >> 3) / rows : 0;
-      const float rs = rs_s[r];
-      float o[8 * kLoads];
-      float am = 0.f;
-      if (on) {
+    for (int off = 4; off > 0; off >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, off);
+    if (sub == 0 && r < rows) rs_s[r] = rsqrtf(ssum / (float)p.k_total + p.neps);
+  }
+  epi_bar();
+#pragma unroll 1
+  for (int cu = units < 128 ? et % units : et; cu < units && g < groups; cu += 128) {
+    const int c = cu >> 3, j = cu & 7;
+    const int k = (kb_first + c) * kElems + j * (kElems / 8);
+    uint4 gv[kLoads];
+#pragma unroll
+    for (int l = 0; l < kLoads; ++l) gv[l] = __ldg(reinterpret_cast<const uint4*>(p.ngamma + k + 8 * l));
+#pragma unroll 1
+    for (int r0 = g; r0 < rows; r0 += 4 * groups) {
+      uint4 xv[4][kLoads];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int r = r0 + b * groups;
+#pragma unroll
+        for (int l = 0; l < kLoads; ++l)
+          xv[b][l] = r < rows ? *reinterpret_cast<const uint4*>(p.nx + (size_t)r * p.k_total + k + 8 * l) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int r = r0 + b * groups;
+        const bool on = r < rows;
+        const float rs = rs_s[on ? r : 0];
+        float o[8 * kLoads];
 #pragma unroll
         for (int l = 0; l < kLoads; ++l) {
           const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xv[b][l]);
-          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv[b][l]);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv[l]);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
-            o[8 * l + 2 * q] = round_bf16(f.x * rs * g.x);
-            o[8 * l + 2 * q + 1] = round_bf16(f.y * rs * g.y);
+            const float2 f = __bfloat1622float2(h[q]), gg = __bfloat1622float2(gh[q]);
+            o[8 * l + 2 * q] = round_bf16(f.x * rs * gg.x);
+            o[8 * l + 2 * q + 1] = round_bf16(f.y * rs * gg.y);
           }
         }
-      }
-      uint4 w;
-      if (!FP8) {
-        __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+        uint4 w;
+        if (!FP8) {
+          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) wh[q] = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
-      } else {
-        // the 8 units of a (row, chunk) sit in 8 consecutive lanes
-        if (on) {
+          for (int q = 0; q < 4; ++q) wh[q] = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
+        } else {
+          // the 8 units of a (row, chunk) sit in 8 consecutive lanes (same row group, same chunk)
+          float am = 0.f;
 #pragma unroll
           for (int q = 0; q < 8 * kLoads; ++q) am = fmaxf(am, fabsf(o[q]));
+#pragma unroll
+          for (int off = 4; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffu << (et & 24), am, off));
+          const float sc = pow2_scale(am);
+          const float inv = 1.0f / sc;                 // a power of two: the product is the exact quotient
+          uint8_t* wb = reinterpret_cast<uint8_t*>(&w);
+#pragma unroll
+          for (int q = 0; q < 8 * kLoads; ++q) wb[q] = e4m3_bits(o[q] * inv);
+          if (on && j == 0) bscale[r * kb_count + c] = sc;
         }
-#pragma unroll
-        for (int off = 4; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-        const float sc = pow2_scale(am);
-        uint8_t* wb = reinterpret_cast<uint8_t*>(&w);
-#pragma unroll
-        for (int q = 0; q < 8 * kLoads; ++q) wb[q] = e4m3_bits(o[q] / sc);
-        if (on && j == 0) bscale[r * kb_count + c] = sc;
+        if (on)
+          *reinterpret_cast<uint4*>(ball + c * kBTileBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = w;
       }
-      if (on)
-        *reinterpret_cast<uint4*>(ball + c * kBTileBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = w;
     }
   }
 }

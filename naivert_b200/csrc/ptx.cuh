@@ -81,10 +81,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: polls until a wall-clock deadline (kWaitLimitNs after the first slow poll).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site) {
-  for (uint32_t i = 0; i < 64; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+// The deadline logic is one out-of-line function: a wait appears at dozens of sites in a kernel, and code that runs
+// once per launch is paid for in instruction fetch.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site) {
   const uint64_t deadline = globaltimer() + kWaitLimitNs;
+#pragma unroll 1
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u) {
@@ -94,6 +95,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   }
   report(status, site);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, site);
 }
 // After a failed wait, give this CTA's asynchronous copies time to land before it exits.
 __device__ __forceinline__ void drain_on_error(const uint32_t* status) {
@@ -133,8 +140,9 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site) {
+static __device__ __noinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site) {
   const uint64_t deadline = globaltimer() + kWaitLimitNs;
+#pragma unroll 1
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((i & 63u) == 63u) {
@@ -250,9 +258,10 @@ __device__ __forceinline__ void ld_tagged(const uint64_t* src, uint32_t& tag, ui
   asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(payload), "=r"(tag) : "l"(src) : "memory");
 }
 // Poll until the word carries `tag`; bounded by a poll count and a wall-clock deadline.
-__device__ __forceinline__ bool wait_tagged(const uint64_t* src, uint32_t tag, uint32_t& payload, uint64_t deadline_ns,
-                                            uint32_t* status, uint32_t site) {
+static __device__ __noinline__ bool wait_tagged(const uint64_t* src, uint32_t tag, uint32_t& payload, uint64_t deadline_ns,
+                                         uint32_t* status, uint32_t site) {
   uint32_t t;
+#pragma unroll 1
   for (uint32_t i = 0;; ++i) {
     ld_tagged(src, t, payload);
     if (t == tag) return true;
