@@ -38,6 +38,7 @@ constexpr int kDnBufs = 8, kDnCols = kTok, kDnBase = 128;    // TMEM columns [12
 constexpr int kMoeTmemCols = 256;
 constexpr int kRanges = 4;                                    // expert-id ranges that share one output tile
 constexpr int kGuTilesMax = 16;
+constexpr int kDnStaged = 256;                                // down units whose scales are staged in shared memory
 
 struct MoeArgs {
   RouterArgs r;
@@ -62,6 +63,9 @@ struct MoeSmem {
   RouterSmem router;
   float probs[kSlotsMax * kTok];
   int active[kSlotsMax];
+  alignas(16) float xs_t[64][kArRows];        // read as float4; gate/up activation scales, [K block][row] (hidden <= 8192)
+  alignas(16) float dn_sc[kDnStaged][kArRows];   // read as float4; down: y scales of this CTA's first kDnStaged units, [unit][row]
+  float dn_w[kDnStaged];          // and their weight-block scales
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
@@ -292,48 +296,52 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     const int rows = p.r.rows;
     bool ok = true;
     // ---- gate/up items
+    // Steps have at most eight token rows: the epilogue reads the first eight columns of an accumulator.  The
+    // activation scales are the same for every item: staged once as [K block][row].
+    constexpr int kR = kArRows;
+    for (int i = tid - 64; i < kbH * kR; i += 128) {
+      const int kb = i / kR, r = i - kb * kR;
+      sm.xs_t[kb][r] = r < rows ? p.r.xs[r * kbH + kb] : 0.f;
+    }
+    epi_bar();
     int ug = 0;
+#pragma unroll 1
     for (int it = cta; it < gu_items && ok; it += kMoeCtas) {
       const int slot = it / kbI, tile = it - slot * kbI;
       const int z = sm.active[slot];
       const int n = tile * kTileN + row;
-      float acc0[kTok], acc1[kTok];
+      float acc0[kR], acc1[kR];
 #pragma unroll
-      for (int r = 0; r < kTok; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+      for (int r = 0; r < kR; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
       const float* ws0 = p.gate_s + ((size_t)z * kbI + tile) * kbH;
       const float* ws1 = p.up_s + ((size_t)z * kbI + tile) * kbH;
+#pragma unroll 1
       for (int kb = 0; kb < kbH; ++kb, ++ug) {
         const int buf = ug % kGuBufs;
-        float sc[kTok];
-#pragma unroll
-        // written by other CTAs before the arrival counter and never read here before: a plain (L1-cached) load is
-        // coherent, and the 32 scales of a row share one line
-        for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? p.r.xs[r * kbH + kb] : 0.f;
+        const float4 s0 = *reinterpret_cast<const float4*>(&sm.xs_t[kb][0]), s1 = *reinterpret_cast<const float4*>(&sm.xs_t[kb][4]);
+        const float sc[kR] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
         const float w0 = __ldg(ws0 + kb), w1 = __ldg(ws1 + kb);
         if (!mbar_wait(&sm.gu_full[buf], (ug / kGuBufs) & 1, status, kSiteAccFull | buf)) { ok = false; break; }
         tc_fence_after();
-        float v0[kTok], v1[kTok];
-        tmem_ld16(lane_addr + buf * kGuCols, v0);
-        tmem_ld16(lane_addr + buf * kGuCols + kTok, v1);
+        float v0[kR], v1[kR];
+        tmem_ld8(lane_addr + buf * kGuCols, v0);
+        tmem_ld8(lane_addr + buf * kGuCols + kTok, v1);
         tc_fence_before();
         mbar_arrive(&sm.gu_empty[buf]);
 #pragma unroll
-        for (int r = 0; r < kTok; ++r) {
+        for (int r = 0; r < kR; ++r) {
           acc0[r] += v0[r] * (sc[r] * w0);
           acc1[r] += v1[r] * (sc[r] * w1);
         }
       }
       if (!ok) break;
       // y = silu(gate) * up, one power-of-two scale per (row, this tile), e4m3
-      float y[kTok];
+      float y[kR];
 #pragma unroll
-      for (int r = 0; r < kTok; ++r) {
-        y[r] = 0.f;
-        if (r < rows) {
-          y[r] = silu(acc0[r]) * acc1[r];
-          const float m = warp_max_f(fabsf(y[r]));
-          if (lane == 0) tail->red[quad][r] = m;
-        }
+      for (int r = 0; r < kR; ++r) {
+        y[r] = silu(acc0[r]) * acc1[r];
+        const float m = warp_max_f(fabsf(y[r]));
+        if (lane == 0) tail->red[quad][r] = m;
       }
       epi_bar();
       if (row < rows) {
@@ -342,7 +350,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
       }
       epi_bar();
 #pragma unroll
-      for (int r = 0; r < kTok; ++r)
+      for (int r = 0; r < kR; ++r)
         if (r < rows) {
           const float s = tail->rs[r];
           p.y8[((size_t)slot * kTok + r) * p.inter + n] = e4m3_bits(y[r] * (1.0f / s));
@@ -360,41 +368,52 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     const int n = dn_tile * kTileN + row;
     int ud = 0;
     // The y scales of a slot are final once the producer has seen the slot flags, i.e. once this CTA's first down
-    // accumulator has completed (all flags are polled before the first activation tile is requested); from then on
-    // they are fetched ahead of the accumulator wait.
-    bool flags_seen = false;
+    // accumulator has completed (all flags are polled before the first activation tile is requested).  At that point
+    // the epilogue warps fetch the scales of all their units in one round of loads into shared memory; without that
+    // every unit would pay an L2 round trip of its own and the accumulator ring would fill up behind the epilogue.
+    bool staged = false;
+#pragma unroll 1
     for (int s = 0; s < dn_slots && ok; ++s) {
       const int slot = dn_lo + s;
-      const int z = sm.active[slot];
-      float acc[kTok];
+      float acc[kR];
 #pragma unroll
-      for (int r = 0; r < kTok; ++r) acc[r] = 0.f;
-      const float* ws = p.down_s + ((size_t)z * tilesH + dn_tile) * kbI;
+      for (int r = 0; r < kR; ++r) acc[r] = 0.f;
+#pragma unroll 1
       for (int kb = 0; kb < kbI; ++kb, ++ud) {
         const int buf = ud % kDnBufs;
-        const float w0 = __ldg(ws + kb);
-        float sc[kTok];
-        if (flags_seen) {
-#pragma unroll
-          for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? p.ys[((size_t)slot * kTok + r) * kbI + kb] : 0.f;
-        }
         if (!mbar_wait(&tail->acc_full[buf], (ud / kDnBufs) & 1, status, kSiteAccFull | 0x10 | buf)) { ok = false; break; }
-        if (!flags_seen) {
+        if (!staged) {
+          for (int i = tid - 64; i < min(dn_units, kDnStaged) * kR; i += 128) {
+            const int uu = i / kR, r = i - uu * kR;
+            const int sl = dn_lo + uu / kbI, k2 = uu % kbI;
+            sm.dn_sc[uu][r] = r < rows ? p.ys[((size_t)sl * kTok + r) * kbI + k2] : 0.f;
+            if (r == 0) sm.dn_w[uu] = __ldg(p.down_s + ((size_t)sm.active[sl] * tilesH + dn_tile) * kbI + k2);
+          }
+          epi_bar();
+          staged = true;
+        }
+        float sc[kR];
+        float w0;
+        if (ud < kDnStaged) {
+          const float4 s0 = *reinterpret_cast<const float4*>(&sm.dn_sc[ud][0]), s1 = *reinterpret_cast<const float4*>(&sm.dn_sc[ud][4]);
+          sc[0] = s0.x; sc[1] = s0.y; sc[2] = s0.z; sc[3] = s0.w; sc[4] = s1.x; sc[5] = s1.y; sc[6] = s1.z; sc[7] = s1.w;
+          w0 = sm.dn_w[ud];
+        } else {
 #pragma unroll
-          for (int r = 0; r < kTok; ++r) sc[r] = r < rows ? p.ys[((size_t)slot * kTok + r) * kbI + kb] : 0.f;
-          flags_seen = true;
+          for (int r = 0; r < kR; ++r) sc[r] = r < rows ? p.ys[((size_t)slot * kTok + r) * kbI + kb] : 0.f;
+          w0 = __ldg(p.down_s + ((size_t)sm.active[slot] * tilesH + dn_tile) * kbI + kb);
         }
         tc_fence_after();
-        float v[kTok];
-        tmem_ld16(lane_addr + kDnBase + buf * kDnCols, v);
+        float v[kR];
+        tmem_ld8(lane_addr + kDnBase + buf * kDnCols, v);
         tc_fence_before();
         mbar_arrive(&tail->acc_empty[buf]);
 #pragma unroll
-        for (int r = 0; r < kTok; ++r) acc[r] += v[r] * (sc[r] * w0);
+        for (int r = 0; r < kR; ++r) acc[r] += v[r] * (sc[r] * w0);
       }
       const float* pr = sm.probs + slot * kTok;
 #pragma unroll
-      for (int r = 0; r < kTok; ++r) mix0[r] += pr[r] * acc[r];
+      for (int r = 0; r < kR; ++r) mix0[r] += pr[r] * acc[r];
     }
     if (tid == 64) NRT_STAMP(8);
     // ---- ranges 1..3 hand their partial to range 0 of the tile, which adds them in range order
@@ -445,7 +464,7 @@ extern "C" int nrt_moe_layer(const void* tmGate, const void* tmUp, const void* t
   if (r.w == nullptr && (!r.n_active || !r.active_ids || !r.probs)) return -3;               // routed by nrt_router
   if (r.experts > 2 * kMoeCtas || r.experts > 256 || r.rows < 1 || r.rows > kArRows || r.top_k > 32) return -3;
   if (r.max_slots > kSlotsMax || a.inter / 128 > kGuTilesMax || (r.hidden / 128) * kRanges > kMoeCtas) return -3;
-  if (r.rows * (r.hidden / 128) > 16 * kMoeCtas) return -3;
+  if (r.rows * (r.hidden / 128) > 16 * kMoeCtas || r.hidden / 128 > 64) return -3;
   if (!a.sync || !a.slot_flags || !a.part || !a.part_flags || !a.y8 || !a.ys || !a.ar.status) return -3;
   constexpr int smem = kMoeStages * kMoeStageBytes + 1024 + (int)sizeof(MoeSmem);
   static int resident = -1;
