@@ -35,7 +35,7 @@ def test_tensor_parallel_engine(n):
     r = _run(n)
     assert r["status"] == 0
     assert r["residual_identical"] and r["lockstep"] and r["deterministic"] and r["spec_equals_greedy"], r
-    assert r["verify_mean_rel"] < 0.06 and r["argmax_ok"] and r["sampler_matches_oracle"], r
+    assert r["verify_mean_rel"] < 0.08 and r["argmax_ok"] and r["sampler_matches_oracle"], r
     assert r["real_sampling_tokens"] == 64
 
 
