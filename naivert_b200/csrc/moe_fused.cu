@@ -129,6 +129,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
   if (ROUTE) {
     // ---------------------------------------------------------------- phase R: scores + packet, arrival, selection
     router_scores(p.r, cta, kMoeCtas, sm.router, stamp);     // waits for the upstream grid inside
+    router_packet(p.r, cta, kMoeCtas, sm.router);             // read by other CTAs' TMA after the arrival counter
     __threadfence();
     __syncthreads();
     if (tid == 0) {

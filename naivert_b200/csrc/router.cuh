@@ -103,22 +103,19 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
   if (stamp && threadIdx.x == 0) stamp[12] = globaltimer();
   const __nv_bfloat16* xsrc = inline_norm ? a.x : a.xn;
   const int xld = a.hidden;
-  // e4m3 packet of the normalised rows: pair (row, 128-channel block) number blockIdx.x + gridDim.x * g goes to the
-  // g-th group of 16 threads of this CTA
   const int blocks = a.hidden / 128;
-  const int pairs = (inline_norm && a.x8 != nullptr) ? a.rows * blocks : 0;
-  const int my_pair = cta + n_ctas * (tid >> 4);
-  const bool pk_on = my_pair < pairs;
-  const int pk_r = pk_on ? my_pair % a.rows : 0, pk_b = pk_on ? my_pair / a.rows : 0;
-  uint4 pk_x = make_uint4(0u, 0u, 0u, 0u), pk_g = pk_x;
-  if (pk_on) {
-    const int k = pk_b * 128 + (tid & 15) * 8;
-    pk_x = *reinterpret_cast<const uint4*>(a.x + (size_t)pk_r * a.hidden + k);
-    pk_g = __ldg(reinterpret_cast<const uint4*>(a.gamma + k));
+  // The first four rows' activations are requested before anything waits (they do not depend on the row scales).
+  uint2 xv[4][4];
+  if (fast) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr)
+        xv[i][rr] = (rr < a.rows) ? *reinterpret_cast<const uint2*>(xsrc + (size_t)rr * xld + tid * 4 + 1024 * i) : make_uint2(0u, 0u);
   }
-  // 1 / rms per row from the per-tile sums of squares left behind by the producer of x, then this CTA's share of the
-  // e4m3 packet.  (One copy of this code: the phases below are rolled loops with small bodies on purpose - a kernel
-  // that runs once per layer executes mostly cold code, and instruction fetch is then the top stall reason.)
+  // 1 / rms per row from the per-tile sums of squares left behind by the producer of x.  (The phases below are rolled
+  // loops with small bodies on purpose - a kernel that runs once per layer executes mostly cold code, and instruction
+  // fetch is then the top stall reason.)
   if (inline_norm) {
 #pragma unroll 1
     for (int r = warp; r < a.rows; r += 8) {
@@ -129,44 +126,20 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
       if (lane == 0) rs_s[r] = rsqrtf(ss / (float)a.hidden + a.eps);
     }
     __syncthreads();
-    if (pairs > 0) {                               // uniform over the CTA
-      const float rs = rs_s[pk_r];
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk_x);
-      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&pk_g);
-      float o[8];
-      float am = 0.f;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
-        o[2 * q] = round_bf16(f.x * rs * g.x);
-        o[2 * q + 1] = round_bf16(f.y * rs * g.y);
-        am = fmaxf(am, fmaxf(fabsf(o[2 * q]), fabsf(o[2 * q + 1])));
-      }
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-      const float sc = pow2_scale(am);
-      uint2 q8;
-      uint8_t* qb = reinterpret_cast<uint8_t*>(&q8);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) qb[q] = e4m3_bits(o[q] / sc);
-      if (pk_on) {
-        *reinterpret_cast<uint2*>(a.x8 + (size_t)pk_r * a.hidden + pk_b * 128 + (tid & 15) * 8) = q8;
-        if ((tid & 15) == 0) a.xs[(size_t)pk_r * blocks + pk_b] = sc;
-      }
-    }
   }
   if (stamp && threadIdx.x == 0) stamp[13] = globaltimer();
   if (fast) {
     // four rows at a time: their sixteen loads are in flight together, then the FMAs, then the warp sums
 #pragma unroll 1
     for (int r0 = 0; r0 < a.rows; r0 += 4) {
-      uint2 xv[4][4];
+      if (r0 > 0) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr)
-          xv[i][rr] = (r0 + rr < a.rows) ? *reinterpret_cast<const uint2*>(xsrc + (size_t)(r0 + rr) * xld + tid * 4 + 1024 * i)
-                                         : make_uint2(0u, 0u);
+          for (int rr = 0; rr < 4; ++rr)
+            xv[i][rr] = (r0 + rr < a.rows) ? *reinterpret_cast<const uint2*>(xsrc + (size_t)(r0 + rr) * xld + tid * 4 + 1024 * i)
+                                           : make_uint2(0u, 0u);
+      }
       float acc0[4], acc1[4];
 #pragma unroll
       for (int rr = 0; rr < 4; ++rr) { acc0[rr] = 0.f; acc1[rr] = 0.f; }
@@ -230,6 +203,49 @@ __device__ __forceinline__ void router_scores(const RouterArgs& a, int cta, int 
   }
 }
 
+// This CTA's share of the e4m3 packet of the normalised rows (inline-norm form): pair (row, 128-channel block) number
+// cta + n_ctas * g goes to the g-th group of 16 threads.  Uses the row scales router_scores left in shared memory.
+__device__ __forceinline__ void router_packet(const RouterArgs& a, int cta, int n_ctas, RouterSmem& sm) {
+  if (a.x == nullptr || a.x8 == nullptr) return;
+  const int tid = threadIdx.x;
+  const int blocks = a.hidden / 128;
+  const int pairs = a.rows * blocks;
+  const int my_pair = cta + n_ctas * (tid >> 4);
+  const bool pk_on = my_pair < pairs;
+  const int pk_r = pk_on ? my_pair % a.rows : 0, pk_b = pk_on ? my_pair / a.rows : 0;
+  if (cta >= pairs) return;                          // no group of this CTA has a pair (uniform over the CTA)
+  uint4 pk_x = make_uint4(0u, 0u, 0u, 0u), pk_g = pk_x;
+  if (pk_on) {
+    const int k = pk_b * 128 + (tid & 15) * 8;
+    pk_x = *reinterpret_cast<const uint4*>(a.x + (size_t)pk_r * a.hidden + k);
+    pk_g = __ldg(reinterpret_cast<const uint4*>(a.gamma + k));
+  }
+  const float rs = sm.rs[pk_r];
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk_x);
+  const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&pk_g);
+  float o[8];
+  float am = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 f = __bfloat1622float2(h[q]), g = __bfloat1622float2(gh[q]);
+    o[2 * q] = round_bf16(f.x * rs * g.x);
+    o[2 * q + 1] = round_bf16(f.y * rs * g.y);
+    am = fmaxf(am, fmaxf(fabsf(o[2 * q]), fabsf(o[2 * q + 1])));
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+  const float sc = pow2_scale(am);
+  const float inv = 1.0f / sc;                       // a power of two: the product is the exact quotient
+  uint2 q8;
+  uint8_t* qb = reinterpret_cast<uint8_t*>(&q8);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) qb[q] = e4m3_bits(o[q] * inv);
+  if (pk_on) {
+    *reinterpret_cast<uint2*>(a.x8 + (size_t)pk_r * a.hidden + pk_b * 128 + (tid & 15) * 8) = q8;
+    if ((tid & 15) == 0) a.xs[(size_t)pk_r * blocks + pk_b] = sc;
+  }
+}
+
 // 256 threads; every score must be visible (the caller has synchronised the CTAs).  Results: sm.used / sm.slot_of /
 // sm.n_active, and - when `publish` - the global outputs of RouterArgs.  `probs_s` / `active_s` (shared memory,
 // may be null) receive the slot table for a consumer in the same CTA.
@@ -259,7 +275,6 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
       sc[j] = in ? raw[j] : -FLT_MAX;
       mx = fmaxf(mx, sc[j]);
     }
-    if (stamp && threadIdx.x == 0) { stamp[4] = globaltimer(); stamp[7] = (unsigned long long)(mx != 0.f); }
     if (a.sigmoid) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -280,35 +295,43 @@ __device__ __forceinline__ void router_select(const RouterArgs& a, RouterSmem& s
 #pragma unroll
       for (int j = 0; j < 8; ++j) { sc[j] /= sum; ch[j] = (lane + 32 * j) < a.experts ? sc[j] : -FLT_MAX; }
     }
+    // Every lane sorts its eight candidates once (descending key, lower expert first among equals - the experts of
+    // a lane ascend with j, and the network below never swaps equal keys out of order); a selection step is then
+    // two warp reductions over the lanes' heads and a pop on the winning lane.
     uint32_t kk[8];                                 // order-preserving keys; 0 once taken
+    uint32_t ee[8];                                 // expert of each candidate
 #pragma unroll
-    for (int j = 0; j < 8; ++j) kk[j] = router_order_key(ch[j]);
-    if (stamp && threadIdx.x == 0) stamp[5] = globaltimer() + (kk[0] == 12345u);
+    for (int j = 0; j < 8; ++j) { kk[j] = router_order_key(ch[j]); ee[j] = (uint32_t)(lane + 32 * j); }
+#define NRT_CAS(i, j)                                                                                      \
+    if (kk[j] > kk[i] || (kk[j] == kk[i] && ee[j] < ee[i])) {                                              \
+      const uint32_t tk = kk[i]; kk[i] = kk[j]; kk[j] = tk;                                                \
+      const uint32_t te = ee[i]; ee[i] = ee[j]; ee[j] = te;                                                \
+      const float tp = sc[i]; sc[i] = sc[j]; sc[j] = tp;                                                   \
+    }
+    NRT_CAS(0, 1) NRT_CAS(2, 3) NRT_CAS(4, 5) NRT_CAS(6, 7)
+    NRT_CAS(0, 2) NRT_CAS(1, 3) NRT_CAS(4, 6) NRT_CAS(5, 7)
+    NRT_CAS(1, 2) NRT_CAS(5, 6) NRT_CAS(0, 4) NRT_CAS(3, 7)
+    NRT_CAS(1, 5) NRT_CAS(2, 6)
+    NRT_CAS(1, 4) NRT_CAS(3, 6)
+    NRT_CAS(2, 4) NRT_CAS(3, 5)
+    NRT_CAS(3, 4)
+#undef NRT_CAS
     float psum = 0.f;
     float my_p = 0.f;
     int my_id = -1;
 #pragma unroll 1
     for (int t = 0; t < a.top_k; ++t) {
-      // arg-max over the warp with two hardware reductions: the largest key, then the lowest expert index
-      // among the lanes that hold it
-      uint32_t bk = 0u;
-      int bj = 0;
+      const uint32_t best = __reduce_max_sync(0xffffffffu, kk[0]);
+      const int bi = (int)__reduce_min_sync(0xffffffffu, kk[0] == best ? ee[0] : 0xffffffffu);
+      const float pv = __shfl_sync(0xffffffffu, sc[0], bi & 31);
+      if ((bi & 31) == lane) {                      // pop the head of the winning lane
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (kk[j] > bk) { bk = kk[j]; bj = j; }                     // ascending j keeps the lowest index on ties
-      const uint32_t best = __reduce_max_sync(0xffffffffu, bk);
-      const int bi = (int)__reduce_min_sync(0xffffffffu, bk == best ? (unsigned)(lane + 32 * bj) : 0xffffffffu);
-      float pv = 0.f;
-      if ((bi & 31) == lane) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (j == (bi >> 5)) { pv = sc[j]; kk[j] = 0u; }
+        for (int j = 0; j < 7; ++j) { kk[j] = kk[j + 1]; ee[j] = ee[j + 1]; sc[j] = sc[j + 1]; }
+        kk[7] = 0u;
       }
-      pv = __shfl_sync(0xffffffffu, pv, bi & 31);
       psum += pv;
       if (lane == t) { my_p = pv; my_id = bi; }
     }
-    if (stamp && threadIdx.x == 0) stamp[6] = globaltimer() + (psum == 12345.f);
     const float denom = a.normalize ? psum + 1e-20f : 1.f;
     if (lane < a.top_k) {
       const float p = my_p / denom * a.route_scale;

@@ -841,20 +841,24 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   unsigned long long* stamp = (a.stamps && gridDim.y == 1) ? a.stamps + (size_t)blockIdx.x * 16 : nullptr;
   if (stamp && tid == 0) stamp[0] = globaltimer();
   router_scores(a, blockIdx.x, gridDim.x, sm, stamp);
-  __threadfence();
+  // The CTA's score stores are ordered before the ticket by the barrier (CTA scope) followed by thread 0's fence
+  // (cumulative, GPU scope); the last CTA reads the scores from L2 after the same pair on the acquiring side.
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     const unsigned int t = atomicAdd(a.ticket, 1u);
     last = (t == gridDim.x - 1);
-    if (last) *a.ticket = 0u;
+    if (last) { *a.ticket = 0u; __threadfence(); }
     if (stamp) stamp[1] = globaltimer();
   }
   __syncthreads();
-  if (!last) return;
-  __threadfence();
+  // the activation packet is off the selection's critical path: the other CTAs write their share while the last
+  // one selects
+  if (!last) { router_packet(a, blockIdx.x, gridDim.x, sm); return; }
   if (stamp && tid == 0) stamp[2] = globaltimer();
   router_select(a, sm, true, nullptr, nullptr, stamp);
   if (stamp && tid == 0) stamp[3] = globaltimer();
+  router_packet(a, blockIdx.x, gridDim.x, sm);
 }
 
 }  // namespace
