@@ -131,7 +131,9 @@ def main() -> int:
     ap.add_argument("--model", default="naive-n0.5")
     ap.add_argument("--shape-tp", type=int, default=0,
                     help="diagnostic: run ONE rank's share of a tp-way model on one GPU without peers (not a result)")
-    ap.add_argument("--pdl", action="store_true", help="chain kernels with programmatic dependent launch (default: plain stream order, measured faster)")
+    ap.add_argument("--pdl", dest="pdl", action="store_true", default=None,
+                    help="chain kernels with programmatic dependent launch (default: the engine's default, NAIVERT_PDL)")
+    ap.add_argument("--no-pdl", dest="pdl", action="store_false", help="plain stream order between kernels")
     ap.add_argument("--device-chain", action="store_true", help="the round graph relaunches itself from the device")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
     ap.add_argument("--no-check", action="store_true", help="skip the small-geometry correctness self-check (outside the timed region)")
@@ -267,7 +269,7 @@ def main() -> int:
     check = None
     last_prefill, kv_bytes = eng.last_prefill, eng.kv_bytes()
     kernels_per_round, host_launches = int(r.kernels_per_round), r.host_launches
-    path_info = {"pdl": bool(a.pdl), "device_chain": bool(a.device_chain), "fused_step": bool(r.t.fused),
+    path_info = {"pdl": bool(r.pdl), "device_chain": bool(a.device_chain), "fused_step": bool(r.t.fused),
                  "fused_moe": bool(getattr(r.t, "moe_fused", False)), "markov_chain": bool(getattr(r.draft, "markov_chain", False))}
     if not a.no_check and not a.shape_tp:
         eng.close()

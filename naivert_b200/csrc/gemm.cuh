@@ -674,14 +674,17 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
   // most one successor is resident early (a chain of waiting grids clogs the CTA scheduler).
   // stages whose weight tile is issued before the wait
   const int early = GROUP == kGroupNone ? min(kb_count, Cfg::kStages) : 0;
+  // weight tiles are read once per step: they are the first to leave L2, so the step's activations, KV rows and
+  // hand-off buffers stay resident while gigabytes of weights stream through
+  const uint64_t stream_once = l2_policy_evict_first();
   if (GROUP == kGroupNone) {
     if (warp == 0 && elect_one()) {
       for (int u = 0; u < early; ++u) {
         uint8_t* sa = smem + u * Cfg::kStageBytes;
         mbar_expect_tx(&tail->full[u], Cfg::kStageBytes);
         const int kx = (kb_first + u) * kElemsPerStage;
-        tma_load_3d(sa, &tmA0, &tail->full[u], kx, n0, p.a_group);
-        if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[u], kx, n0, p.a_group);
+        tma_load_3d_hint(sa, &tmA0, &tail->full[u], kx, n0, p.a_group, stream_once);
+        if (DUAL) tma_load_3d_hint(sa + kATileBytes, &tmA1, &tail->full[u], kx, n0, p.a_group, stream_once);
       }
     }
   }
@@ -730,8 +733,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         const int kx = (kb_first + kb) * kElemsPerStage;
         if (u >= early) {
           mbar_expect_tx(&tail->full[st], Cfg::kStageBytes);
-          tma_load_3d(sa, &tmA0, &tail->full[st], kx, n0, z);
-          if (DUAL) tma_load_3d(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z);
+          tma_load_3d_hint(sa, &tmA0, &tail->full[st], kx, n0, z, stream_once);
+          if (DUAL) tma_load_3d_hint(sa + kATileBytes, &tmA1, &tail->full[st], kx, n0, z, stream_once);
         }
         if (BSRC != kBTma) continue;
         const int brow = (GROUP == kGroupLoop) ? slot * kTok : ((GROUP == kGroupItem && p.row_offsets) ? p.row_offsets[slot] : 0);
