@@ -3,7 +3,8 @@
 // One CTA (8 warps) per (KV head, query row, key split).  The query heads that share the KV head are the
 // M = 16 side of bf16 m16n8k16 MMAs, so every key / value row is gathered once per KV head (at tp = 8 the eight
 // local query heads share one KV head: the scalar per-head kernel read each key eight times).  Keys come in
-// chunks of 64 - the row's sliding window, its dense prefix, its top-k selection list, or the draft's context
+// chunks of 128 (a sliding window, or one of sixteen splits of a 2048-key selection, is a single chunk: one gather,
+// one soft-max pass) - the row's sliding window, its dense prefix, its top-k selection list, or the draft's context
 // window followed by the block's own rows - staged with cp.async in two buffers (the next chunk's gather runs
 // under the current chunk's math), scored (S = Q K^T), soft-maxed online per head and accumulated (O += P V,
 // V fragments through ldmatrix.trans).  Long key lists (2048 selected keys) are split over grid.z CTAs; each
@@ -50,7 +51,7 @@ struct AttnArgs {               // must match target_kernels.cu
   unsigned int* tickets;
 };
 
-constexpr int kVd = 128, kChunk = 64, kM = 16, kStagesKV = 2;
+constexpr int kVd = 128, kChunk = 128, kM = 16, kStagesKV = 2;
 constexpr int kVStride = kVd + 8;        // 272-byte rows: ldmatrix rows fall into distinct 16-byte bank groups
 constexpr int kSStride = kVd + 4;        // fp32; also carries the 128 output channels at the end
 constexpr int kPStride = kChunk + 8;     // bf16
@@ -89,13 +90,19 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
 
 // key j of the row's list -> cache row (>= 0) or block row -(id + 1) (draft block mode)
 struct KeyList {
-  int mode, lo, ctx, count, top_k, ring;
+  int mode, lo, ctx, count, top_k, ring, base;
   bool use_sel;
   const int* sel;
   __device__ __forceinline__ int id(int j) const {
     if (mode == 1) return use_sel ? sel[j] : j;
     if (mode == 2) return j < ctx ? lo + j : -(j - ctx) - 1;
     return lo + j;
+  }
+  // cache row of a non-negative id; consecutive window keys wrap around the ring at most once (base = lo % ring)
+  __device__ __forceinline__ size_t slot(int id, int j) const {
+    if (ring <= 0) return (size_t)id;
+    if (mode == 0) { const int s = base + j; return (size_t)(s >= ring ? s - ring : s); }
+    return (size_t)(id % ring);
   }
 };
 
@@ -115,9 +122,9 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
   const int qr = lane >> 2, qc = (lane & 3) * 2;             // fragment row / column pair of this lane
 
   KeyList kl;
-  kl.mode = a.mode; kl.top_k = a.top_k; kl.ring = a.ring; kl.lo = 0; kl.ctx = 0; kl.use_sel = false;
+  kl.mode = a.mode; kl.top_k = a.top_k; kl.ring = a.ring; kl.lo = 0; kl.ctx = 0; kl.use_sel = false; kl.base = 0;
   kl.sel = a.sel + (size_t)r * a.top_k;
-  if (a.mode == 0) { kl.lo = max(0, pos - a.window + 1); kl.count = pos - kl.lo + 1; }
+  if (a.mode == 0) { kl.lo = max(0, pos - a.window + 1); kl.count = pos - kl.lo + 1; kl.base = a.ring > 0 ? kl.lo % a.ring : 0; }
   else if (a.mode == 1) { kl.use_sel = pos + 1 > a.top_k; kl.count = kl.use_sel ? a.top_k : pos + 1; }
   else { kl.lo = max(0, p0 - a.window); kl.ctx = p0 - kl.lo; kl.count = kl.ctx + a.rows; }
   const int count = kl.count;
@@ -134,7 +141,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
       const int id = valid ? kl.id(j) : 0;
       const __nv_bfloat16* src;
       if (id < 0) src = a.k_blk + ((size_t)(-id - 1) * a.kv_heads + g) * HD;
-      else src = a.k_cache + ((a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id) * a.kv_heads + g) * HD;
+      else src = a.k_cache + (kl.slot(id, j) * a.kv_heads + g) * HD;
       cp_async16(&sm.k[stage][t][c * 8], src + c * 8, valid);
     }
     for (int i = tid; i < kChunk * (kVd / 8); i += 256) {
@@ -144,7 +151,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
       const int id = valid ? kl.id(j) : 0;
       const __nv_bfloat16* src;
       if (id < 0) src = a.v_blk + ((size_t)(-id - 1) * a.kv_heads + g) * kVd;
-      else src = a.v_cache + ((a.ring > 0 ? (size_t)(id % a.ring) : (size_t)id) * a.kv_heads + g) * kVd;
+      else src = a.v_cache + (kl.slot(id, j) * a.kv_heads + g) * kVd;
       cp_async16(&sm.v[stage][t][c * 8], src + c * 8, valid);
     }
   };
@@ -181,9 +188,17 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
     cp_async_commit();                                        // (possibly empty) group of chunk ci + 1
     cp_async_wait<1>();                                       // this thread's copies of chunk ci have landed
     __syncthreads();                                          // ... and everybody else's
-    // ---- S = Q K^T: warp w scores keys [8w, 8w + 8) for all heads
-    {
-      const int key0 = warp * 8;
+    // ---- S = Q K^T: warp w scores keys [8w, 8w + 8) and [64 + 8w, 64 + 8w + 8) for all heads
+#pragma unroll
+    for (int nt = 0; nt < kChunk / 64; ++nt) {
+      const int key0 = nt * 64 + warp * 8;
+      if (key0 >= n) {                                        // whole tile beyond the chunk's keys (uniform per warp)
+        if (lane < 16) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sm.s[lane][key0 + j] = -FLT_MAX;
+        }
+        continue;
+      }
       float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {
@@ -233,6 +248,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
       for (int t = 0; t < 2; ++t) { oc[t][0] *= c_lo; oc[t][1] *= c_lo; oc[t][2] *= c_hi; oc[t][3] *= c_hi; }
 #pragma unroll
       for (int kk = 0; kk < kChunk / 16; ++kk) {
+        if (kk * 16 >= n) break;                              // probabilities beyond the chunk's keys are zero
         uint32_t pa[4];
         pa[0] = *reinterpret_cast<const uint32_t*>(&sm.p[qr][kk * 16 + qc]);
         pa[1] = *reinterpret_cast<const uint32_t*>(&sm.p[qr + 8][kk * 16 + qc]);
