@@ -130,32 +130,67 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
 // folding its best candidate into best[step]; the CTA that completes a step's count runs the tensor-parallel
 // exchange, writes block_ids[step + 1] and publishes the step's generation; the others wait for that generation
 // (bounded) and go on with the next previous-token row.  The grid must be resident at once (checked at launch).
-__global__ void __launch_bounds__(256) markov_chain_kernel(const MarkovArgs a, int steps, unsigned long long* arrive,
+__global__ void __launch_bounds__(256, 2) markov_chain_kernel(const MarkovArgs a, int steps, unsigned long long* arrive,
                                                            unsigned int* step_gen) {
   __shared__ float w1s[512];
   __shared__ unsigned long long sbest;
   __shared__ unsigned int s_gen;
   __shared__ int s_last, s_ok;
   __shared__ uint64_t xv[16];
-  griddep_wait();
+  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+  const int per_lane = a.rank_dim / 8;
+  // rank 256 (the shipped geometry): a thread's slice of the second factor - four tokens x 32 channels - does not
+  // depend on the step, so it is loaded once and stays in registers for all steps; per step only the previous
+  // token's row of the first factor and the step's base logits are fetched, all loads in flight together
+  const bool fast = a.rank_dim == 256;
+  uint4 wv[4][4];
+  if (fast) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = blockIdx.x * 128 + i * 32 + grp;
+      const bool on = t < a.vlocal;
+      const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)(on ? t : 0) * 256 + sub * 32);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) wv[i][k] = on ? __ldg(wr + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  griddep_wait();                                  // the factor is a weight: its loads above overlap the predecessor's tail
   griddep_launch();
   const float inv_t = a.params[6];
   const unsigned long long seed = *a.seed;
   const uint32_t round = (uint32_t)a.ctrl[NRT_CTRL_ROUND];
-  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
-  const int per_lane = a.rank_dim / 8;
   for (int step = 0; step < steps; ++step) {
     int prev = step == 0 ? a.block_ids[0] : __ldcg(a.block_ids + step);
     prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
+    float base[4];
+    if (fast) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = blockIdx.x * 128 + i * 32 + grp;
+        base[i] = (t < a.vlocal && sub == 0) ? a.logits[(size_t)step * a.ld + t] : 0.f;
+      }
+    }
     for (int i = threadIdx.x; i < a.rank_dim; i += 256) w1s[i] = __bfloat162float(a.w1[(size_t)prev * a.rank_dim + i]);
     if (threadIdx.x == 0) { sbest = 0ull; s_ok = 1; }
     __syncthreads();
     const uint32_t ctr = round * 8u + (uint32_t)step;
     unsigned long long best = 0ull;
+#pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int t = blockIdx.x * 128 + i * 32 + grp;
       float acc = 0.f;
-      if (t < a.vlocal) {
+      if (fast) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&wv[i][k]);
+          const float* w = w1s + sub * 32 + k * 8;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc += f.x * w[2 * j] + f.y * w[2 * j + 1];
+          }
+        }
+      } else if (t < a.vlocal) {
         const uint4* wr = reinterpret_cast<const uint4*>(a.w2 + (size_t)t * a.rank_dim + sub * per_lane);
         for (int k = 0; k < per_lane / 8; ++k) {
           const uint4 v = wr[k];
@@ -172,7 +207,7 @@ __global__ void __launch_bounds__(256) markov_chain_kernel(const MarkovArgs a, i
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       if (sub == 0 && t < a.vlocal) {
-        const float z = a.logits[(size_t)step * a.ld + t] + round_bf16(acc);
+        const float z = (fast ? base[i] : a.logits[(size_t)step * a.ld + t]) + round_bf16(acc);
         a.zq[(size_t)step * a.ld + t] = z;
         const float u = philox_uniform(seed, 3u, ctr, (uint32_t)(t + a.vbase));
         const float g = -__logf(-__logf(u));

@@ -30,6 +30,7 @@ namespace {
 constexpr int kRowsP = 8, kRowsQ = 7, kDist = kRowsP + kRowsQ;
 constexpr int kTile = 2048;                 // vocabulary entries per CTA
 constexpr int kThreads = 256;
+constexpr int kPer = kTile / kThreads;      // vocabulary entries per thread and tile
 
 enum Domain : uint32_t { kDomAccept = 0, kDomResample = 1, kDomForced = 2, kDomDraft = 3, kDomAnchor = 4 };
 
@@ -63,6 +64,10 @@ struct SamplerArgs {
   int n_rows_p, n_rows_q;      // 8,7 for a round; 1,0 for the anchor sample
   SamplerState* st;
   XchgArgs x;
+  // opt-in phase stamps of the single-launch sampler (%globaltimer, ns), [32]: word 2p = the last CTA of phase p has
+  // arrived, 2p + 1 = phase p released (phases: 0 maxima, 1 codes, 2..5 nucleus passes (+ accept after the last),
+  // 6 tile masses / draw done); word 30 = kernel entry of CTA (0, 0).  Null: none.
+  unsigned long long* stamps;
 };
 
 __device__ __forceinline__ float penalised(const SamplerArgs& a, const float* params, float z, int t) {
@@ -105,6 +110,14 @@ __device__ __forceinline__ bool last_block(unsigned int* ticket) {
 template <typename T>
 __device__ __forceinline__ T ldg2(const T* p) { return __ldcg(p); }
 
+// 64-bit shared-memory atomics are compare-and-swap loops: 256 threads adding to one word serialise for microseconds.
+// Sums are therefore folded inside the warp first and one lane per warp touches shared memory.
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 // ---------------------------------------------------------------- pass A: row maxima
 __device__ __forceinline__ void work_max(const SamplerArgs& a, int bx, int d) {
   __shared__ unsigned int smax;
@@ -115,10 +128,18 @@ __device__ __forceinline__ void work_max(const SamplerArgs& a, int bx, int d) {
     const float* z = row_logits(a, d, inv_t);
     unsigned int best = 0u;
     const int t0 = bx * kTile;
-    for (int i = threadIdx.x; i < kTile; i += kThreads) {
-      const int t = t0 + i;
+    // a thread's eight entries are requested together (one memory round trip instead of eight)
+    float zv[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int t = t0 + threadIdx.x + j * kThreads;
+      zv[j] = t < a.vlocal ? z[t] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int t = t0 + threadIdx.x + j * kThreads;
       if (t < a.vlocal) {
-        float v = d < kRowsP ? penalised(a, a.params, z[t], t) : z[t];
+        float v = d < kRowsP ? penalised(a, a.params, zv[j], t) : zv[j];
         best = max(best, float_order(__fmul_rn(v, inv_t)));
       }
     }
@@ -160,16 +181,24 @@ __device__ __forceinline__ void work_exp(const SamplerArgs& a, int bx, int d) {
     const float m = ldg2(&a.st->rowmax[d]);
     unsigned long long acc = 0ull;
     const int t0 = bx * kTile;
-    for (int i = threadIdx.x; i < kTile; i += kThreads) {
-      const int t = t0 + i;
+    float zv[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int t = t0 + threadIdx.x + j * kThreads;
+      zv[j] = t < a.vlocal ? z[t] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int t = t0 + threadIdx.x + j * kThreads;
       if (t < a.vlocal) {
-        float v = d < kRowsP ? penalised(a, a.params, z[t], t) : z[t];
+        float v = d < kRowsP ? penalised(a, a.params, zv[j], t) : zv[j];
         const unsigned int e = (unsigned int)rintf(expf(__fsub_rn(__fmul_rn(v, inv_t), m)) * 2147483648.0f);
         a.e[(size_t)d * a.vlocal + t] = e;
         acc += e;
       }
     }
-    atomicAdd(&ssum, acc);
+    acc = warp_sum_u64(acc);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&ssum, acc);
     __syncthreads();
     if (threadIdx.x == 0) atomicAdd(&a.st->total[d], ssum);
   }
@@ -196,62 +225,94 @@ __global__ void __launch_bounds__(kThreads) samp_exp_kernel(const SamplerArgs a)
 
 // ---------------------------------------------------------------- passes C0..C3: nucleus radix select
 __device__ __forceinline__ void work_hist(const SamplerArgs& a, int bx, int d, int pass) {
-  __shared__ unsigned long long sh[256];
+  // Bin sums are kept as two 32-bit words (low / high 16 bits of the codes: a tile's sums fit) because 32-bit
+  // shared-memory atomics are native while 64-bit ones are compare-and-swap loops.
+  __shared__ unsigned int sh_lo[256], sh_hi[256];
   const int shift = 24 - 8 * pass;
   const unsigned int mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-  for (int i = threadIdx.x; i < 256; i += kThreads) sh[i] = 0ull;
+  for (int i = threadIdx.x; i < 256; i += kThreads) { sh_lo[i] = 0u; sh_hi[i] = 0u; }
   __syncthreads();
   if (row_active(a, d)) {
     const unsigned int prefix = ldg2(&a.st->prefix[d]);
     const unsigned int* e = a.e + (size_t)d * a.vlocal;
     const int t0 = bx * kTile;
-    // Nearly all codes of a pass fall into one bin (tiny probabilities): keep a run-length
-    // accumulator per thread and touch shared memory only when the bin changes.
-    unsigned int cur = 0xFFFFFFFFu;
-    unsigned long long run = 0ull;
-    for (int i = threadIdx.x; i < kTile; i += kThreads) {
-      const int t = t0 + i;
-      const unsigned int v = t < a.vlocal ? e[t] : 0u;
-      if ((v & mask) == prefix && v != 0u) {
-        const unsigned int bin = (v >> shift) & 255u;
-        if (bin != cur) {
-          if (run) atomicAdd(&sh[cur], run);
-          cur = bin;
-          run = 0ull;
+    unsigned int ev[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int t = t0 + threadIdx.x + j * kThreads;
+      ev[j] = t < a.vlocal ? __ldcg(e + t) : 0u;
+    }
+    // In the first pass nearly all codes of a warp fall into one bin (tiny probabilities): then the warp adds once.
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const unsigned int v = ev[j];
+      const bool in = (v & mask) == prefix && v != 0u;
+      const unsigned int bin = in ? (v >> shift) & 255u : 0xFFFFFFFFu;
+      const unsigned int b0 = __shfl_sync(0xffffffffu, bin, 0);
+      if (__all_sync(0xffffffffu, bin == b0)) {
+        if (b0 != 0xFFFFFFFFu) {
+          const unsigned int lo = __reduce_add_sync(0xffffffffu, v & 0xFFFFu), hi = __reduce_add_sync(0xffffffffu, v >> 16);
+          if ((threadIdx.x & 31) == 0) { atomicAdd(&sh_lo[b0], lo); atomicAdd(&sh_hi[b0], hi); }
         }
-        run += v;
+      } else if (in) {
+        atomicAdd(&sh_lo[bin], v & 0xFFFFu);
+        atomicAdd(&sh_hi[bin], v >> 16);
       }
     }
-    if (run) atomicAdd(&sh[cur], run);
     __syncthreads();
-    for (int i = threadIdx.x; i < 256; i += kThreads)
-      if (sh[i]) atomicAdd(&a.st->hist[d * 256 + i], sh[i]);
+    for (int i = threadIdx.x; i < 256; i += kThreads) {
+      const unsigned long long tot = ((unsigned long long)sh_hi[i] << 16) + sh_lo[i];
+      if (tot) atomicAdd(&a.st->hist[d * 256 + i], tot);
+    }
   }
 }
 __device__ __forceinline__ void post_hist(const SamplerArgs& a, uint64_t* xv, int pass) {
   const int shift = 24 - 8 * pass;
-  for (int i = threadIdx.x; i < kDist * 256; i += kThreads)
-    xv[i] = *reinterpret_cast<volatile unsigned long long*>(&a.st->hist[i]);
+#pragma unroll
+  for (int j = 0; j < kDist; ++j)                    // fifteen independent L2 loads per thread, in flight together
+    xv[threadIdx.x + j * kThreads] = __ldcg(reinterpret_cast<const unsigned long long*>(&a.st->hist[threadIdx.x + j * kThreads]));
   __syncthreads();
   xchg_reduce_u64<kXSum>(xv, kDist * 256, a.x, 2 + pass);
-  if (threadIdx.x < kDist && row_active(a, threadIdx.x)) {
-    const int r = threadIdx.x;
+  // Threshold digit of every distribution: the largest bin b >= 1 whose suffix sum S(b) = sum of bins >= b reaches
+  // the target (bin 0 when none does).  One warp per distribution; a lane holds eight bins and their suffix sums.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = warp; r < kDist; r += kThreads / 32) {
+    if (!row_active(a, r)) continue;                                   // uniform over the warp
     const double top_p = (double)a.params[1];
     const unsigned long long target = (unsigned long long)ceil(top_p * (double)ldg2(&a.st->total[r]));
-    unsigned long long above = ldg2(&a.st->above[r]), cum = 0ull;
-    int b = 255;
-    for (; b > 0; --b) {
-      cum += xv[r * 256 + b];
-      if (above + cum >= target) break;
+    const unsigned long long above = ldg2(&a.st->above[r]);
+    unsigned long long bin[8], suf[8];
+    unsigned long long mine = 0ull;
+#pragma unroll
+    for (int i = 7; i >= 0; --i) { bin[i] = xv[r * 256 + lane * 8 + i]; mine += bin[i]; suf[i] = mine; }   // suffix inside the lane
+    unsigned long long higher = mine;                                  // inclusive suffix over lanes, then made exclusive
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long v = __shfl_down_sync(0xffffffffu, higher, o);
+      if (lane + o < 32) higher += v;
     }
-    if (b == 0) cum += xv[r * 256];
-    const unsigned long long in_bin = xv[r * 256 + b];
-    a.st->above[r] = above + cum - in_bin;
-    a.st->prefix[r] = ldg2(&a.st->prefix[r]) | ((unsigned int)b << shift);
-    if (pass == 3) a.st->kept[r] = above + cum;      // Z: everything with e >= tau
+    higher -= mine;
+    int cand = -1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (lane * 8 + i >= 1 && above + higher + suf[i] >= target) cand = lane * 8 + i;      // ascending i keeps the largest
+    const int b = max(0, (int)__reduce_max_sync(0xffffffffu, cand));
+    const int owner = b >> 3;
+    unsigned long long cum = 0ull, in_bin = 0ull;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i == (b & 7)) { cum = higher + suf[i]; in_bin = bin[i]; }
+    cum = __shfl_sync(0xffffffffu, cum, owner);
+    in_bin = __shfl_sync(0xffffffffu, in_bin, owner);
+    if (lane == 0) {
+      a.st->above[r] = above + cum - in_bin;
+      a.st->prefix[r] = ldg2(&a.st->prefix[r]) | ((unsigned int)b << shift);
+      if (pass == 3) a.st->kept[r] = above + cum;      // Z: everything with e >= tau
+    }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < kDist * 256; i += kThreads) a.st->hist[i] = 0ull;
+#pragma unroll
+  for (int j = 0; j < kDist; ++j) a.st->hist[threadIdx.x + j * kThreads] = 0ull;
 }
 __global__ void __launch_bounds__(kThreads) samp_hist_kernel(const SamplerArgs a, int pass) {
   __shared__ uint64_t xv[kDist * 256];
@@ -308,34 +369,58 @@ __global__ void __launch_bounds__(64) samp_accept_kernel(const SamplerArgs a) {
   do_accept(a, xv);
 }
 
-// residual / bonus mass of token t of the row being resampled (40-bit fixed point of a probability)
-__device__ __forceinline__ unsigned long long resample_mass(const SamplerArgs& a, int m, int t, bool from_p) {
-  unsigned int ep = ldg2(&a.e[(size_t)m * a.vlocal + t]);
-  if (ep < ldg2(&a.st->prefix[m])) ep = 0u;
-  if (from_p || m >= a.n_rows_q) return (unsigned long long)ep;    // bonus / anchor row / empty residual: sample from p'
-  unsigned int eq = ldg2(&a.e[(size_t)(kRowsP + m) * a.vlocal + t]);
-  if (eq < ldg2(&a.st->prefix[kRowsP + m])) eq = 0u;
-  const double r = (double)ep / (double)ldg2(&a.st->kept[m]) - (double)eq / (double)ldg2(&a.st->kept[kRowsP + m]);
-  return r > 0.0 ? (unsigned long long)(r * 1099511627776.0) : 0ull;
+// residual / bonus mass of token t of the row being resampled (40-bit fixed point of a probability).  The row's
+// scalars are fetched once (ResampleRow); the per-token part works on the two loaded codes.
+struct ResampleRow {
+  unsigned int prefix_p, prefix_q;
+  double kept_p, kept_q;
+  bool has_q;
+  const unsigned int* ep;     // codes of the target row
+  const unsigned int* eq;     // codes of the draft row (valid when has_q)
+};
+__device__ __forceinline__ ResampleRow resample_row(const SamplerArgs& a, int m) {
+  ResampleRow r;
+  r.has_q = m < a.n_rows_q;
+  r.ep = a.e + (size_t)m * a.vlocal;
+  r.eq = a.e + (size_t)(kRowsP + (r.has_q ? m : 0)) * a.vlocal;
+  r.prefix_p = ldg2(&a.st->prefix[m]);
+  r.prefix_q = r.has_q ? ldg2(&a.st->prefix[kRowsP + m]) : 0u;
+  r.kept_p = (double)ldg2(&a.st->kept[m]);
+  r.kept_q = r.has_q ? (double)ldg2(&a.st->kept[kRowsP + m]) : 1.0;
+  return r;
+}
+__device__ __forceinline__ unsigned long long resample_mass_of(const ResampleRow& r, unsigned int ep, unsigned int eq, bool from_p) {
+  if (ep < r.prefix_p) ep = 0u;
+  if (from_p || !r.has_q) return (unsigned long long)ep;          // bonus / anchor row / empty residual: sample from p'
+  if (eq < r.prefix_q) eq = 0u;
+  const double v = (double)ep / r.kept_p - (double)eq / r.kept_q;
+  return v > 0.0 ? (unsigned long long)(v * 1099511627776.0) : 0ull;
 }
 
 // ---------------------------------------------------------------- resample: per-tile masses
 __device__ __forceinline__ void work_tile_mass(const SamplerArgs& a, int bx) {
-  __shared__ unsigned long long ssum;
-  if (threadIdx.x == 0) ssum = 0ull;
+  __shared__ unsigned long long ssum, ssum_p;
+  if (threadIdx.x == 0) { ssum = 0ull; ssum_p = 0ull; }
   __syncthreads();
   const int m = ldg2(&a.st->accepted);
-  __shared__ unsigned long long ssum_p;
-  if (threadIdx.x == 0) ssum_p = 0ull;
-  __syncthreads();
+  const ResampleRow rr = resample_row(a, m);
   unsigned long long acc = 0ull, acc_p = 0ull;
   const int t0 = bx * kTile;
-  for (int i = threadIdx.x; i < kTile; i += kThreads) {
-    const int t = t0 + i;
-    if (t < a.vlocal) { acc += resample_mass(a, m, t, false); acc_p += resample_mass(a, m, t, true); }
+  unsigned int ep[kPer], eq[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {                  // all of a thread's codes are requested together
+    const int t = t0 + threadIdx.x + j * kThreads;
+    ep[j] = t < a.vlocal ? __ldcg(rr.ep + t) : 0u;
+    eq[j] = (t < a.vlocal && rr.has_q) ? __ldcg(rr.eq + t) : 0u;
   }
-  atomicAdd(&ssum, acc);
-  atomicAdd(&ssum_p, acc_p);
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    acc += resample_mass_of(rr, ep[j], eq[j], false);
+    acc_p += resample_mass_of(rr, ep[j], eq[j], true);
+  }
+  acc = warp_sum_u64(acc);
+  acc_p = warp_sum_u64(acc_p);
+  if ((threadIdx.x & 31) == 0) { atomicAdd(&ssum, acc); atomicAdd(&ssum_p, acc_p); }
   __syncthreads();
   if (threadIdx.x == 0) { a.st->tile_mass[bx] = ssum; a.st->tile_mass[128 + bx] = ssum_p; }
 }
@@ -349,12 +434,16 @@ __global__ void __launch_bounds__(kThreads) samp_tile_mass_kernel(const SamplerA
 __device__ __forceinline__ void do_draw(const SamplerArgs& a, int tiles, int domain, uint64_t* xv) {
   __shared__ unsigned long long part[kThreads];
   __shared__ int s_tok;
+  __shared__ unsigned long long tmass[256];        // tile masses of this rank: residual [0, 128), bonus [128, 256)
+  __shared__ int s_th;
+  __shared__ unsigned long long s_rem;
   const int m = ldg2(&a.st->accepted);
   if (threadIdx.x < 16) xv[threadIdx.x] = 0ull;
+  tmass[threadIdx.x] = (threadIdx.x & 127) < tiles ? ldg2(&a.st->tile_mass[threadIdx.x]) : 0ull;   // one round of loads
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned long long tot = 0ull, tot_p = 0ull;
-    for (int i = 0; i < tiles; ++i) { tot += ldg2(&a.st->tile_mass[i]); tot_p += ldg2(&a.st->tile_mass[128 + i]); }
+    for (int i = 0; i < tiles; ++i) { tot += tmass[i]; tot_p += tmass[128 + i]; }
     xv[a.x.rank] = tot;
     xv[8 + a.x.rank] = tot_p;
     s_tok = -1;
@@ -375,15 +464,27 @@ __device__ __forceinline__ void do_draw(const SamplerArgs& a, int tiles, int dom
     unsigned long long local = target - before;       // uniform across the CTA
     int tile = 0;
     for (; tile < tiles - 1; ++tile) {
-      const unsigned long long tm = ldg2(&a.st->tile_mass[mo + tile]);
+      const unsigned long long tm = tmass[mo + tile];
       if (local < tm) break;
       local -= tm;
     }
-    // scan the tile: each thread owns 8 consecutive tokens
-    const int t0 = tile * kTile + threadIdx.x * (kTile / kThreads);
+    // scan the tile: each thread owns 8 consecutive tokens, whose codes it requests together and keeps
+    const ResampleRow rr = resample_row(a, m);
+    const int t0 = tile * kTile + threadIdx.x * kPer;
+    unsigned long long w[kPer];
+    {
+      unsigned int ep[kPer], eq[kPer];
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        ep[i] = t0 + i < a.vlocal ? __ldcg(rr.ep + t0 + i) : 0u;
+        eq[i] = (t0 + i < a.vlocal && rr.has_q) ? __ldcg(rr.eq + t0 + i) : 0u;
+      }
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) w[i] = t0 + i < a.vlocal ? resample_mass_of(rr, ep[i], eq[i], from_p) : 0ull;
+    }
     unsigned long long mine_sum = 0ull;
-    for (int i = 0; i < kTile / kThreads; ++i)
-      if (t0 + i < a.vlocal) mine_sum += resample_mass(a, m, t0 + i, from_p);
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) mine_sum += w[i];
     part[threadIdx.x] = mine_sum;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -393,15 +494,19 @@ __device__ __forceinline__ void do_draw(const SamplerArgs& a, int tiles, int dom
         if (local < run + part[th]) break;
         run += part[th];
       }
-      unsigned long long rem = local - run;
-      const int b0 = tile * kTile + th * (kTile / kThreads);
-      int tok = b0;
-      for (int i = 0; i < kTile / kThreads; ++i) {
-        if (b0 + i >= a.vlocal) break;
-        const unsigned long long w = resample_mass(a, m, b0 + i, from_p);
-        tok = b0 + i;
-        if (rem < w) break;
-        rem -= w;
+      s_th = th;
+      s_rem = local - run;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x == s_th) {                  // the owner of the eight tokens walks its own masses
+      unsigned long long rem = s_rem;
+      int tok = t0;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        if (t0 + i >= a.vlocal) break;
+        tok = t0 + i;
+        if (rem < w[i]) break;
+        rem -= w[i];
       }
       s_tok = tok + a.vbase;
     }
@@ -482,20 +587,25 @@ __global__ void __launch_bounds__(kThreads, 2) samp_persistent_kernel(const Samp
   const int bx = blockIdx.x, d = blockIdx.y;
   PhaseSync ps{arrive, gen, a.x.status, gridDim.x * gridDim.y};
   unsigned int g;
+#define NRT_SSTAMP(i) do { if (a.stamps && threadIdx.x == 0) a.stamps[i] = globaltimer(); } while (0)
+  if (bx == 0 && d == 0) NRT_SSTAMP(30);
   work_max(a, bx, d);
-  if (phase_arrive(ps, g)) { post_max(a, xv); phase_release(ps, g); } else if (!phase_wait(ps, g, 0)) return;
+  if (phase_arrive(ps, g)) { NRT_SSTAMP(0); post_max(a, xv); phase_release(ps, g); NRT_SSTAMP(1); } else if (!phase_wait(ps, g, 0)) return;
   work_exp(a, bx, d);
-  if (phase_arrive(ps, g)) { post_exp(a, xv); phase_release(ps, g); } else if (!phase_wait(ps, g, 1)) return;
+  if (phase_arrive(ps, g)) { NRT_SSTAMP(2); post_exp(a, xv); phase_release(ps, g); NRT_SSTAMP(3); } else if (!phase_wait(ps, g, 1)) return;
   for (int pass = 0; pass < 4; ++pass) {
     work_hist(a, bx, d, pass);
     if (phase_arrive(ps, g)) {
+      NRT_SSTAMP(4 + 2 * pass);
       post_hist(a, xv, pass);
       if (pass == 3) { __syncthreads(); do_accept(a, xv); }
       phase_release(ps, g);
+      NRT_SSTAMP(5 + 2 * pass);
     } else if (!phase_wait(ps, g, 2 + pass)) return;
   }
   if (d == 0) work_tile_mass(a, bx);
-  if (phase_arrive(ps, g)) do_draw(a, tiles, domain, xv);
+  if (phase_arrive(ps, g)) { NRT_SSTAMP(12); do_draw(a, tiles, domain, xv); NRT_SSTAMP(13); }
+#undef NRT_SSTAMP
 }
 
 // ---------------------------------------------------------------- tail: commit + next-round geometry

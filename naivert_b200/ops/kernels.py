@@ -334,7 +334,7 @@ def argmax_rows(args: ArgmaxArgs, pdl=True):
 class SamplerArgs(C.Structure):
     _fields_ = [("zp", VP), ("ldp", I32), ("zq", VP), ("ldq", I32), ("vlocal", I32), ("vbase", I32), ("e", VP),
                 ("counts", VP), ("params", VP), ("seed", VP), ("ctrl", VP), ("block_ids", VP),
-                ("n_rows_p", I32), ("n_rows_q", I32), ("st", VP), ("x", XchgArgs)]
+                ("n_rows_p", I32), ("n_rows_q", I32), ("st", VP), ("x", XchgArgs), ("stamps", VP)]
 
 
 class TailArgs(C.Structure):

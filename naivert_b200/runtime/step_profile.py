@@ -81,6 +81,10 @@ def main(argv: List[str] = None) -> int:
                 d[key].ar.stamps = b.data_ptr()
             else:
                 d[key].stamps = b.data_ptr()
+    samp_stamps = None
+    if a.stamp_layer >= 0:
+        samp_stamps = torch.zeros(32, dtype=torch.int64, device=dev)
+        eng.round.args_sampler.stamps = samp_stamps.data_ptr()
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, spec.vocab, (a.prompt,), generator=g, dtype=torch.int32)
     sp = SamplingParams(temperature=0.4, top_p=0.95, seed=1234, forced_accept_p=0.7)
@@ -137,6 +141,13 @@ def main(argv: List[str] = None) -> int:
                 if names is None and i == 10:
                     continue
                 lines.append(f"   {label:26s} {(np.median(col) - t0) / 1e3:8.2f} / {(col.max() - t0) / 1e3:8.2f}   ({len(col)} CTAs)")
+    if samp_stamps is not None:
+        t = samp_stamps.cpu().tolist()
+        if t[30] > 0:
+            names = ["maxima", "codes", "nucleus pass 0", "nucleus pass 1", "nucleus pass 2", "nucleus pass 3 + accept", "tile masses / draw"]
+            lines.append("sampler (single launch): us after kernel entry - last CTA of the phase arrived / phase released")
+            for ph, nm in enumerate(names):
+                lines.append(f"   {nm:26s} {(t[2 * ph] - t[30]) / 1e3:8.2f} / {(t[2 * ph + 1] - t[30]) / 1e3:8.2f}")
     eng.close()
     text = "\n".join(lines)
     print(text)
