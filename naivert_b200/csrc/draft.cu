@@ -104,7 +104,12 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
       best = key > best ? key : best;
     }
   }
-  atomicMax(&sbest, best);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) atomicMax(&sbest, best);
   __syncthreads();
   if (threadIdx.x == 0) {
     atomicMax(a.best, sbest);
@@ -216,7 +221,13 @@ __global__ void __launch_bounds__(256, 2) markov_chain_kernel(const MarkovArgs a
         best = key > best ? key : best;
       }
     }
-    atomicMax(&sbest, best);
+    // 64-bit shared-memory atomics are compare-and-swap loops: fold inside the warp, one lane per warp updates
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) atomicMax(&sbest, best);
     __syncthreads();
     if (threadIdx.x == 0) {
       atomicMax(a.best + step, sbest);
