@@ -134,6 +134,8 @@ def main() -> int:
     ap.add_argument("--pdl", dest="pdl", action="store_true", default=None,
                     help="chain kernels with programmatic dependent launch (default: the engine's default, NAIVERT_PDL)")
     ap.add_argument("--no-pdl", dest="pdl", action="store_false", help="plain stream order between kernels")
+    ap.add_argument("--stamp-layer", type=int, default=-1,
+                    help="diagnostic: print the phase stamps of this layer's kernels (rank 0, stderr) after the run")
     ap.add_argument("--device-chain", action="store_true", help="the round graph relaunches itself from the device")
     ap.add_argument("--no-graph", action="store_true", help="diagnostic: eager launches instead of graph replays")
     ap.add_argument("--no-check", action="store_true", help="skip the small-geometry correctness self-check (outside the timed region)")
@@ -177,6 +179,10 @@ def main() -> int:
                        device_chain=a.device_chain, prefill_chunk=0 if a.shape_tp else a.prefill_chunk)
     build_s = time.perf_counter() - t_build
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
+    stamp_bufs = None
+    if a.stamp_layer >= 0:                                    # diagnostic: in-kernel phase times of one layer (rank 0 prints them)
+        from naivert_b200.runtime.step_profile import attach_stamps
+        stamp_bufs = attach_stamps(eng, a.stamp_layer)
 
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, spec.vocab, (a.prompt,), generator=g, dtype=torch.int32).pin_memory()
@@ -267,6 +273,9 @@ def main() -> int:
     # ------------------------------------------------------------------ correctness record for this TP degree
     # (small W8A8 geometry, same kernels and code paths: oracle error, lockstep, determinism, speculative == greedy)
     check = None
+    if stamp_bufs is not None and rank == 0:
+        from naivert_b200.runtime.step_profile import report_stamps
+        print("\n".join(report_stamps(stamp_bufs, a.stamp_layer)), file=sys.stderr)
     last_prefill, kv_bytes = eng.last_prefill, eng.kv_bytes()
     kernels_per_round, host_launches = int(r.kernels_per_round), r.host_launches
     path_info = {"pdl": bool(r.pdl), "device_chain": bool(a.device_chain), "fused_step": bool(r.t.fused),

@@ -45,6 +45,49 @@ def _short(name: str) -> str:
     return name.replace("(anonymous namespace)::", "").replace("void ", "").replace("nrt::", "").split("(")[0][:70]
 
 
+def attach_stamps(eng, layer: int) -> Dict[str, torch.Tensor]:
+    """Point the stamp words of layer ``layer``'s projection / router / MoE kernels at fresh buffers.  Call before the
+    round graph is captured (the pointers are kernel arguments)."""
+    bufs: Dict[str, torch.Tensor] = {}
+    d = eng.target.layers[layer]
+    for key in ("args_qkv", "args_o", "args_router", "args_moe", "args_gu", "args_down"):
+        if key not in d:
+            continue
+        b = torch.zeros(300 * 16, dtype=torch.int64, device=eng.target.x.device)
+        bufs[key] = b
+        if key == "args_moe":
+            d[key].ar.stamps = b.data_ptr()
+        else:
+            d[key].stamps = b.data_ptr()
+    return bufs
+
+
+def report_stamps(bufs: Dict[str, torch.Tensor], layer: int) -> List[str]:
+    import numpy as np
+    torch.cuda.synchronize()
+    lines: List[str] = []
+    T = {k: b.view(300, 16).cpu().numpy() for k, b in bufs.items()}
+    t0 = min(t[:, 0][t[:, 0] > 0].min() for t in T.values() if (t[:, 0] > 0).any())
+    for k, t in T.items():
+        t = t[t[:, 0] > 0]
+        if len(t) == 0:
+            continue
+        names = STAMP_NAMES["router"] if k == "args_router" else STAMP_NAMES["moe"] if k == "args_moe" else None
+        lines.append(f"layer {layer} {k[5:]}: {len(t)} CTAs; us after the layer's first stamp (median over CTAs / last CTA)")
+        order = sorted(range(16), key=lambda i: np.median(t[:, i][t[:, i] > t0]) if (t[:, i] > t0).any() else 1e30)
+        for i in order:
+            col = t[:, i]
+            col = col[col > t0]                     # stamps of earlier replays (a CTA that was not last this time) lie before t0
+            if len(col) == 0:
+                continue
+            if names is None and i == 10:
+                lines.append(f"   {'mailbox sweeps (max)':26s} {int(t[:, 10].max()):8d}")
+                continue
+            label = names.get(i, str(i)) if names else STAMP_NAMES["gemm"][i] if i < 12 else str(i)
+            lines.append(f"   {label:26s} {(np.median(col) - t0) / 1e3:8.2f} / {(col.max() - t0) / 1e3:8.2f}   ({len(col)} CTAs)")
+    return lines
+
+
 def main(argv: List[str] = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", default="naive-n0.5")
@@ -69,18 +112,7 @@ def main(argv: List[str] = None) -> int:
     dev = torch.device("cuda", 0)
     eng = Engine.build(spec, rank=0, tp=1, group=None, capacity=a.prompt + 1024, seed=0, device=dev, pdl=a.pdl, shape_tp=a.shape_tp)
     eng.round.stop_ids.fill_(-1)
-    bufs: Dict[str, torch.Tensor] = {}
-    if a.stamp_layer >= 0:
-        d = eng.target.layers[a.stamp_layer]
-        for key in ("args_qkv", "args_o", "args_router", "args_moe", "args_gu", "args_down"):
-            if key not in d:
-                continue
-            b = torch.zeros(300 * 16, dtype=torch.int64, device=dev)
-            bufs[key] = b
-            if key == "args_moe":
-                d[key].ar.stamps = b.data_ptr()
-            else:
-                d[key].stamps = b.data_ptr()
+    bufs = attach_stamps(eng, a.stamp_layer) if a.stamp_layer >= 0 else {}
     samp_stamps = None
     if a.stamp_layer >= 0:
         samp_stamps = torch.zeros(32, dtype=torch.int64, device=dev)
@@ -121,26 +153,7 @@ def main(argv: List[str] = None) -> int:
             lines.append(f"{k:70s} n/round {v[0] / a.rounds:6.1f} us {v[1] / v[0]:7.2f} gap before {v[2] / v[0]:5.2f} "
                          f"us/round {(v[1] + v[2]) / a.rounds:8.1f}")
     if bufs:
-        import numpy as np
-        torch.cuda.synchronize()
-        T = {k: b.view(300, 16).cpu().numpy() for k, b in bufs.items()}
-        t0 = min(t[:, 0][t[:, 0] > 0].min() for t in T.values() if (t[:, 0] > 0).any())
-        for k, t in T.items():
-            t = t[t[:, 0] > 0]
-            if len(t) == 0:
-                continue
-            names = STAMP_NAMES["router"] if k == "args_router" else STAMP_NAMES["moe"] if k == "args_moe" else None
-            lines.append(f"layer {a.stamp_layer} {k[5:]}: {len(t)} CTAs; us after the layer's first stamp (median over CTAs / last CTA)")
-            order = sorted(range(16), key=lambda i: np.median(t[:, i][t[:, i] > t0]) if (t[:, i] > t0).any() else 1e30)
-            for i in order:
-                col = t[:, i]
-                col = col[col > t0]                     # stamps of earlier replays (a CTA that was not last this time) lie before t0
-                if len(col) == 0:
-                    continue
-                label = names.get(i, str(i)) if names else STAMP_NAMES["gemm"][i] if i < 12 else str(i)
-                if names is None and i == 10:
-                    continue
-                lines.append(f"   {label:26s} {(np.median(col) - t0) / 1e3:8.2f} / {(col.max() - t0) / 1e3:8.2f}   ({len(col)} CTAs)")
+        lines += report_stamps(bufs, a.stamp_layer)
     if samp_stamps is not None:
         t = samp_stamps.cpu().tolist()
         if t[30] > 0:
