@@ -175,6 +175,24 @@ def pick_split(n_tiles: int, k_blocks: int, max_ctas: int = 160, max_split: int 
     return 1
 
 
+def norm_split(n_tiles: int, k_total: int, fp8: bool, dual: bool, max_split: int = 8) -> int:
+    """``pick_split`` for the projections that build their normalised token operand in shared memory: the CTA's whole
+    K slice of the operand sits beside the weight ring, so a small grid may not keep K unsplit.  The split is raised
+    (even past one wave of CTAs) until ring + operand + epilogue staging + split partials fit the 227 KiB of an SM."""
+    kb_total = k_total // (128 if fp8 else 64)
+    tile_a = 128 * 128                                    # bytes of one weight stage per matrix (128 rows x 128 B)
+    ring = (4 if dual else 8) * (2 if dual else 1) * tile_a
+    def fits(split: int) -> bool:
+        kb = kb_total // split
+        operand = kb * 2048 + (((kb * 16 * 4 + 1023) // 1024) * 1024 if fp8 else 0)
+        part = (2 if dual else 1) * (split - 1) * 8 * 128 * 4 if split > 1 else 0
+        return ring + operand + 1024 + 1024 + 16 * 128 * 4 + part <= 227 * 1024
+    s = pick_split(n_tiles, kb_total, max_split=max_split)
+    while not fits(s) and s < 8 and kb_total % (2 * s) == 0:
+        s *= 2
+    return s
+
+
 # ----------------------------------------------------------------------------- launches
 def gemm(variant: int, a0: TensorMap, a1: Optional[TensorMap], b: Optional[TensorMap], args: GemmArgs, grid_x: int,
          grid_y: int = 1, pdl: bool = True) -> None:

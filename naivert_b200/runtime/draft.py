@@ -223,7 +223,7 @@ class DraftRuntime:
             K.gemm(self.V_AR, self.map_fc, None, self.map_feats, self.args_fc, d.hidden // 128,
                    K.pick_split(d.hidden // 128, self.kf // 64), pdl=pdl)
             nt = self.wkv.shape[0] // 128
-            K.gemm(self.V_QKV_POST, self.map_kv, None, None, self.args_kv, nt, K.pick_split(nt, d.hidden // 64, max_split=8), pdl=pdl)
+            K.gemm(self.V_QKV_POST, self.map_kv, None, None, self.args_kv, nt, K.norm_split(nt, d.hidden, False, False), pdl=pdl)
             return
         K.rope_table(self.ctrl_ingest_pos, R, d.head_dim, d.rope_theta, self.rope_ing, pdl=pdl)
         K.gemm(self.V_AR, self.map_fc, None, self.map_feats, self.args_fc, d.hidden // 128,
@@ -241,7 +241,7 @@ class DraftRuntime:
                 K.step_prologue(self.args_prologue, pdl=pdl)
             for L in self.layers:
                 nt = L["wqkv"].shape[0] // 128
-                K.gemm(self.V_QKV_POST, L["map_qkv"], None, None, L["args_qkv"], nt, K.pick_split(nt, d.hidden // 64, max_split=8), pdl=pdl)
+                K.gemm(self.V_QKV_POST, L["map_qkv"], None, None, L["args_qkv"], nt, K.norm_split(nt, d.hidden, False, False), pdl=pdl)
                 if L["attn_tc"]:
                     K.attn_decode(L["args_attn"], self.tc_splits, pdl=pdl)
                 else:
@@ -249,7 +249,7 @@ class DraftRuntime:
                 K.gemm(self.V_AR, L["map_wo"], None, self.map_o, L["args_o"], d.hidden // 128,
                        K.pick_split(d.hidden // 128, self.nh * d.head_dim // 64), pdl=pdl)
                 K.gemm(self.V_GU_NORM, L["map_gate"], L["map_up"], None, L["args_gu"], self.I // 128,
-                       K.pick_split(self.I // 128, d.hidden // 64, max_split=8), pdl=pdl)
+                       K.norm_split(self.I // 128, d.hidden, False, True), pdl=pdl)
                 K.gemm(self.V_AR, L["map_down"], None, self.map_y, L["args_down"], d.hidden // 128,
                        K.pick_split(d.hidden // 128, self.I // 64), pdl=pdl)
             return

@@ -379,7 +379,7 @@ class TargetRuntime:
         K.step_prologue(self.args_prologue, pdl=pdl)
         for L, d in enumerate(self.layers):
             nt = d["wqkv"].shape[0] // 128
-            K.gemm(self.V_QKV_POST, d["map_qkv"], None, None, d["args_qkv"], nt, K.pick_split(nt, s.hidden // 64, max_split=8), pdl=pdl)
+            K.gemm(self.V_QKV_POST, d["map_qkv"], None, None, d["args_qkv"], nt, K.norm_split(nt, s.hidden, False, False), pdl=pdl)
             if d["kind"] == FULL_DSA:
                 if self.use_sweep:
                     K.index_sweep(*d["sweep_maps"], d["args_sweep"], min(148, -(-self.capacity // 128)), pdl=pdl)
@@ -401,7 +401,7 @@ class TargetRuntime:
                 dn = d["dense"]
                 nt = dn["gate"].n // 128
                 K.gemm(self.V_FP8_GU_NORM, dn["gate"].map, dn["up"].map, None, d["args_gu"], nt,
-                       K.pick_split(nt, s.hidden // 128), pdl=pdl)
+                       K.norm_split(nt, s.hidden, True, True, max_split=4), pdl=pdl)
                 K.gemm(self.V_FP8_AR, dn["down"].map, None, self.map_yd8, d["args_down"], s.hidden // 128,
                        K.pick_split(s.hidden // 128, dn["down"].k // 128), pdl=pdl)
             elif self.moe_fused and self._moe_fused_layer(d, pdl):

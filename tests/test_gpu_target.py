@@ -272,3 +272,32 @@ def test_rows1_matches_rows8():
     torch.cuda.synchronize()
     a, b = rt8.logits[7].float(), rt1.logits[0].float()
     assert (a - b).abs().max().item() <= 0.03 * a.abs().max().item()
+
+
+def test_full_dimension_layers_match_oracle():
+    """The shipped geometry itself (hidden 4096, 64 heads of 192, 256 experts of 2048, vocabulary 152,576) cut to its
+    first two layers - a DSA + dense layer and a sliding-window + MoE layer - at tp = 1 against the torch oracle:
+    the kernels' tile counts, cluster splits, fused operand builds and the fused MoE block at the sizes that ship."""
+    from naivert_b200.models.reference import ReferenceModel
+    from naivert_b200.models.registry import resolve_model
+    from naivert_b200.models.weights import init_state_dict, prepare_weights, shard_weights
+    from naivert_b200.runtime.target import LocalFabric, TargetRuntime
+    spec = resolve_model("naive-n0.5").with_layers(2)
+    w = prepare_weights(spec, init_state_dict(spec, seed=0, device="cuda"))
+    rt = TargetRuntime(spec, shard_weights(spec, w, 0, 1), LocalFabric("cuda"), rows=8, capacity=256)
+    ref = ReferenceModel(spec, w, tp=1, capacity=256, device="cuda")
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, spec.vocab, (24,), generator=g)
+    rels = []
+    for i in range(3):
+        chunk = toks[i * 8:(i + 1) * 8]
+        rt.set_inputs(chunk, i * 8)
+        rt.step()
+        want = ref.step(chunk.cuda(), i * 8)
+        rt.fab.check()
+        got = rt.logits[:8].float()
+        assert torch.isfinite(got).all()
+        rels.append(((got - want).abs().mean() / want.abs().mean()).item())
+        assert (got.argmax(-1) == want.argmax(-1)).float().mean().item() >= 0.75, rels
+    assert max(rels) < 0.08, rels
+    assert rt.fused and rt.moe_fused                        # the default (fused) path is the one under test
