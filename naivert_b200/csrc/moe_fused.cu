@@ -23,6 +23,7 @@
 #include "launch.hpp"
 #include "router.cuh"
 
+#include <stdlib.h>
 #include <string.h>
 
 using namespace nrt;
@@ -69,6 +70,7 @@ struct MoeSmem {
   alignas(16) float xs_t[64][kArRows];        // read as float4; gate/up activation scales, [K block][row] (hidden <= 8192)
   alignas(16) float dn_sc[kDnStaged][kArRows];   // read as float4; down: y scales of this CTA's first kDnStaged units, [unit][row]
   float dn_w[kDnStaged];          // and their weight-block scales
+  float part_s[(kRanges - 1) * kArRows * kTileN];   // cluster launch: partial sums of ranges 1..3, written by the peers
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
@@ -113,6 +115,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     for (int i = 0; i < kMoeStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
     for (int i = 0; i < kGuBufs; ++i) { mbar_init(&sm.gu_full[i], 1); mbar_init(&sm.gu_empty[i], 128); }
     for (int i = 0; i < kDnBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
+    mbar_init(&tail->split_bar, 128 * (kRanges - 1));
     mbar_fence_init();
     tma_prefetch_desc(&tmGate);
     tma_prefetch_desc(&tmUp);
@@ -124,6 +127,12 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
   if (warp == 1) { tmem_alloc(&tail->tmem_base, kMoeTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
+  // Launched as clusters of kRanges CTAs (the four expert-id ranges of one output tile) where the device can keep all
+  // of them resident: the ranges then merge through distributed shared memory instead of global memory and flags.
+  uint32_t cluster_x;
+  asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(cluster_x));
+  const bool clustered = cluster_x == (uint32_t)kRanges;
+  if (clustered) cluster_sync_all();             // the peers' barriers are initialised before any remote arrive
   tc_fence_after();
   const uint32_t tmem = tail->tmem_base;
 
@@ -435,7 +444,24 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     if (tid == 64) NRT_STAMP(8);
     // ---- ranges 1..3 hand their partial to range 0 of the tile, which adds them in range order
     bool leader = dn_on && dn_range == 0;
-    if (dn_on && dn_range != 0) {
+    if (clustered) {
+      if (dn_on && dn_range != 0) {
+        const uint32_t dst = mapa_shared(smem_u32(sm.part_s), 0);
+#pragma unroll
+        for (int r = 0; r < kArRows; ++r)
+          st_cluster_f32(dst + (uint32_t)((((dn_range - 1) * kArRows + r) * kTileN + row) * 4), mix0[r]);
+        mbar_arrive_cluster(mapa_shared(smem_u32(&tail->split_bar), 0));
+      } else if (leader) {
+        if (mbar_wait_cluster(&tail->split_bar, 0, status, kSiteCluster)) {
+#pragma unroll 1
+          for (int y = 1; y < kRanges; ++y)
+#pragma unroll
+            for (int r = 0; r < kArRows; ++r) mix0[r] += sm.part_s[((y - 1) * kArRows + r) * kTileN + row];
+        } else {
+          ok = false;
+        }
+      }
+    } else if (dn_on && dn_range != 0) {
       float* dst = p.part + ((size_t)(dn_tile * (kRanges - 1) + dn_range - 1) * kArRows) * kTileN + row;
 #pragma unroll
       for (int r = 0; r < kArRows; ++r) dst[(size_t)r * kTileN] = mix0[r];
@@ -503,15 +529,39 @@ extern "C" int nrt_moe_layer(const void* tmGate, const void* tmUp, const void* t
     resident = worst;
   }
   if (resident < kMoeCtas) return -9;
+  // clusters of kRanges CTAs when all 32 of them fit on the device at once (checked per instantiation)
+  static int cluster_ok[2] = {-1, -1};
+  const int inst = r.w != nullptr ? 1 : 0;
+  if (cluster_ok[inst] < 0) {
+    const char* env = getenv("NAIVERT_MOE_CLUSTER");
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kMoeCtas);
+    cfg.blockDim = dim3(kMoeThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = kRanges;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = inst ? cudaOccupancyMaxActiveClusters(&n, moe_layer_kernel<true>, &cfg)
+                         : cudaOccupancyMaxActiveClusters(&n, moe_layer_kernel<false>, &cfg);
+    cluster_ok[inst] = (e == cudaSuccess && n >= kMoeCtas / kRanges && !(env && env[0] == '0')) ? 1 : 0;
+    if (e != cudaSuccess) cudaGetLastError();
+  }
   CUtensorMap g, u, d, x, y;
   memcpy(&g, tmGate, sizeof(g));
   memcpy(&u, tmUp, sizeof(u));
   memcpy(&d, tmDown, sizeof(d));
   memcpy(&x, tmX8, sizeof(x));
   memcpy(&y, tmY8, sizeof(y));
-  if (r.w != nullptr)
-    return launch_pdl(moe_layer_kernel<true>, dim3(kMoeCtas), dim3(kMoeThreads), smem, reinterpret_cast<cudaStream_t>(stream),
-                      pdl != 0, g, u, d, x, y, a);
-  return launch_pdl(moe_layer_kernel<false>, dim3(kMoeCtas), dim3(kMoeThreads), smem, reinterpret_cast<cudaStream_t>(stream),
-                    pdl != 0, g, u, d, x, y, a);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (cluster_ok[inst]) {
+    if (inst) return launch_cluster(moe_layer_kernel<true>, dim3(kMoeCtas), dim3(kMoeThreads), dim3(kRanges), smem, st, pdl != 0, g, u, d, x, y, a);
+    return launch_cluster(moe_layer_kernel<false>, dim3(kMoeCtas), dim3(kMoeThreads), dim3(kRanges), smem, st, pdl != 0, g, u, d, x, y, a);
+  }
+  if (inst) return launch_pdl(moe_layer_kernel<true>, dim3(kMoeCtas), dim3(kMoeThreads), smem, st, pdl != 0, g, u, d, x, y, a);
+  return launch_pdl(moe_layer_kernel<false>, dim3(kMoeCtas), dim3(kMoeThreads), smem, st, pdl != 0, g, u, d, x, y, a);
 }
