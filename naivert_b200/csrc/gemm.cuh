@@ -271,6 +271,25 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
   const int units = kb_count * 8;
   const int groups = units < 128 ? 128 / units : 1;
   const int g = units < 128 ? et / units : 0;
+  // The first batch of activations and norm weights does not depend on the row scales: it is requested before them,
+  // so the two memory round trips overlap.
+  const int cu0 = units < 128 ? et % units : et;
+  uint4 gv[kLoads];
+  uint4 xv[4][kLoads];
+  auto load_batch = [&](int cu, int r0) {
+    const int k = (kb_first + (cu >> 3)) * kElems + (cu & 7) * (kElems / 8);
+#pragma unroll
+    for (int l = 0; l < kLoads; ++l) gv[l] = __ldg(reinterpret_cast<const uint4*>(p.ngamma + k + 8 * l));
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int r = r0 + b * groups;
+#pragma unroll
+      for (int l = 0; l < kLoads; ++l)
+        xv[b][l] = r < rows ? *reinterpret_cast<const uint4*>(p.nx + (size_t)r * p.k_total + k + 8 * l) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  const bool active = cu0 < units && g < groups && g < rows;
+  if (active) load_batch(cu0, g);
   // 1 / rms of every row in one round trip: 8 threads per row, each adds the tiles t = sub, sub + 8, ...
   {
     const int r = et >> 3, sub = et & 7;
@@ -285,22 +304,11 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
   }
   epi_bar();
 #pragma unroll 1
-  for (int cu = units < 128 ? et % units : et; cu < units && g < groups; cu += 128) {
+  for (int cu = cu0; cu < units && g < groups; cu += 128) {
     const int c = cu >> 3, j = cu & 7;
-    const int k = (kb_first + c) * kElems + j * (kElems / 8);
-    uint4 gv[kLoads];
-#pragma unroll
-    for (int l = 0; l < kLoads; ++l) gv[l] = __ldg(reinterpret_cast<const uint4*>(p.ngamma + k + 8 * l));
 #pragma unroll 1
     for (int r0 = g; r0 < rows; r0 += 4 * groups) {
-      uint4 xv[4][kLoads];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int r = r0 + b * groups;
-#pragma unroll
-        for (int l = 0; l < kLoads; ++l)
-          xv[b][l] = r < rows ? *reinterpret_cast<const uint4*>(p.nx + (size_t)r * p.k_total + k + 8 * l) : make_uint4(0u, 0u, 0u, 0u);
-      }
+      if (cu != cu0 || r0 != g) load_batch(cu, r0);
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         const int r = r0 + b * groups;

@@ -31,8 +31,11 @@ using namespace nrt;
 namespace {
 
 constexpr int kMoeCtas = 128, kMoeThreads = 256, kMoeStages = 5;
-constexpr int kMoeStageA = 2 * kATileBytes;                 // gate + up tile; the down phase uses the first half
-constexpr int kMoeStageBytes = kMoeStageA + kBTileBytes;    // 34 KiB
+constexpr int kMoeStageA = 2 * kATileBytes;                 // gate + up tile
+constexpr int kMoeStageBytes = kMoeStageA + 2 * kBTileBytes;   // 36 KiB: | gate | up | token tile | second token tile |
+// The down phase cuts every stage into two half slots (a 16 KiB weight tile each, and one of the two token tiles), so
+// ten down tiles per CTA are in flight while the phases hand over instead of five.
+constexpr int kDnSlots = 2 * kMoeStages;
 constexpr int kSlotsMax = 128;
 constexpr int kGuBufs = 4, kGuCols = 2 * kTok;               // TMEM columns [0, 128): dual accumulators
 constexpr int kDnBufs = 8, kDnCols = kTok, kDnBase = 128;    // TMEM columns [128, 256)
@@ -62,6 +65,7 @@ struct MoeArgs {
 struct MoeSmem {
   GemmSmemTail tail;              // full / empty: weight ring; acc_full / acc_empty: down accumulators; red: reductions
   uint64_t gu_full[kGuBufs], gu_empty[kGuBufs];
+  uint64_t dn_full[kDnSlots], dn_empty[kDnSlots];   // half slots of the down phase
   uint32_t gen;
   int ok;
   RouterSmem router;
@@ -115,6 +119,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     for (int i = 0; i < kMoeStages; ++i) { mbar_init(&tail->full[i], 1); mbar_init(&tail->empty[i], 1); }
     for (int i = 0; i < kGuBufs; ++i) { mbar_init(&sm.gu_full[i], 1); mbar_init(&sm.gu_empty[i], 128); }
     for (int i = 0; i < kDnBufs; ++i) { mbar_init(&tail->acc_full[i], 1); mbar_init(&tail->acc_empty[i], 128); }
+    for (int i = 0; i < kDnSlots; ++i) { mbar_init(&sm.dn_full[i], 1); mbar_init(&sm.dn_empty[i], 1); }
     mbar_init(&tail->split_bar, 128 * (kRanges - 1));
     mbar_fence_init();
     tma_prefetch_desc(&tmGate);
@@ -222,7 +227,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
           const int st = u % kMoeStages;
           if (u >= kMoeStages && !mbar_wait(&tail->empty[st], ((u / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = 0; break; }
           uint8_t* sa = smem + st * kMoeStageBytes;
-          mbar_expect_tx(&tail->full[st], kMoeStageBytes);
+          mbar_expect_tx(&tail->full[st], kMoeStageA + kBTileBytes);
           tma_load_3d_hint(sa, &tmGate, &tail->full[st], kb * 128, tile * kTileN, z, stream_once);
           tma_load_3d_hint(sa + kATileBytes, &tmUp, &tail->full[st], kb * 128, tile * kTileN, z, stream_once);
           tma_load_2d(sa + kMoeStageA, &tmX8, &tail->full[st], kb * 128, 0);
@@ -240,15 +245,25 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     // down: the weight tiles of the first ring-full of units are requested before anything waits for their
     // activations; then every lane polls a share of the (slot, tile) flags of this CTA's experts (one round of
     // loads for all of them), and the activation tiles follow
-    const int u0 = gu_units;                                  // == u on the issuing lane unless a wait failed
-    const int npre = min(dn_units, kMoeStages);
+    // Half slot h of the down phase lives in stage h % kMoeStages (weights at + (h / kMoeStages) * 16 KiB, token tile
+    // number h / kMoeStages).  Its first use has to wait for the last gate/up unit that used that stage.
+    const int npre = min(dn_units, kDnSlots);
+    auto slot_free = [&](int i) -> bool {                     // down unit i may overwrite its half slot
+      const int h = i % kDnSlots;
+      if (i >= kDnSlots) return mbar_wait(&sm.dn_empty[h], ((i / kDnSlots) & 1) ^ 1, status, kSiteStageEmpty | 0x10 | h);
+      const int st = h % kMoeStages;
+      if (gu_units <= st) return true;                        // the gate/up phase never used this stage
+      const int last = ((gu_units - 1 - st) / kMoeStages) * kMoeStages + st;       // last gate/up unit of the stage
+      return mbar_wait(&tail->empty[st], (last / kMoeStages) & 1, status, kSiteStageEmpty | st);
+    };
+    auto slot_w = [&](int i) -> uint8_t* { const int h = i % kDnSlots; return smem + (h % kMoeStages) * kMoeStageBytes + (h / kMoeStages) * kATileBytes; };
+    auto slot_b = [&](int i) -> uint8_t* { const int h = i % kDnSlots; return smem + (h % kMoeStages) * kMoeStageBytes + kMoeStageA + (h / kMoeStages) * kBTileBytes; };
     if (issuer && ok) {
       for (int i = 0; i < npre; ++i) {
-        const int uu = u0 + i, st = uu % kMoeStages;
-        if (uu >= kMoeStages && !mbar_wait(&tail->empty[st], ((uu / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) { ok = 0; break; }
+        if (!slot_free(i)) { ok = 0; break; }
         const int slot = dn_lo + i / kbI, kb = i % kbI;
-        mbar_expect_tx(&tail->full[st], kATileBytes + kBTileBytes);
-        tma_load_3d_hint(smem + st * kMoeStageBytes, &tmDown, &tail->full[st], kb * 128, dn_tile * kTileN, sm.active[slot],
+        mbar_expect_tx(&sm.dn_full[i % kDnSlots], kATileBytes + kBTileBytes);
+        tma_load_3d_hint(slot_w(i), &tmDown, &sm.dn_full[i % kDnSlots], kb * 128, dn_tile * kTileN, sm.active[slot],
                          l2_policy_evict_first());
       }
     }
@@ -263,15 +278,13 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     if (issuer && ok) {
       asm volatile("fence.proxy.async;" ::: "memory");
       for (int i = 0; i < dn_units; ++i) {
-        const int uu = u0 + i, st = uu % kMoeStages;
         const int slot = dn_lo + i / kbI, kb = i % kbI;
-        uint8_t* sa = smem + st * kMoeStageBytes;
         if (i >= npre) {
-          if (uu >= kMoeStages && !mbar_wait(&tail->empty[st], ((uu / kMoeStages) & 1) ^ 1, status, kSiteStageEmpty | st)) break;
-          mbar_expect_tx(&tail->full[st], kATileBytes + kBTileBytes);
-          tma_load_3d_hint(sa, &tmDown, &tail->full[st], kb * 128, dn_tile * kTileN, sm.active[slot], l2_policy_evict_first());
+          if (!slot_free(i)) break;
+          mbar_expect_tx(&sm.dn_full[i % kDnSlots], kATileBytes + kBTileBytes);
+          tma_load_3d_hint(slot_w(i), &tmDown, &sm.dn_full[i % kDnSlots], kb * 128, dn_tile * kTileN, sm.active[slot], l2_policy_evict_first());
         }
-        tma_load_2d(sa + kMoeStageA, &tmY8, &tail->full[st], kb * 128, slot * kTok);
+        tma_load_2d(slot_b(i), &tmY8, &sm.dn_full[i % kDnSlots], kb * 128, slot * kTok);
       }
     }
   } else if (warp == 1) {
@@ -299,17 +312,18 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
         umma_commit(&sm.gu_full[buf]);
       }
       NRT_STAMP(5);
-      for (int ud = 0; ud < dn_units && ok; ++ud, ++u) {
-        const int st = u % kMoeStages, buf = ud % kDnBufs;
+      for (int ud = 0; ud < dn_units && ok; ++ud) {
+        const int h = ud % kDnSlots, buf = ud % kDnBufs;
         if (ud >= kDnBufs && !mbar_wait(&tail->acc_empty[buf], ((ud / kDnBufs) & 1) ^ 1, status, kSiteAccEmpty | 0x10 | buf)) { ok = false; break; }
-        if (!mbar_wait(&tail->full[st], (u / kMoeStages) & 1, status, kSiteTmaFull | 0x10 | st)) { ok = false; break; }
+        if (!mbar_wait(&sm.dn_full[h], (ud / kDnSlots) & 1, status, kSiteTmaFull | 0x10 | h)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + st * kMoeStageBytes);
-        const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kMoeStageA);
+        const uint32_t base = smem_u32(smem + (h % kMoeStages) * kMoeStageBytes);
+        const uint64_t da = umma_desc_sw128(base + (h / kMoeStages) * kATileBytes);
+        const uint64_t db = umma_desc_sw128(base + kMoeStageA + (h / kMoeStages) * kBTileBytes);
         const uint32_t d0 = tmem + kDnBase + buf * kDnCols;
 #pragma unroll
         for (int j = 0; j < 4; ++j) umma_f8(d0, da + 2 * j, db + 2 * j, idesc, j > 0);
-        umma_commit(&tail->empty[st]);
+        umma_commit(&sm.dn_empty[h]);
         umma_commit(&tail->acc_full[buf]);
       }
       NRT_STAMP(6);
