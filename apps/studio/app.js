@@ -1,26 +1,29 @@
 import { SseParser, Throughput } from "./sse.js";
+import { RequestQueue } from "./queue.js";
+import { curvePoints, thin } from "./curve.js";
+import { renderMarkdown } from "./markdown.js";
+import { normalizeBase, buildRequest, assistantTurn, describeHealth, statsLine } from "./core.js";
 
 const $ = (id) => document.getElementById(id);
 let controller = null;
 const history = [];
-const pending = [];
+const base = () => normalizeBase($("base").value);
 
 async function health() {
   try {
-    const r = await fetch($("base").value + "/health");
-    const j = await r.json();
-    $("health").textContent = `health: ${j.status} slot=${j.slot} queued=${j.queued}`;
-  } catch (e) { $("health").textContent = "health: unreachable"; }
+    const r = await fetch(base() + "/health");
+    $("health").textContent = "health: " + describeHealth(await r.json());
+  } catch (e) { $("health").textContent = "health: " + describeHealth(null); }
 }
 setInterval(health, 2000); health();
 
 function drawCurve(points) {
   const c = $("curve"), g = c.getContext("2d");
   g.clearRect(0, 0, c.width, c.height);
-  if (points.length < 2) return;
-  const max = Math.max(...points.map((p) => p[1]), 1), t0 = points[0][0], t1 = points[points.length - 1][0] || 1;
+  const { points: xy, max } = curvePoints(points, c.width, c.height);
+  if (xy.length < 2) return;
   g.beginPath();
-  points.forEach(([t, v], i) => { const x = (t - t0) / (t1 - t0 || 1) * c.width, y = c.height - v / max * (c.height - 4); i ? g.lineTo(x, y) : g.moveTo(x, y); });
+  xy.forEach(([x, y], i) => { i ? g.lineTo(x, y) : g.moveTo(x, y); });
   g.strokeStyle = "#3b82f6"; g.stroke();
   g.fillText(`${max.toFixed(0)} tok/s`, 4, 10);
 }
@@ -30,17 +33,16 @@ async function run(prompt) {
   const span = (cls) => { const s = document.createElement("span"); s.className = cls; out.appendChild(s); return s; };
   out.appendChild(document.createTextNode(`\n> ${prompt}\n`));
   history.push({ role: "user", content: prompt });
-  const body = { model: $("model").value, max_tokens: +$("max").value, temperature: +$("temp").value, top_p: +$("topp").value,
-                 seed: +$("seed").value, stream: true, messages: history.slice() };
-  if ($("think").checked) body.thinking = { type: "enabled", budget_tokens: 1024 };
+  const { body, headers } = buildRequest({ model: $("model").value, maxTokens: +$("max").value, temperature: +$("temp").value,
+    topP: +$("topp").value, seed: +$("seed").value, thinking: $("think").checked, session: $("session").value }, history);
   controller = new AbortController();
   const t0 = performance.now();
-  const tp = new Throughput(1000), parser = new SseParser(), curve = [];
+  const tp = new Throughput(1000), parser = new SseParser();
+  let curve = [];
   const blocks = [];
   let current = null, firstContent = null;
   try {
-    const r = await fetch($("base").value + "/v1/messages", { method: "POST", signal: controller.signal,
-      headers: { "content-type": "application/json", "x-session-id": $("session").value, "x-naivert-token-progress": "1" }, body: JSON.stringify(body) });
+    const r = await fetch(base() + "/v1/messages", { method: "POST", signal: controller.signal, headers, body: JSON.stringify(body) });
     if (!r.ok) { out.appendChild(document.createTextNode(`[${r.status}] ${await r.text()}\n`)); history.pop(); return; }
     const reader = r.body.getReader(), dec = new TextDecoder();
     for (;;) {
@@ -51,32 +53,26 @@ async function run(prompt) {
         else if (event === "content_block_delta") {
           const d = data.delta, piece = d.text ?? d.thinking ?? d.partial_json ?? "";
           if (firstContent === null) firstContent = performance.now() - t0;
-          current.text += piece; current.el.textContent += piece;
+          current.text += piece;
+          if (current.type === "text" && $("md").checked) current.el.innerHTML = renderMarkdown(current.text); else current.el.textContent += piece;
           const n = data.naivert?.generated_tokens;
-          if (n !== undefined) { const now = performance.now() - t0; curve.push([now, tp.push(now, n)]); drawCurve(curve); }
+          if (n !== undefined) { const now = performance.now() - t0; curve.push([now, tp.push(now, n)]); curve = thin(curve, 2000); drawCurve(curve); }
         } else if (event === "message_delta") {
           const tm = data.naivert?.timings || {};
-          $("stats").textContent = `stop=${data.delta.stop_reason} out=${data.usage.output_tokens} cache_read=${data.usage.cache_read_input_tokens} ` +
-            `device=${tm.decode_tok_s_device ?? "?"} tok/s peak1s=${tp.peak.toFixed(0)} tok/s first=${(firstContent ?? 0).toFixed(0)} ms total=${(performance.now() - t0).toFixed(0)} ms`;
+          $("stats").textContent = statsLine(data, tm, { peak: tp.peak, firstMs: firstContent ?? 0, totalMs: performance.now() - t0 });
         } else if (event === "error") { out.appendChild(document.createTextNode(`\n[error] ${data.error?.message}\n`)); }
       }
       out.scrollTop = out.scrollHeight;
     }
-    history.push({ role: "assistant", content: blocks.map((b) => b.type === "thinking" ? { type: "thinking", thinking: b.text } : b.type === "tool_use" ? { ...b.block, input: JSON.parse(b.text || "{}") } : { type: "text", text: b.text }) });
+    history.push(assistantTurn(blocks));
   } catch (e) { out.appendChild(document.createTextNode(`\n[stopped] ${e.name}\n`)); history.pop(); }
   finally { controller = null; }
 }
 
-async function drain() {
-  while (pending.length) {
-    const p = pending[0];
-    renderQueue();
-    await run(p);
-    pending.shift();
-    renderQueue();
-  }
-}
-function renderQueue() { $("queue").innerHTML = pending.map((p, i) => `<li>${i === 0 ? "▶" : "…"} ${p.slice(0, 40)}</li>`).join(""); }
+const queue = new RequestQueue((item) => run(item.prompt));
+queue.onChange(({ active, waiting }) => {
+  $("queue").innerHTML = (active ? [`<li>▶ ${active.prompt.slice(0, 40)}</li>`] : []).concat(waiting.map((w) => `<li>… ${w.prompt.slice(0, 40)}</li>`)).join("");
+});
 
-$("send").onclick = () => { const p = $("prompt").value.trim(); if (!p) return; $("prompt").value = ""; pending.push(p); if (pending.length === 1) drain(); else renderQueue(); };
+$("send").onclick = () => { const p = $("prompt").value.trim(); if (!p) return; $("prompt").value = ""; queue.push(p); };
 $("stop").onclick = () => controller?.abort();

@@ -76,3 +76,52 @@ def test_compose_file_is_consistent_with_the_entrypoint():
     for key in svc["environment"]:
         if key.startswith("NAIVERT_"):
             assert key in known, f"{key} is set by compose but not read by the entrypoint"
+
+
+def test_studio_local_server_serves_files_and_proxies_streams():
+    """Static files from apps/studio and a pass-through of /health and a chunked /v1/messages stream."""
+    import http.client
+    import importlib.util
+    import threading
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    class Api(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            body = b'{"status": "ok"}'
+            self.send_response(200); self.send_header("content-type", "application/json")
+            self.send_header("content-length", str(len(body))); self.end_headers(); self.wfile.write(body)
+
+        def do_POST(self):
+            n = int(self.headers.get("content-length") or 0)
+            sent = self.rfile.read(n)
+            self.send_response(200); self.send_header("content-type", "text/event-stream")
+            self.send_header("x-echo-session", self.headers.get("x-session-id", "")); self.send_header("Transfer-Encoding", "chunked"); self.end_headers()
+            for piece in (b"event: message_start\ndata: {}\n\n", b"event: echo\ndata: " + sent + b"\n\n"):
+                self.wfile.write(f"{len(piece):x}\r\n".encode() + piece + b"\r\n"); self.wfile.flush()
+            self.wfile.write(b"0\r\n\r\n")
+
+    api = ThreadingHTTPServer(("127.0.0.1", 0), Api)
+    threading.Thread(target=api.serve_forever, daemon=True).start()
+    spec = importlib.util.spec_from_file_location("studio_local_server", os.path.join(ROOT, "apps", "studio", "local_server.py"))
+    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    srv = mod.serve(f"http://127.0.0.1:{api.server_address[1]}", port=0)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", srv.server_address[1], timeout=10)
+        c.request("GET", "/index.html"); r = c.getresponse(); page = r.read()
+        assert r.status == 200 and b"<html" in page.lower()
+        c.request("GET", "/health"); r = c.getresponse()
+        assert r.status == 200 and json.loads(r.read())["status"] == "ok"
+        c.request("POST", "/v1/messages", body=b'{"x": 1}', headers={"content-type": "application/json", "x-session-id": "S"})
+        r = c.getresponse(); text = r.read().decode()
+        assert r.status == 200 and r.getheader("x-echo-session") == "S"
+        assert "event: message_start" in text and 'data: {"x": 1}' in text
+        c.request("POST", "/other", body=b""); r = c.getresponse(); r.read()
+        assert r.status == 405
+    finally:
+        srv.shutdown(); api.shutdown()
