@@ -197,3 +197,18 @@ def test_xid_delta_check(tmp_path):
     assert X.main(["compare", str(a), str(a)]) == 0 and X.main(["compare", str(a), str(b)]) == 1
     assert X.main(["snapshot", str(c), "--source", str(tmp_path / "missing.log")]) == 0
     assert X.main(["compare", str(a), str(c)]) == 0 and X.main(["compare", str(a), str(c), "--strict"]) == 1
+
+
+def test_ctypes_mirrors_match_the_c_argument_structs():
+    """Field names, offsets and sizes of every kernel argument struct, parsed from the CUDA sources, equal the ctypes
+    classes of ops/kernels.py; structs declared in several translation units are identical there."""
+    from naivert_b200.ops import abi
+    problems = abi.check_all()
+    assert not problems, problems
+    assert len(abi.check_all.report) == len(abi.STRUCTS) >= 18
+    # the parser itself: layout of a struct with padding, arrays and a nested struct
+    inner = abi.parse_fields("int a; const float* p; unsigned char pad[3];", {})
+    lay, size, align = abi.layout(inner)
+    assert lay == [("a", 0, 4), ("p", 8, 8), ("pad", 16, 3)] and size == 24 and align == 8
+    outer = abi.parse_fields("Inner x[2]; unsigned long long t; uint16_t h;", {"Inner": (24, 8)})
+    assert abi.layout(outer)[0] == [("x", 0, 48), ("t", 48, 8), ("h", 56, 2)] and abi.layout(outer)[1] == 64
