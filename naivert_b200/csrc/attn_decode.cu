@@ -49,6 +49,7 @@ struct AttnArgs {               // must match target_kernels.cu
   float* o_scale;
   float* part;
   unsigned int* tickets;
+  unsigned long long* stamps;   // opt-in phase stamps of the tensor-core decode kernel (%globaltimer, ns), [CTA][8]; null: none
 };
 
 constexpr int kVd = 128, kChunk = 128, kM = 16, kStagesKV = 2;
@@ -110,13 +111,17 @@ template <int HD>
 __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
   extern __shared__ uint4 smem_raw[];
   Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>(smem_raw);
-  griddep_wait();
-  griddep_launch();
+  unsigned long long* stamp = a.stamps ? a.stamps + (size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 : nullptr;
+#define NRT_ASTAMP(i) do { if (stamp && threadIdx.x == 0) stamp[i] = globaltimer(); } while (0)
+  NRT_ASTAMP(0);
   const int g = blockIdx.x, r = blockIdx.y, sp = blockIdx.z, splits = gridDim.z;
-  if (r >= a.rows) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hpg = a.heads / a.kv_heads;                      // live query heads (<= 16)
   const int h0 = g * hpg;
+  // The position word was written by the previous round's tail (or the step's cursor kernel), at least two launches
+  // back: with programmatic dependent launch that work is complete before this grid may start, so the word - and the
+  // cache rows of earlier steps - are read before the wait for the immediate predecessor (the projection that
+  // appends this step's rows).
   const int p0 = *a.pos0;
   const int pos = p0 + r;
   const int qr = lane >> 2, qc = (lane & 3) * 2;             // fragment row / column pair of this lane
@@ -133,30 +138,40 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
   const int c_first = sp * per, c_last = min(nchunks_all, (sp + 1) * per);      // this CTA's chunks
   const int nchunks = max(0, c_last - c_first);
 
-  auto issue = [&](int c0, int stage) {
-    for (int i = tid; i < kChunk * (HD / 8); i += 256) {
-      const int t = i / (HD / 8), c = i - t * (HD / 8);
-      const int j = c0 + t;
-      const bool valid = j < count;
-      const int id = valid ? kl.id(j) : 0;
-      const __nv_bfloat16* src;
-      if (id < 0) src = a.k_blk + ((size_t)(-id - 1) * a.kv_heads + g) * HD;
-      else src = a.k_cache + (kl.slot(id, j) * a.kv_heads + g) * HD;
-      cp_async16(&sm.k[stage][t][c * 8], src + c * 8, valid);
+  // Two threads per key: the row address is worked out once per key, then the thread copies its half of the row's
+  // 16-byte pieces.  `which`: 0 = keys appended by earlier steps (cache rows before this step's first position),
+  // 1 = this step's own rows (written by the predecessor kernel), 2 = all.
+  auto issue = [&](int c0, int stage, int which) {
+    const int t = tid >> 1, half = tid & 1;
+    const int j = c0 + t;
+    const bool valid = j < count;
+    const int id = valid ? kl.id(j) : 0;
+    const bool own = id < 0 || (a.mode != 1 && id >= p0);       // a row of the running step
+    const bool take = which == 2 || (which == 1) == own;
+    if (!take) return;
+    const __nv_bfloat16 *ksrc, *vsrc;
+    if (id < 0) {
+      ksrc = a.k_blk + ((size_t)(-id - 1) * a.kv_heads + g) * HD;
+      vsrc = a.v_blk + ((size_t)(-id - 1) * a.kv_heads + g) * kVd;
+    } else {
+      const size_t row = kl.slot(id, j);
+      ksrc = a.k_cache + (row * a.kv_heads + g) * HD;
+      vsrc = a.v_cache + (row * a.kv_heads + g) * kVd;
     }
-    for (int i = tid; i < kChunk * (kVd / 8); i += 256) {
-      const int t = i / (kVd / 8), c = i - t * (kVd / 8);
-      const int j = c0 + t;
-      const bool valid = j < count;
-      const int id = valid ? kl.id(j) : 0;
-      const __nv_bfloat16* src;
-      if (id < 0) src = a.v_blk + ((size_t)(-id - 1) * a.kv_heads + g) * kVd;
-      else src = a.v_cache + (kl.slot(id, j) * a.kv_heads + g) * kVd;
-      cp_async16(&sm.v[stage][t][c * 8], src + c * 8, valid);
-    }
+#pragma unroll
+    for (int c = 0; c < HD / 16; ++c) cp_async16(&sm.k[stage][t][(half * (HD / 16) + c) * 8], ksrc + (half * (HD / 16) + c) * 8, valid);
+#pragma unroll
+    for (int c = 0; c < kVd / 16; ++c) cp_async16(&sm.v[stage][t][(half * (kVd / 16) + c) * 8], vsrc + (half * (kVd / 16) + c) * 8, valid);
   };
+  // sliding window / draft context: the rows of earlier steps are requested before the wait for the predecessor
+  const bool early = a.mode != 1 && nchunks > 0 && r < a.rows;
+  if (early) issue(c_first * kChunk, 0, 0);
+  griddep_wait();
+  griddep_launch();
+  NRT_ASTAMP(1);
+  if (r >= a.rows) return;
   // the first gather is in flight while Q is staged
-  if (nchunks > 0) issue(c_first * kChunk, 0);
+  if (nchunks > 0) issue(c_first * kChunk, 0, early ? 1 : 2);
   cp_async_commit();
   for (int i = tid; i < kM * (HD / 8); i += 256) {
     const int h = i / (HD / 8), c = i - h * (HD / 8);
@@ -184,10 +199,11 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
   for (int ci = 0; ci < nchunks; ++ci) {
     const int c0 = (c_first + ci) * kChunk, st = ci & 1;
     const int n = min(kChunk, count - c0);
-    if (ci + 1 < nchunks) issue(c0 + kChunk, st ^ 1);
+    if (ci + 1 < nchunks) issue(c0 + kChunk, st ^ 1, 2);
     cp_async_commit();                                        // (possibly empty) group of chunk ci + 1
     cp_async_wait<1>();                                       // this thread's copies of chunk ci have landed
     __syncthreads();                                          // ... and everybody else's
+    if (ci == 0) NRT_ASTAMP(2);
     // ---- S = Q K^T: warp w scores keys [8w, 8w + 8) and [64 + 8w, 64 + 8w + 8) for all heads
 #pragma unroll
     for (int nt = 0; nt < kChunk / 64; ++nt) {
@@ -266,6 +282,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
   }
   cp_async_wait<0>();
   __syncthreads();
+  NRT_ASTAMP(3);
 
   // unnormalised O of this CTA -> shared memory (heads x channels)
 #pragma unroll
@@ -299,6 +316,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
     __syncthreads();
     if (!sm.last) return;
     __threadfence();
+    NRT_ASTAMP(4);
     const float* all = a.part + ((size_t)r * a.kv_heads + g) * splits * kM * kPartStride;
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -354,6 +372,8 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
       if (lane == 0) a.o_scale[(size_t)r * (ldo / 128) + h0 + h] = sc;
     }
   }
+  NRT_ASTAMP(5);
+#undef NRT_ASTAMP
 }
 
 template <int HD>

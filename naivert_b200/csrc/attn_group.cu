@@ -49,6 +49,7 @@ struct AttnArgs {               // must match target_kernels.cu
   float* o_scale;
   float* part;
   unsigned int* tickets;
+  unsigned long long* stamps;   // opt-in phase stamps of the tensor-core decode kernel (%globaltimer, ns), [CTA][8]; null: none
 };
 
 constexpr int kHd = 192, kVd = 128, kChunk = 64, kM = 16, kStagesKV = 2;

@@ -341,6 +341,7 @@ struct AttnArgs {
   // and the last CTA to arrive merges them in split order.
   float* part;                   // [16][heads][splits][v_dim + 2]
   unsigned int* tickets;         // [16][heads], zero between launches
+  unsigned long long* stamps;   // opt-in phase stamps of the tensor-core decode kernel (%globaltimer, ns), [CTA][8]; null: none
 };
 
 // One CTA (128 threads) per (head, row); keys are processed in chunks of 128 with an online softmax.

@@ -68,7 +68,7 @@ class AttnArgs(C.Structure):
                 ("rows", I32), ("heads", I32), ("kv_heads", I32), ("head_dim", I32), ("v_dim", I32),
                 ("scale", F32), ("mode", I32), ("window", I32), ("ring", I32), ("sink", VP), ("sel", VP),
                 ("top_k", I32), ("k_blk", VP), ("v_blk", VP), ("o_bf16", VP), ("o8", VP), ("o_scale", VP),
-                ("part", VP), ("tickets", VP)]
+                ("part", VP), ("tickets", VP), ("stamps", VP)]
 
 
 class IndexArgs(C.Structure):

@@ -84,7 +84,8 @@ class DraftRuntime:
         self.y = torch.zeros(PAD_ROWS, self.I, dtype=bf, device=dev)
         self.map_y = K.act_tmap(self.y)
         self.attn_splits = 3
-        self.tc_splits = 8
+        # one 128-key chunk per CTA: the context window plus the block's own rows
+        self.tc_splits = max(1, -(-(d.window + PAD_ROWS) // 128))
         self.attn_part = torch.zeros(max(PAD_ROWS * self.nh * self.attn_splits * (hd + 2),
                                          K.attn_decode_part_floats(PAD_ROWS, self.nkv, self.tc_splits)), dtype=f32, device=dev)
         self.attn_tickets = torch.zeros(PAD_ROWS * self.nh, dtype=i32, device=dev)

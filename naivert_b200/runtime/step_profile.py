@@ -31,6 +31,7 @@ from typing import Dict, List
 import torch
 
 STAMP_NAMES = {
+    "attn": ["entry", "upstream done", "first chunk landed", "chunks done", "merge begins (last CTA)", "done"],
     "gemm": ["entry", "barriers+tmem", "upstream done", "operand built", "first stage", "last mma", "acc read",
              "partials merged", "peer words pushed", "peer words arrived", "(polls)", "epilogue done"],
     "router": {0: "entry", 12: "upstream done", 13: "row scales", 14: "dot products", 1: "scores published",
@@ -50,7 +51,7 @@ def attach_stamps(eng, layer: int) -> Dict[str, torch.Tensor]:
     round graph is captured (the pointers are kernel arguments)."""
     bufs: Dict[str, torch.Tensor] = {}
     d = eng.target.layers[layer]
-    for key in ("args_qkv", "args_o", "args_router", "args_moe", "args_gu", "args_down"):
+    for key in ("args_qkv", "args_attn", "args_o", "args_router", "args_moe", "args_gu", "args_down"):
         if key not in d:
             continue
         b = torch.zeros(300 * 16, dtype=torch.int64, device=eng.target.x.device)
@@ -73,6 +74,16 @@ def report_stamps(bufs: Dict[str, torch.Tensor], layer: int) -> List[str]:
         if len(t) == 0:
             continue
         names = STAMP_NAMES["router"] if k == "args_router" else STAMP_NAMES["moe"] if k == "args_moe" else None
+        if k == "args_attn":
+            t8 = bufs[k][:300 * 16].view(600, 8).cpu().numpy()
+            t8 = t8[t8[:, 0] > 0]
+            lines.append(f"layer {layer} attn: {len(t8)} CTAs; us after the layer's first stamp (median over CTAs / last CTA)")
+            for i, label in enumerate(["entry", "upstream done", "first chunk landed", "chunks done", "merge begins (last CTA)", "done"]):
+                col = t8[:, i]
+                col = col[col > t0]
+                if len(col):
+                    lines.append(f"   {label:26s} {(np.median(col) - t0) / 1e3:8.2f} / {(col.max() - t0) / 1e3:8.2f}   ({len(col)} CTAs)")
+            continue
         lines.append(f"layer {layer} {k[5:]}: {len(t)} CTAs; us after the layer's first stamp (median over CTAs / last CTA)")
         order = sorted(range(16), key=lambda i: np.median(t[:, i][t[:, i] > t0]) if (t[:, i] > t0).any() else 1e30)
         for i in order:
