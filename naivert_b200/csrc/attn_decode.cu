@@ -322,18 +322,30 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
     for (int t = 0; t < 2; ++t) {
       const int h = warp * 2 + t;
       float m_run = -FLT_MAX, l_run = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int q = 0; q < splits; ++q) {                     // fixed merge order: deterministic
-        const float* o = all + ((size_t)q * kM + h) * kPartStride;
-        const float mq = __ldcg(o), lq = __ldcg(o + 1);
-        float aq[4];
+      // eight splits per batch: their 48 loads are in flight together, then they are folded in split order
+#pragma unroll 1
+      for (int q0 = 0; q0 < splits; q0 += 8) {
+        float mq[8], lq[8], aq[8][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) aq[j] = __ldcg(o + 2 + lane + 32 * j);
-        const float m_new = fmaxf(m_run, mq);
-        const float c_old = __expf(m_run - m_new), c_new = __expf(mq - m_new);
-        l_run = l_run * c_old + lq * c_new;
+        for (int i = 0; i < 8; ++i) {
+          const int q = min(q0 + i, splits - 1);
+          const float* o = all + ((size_t)q * kM + h) * kPartStride;
+          mq[i] = __ldcg(o);
+          lq[i] = __ldcg(o + 1);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = acc[j] * c_old + aq[j] * c_new;
-        m_run = m_new;
+          for (int j = 0; j < 4; ++j) aq[i][j] = __ldcg(o + 2 + lane + 32 * j);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (q0 + i < splits) {                              // fixed merge order: deterministic
+            const float m_new = fmaxf(m_run, mq[i]);
+            const float c_old = __expf(m_run - m_new), c_new = __expf(mq[i] - m_new);
+            l_run = l_run * c_old + lq[i] * c_new;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = acc[j] * c_old + aq[i][j] * c_new;
+            m_run = m_new;
+          }
+        }
       }
       if (lane == 0) { sm.m[h] = m_run; sm.l[h] = l_run; }
 #pragma unroll

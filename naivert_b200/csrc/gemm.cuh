@@ -529,8 +529,11 @@ __device__ __forceinline__ void qkv_post_epilogue(const AttnPostArgs& a_in, cons
 // words are polled from the local mailbox and all ranks' values are added in rank order in fp32 on top of the
 // residual; the bf16 result (and optionally its per-tile sums of squares for the next RMSNorm) is stored.
 #define NRT_STAMP(i) do { if (stamp) stamp[i] = globaltimer(); } while (0)
+// `resid_pre`: the residual values of this thread's feature for rows 0..7, loaded by the caller while the MMAs were
+// still running (null: they are loaded here).
 __device__ __forceinline__ void allreduce_epilogue(const GemmArgs& p, float (&mix0)[kTok], int n, int n_tile, int row, int lane,
-                                                   int quad, bool leader, GemmSmemTail* tail, unsigned long long* stamp) {
+                                                   int quad, bool leader, GemmSmemTail* tail, unsigned long long* stamp,
+                                                   const float* resid_pre = nullptr) {
   const FabricArgs& f = p.fab;
   const int owner = f.mode == 1 ? n / (p.n_total / f.tp) : f.rank;        // reduce-scatter: one owner per feature
   const bool col_ok = leader && n < p.n_total;
@@ -542,7 +545,8 @@ __device__ __forceinline__ void allreduce_epilogue(const GemmArgs& p, float (&mi
   float sum[kArRows];
 #pragma unroll
   for (int r = 0; r < kArRows; ++r)
-    sum[r] = (p.resid && r < p.rows && col_ok) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
+    sum[r] = resid_pre ? (col_ok ? resid_pre[r] : 0.f)
+                       : ((p.resid && r < p.rows && col_ok) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f);
   uint32_t own[kArPairs];
 #pragma unroll
   for (int j = 0; j < kArPairs; ++j) own[j] = pack_bf16x2(mix0[2 * j], mix0[2 * j + 1]);
@@ -829,6 +833,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
     }
     PostCtx post_ctx;
     if (EPI == kEpiQkvPost) post_ctx = qkv_post_prepare(p.post, n0, quad, lane, p.rows);
+    // the residual rows were written by an earlier kernel: fetched now, added when the sums are complete
+    float resid_pre[kArRows];
+    if (EPI == kEpiAllReduce) {
+#pragma unroll
+      for (int r = 0; r < kArRows; ++r)
+        resid_pre[r] = (p.resid && r < p.rows && crank == 0 && n < p.n_total) ? __bfloat162float(p.resid[(size_t)r * p.ld_out + n]) : 0.f;
+    }
     float mix0[kTok];
 #pragma unroll
     for (int r = 0; r < kTok; ++r) mix0[r] = 0.f;
@@ -993,7 +1004,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         }
       }
     } else if (EPI == kEpiAllReduce) {
-      allreduce_epilogue(p, mix0, n, n_tile, row, lane, quad, leader, tail, stamp);
+      allreduce_epilogue(p, mix0, n, n_tile, row, lane, quad, leader, tail, stamp, resid_pre);
     }
     (void)ok;
     if (threadIdx.x == 64) NRT_STAMP(11);

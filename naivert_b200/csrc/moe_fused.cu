@@ -335,6 +335,15 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     const uint32_t lane_addr = tmem + (uint32_t(quad * 32) << 16);
     const int rows = p.r.rows;
     bool ok = true;
+    // the residual rows of the down epilogue (written by the predecessor kernel) are fetched now, long before use
+    float resid_pre[kArRows];
+    {
+      const int nres = dn_tile * kTileN + row;
+#pragma unroll
+      for (int r = 0; r < kArRows; ++r)
+        resid_pre[r] = (p.ar.resid && r < p.ar.rows && dn_on && dn_range == 0 && nres < p.ar.n_total)
+                           ? __bfloat162float(p.ar.resid[(size_t)r * p.ar.ld_out + nres]) : 0.f;
+    }
     // ---- gate/up items
     // Steps have at most eight token rows: the epilogue reads the first eight columns of an accumulator.  The
     // activation scales are the same for every item: staged once as [K block][row].
@@ -492,7 +501,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     }
     if (tid == 64) NRT_STAMP(9);
     // every CTA takes part in the epilogue's barriers; only the leaders exchange and store
-    allreduce_epilogue(p.ar, mix0, n, dn_tile, row, lane, quad, leader, tail, nullptr);
+    allreduce_epilogue(p.ar, mix0, n, dn_tile, row, lane, quad, leader, tail, nullptr, resid_pre);
     if (tid == 64) NRT_STAMP(11);
   }
 #undef NRT_STAMP
