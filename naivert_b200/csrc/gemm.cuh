@@ -700,6 +700,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
       }
     }
   }
+  if (BSRC != kBTma && warp >= 2) {
+    // the norm weights of this thread's first operand unit are a cold HBM line once per step: requested into L2 now,
+    // so the load after the wait does not pay the DRAM (and page-table) round trip
+    const int et = (int)threadIdx.x - 64, units = kb_count * 8;
+    const int cu0 = units < 128 ? et % units : et;
+    if (cu0 < units) prefetch_l2(p.ngamma + (kb_first + (cu0 >> 3)) * kElemsPerStage + (cu0 & 7) * (kElemsPerStage / 8));
+  }
   griddep_wait();
   griddep_launch();
   if (threadIdx.x == 0) NRT_STAMP(2);

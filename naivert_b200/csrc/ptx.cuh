@@ -190,6 +190,9 @@ __device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int x, 
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
+}
 // generic-proxy writes to shared memory -> visible to the async proxy (UMMA / TMA reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
