@@ -567,21 +567,49 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
   const int per = (((n + 1023) / 1024) + 3) & ~3;   // elements per thread, a multiple of 4
   const int lo = tid * per, hi = min(n, lo + per);
 
+  // Rows of up to 16,384 keys: a thread's (at most sixteen) keys are loaded once and stay in registers for the four
+  // radix passes and the final sweep, instead of five trips to L2.
+  constexpr int kCache = 16;
+  const bool cached = per <= kCache;
+  uint32_t kc[kCache];
+  uint32_t vmask = 0u;
+  if (cached) {
+#pragma unroll
+    for (int q = 0; q < kCache; q += 4) {
+      const int i = lo + q;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (q < per && i < hi) {
+        if (vec && i + 4 <= n) { const float4 f = *reinterpret_cast<const float4*>(row + i); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+        else { for (int c = 0; c < 4; ++c) v[c] = i + c < n ? row[i + c] : 0.f; }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        kc[q + c] = order_key(v[c]);
+        if (q < per && i + c < hi) vmask |= 1u << (q + c);
+      }
+    }
+  }
   uint32_t prefix = 0, mask = 0, need = top_k;
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    for (int i = lo; i < hi; i += 4) {
-      float v[4];
-      if (vec && i + 4 <= n) { const float4 f = *reinterpret_cast<const float4*>(row + i); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
-      else { for (int c = 0; c < 4; ++c) v[c] = i + c < n ? row[i + c] : 0.f; }
+    if (cached) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        if (i + c < hi) {
-          const uint32_t k = order_key(v[c]);
-          if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
-        }
+      for (int q = 0; q < kCache; ++q)
+        if (((vmask >> q) & 1u) && (kc[q] & mask) == prefix) atomicAdd(&hist[(kc[q] >> shift) & 255u], 1u);
+    } else {
+      for (int i = lo; i < hi; i += 4) {
+        float v[4];
+        if (vec && i + 4 <= n) { const float4 f = *reinterpret_cast<const float4*>(row + i); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+        else { for (int c = 0; c < 4; ++c) v[c] = i + c < n ? row[i + c] : 0.f; }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (i + c < hi) {
+            const uint32_t k = order_key(v[c]);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+          }
+      }
     }
     __syncthreads();
     if (warp == 0) {
@@ -615,7 +643,14 @@ __global__ void __launch_bounds__(1024) topk_rows_kernel(const float* __restrict
   // prefix = exact threshold key; `need` elements equal to it are taken, lowest index first
   const uint32_t thr = prefix;
   unsigned long long m_gt = 0ull, m_eq = 0ull;      // winners of this thread's segment (per <= 64: rows up to 65536)
-  if (per <= 64) {
+  if (cached) {
+#pragma unroll
+    for (int q = 0; q < kCache; ++q)
+      if ((vmask >> q) & 1u) {
+        if (kc[q] > thr) m_gt |= 1ull << q;
+        else if (kc[q] == thr) m_eq |= 1ull << q;
+      }
+  } else if (per <= 64) {
     for (int i = lo; i < hi; i += 4) {
       float v[4];
       if (vec && i + 4 <= n) { const float4 f = *reinterpret_cast<const float4*>(row + i); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
