@@ -60,7 +60,7 @@ struct EpArgs {
 
 // ----------------------------------------------------------------------------- counts + layout
 __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
-  __shared__ unsigned int hist[kEpMaxExperts];
+  __shared__ unsigned int hist[kEpMaxExperts + 1];
   __shared__ uint64_t xv[kXchgMaxWords];          // [tp][experts]
   __shared__ int seg_base[kEpMaxExperts + 1];
   griddep_wait();
@@ -99,6 +99,45 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (a.experts <= 256 && tp * a.experts <= kXchgMaxWords / 2) {
+    // Every warp owns one contiguous range of the pairs.  Pass 1 counts the range's pairs per expert (warp-private
+    // row of 16-bit counters), a prefix over the warps turns the counts into each range's offset inside the expert's
+    // segment, pass 2 walks the range in index order and hands out rows.  Same stable order as ranking the pairs one
+    // by one (lower index first), with three block barriers instead of two thousand.
+    // (the counters live in the unused upper half of the exchange buffer: 32 x 256 x 2 bytes)
+    unsigned short (*wc)[256] = reinterpret_cast<unsigned short (*)[256]>(xv + kXchgMaxWords / 2);
+    for (int i = threadIdx.x; i < 32 * 256; i += 1024) (&wc[0][0])[i] = 0;
+    __syncthreads();
+    const int per = (n + 31) / 32;
+    const int lo = warp * per, hi = min(n, lo + per);
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+      const int i = i0 + lane;
+      const int e = i < hi ? a.topk_ids[i] : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (e >= 0 && (peers & ((1u << lane) - 1u)) == 0u) wc[warp][e] += (unsigned short)__popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < a.experts) {
+      unsigned run = 0;
+      for (int w = 0; w < 32; ++w) { const unsigned t = wc[w][threadIdx.x]; wc[w][threadIdx.x] = (unsigned short)run; run += t; }
+    }
+    __syncthreads();
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+      const int i = i0 + lane;
+      const int e = i < hi ? a.topk_ids[i] : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      const int below = __popc(peers & ((1u << lane) - 1u));
+      if (e >= 0) {
+        unsigned base = 0;
+        if (below == 0) { base = hist[e] + wc[warp][e]; wc[warp][e] += (unsigned short)__popc(peers); }
+        base = __shfl_sync(peers, base, __ffs(peers) - 1);
+        a.slot_of[i] = (int)base + below;
+      }
+      __syncwarp();
+    }
+    __syncthreads();
+  } else
   for (int c0 = 0; c0 < n; c0 += 1024) {
     const int i = c0 + threadIdx.x;
     const int e = i < n ? a.topk_ids[i] : -1;
@@ -115,20 +154,34 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpArgs a) {
       __syncthreads();
     }
   }
-  // work list of my own experts
-  if (threadIdx.x == 0) {
-    int items = 0;
-    for (int el = 0; el < a.experts_local; ++el) {
+  // work list of my own experts: one thread per local expert counts its row groups, a prefix over the experts gives
+  // each its first item, then every thread writes its own items (same list as a sequential walk over the experts)
+  {
+    int* first_item = reinterpret_cast<int*>(hist);          // hist is free again: [experts_local + 1]
+    int my_rows = 0, my_items = 0;
+    const int el = threadIdx.x;
+    if (el < a.experts_local) {
       const int e = rank * a.experts_local + el;
-      int rows = 0;
-      for (int s = 0; s < tp; ++s) rows += (int)xv[s * a.experts + e];
-      a.seg_rows[el] = rows;
-      for (int r0 = 0; r0 < rows; r0 += ir) {
-        if (items < a.max_items) { a.item_expert[items] = el; a.item_row[items] = seg_base[e] + r0; }
-        ++items;
+      for (int s = 0; s < tp; ++s) my_rows += (int)xv[s * a.experts + e];
+      a.seg_rows[el] = my_rows;
+      my_items = (my_rows + ir - 1) / ir;
+    }
+    __syncthreads();                                          // everybody is done with hist as running positions
+    if (el < a.experts_local) first_item[el + 1] = my_items;
+    if (el == 0) first_item[0] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < a.experts_local; ++i) first_item[i + 1] += first_item[i];
+      *a.n_items = first_item[a.experts_local] < a.max_items ? first_item[a.experts_local] : a.max_items;
+    }
+    __syncthreads();
+    if (el < a.experts_local) {
+      const int e = rank * a.experts_local + el;
+      for (int k = 0; k < my_items; ++k) {
+        const int idx = first_item[el] + k;
+        if (idx < a.max_items) { a.item_expert[idx] = el; a.item_row[idx] = seg_base[e] + k * ir; }
       }
     }
-    *a.n_items = items < a.max_items ? items : a.max_items;
   }
 }
 

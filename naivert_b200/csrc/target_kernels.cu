@@ -876,6 +876,14 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
   const int tid = threadIdx.x;
   unsigned long long* stamp = (a.stamps && gridDim.y == 1) ? a.stamps + (size_t)blockIdx.x * 16 : nullptr;
   if (stamp && tid == 0) stamp[0] = globaltimer();
+  if (a.w == nullptr) {
+    // selection only: the score matrix was filled by the caller (chunked prefill computes it as one fp32 matrix
+    // product for thousands of rows); one CTA per group of 16 rows
+    griddep_wait();
+    griddep_launch();
+    router_select(a, sm, true, nullptr, nullptr, nullptr);
+    return;
+  }
   router_scores(a, blockIdx.x, gridDim.x, sm, stamp);
   // The CTA's score stores are ordered before the ticket by the barrier (CTA scope) followed by thread 0's fence
   // (cumulative, GPU scope); the last CTA reads the scores from L2 after the same pair on the acquiring side.
@@ -990,7 +998,8 @@ extern "C" int nrt_router(const void* args, void* stream, int pdl) {
   if (a.x && a.x8 && (!a.xs || a.rows * (a.hidden / 128) > 16 * ((a.experts + 1) / 2))) return -3;
   const int groups = a.rows > kMaxRows ? (a.rows + kMaxRows - 1) / kMaxRows : 1;
   if (groups > 1 && (a.x || a.probs)) return -3;                      // row groups: plain routing of normed rows only
-  return launch_pdl(router_kernel, dim3((a.experts + 1) / 2, groups), dim3(256), smem, S(stream), pdl != 0, a);
+  if (!a.w && (!a.scores || a.x)) return -3;                          // selection only: needs the caller's score matrix
+  return launch_pdl(router_kernel, dim3(a.w ? (a.experts + 1) / 2 : 1, groups), dim3(256), smem, S(stream), pdl != 0, a);
 }
 
 // ============================================================================= allocation-free routing

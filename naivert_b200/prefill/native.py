@@ -238,7 +238,9 @@ class NativePrefill:
             else:
                 rt = s.routing
                 r = K.RouterArgs()
-                r.w, r.bias, r.xn = d["router_w"].data_ptr(), d["router_b"].data_ptr(), self.xn.data_ptr()
+                r.w, r.bias, r.xn = None, d["router_b"].data_ptr(), self.xn.data_ptr()      # selection only (scores by torch.mm)
+                if "router_wt" not in d:
+                    d["router_wt"] = d["router_w"].float().t().contiguous()                 # [hidden][experts]
                 r.hidden, r.experts, r.top_k = H, rt.expert_count, rt.top_k
                 r.sigmoid, r.normalize, r.route_scale = int(rt.score_func == "sigmoid"), int(rt.normalize_top_k), rt.route_scale
                 r.scores, r.ticket = self.scores.data_ptr(), self.tickets.data_ptr()
@@ -359,6 +361,12 @@ class NativePrefill:
                 src = self.xl if self.ep else x
                 with self._stage("router"):
                     K.prep_norm(src, d["g_post"], T, s.norm_eps, xn=xn, pdl=pdl)
+                    # scores of all chunk rows as one fp32 matrix product (library GEMM, no TF32: the same products as
+                    # the step's FMA loop, summed in another order), selection by the router kernel per 16 rows
+                    tf32 = torch.backends.cuda.matmul.allow_tf32
+                    torch.backends.cuda.matmul.allow_tf32 = False
+                    torch.mm(xn[:T].float(), d["router_wt"], out=self.scores[:T])
+                    torch.backends.cuda.matmul.allow_tf32 = tf32
                     e["router"].rows = T
                     K.router(e["router"], pdl=pdl)
                 self.moe.stage = self._stage if self.profile else None
