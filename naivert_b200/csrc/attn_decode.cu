@@ -318,9 +318,9 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
     __threadfence();
     NRT_ASTAMP(4);
     const float* all = a.part + ((size_t)r * a.kv_heads + g) * splits * kM * kPartStride;
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int h = warp * 2 + t;
+    // one live head per warp at a time (heads warp, warp + 8): with eight query heads per KV head all warps work
+#pragma unroll 1
+    for (int h = warp; h < hpg; h += 8) {
       float m_run = -FLT_MAX, l_run = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
       // eight splits per batch: their 48 loads are in flight together, then they are folded in split order
 #pragma unroll 1
@@ -356,10 +356,8 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
 
   // ---- sink column (no value), normalisation, bf16 rounding, outputs: warp w finishes heads 2w and 2w + 1
   const size_t ldo = (size_t)a.heads * kVd;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int h = warp * 2 + t;
-    if (h >= hpg) continue;
+#pragma unroll 1
+  for (int h = warp; h < hpg; h += 8) {
     float m = sm.m[h], l = sm.l[h], corr = 1.f;
     if (a.sink) {
       const float sv = __bfloat162float(a.sink[h0 + h]);

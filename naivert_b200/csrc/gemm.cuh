@@ -264,9 +264,10 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
   // Rows >= p.rows are left as they are: an MMA column depends on its own token row only, and the columns of
   // dead rows are never stored.
   // A unit is 16 bytes of operand: 8 bf16 elements, or 16 e4m3 elements (two 16-byte loads of x).  A thread owns one
-  // column unit (chunk c, unit j) - its norm weights are loaded once - and walks token rows in batches of four whose
+  // column unit (chunk c, unit j) - its norm weights are loaded once - and walks token rows in batches of eight (four for e4m3) whose
   // loads are all in flight together.  With fewer than 128 column units the threads form 128 / units row groups.
   constexpr int kLoads = FP8 ? 2 : 1;
+  constexpr int kRB = FP8 ? 4 : 8;              // token rows per batch: every load of a batch is in flight together
   constexpr int kElems = FP8 ? 128 : 64;
   const int units = kb_count * 8;
   const int groups = units < 128 ? 128 / units : 1;
@@ -275,13 +276,13 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
   // so the two memory round trips overlap.
   const int cu0 = units < 128 ? et % units : et;
   uint4 gv[kLoads];
-  uint4 xv[4][kLoads];
+  uint4 xv[kRB][kLoads];
   auto load_batch = [&](int cu, int r0) {
     const int k = (kb_first + (cu >> 3)) * kElems + (cu & 7) * (kElems / 8);
 #pragma unroll
     for (int l = 0; l < kLoads; ++l) gv[l] = __ldg(reinterpret_cast<const uint4*>(p.ngamma + k + 8 * l));
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
+    for (int b = 0; b < kRB; ++b) {
       const int r = r0 + b * groups;
 #pragma unroll
       for (int l = 0; l < kLoads; ++l)
@@ -307,10 +308,10 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
   for (int cu = cu0; cu < units && g < groups; cu += 128) {
     const int c = cu >> 3, j = cu & 7;
 #pragma unroll 1
-    for (int r0 = g; r0 < rows; r0 += 4 * groups) {
+    for (int r0 = g; r0 < rows; r0 += kRB * groups) {
       if (cu != cu0 || r0 != g) load_batch(cu, r0);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
+      for (int b = 0; b < kRB; ++b) {
         const int r = r0 + b * groups;
         const bool on = r < rows;
         const float rs = rs_s[on ? r : 0];
