@@ -143,9 +143,14 @@ struct GemmArgs {
   // opt-in phase stamps (%globaltimer, ns): [CTA][16] words, CTA = blockIdx.y * gridDim.x + blockIdx.x.
   // 0 entry, 1 barriers + TMEM ready, 2 upstream grid done, 3 token operand built, 4 first weight stage landed,
   // 5 last MMA issued, 6 accumulators read, 7 cluster partials merged, 8 peer words pushed, 9 peer words arrived
-  // (word 10: polls of the local mailbox), 11 epilogue done.  Null: no stamps.
+  // (word 10: polls of the local mailbox), 11 epilogue done, 12 row scales of the fused RMSNorm ready, 14 normalised
+  // operand stored.  Null: no stamps.
   unsigned long long* stamps;
   unsigned int publish_delay_ns;  // test knob: this rank delays its mailbox publish by this long (a late peer that still arrives)
+  // Region a later kernel streams from HBM (the next projection's weights): every CTA requests its share into L2 once
+  // its own weight loads are issued, so the next kernel's loads - and the small loads queued behind them - hit L2.
+  const void* pf_ptr;
+  unsigned long long pf_bytes;
 };
 
 constexpr int kOutStageBytes = kTok * kTileN * 4;      // accumulators of a tile as [row][feature] for row-wise epilogues
@@ -258,7 +263,7 @@ __device__ __forceinline__ uint8_t e4m3_bits(float v) {
 // stored in bscale[r * kb_count + c].  Rows >= p.rows are zero.
 template <bool FP8>
 __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* ball, float* bscale, float* rs_s,
-                                                   int kb_first, int kb_count, int et) {
+                                                   int kb_first, int kb_count, int et, unsigned long long* stamp = nullptr) {
   const int rows = p.rows;
   const int tiles = p.k_total / 128;
   // Rows >= p.rows are left as they are: an MMA column depends on its own token row only, and the columns of
@@ -290,18 +295,25 @@ __device__ __forceinline__ void build_norm_operand(const GemmArgs& p, uint8_t* b
     }
   };
   const bool active = cu0 < units && g < groups && g < rows;
-  if (active) load_batch(cu0, g);
-  // 1 / rms of every row in one round trip: 8 threads per row, each adds the tiles t = sub, sub + 8, ...
+  // 1 / rms of every row: 8 threads per row, each adds the tiles t = sub, sub + 8, ...  These loads gate everything
+  // else, so they are issued first; the operand's own loads queue up behind them.
   {
     const int r = et >> 3, sub = et & 7;
-    float ssum = 0.f;
-    if (r < rows) {
-#pragma unroll 4
-      for (int t = sub; t < tiles; t += 8) ssum += __ldcg(p.nssq + t * kTok + r);
+    float sv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = sub + 8 * i;
+      sv[i] = (r < rows && t < tiles) ? __ldcg(p.nssq + t * kTok + r) : 0.f;
     }
+    if (active) load_batch(cu0, g);
+    float ssum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ssum += sv[i];
+    for (int t = sub + 64; t < tiles && r < rows; t += 8) ssum += __ldcg(p.nssq + t * kTok + r);     // hidden > 8192
 #pragma unroll
     for (int off = 4; off > 0; off >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, off);
     if (sub == 0 && r < rows) rs_s[r] = rsqrtf(ssum / (float)p.k_total + p.neps);
+    if (stamp && et == 0) stamp[12] = globaltimer();
   }
   epi_bar();
 #pragma unroll 1
@@ -786,6 +798,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
         }
         tma_load_2d(sa + Cfg::kABytes, &tmB, &tail->full[st], kx, brow);
       }
+      prefetch_share_l2(p.pf_ptr, p.pf_bytes, (int)(blockIdx.y * gridDim.x + blockIdx.x), (int)(gridDim.x * gridDim.y));
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
@@ -833,7 +846,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_consta
     if (BSRC != kBTma) {
       // the epilogue warps are idle until the first accumulator completes: they normalise (and quantise)
       // the CTA's token rows into shared memory while the weight tiles stream in
-      if (units > 0) build_norm_operand<FP8>(p, ball, bscale, tail->rs, kb_first, kb_count, (int)threadIdx.x - 64);
+      if (units > 0) build_norm_operand<FP8>(p, ball, bscale, tail->rs, kb_first, kb_count, (int)threadIdx.x - 64, stamp);
+      if (threadIdx.x == 64) NRT_STAMP(14);
       fence_proxy_async_smem();
       mbar_arrive(&tail->b_ready);
       epi_bar();                                     // bscale of every thread is visible to the epilogue

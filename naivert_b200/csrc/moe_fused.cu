@@ -287,6 +287,9 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
         tma_load_2d(slot_b(i), &tmY8, &sm.dn_full[i % kDnSlots], kb * 128, slot * kTok);
       }
     }
+    // the down stream of this CTA is issued: HBM goes quiet during the merge and the all-reduce - the next kernel's
+    // weights are requested into L2 in that gap
+    if (issuer) prefetch_share_l2(p.ar.pf_ptr, p.ar.pf_bytes, cta, kMoeCtas);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer (both phases)
     if (elect_one()) {

@@ -190,6 +190,23 @@ __device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int x, 
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// Ask for `bytes` (a multiple of 16, 16-byte aligned) of global memory to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// This CTA's share of a region that a later kernel will stream (typically the next projection's weights): requested
+// into L2 in 8 KiB pieces by one thread, at a point where this kernel's own HBM traffic is over.
+__device__ __forceinline__ void prefetch_share_l2(const void* base, unsigned long long bytes, int part, int parts) {
+  if (base == nullptr || bytes == 0ull) return;
+  const unsigned long long per = ((bytes / (unsigned long long)parts) + 15ull) & ~15ull;
+  unsigned long long lo = per * (unsigned long long)part;
+  const unsigned long long hi = lo + per < bytes ? lo + per : bytes;
+  const char* p8 = reinterpret_cast<const char*>(base);
+  for (; lo + 16ull <= hi; lo += 8192ull) {
+    const unsigned long long n = hi - lo < 8192ull ? (hi - lo) & ~15ull : 8192ull;
+    bulk_prefetch_l2(p8 + lo, (uint32_t)n);
+  }
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
 }

@@ -60,7 +60,7 @@ class GemmArgs(C.Structure):
                 ("row_offsets", VP), ("ep_meta", VP), ("ep_combine", VP * K_MAX_PEERS), ("ep_top_k", I32),
                 ("ep_dispatch_call", I32), ("ep_return_call", I32),
                 ("nx", VP), ("ngamma", VP), ("nssq", VP), ("neps", F32), ("ssq_out", VP), ("post", AttnPostArgs),
-                ("stamps", VP), ("publish_delay_ns", C.c_uint)]
+                ("stamps", VP), ("publish_delay_ns", C.c_uint), ("pf_ptr", VP), ("pf_bytes", U64)]
 
 
 class AttnArgs(C.Structure):

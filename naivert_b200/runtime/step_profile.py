@@ -94,7 +94,7 @@ def report_stamps(bufs: Dict[str, torch.Tensor], layer: int) -> List[str]:
             if names is None and i == 10:
                 lines.append(f"   {'mailbox sweeps (max)':26s} {int(t[:, 10].max()):8d}")
                 continue
-            label = names.get(i, str(i)) if names else STAMP_NAMES["gemm"][i] if i < 12 else str(i)
+            label = names.get(i, str(i)) if names else STAMP_NAMES["gemm"][i] if i < 12 else {12: "row scales ready", 14: "operand stored"}.get(i, str(i))
             lines.append(f"   {label:26s} {(np.median(col) - t0) / 1e3:8.2f} / {(col.max() - t0) / 1e3:8.2f}   ({len(col)} CTAs)")
     return lines
 

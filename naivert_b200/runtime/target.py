@@ -350,6 +350,18 @@ class TargetRuntime:
         g = self._gemm_args(self.lm_head.shape[0], H, R)
         g.out_f32, g.ld_out = self.logits.data_ptr(), self.logits.shape[1]
         self.args_head = g
+        # Weights of the next projection are requested into L2 by the kernel before it, at the point where that
+        # kernel's own HBM stream is over: the q/k/v projection asks for o_proj's weights, the MoE block (or the dense
+        # down projection) for the next layer's q/k/v weights.  NAIVERT_NEXT_WEIGHTS_L2=0 turns it off.
+        import os
+        if self.fused and os.environ.get("NAIVERT_NEXT_WEIGHTS_L2", "1") == "1":
+            for L, d in enumerate(self.layers):
+                wo = d["wo"].w
+                d["args_qkv"].pf_ptr, d["args_qkv"].pf_bytes = wo.data_ptr(), wo.numel() * wo.element_size()
+                if L + 1 < len(self.layers):
+                    nq = self.layers[L + 1]["wqkv"]
+                    tail = d["args_moe"].ar if "args_moe" in d else d["args_down"]
+                    tail.pf_ptr, tail.pf_bytes = nq.data_ptr(), nq.numel() * nq.element_size()
         pa = K.PrologueArgs()
         pa.tokens, pa.table, pa.x, pa.ssq = self.tokens.data_ptr(), self.embed.data_ptr(), self.x.data_ptr(), self.ssq.data_ptr()
         pa.hidden, pa.rows, pa.vocab, pa.mode = H, R, self.embed.shape[0], 0
