@@ -54,13 +54,22 @@ __device__ __forceinline__ bool xchg_reduce_u64(uint64_t* vals, int n, const Xch
     }
     const uint64_t* base = x.box[x.rank] + (slab * kXchgMaxWords + i) * 2;
     for (uint32_t sweep = 0; need != 0; ++sweep) {
+      // every outstanding word is requested before any answer is examined (the guards test a snapshot of the mask), so
+      // the loads of a sweep overlap instead of each waiting for the previous comparison
+      const uint32_t snap = need;
+      uint32_t t[2 * kXchgPeers], v[2 * kXchgPeers];
 #pragma unroll
-      for (int s = 0; s < kXchgPeers; ++s) {
-        const uint64_t* src = base + (size_t)s * kXchgMaxWords * 2;
-        uint32_t t, v;
-        if (need & (1u << (2 * s))) { ld_tagged(src, t, v); if (t == tag) { lo[s] = v; need &= ~(1u << (2 * s)); } }
-        if (need & (2u << (2 * s))) { ld_tagged(src + 1, t, v); if (t == tag) { hi[s] = v; need &= ~(2u << (2 * s)); } }
+      for (int q = 0; q < 2 * kXchgPeers; ++q) {
+        t[q] = ~tag;
+        v[q] = 0u;
+        if (snap & (1u << q)) ld_tagged(base + (size_t)(q >> 1) * kXchgMaxWords * 2 + (q & 1), t[q], v[q]);
       }
+#pragma unroll
+      for (int q = 0; q < 2 * kXchgPeers; ++q)
+        if ((snap & (1u << q)) && t[q] == tag) {
+          if (q & 1) hi[q >> 1] = v[q]; else lo[q >> 1] = v[q];
+          need &= ~(1u << q);
+        }
       if ((sweep & 255u) == 255u) {
         if (*reinterpret_cast<volatile uint32_t*>(x.status) != 0u) { ok = false; break; }
         if (globaltimer() > deadline) { report(x.status, kSiteRendezvous | (uint32_t)call); ok = false; break; }

@@ -594,15 +594,23 @@ __device__ __forceinline__ void allreduce_epilogue(const GemmArgs& p, float (&mi
     const uint64_t deadline = globaltimer() + f.timeout_ns;
     const uint64_t* base = f.mailbox[f.rank] + slab * kRowPairs * f.features + n;
     for (uint32_t sweep = 0; missing != 0; ++sweep) {
+      // One sweep = every outstanding word requested before any answer is looked at: the guards test a snapshot of
+      // the mask, so no load waits for the previous load's comparison and the fabric round trips overlap.
+      const uint64_t need = missing;
+      uint32_t tt[kMaxPeers][kArPairs], vv[kMaxPeers][kArPairs];
+#pragma unroll
+      for (int s = 0; s < kMaxPeers; ++s)
+#pragma unroll
+        for (int j = 0; j < kArPairs; ++j) {
+          tt[s][j] = ~tag;
+          vv[s][j] = 0u;
+          if (need & (1ull << (s * kArPairs + j))) ld_tagged(base + ((size_t)s * kRowPairs + j) * f.features, tt[s][j], vv[s][j]);
+        }
 #pragma unroll
       for (int s = 0; s < kMaxPeers; ++s)
 #pragma unroll
         for (int j = 0; j < kArPairs; ++j)
-          if (missing & (1ull << (s * kArPairs + j))) {
-            uint32_t t, v;
-            ld_tagged(base + ((size_t)s * kRowPairs + j) * f.features, t, v);
-            if (t == tag) { w[s][j] = v; missing &= ~(1ull << (s * kArPairs + j)); }
-          }
+          if ((need & (1ull << (s * kArPairs + j))) && tt[s][j] == tag) { w[s][j] = vv[s][j]; missing &= ~(1ull << (s * kArPairs + j)); }
       if ((sweep & 255u) == 255u) {
         if (*reinterpret_cast<volatile uint32_t*>(f.status) != 0u) break;
         if (globaltimer() > deadline) { report(f.status, kSiteMailbox | (uint32_t)__ffsll((long long)missing)); break; }

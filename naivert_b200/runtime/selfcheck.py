@@ -58,7 +58,7 @@ def tp_selfcheck(rank: int, world: int, group, device, layers: int = 4, generate
     from ..ops import kernels as K
     from .engine import Engine
 
-    spec = small_w8a8_spec(layers)
+    spec = small_w8a8_spec(max(layers, world))              # one draft feature tap per layer: their count must split over the ranks
     w = prepare_weights(spec, init_state_dict(spec, seed=0, device=device))
     dw = prepare_draft_weights(spec, init_draft_state_dict(spec, seed=1, device=device))
     eng = Engine.build(spec, rank=rank, tp=world, group=group, capacity=1024, device=device,
