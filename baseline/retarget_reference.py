@@ -58,7 +58,8 @@ def retarget(source: str) -> list:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--source", default="/root/reference")
+    ap.add_argument("--source", default=os.environ.get("NAIVERT_REFERENCE_SRC"), required="NAIVERT_REFERENCE_SRC" not in os.environ,
+                    help="checkout of the reference repository (or set NAIVERT_REFERENCE_SRC)")
     a = ap.parse_args()
     edits = retarget(a.source)
     with open(os.path.join(HERE, "RETARGET.txt"), "w") as f:

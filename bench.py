@@ -52,7 +52,7 @@ def reference_arm(a) -> int:
         return 0
 
     if not os.path.isdir(ref):
-        return unavailable("baseline/_ref is absent (python baseline/retarget_reference.py copies and retargets the reference)")
+        return unavailable("baseline/_ref is absent (python baseline/retarget_reference.py --source <reference checkout> copies and retargets the reference)")
     ver = _nvcc_version()
     if ver is None or ver < (13, 1):
         return unavailable(f"reference kernels do not build with nvcc {ver}: they need CUDA >= 13.1 (cvt.rn.bf16x2.e4m3x2, "
@@ -181,8 +181,9 @@ def main() -> int:
     eng.round.stop_ids.fill_(-1)                              # random weights: never stop on a sampled EOS id
     stamp_bufs = None
     if a.stamp_layer >= 0:                                    # diagnostic: in-kernel phase times of one layer (rank 0 prints them)
-        from naivert_b200.runtime.step_profile import attach_stamps
+        from naivert_b200.runtime.step_profile import attach_sampler_stamps, attach_stamps
         stamp_bufs = attach_stamps(eng, a.stamp_layer)
+        samp_buf = attach_sampler_stamps(eng)
 
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, spec.vocab, (a.prompt,), generator=g, dtype=torch.int32).pin_memory()
@@ -274,8 +275,8 @@ def main() -> int:
     # (small W8A8 geometry, same kernels and code paths: oracle error, lockstep, determinism, speculative == greedy)
     check = None
     if stamp_bufs is not None and rank == 0:
-        from naivert_b200.runtime.step_profile import report_stamps
-        print("\n".join(report_stamps(stamp_bufs, a.stamp_layer)), file=sys.stderr)
+        from naivert_b200.runtime.step_profile import report_sampler_stamps, report_stamps
+        print("\n".join(report_stamps(stamp_bufs, a.stamp_layer) + report_sampler_stamps(samp_buf)), file=sys.stderr)
     last_prefill, kv_bytes = eng.last_prefill, eng.kv_bytes()
     kernels_per_round, host_launches = int(r.kernels_per_round), r.host_launches
     path_info = {"pdl": bool(r.pdl), "device_chain": bool(a.device_chain), "fused_step": bool(r.t.fused),

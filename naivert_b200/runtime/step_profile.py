@@ -63,6 +63,23 @@ def attach_stamps(eng, layer: int) -> Dict[str, torch.Tensor]:
     return bufs
 
 
+def attach_sampler_stamps(eng) -> torch.Tensor:
+    buf = torch.zeros(32, dtype=torch.int64, device=eng.target.x.device)
+    eng.round.args_sampler.stamps = buf.data_ptr()
+    return buf
+
+
+def report_sampler_stamps(buf: torch.Tensor) -> List[str]:
+    t = buf.cpu().tolist()
+    if t[30] <= 0:
+        return []
+    names = ["maxima", "codes", "nucleus pass 0", "nucleus pass 1", "nucleus pass 2", "nucleus pass 3 + accept", "tile masses / draw"]
+    lines = ["sampler (single launch): us after kernel entry - last CTA of the phase arrived / phase released"]
+    for ph, nm in enumerate(names):
+        lines.append(f"   {nm:26s} {(t[2 * ph] - t[30]) / 1e3:8.2f} / {(t[2 * ph + 1] - t[30]) / 1e3:8.2f}")
+    return lines
+
+
 def report_stamps(bufs: Dict[str, torch.Tensor], layer: int) -> List[str]:
     import numpy as np
     torch.cuda.synchronize()
@@ -124,10 +141,7 @@ def main(argv: List[str] = None) -> int:
     eng = Engine.build(spec, rank=0, tp=1, group=None, capacity=a.prompt + 1024, seed=0, device=dev, pdl=a.pdl, shape_tp=a.shape_tp)
     eng.round.stop_ids.fill_(-1)
     bufs = attach_stamps(eng, a.stamp_layer) if a.stamp_layer >= 0 else {}
-    samp_stamps = None
-    if a.stamp_layer >= 0:
-        samp_stamps = torch.zeros(32, dtype=torch.int64, device=dev)
-        eng.round.args_sampler.stamps = samp_stamps.data_ptr()
+    samp_stamps = attach_sampler_stamps(eng) if a.stamp_layer >= 0 else None
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, spec.vocab, (a.prompt,), generator=g, dtype=torch.int32)
     sp = SamplingParams(temperature=0.4, top_p=0.95, seed=1234, forced_accept_p=0.7)
@@ -166,12 +180,7 @@ def main(argv: List[str] = None) -> int:
     if bufs:
         lines += report_stamps(bufs, a.stamp_layer)
     if samp_stamps is not None:
-        t = samp_stamps.cpu().tolist()
-        if t[30] > 0:
-            names = ["maxima", "codes", "nucleus pass 0", "nucleus pass 1", "nucleus pass 2", "nucleus pass 3 + accept", "tile masses / draw"]
-            lines.append("sampler (single launch): us after kernel entry - last CTA of the phase arrived / phase released")
-            for ph, nm in enumerate(names):
-                lines.append(f"   {nm:26s} {(t[2 * ph] - t[30]) / 1e3:8.2f} / {(t[2 * ph + 1] - t[30]) / 1e3:8.2f}")
+        lines += report_sampler_stamps(samp_stamps)
     eng.close()
     text = "\n".join(lines)
     print(text)
