@@ -56,11 +56,34 @@ def retarget(source: str) -> list:
     return edits
 
 
+def make_overlay() -> str:
+    """Directory of symbolic links to the newest CCCL / CUTLASS header trees installed with the Python packages
+    (flashinfer vendors CCCL 3.x and CUTLASS 4.5), for the reference's own include-path knob."""
+    import importlib.util
+    spec = importlib.util.find_spec("flashinfer")
+    if spec is None or not spec.submodule_search_locations:
+        raise SystemExit("flashinfer (the package that vendors the headers) is not installed")
+    data = os.path.join(list(spec.submodule_search_locations)[0], "data")
+    links = {"cub": "cccl/cub/cub", "cuda": "cccl/libcudacxx/include/cuda", "nv": "cccl/libcudacxx/include/nv",
+             "thrust": "cccl/thrust/thrust", "cute": "cutlass/include/cute", "cutlass": "cutlass/include/cutlass"}
+    out = os.path.join(HERE, "include_overlay")
+    os.makedirs(out, exist_ok=True)
+    for name, rel in links.items():
+        dst = os.path.join(out, name)
+        if os.path.islink(dst):
+            os.unlink(dst)
+        os.symlink(os.path.join(data, rel), dst)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--source", default=os.environ.get("NAIVERT_REFERENCE_SRC"), required="NAIVERT_REFERENCE_SRC" not in os.environ,
                     help="checkout of the reference repository (or set NAIVERT_REFERENCE_SRC)")
+    ap.add_argument("--overlay", action="store_true", help="also (re)create baseline/include_overlay")
     a = ap.parse_args()
+    if a.overlay:
+        print("include overlay:", make_overlay())
     edits = retarget(a.source)
     with open(os.path.join(HERE, "RETARGET.txt"), "w") as f:
         f.write("# lines of the reference copy that differ from the source (architecture string only)\n")
