@@ -26,8 +26,9 @@ struct XchgArgs {
 enum XchgOp : int { kXSum = 0, kXMax = 1 };
 
 // Called by all threads of ONE CTA.  vals[0..n) (shared or global, local to this rank) are
-// replaced by the reduction over ranks.  `call` must be unique inside one epoch (< 64).
-template <int OP>
+// replaced by the reduction over ranks.  `call` must be unique inside one epoch (< 64).  kVB values of a thread are
+// polled together (2 for exchanges of many values per thread; costs registers).
+template <int OP, int kVB = 1>
 __device__ __forceinline__ bool xchg_reduce_u64(uint64_t* vals, int n, const XchgArgs& x, int call) {
   if (x.tp <= 1) return true;
   const uint32_t tag = (*x.epoch) * 64u + (uint32_t)call + 1u;
@@ -43,47 +44,61 @@ __device__ __forceinline__ bool xchg_reduce_u64(uint64_t* vals, int n, const Xch
     }
   }
   const uint64_t deadline = globaltimer() + x.timeout_ns;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    // batched poll: all outstanding words of all sources are re-read per sweep
-    uint32_t lo[kXchgPeers], hi[kXchgPeers];
-    uint32_t need = 0;
+  // All outstanding words of a thread's kVB values are requested before any answer is examined - the guards test a
+  // snapshot of the masks - so the loads of a sweep overlap instead of each waiting for the previous comparison.
+  for (int i0 = threadIdx.x; i0 < n; i0 += kVB * blockDim.x) {
+    uint32_t lo[kVB][kXchgPeers], hi[kVB][kXchgPeers];
+    uint32_t need[kVB];
 #pragma unroll
-    for (int s = 0; s < kXchgPeers; ++s) {
-      lo[s] = hi[s] = 0u;
-      if (s < x.tp && s != x.rank) need |= 3u << (2 * s);
+    for (int b = 0; b < kVB; ++b) {
+      need[b] = 0u;
+#pragma unroll
+      for (int s = 0; s < kXchgPeers; ++s) {
+        lo[b][s] = hi[b][s] = 0u;
+        if (i0 + b * (int)blockDim.x < n && s < x.tp && s != x.rank) need[b] |= 3u << (2 * s);
+      }
     }
-    const uint64_t* base = x.box[x.rank] + (slab * kXchgMaxWords + i) * 2;
-    for (uint32_t sweep = 0; need != 0; ++sweep) {
-      // every outstanding word is requested before any answer is examined (the guards test a snapshot of the mask), so
-      // the loads of a sweep overlap instead of each waiting for the previous comparison
-      const uint32_t snap = need;
-      uint32_t t[2 * kXchgPeers], v[2 * kXchgPeers];
+    for (uint32_t sweep = 0; (need[0] | need[kVB - 1]) != 0u; ++sweep) {
+      uint32_t snap[kVB], t[kVB][2 * kXchgPeers], v[kVB][2 * kXchgPeers];
 #pragma unroll
-      for (int q = 0; q < 2 * kXchgPeers; ++q) {
-        t[q] = ~tag;
-        v[q] = 0u;
-        if (snap & (1u << q)) ld_tagged(base + (size_t)(q >> 1) * kXchgMaxWords * 2 + (q & 1), t[q], v[q]);
+      for (int b = 0; b < kVB; ++b) {
+        snap[b] = need[b];
+        const uint64_t* base = x.box[x.rank] + (slab * kXchgMaxWords + (size_t)(i0 + b * (int)blockDim.x)) * 2;
+#pragma unroll
+        for (int q = 0; q < 2 * kXchgPeers; ++q) {
+          t[b][q] = ~tag;
+          v[b][q] = 0u;
+          if (snap[b] & (1u << q)) ld_tagged(base + (size_t)(q >> 1) * kXchgMaxWords * 2 + (q & 1), t[b][q], v[b][q]);
+        }
       }
 #pragma unroll
-      for (int q = 0; q < 2 * kXchgPeers; ++q)
-        if ((snap & (1u << q)) && t[q] == tag) {
-          if (q & 1) hi[q >> 1] = v[q]; else lo[q >> 1] = v[q];
-          need &= ~(1u << q);
-        }
+      for (int b = 0; b < kVB; ++b)
+#pragma unroll
+        for (int q = 0; q < 2 * kXchgPeers; ++q)
+          if ((snap[b] & (1u << q)) && t[b][q] == tag) {
+            if (q & 1) hi[b][q >> 1] = v[b][q]; else lo[b][q >> 1] = v[b][q];
+            need[b] &= ~(1u << q);
+          }
       if ((sweep & 255u) == 255u) {
         if (*reinterpret_cast<volatile uint32_t*>(x.status) != 0u) { ok = false; break; }
         if (globaltimer() > deadline) { report(x.status, kSiteRendezvous | (uint32_t)call); ok = false; break; }
       }
     }
-    uint64_t acc = vals[i];
 #pragma unroll
-    for (int s = 0; s < kXchgPeers; ++s) {
-      if (s < x.tp && s != x.rank) {
-        const uint64_t o = ((uint64_t)hi[s] << 32) | lo[s];
-        acc = OP == kXSum ? acc + o : (o > acc ? o : acc);
+    for (int b = 0; b < kVB; ++b) {
+      const int i = i0 + b * (int)blockDim.x;
+      if (i < n) {
+        uint64_t acc = vals[i];
+#pragma unroll
+        for (int s = 0; s < kXchgPeers; ++s) {
+          if (s < x.tp && s != x.rank) {
+            const uint64_t o = ((uint64_t)hi[b][s] << 32) | lo[b][s];
+            acc = OP == kXSum ? acc + o : (o > acc ? o : acc);
+          }
+        }
+        vals[i] = acc;
       }
     }
-    vals[i] = acc;
   }
   __syncthreads();
   return ok;

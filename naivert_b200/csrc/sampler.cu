@@ -272,7 +272,7 @@ __device__ __forceinline__ void post_hist(const SamplerArgs& a, uint64_t* xv, in
   for (int j = 0; j < kDist; ++j)                    // fifteen independent L2 loads per thread, in flight together
     xv[threadIdx.x + j * kThreads] = __ldcg(reinterpret_cast<const unsigned long long*>(&a.st->hist[threadIdx.x + j * kThreads]));
   __syncthreads();
-  xchg_reduce_u64<kXSum>(xv, kDist * 256, a.x, 2 + pass);
+  xchg_reduce_u64<kXSum, 2>(xv, kDist * 256, a.x, 2 + pass);
   // Threshold digit of every distribution: the largest bin b >= 1 whose suffix sum S(b) = sum of bins >= b reaches
   // the target (bin 0 when none does).  One warp per distribution; a lane holds eight bins and their suffix sums.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
