@@ -1,6 +1,7 @@
 // Small-message exchange over the peer-memory fabric: every rank pushes its values to every
 // peer as tagged words and combines the tp contributions locally (integers: order-free; the
-// float variants combine in rank order).  Used by the sampler, the draft head and the tail
+// float variants combine in rank order); many values go through a reduce-scatter form in which
+// each group of values has one owning rank.  Used by the sampler, the draft head and the tail
 // for maxima, integer masses, histograms and token broadcasts.  All waits are bounded.
 //
 // Reference counterpart: the per-stage rendezvous and tagged inbox exchange of
@@ -25,9 +26,76 @@ struct XchgArgs {
 
 enum XchgOp : int { kXSum = 0, kXMax = 1 };
 
+// Collects kVB values of this thread from every peer's slot of the local box: vals[idx[b]] (idx < 0: none) becomes the
+// reduction of the local value with the tp - 1 words pairs tagged `tag`.  All outstanding words of the kVB values are
+// requested before any answer is examined - the guards test a snapshot of the masks - so the loads of a sweep overlap
+// instead of each waiting for the previous comparison.  Bounded: gives up at `deadline` or when the status word is set.
+template <int OP, int kVB>
+__device__ __forceinline__ bool xchg_collect(uint64_t* vals, const int (&idx)[kVB], const XchgArgs& x, uint32_t tag, size_t slab,
+                                             int call, uint64_t deadline) {
+  bool ok = true;
+  uint32_t lo[kVB][kXchgPeers], hi[kVB][kXchgPeers];
+  uint32_t need[kVB], any = 0u;
+#pragma unroll
+  for (int b = 0; b < kVB; ++b) {
+    need[b] = 0u;
+#pragma unroll
+    for (int s = 0; s < kXchgPeers; ++s) {
+      lo[b][s] = hi[b][s] = 0u;
+      if (idx[b] >= 0 && s < x.tp && s != x.rank) need[b] |= 3u << (2 * s);
+    }
+    any |= need[b];
+  }
+  for (uint32_t sweep = 0; any != 0u; ++sweep) {
+    uint32_t snap[kVB], t[kVB][2 * kXchgPeers], v[kVB][2 * kXchgPeers];
+#pragma unroll
+    for (int b = 0; b < kVB; ++b) {
+      snap[b] = need[b];
+      const uint64_t* base = x.box[x.rank] + (slab * kXchgMaxWords + (size_t)max(idx[b], 0)) * 2;
+#pragma unroll
+      for (int q = 0; q < 2 * kXchgPeers; ++q) {
+        t[b][q] = ~tag;
+        v[b][q] = 0u;
+        if (snap[b] & (1u << q)) ld_tagged(base + (size_t)(q >> 1) * kXchgMaxWords * 2 + (q & 1), t[b][q], v[b][q]);
+      }
+    }
+    any = 0u;
+#pragma unroll
+    for (int b = 0; b < kVB; ++b) {
+#pragma unroll
+      for (int q = 0; q < 2 * kXchgPeers; ++q)
+        if ((snap[b] & (1u << q)) && t[b][q] == tag) {
+          if (q & 1) hi[b][q >> 1] = v[b][q]; else lo[b][q >> 1] = v[b][q];
+          need[b] &= ~(1u << q);
+        }
+      any |= need[b];
+    }
+    if ((sweep & 255u) == 255u) {
+      if (*reinterpret_cast<volatile uint32_t*>(x.status) != 0u) { ok = false; break; }
+      if (globaltimer() > deadline) { report(x.status, kSiteRendezvous | (uint32_t)call); ok = false; break; }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < kVB; ++b) {
+    if (idx[b] >= 0) {
+      uint64_t acc = vals[idx[b]];
+#pragma unroll
+      for (int s = 0; s < kXchgPeers; ++s) {
+        if (s < x.tp && s != x.rank) {
+          const uint64_t o = ((uint64_t)hi[b][s] << 32) | lo[b][s];
+          acc = OP == kXSum ? acc + o : (o > acc ? o : acc);
+        }
+      }
+      vals[idx[b]] = acc;
+    }
+  }
+  return ok;
+}
+
 // Called by all threads of ONE CTA.  vals[0..n) (shared or global, local to this rank) are
-// replaced by the reduction over ranks.  `call` must be unique inside one epoch (< 64).  kVB values of a thread are
-// polled together (2 for exchanges of many values per thread; costs registers).
+// replaced by the reduction over ranks.  `call` must be unique inside one epoch (< 64).  Consecutive calls of a rank
+// must use different slabs (call % kXchgSlabs): a peer may already push the next call's words while this rank still
+// polls the current one.  kVB values of a thread are polled together (costs registers).
 template <int OP, int kVB = 1>
 __device__ __forceinline__ bool xchg_reduce_u64(uint64_t* vals, int n, const XchgArgs& x, int call) {
   if (x.tp <= 1) return true;
@@ -44,60 +112,48 @@ __device__ __forceinline__ bool xchg_reduce_u64(uint64_t* vals, int n, const Xch
     }
   }
   const uint64_t deadline = globaltimer() + x.timeout_ns;
-  // All outstanding words of a thread's kVB values are requested before any answer is examined - the guards test a
-  // snapshot of the masks - so the loads of a sweep overlap instead of each waiting for the previous comparison.
-  for (int i0 = threadIdx.x; i0 < n; i0 += kVB * blockDim.x) {
-    uint32_t lo[kVB][kXchgPeers], hi[kVB][kXchgPeers];
-    uint32_t need[kVB];
+  for (int i0 = threadIdx.x; i0 < n && ok; i0 += kVB * blockDim.x) {
+    int idx[kVB];
 #pragma unroll
-    for (int b = 0; b < kVB; ++b) {
-      need[b] = 0u;
-#pragma unroll
-      for (int s = 0; s < kXchgPeers; ++s) {
-        lo[b][s] = hi[b][s] = 0u;
-        if (i0 + b * (int)blockDim.x < n && s < x.tp && s != x.rank) need[b] |= 3u << (2 * s);
-      }
+    for (int b = 0; b < kVB; ++b) idx[b] = i0 + b * (int)blockDim.x < n ? i0 + b * (int)blockDim.x : -1;
+    ok = xchg_collect<OP, kVB>(vals, idx, x, tag, slab, call, deadline);
+  }
+  __syncthreads();
+  return ok;
+}
+
+// Reduce-scatter form for many values: vals holds `groups` groups of `gsize` values; group g is owned by rank
+// g % tp.  Every rank pushes the values of the live groups (bit g of `live`) it does not own to their owners only -
+// 1/tp of the stores of the all-to-all form - and afterwards an owner's groups hold the sums over ranks; the groups of
+// other owners keep the local values.  Same slab rule as xchg_reduce_u64.
+template <int kVB>
+__device__ __forceinline__ bool xchg_reduce_scatter_u64(uint64_t* vals, int groups, int gsize, uint32_t live, const XchgArgs& x,
+                                                        int call) {
+  if (x.tp <= 1) return true;
+  const uint32_t tag = (*x.epoch) * 64u + (uint32_t)call + 1u;
+  const size_t slab = (size_t)(call % kXchgSlabs) * x.tp;
+  for (int g = 0; g < groups; ++g) {
+    const int owner = g % x.tp;
+    if (owner == x.rank || !((live >> g) & 1u)) continue;
+    for (int t = threadIdx.x; t < gsize; t += blockDim.x) {
+      const int i = g * gsize + t;
+      const uint64_t v = vals[i];
+      uint64_t* dst = x.box[owner] + ((slab + x.rank) * kXchgMaxWords + i) * 2;
+      st_tagged(dst, tag, (uint32_t)v);
+      st_tagged(dst + 1, tag, (uint32_t)(v >> 32));
     }
-    for (uint32_t sweep = 0; (need[0] | need[kVB - 1]) != 0u; ++sweep) {
-      uint32_t snap[kVB], t[kVB][2 * kXchgPeers], v[kVB][2 * kXchgPeers];
+  }
+  const uint64_t deadline = globaltimer() + x.timeout_ns;
+  bool ok = true;
+  for (int t = threadIdx.x; t < gsize; t += blockDim.x) {
+    for (int g0 = x.rank; g0 < groups && ok; g0 += kVB * x.tp) {
+      int idx[kVB];
 #pragma unroll
       for (int b = 0; b < kVB; ++b) {
-        snap[b] = need[b];
-        const uint64_t* base = x.box[x.rank] + (slab * kXchgMaxWords + (size_t)(i0 + b * (int)blockDim.x)) * 2;
-#pragma unroll
-        for (int q = 0; q < 2 * kXchgPeers; ++q) {
-          t[b][q] = ~tag;
-          v[b][q] = 0u;
-          if (snap[b] & (1u << q)) ld_tagged(base + (size_t)(q >> 1) * kXchgMaxWords * 2 + (q & 1), t[b][q], v[b][q]);
-        }
+        const int g = g0 + b * x.tp;
+        idx[b] = (g < groups && ((live >> g) & 1u)) ? g * gsize + t : -1;
       }
-#pragma unroll
-      for (int b = 0; b < kVB; ++b)
-#pragma unroll
-        for (int q = 0; q < 2 * kXchgPeers; ++q)
-          if ((snap[b] & (1u << q)) && t[b][q] == tag) {
-            if (q & 1) hi[b][q >> 1] = v[b][q]; else lo[b][q >> 1] = v[b][q];
-            need[b] &= ~(1u << q);
-          }
-      if ((sweep & 255u) == 255u) {
-        if (*reinterpret_cast<volatile uint32_t*>(x.status) != 0u) { ok = false; break; }
-        if (globaltimer() > deadline) { report(x.status, kSiteRendezvous | (uint32_t)call); ok = false; break; }
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < kVB; ++b) {
-      const int i = i0 + b * (int)blockDim.x;
-      if (i < n) {
-        uint64_t acc = vals[i];
-#pragma unroll
-        for (int s = 0; s < kXchgPeers; ++s) {
-          if (s < x.tp && s != x.rank) {
-            const uint64_t o = ((uint64_t)hi[b][s] << 32) | lo[b][s];
-            acc = OP == kXSum ? acc + o : (o > acc ? o : acc);
-          }
-        }
-        vals[i] = acc;
-      }
+      ok = xchg_collect<kXSum, kVB>(vals, idx, x, tag, slab, call, deadline);
     }
   }
   __syncthreads();

@@ -267,17 +267,26 @@ __device__ __forceinline__ void work_hist(const SamplerArgs& a, int bx, int d, i
   }
 }
 __device__ __forceinline__ void post_hist(const SamplerArgs& a, uint64_t* xv, int pass) {
+  // The 256 bins of a distribution are summed over ranks at ONE rank (distribution r at rank r mod tp), which finds
+  // the threshold digit and tells everybody the three numbers that come out of it: the all-to-all form would push
+  // tp times as many words through one CTA.
+  __shared__ uint64_t res[48];                       // [r] suffix mass at the digit, [16 + r] mass of its bin, [32 + r] digit
   const int shift = 24 - 8 * pass;
+  const int tp = a.x.tp > 1 ? a.x.tp : 1, rank = a.x.tp > 1 ? a.x.rank : 0;
+  uint32_t live = 0u;
 #pragma unroll
-  for (int j = 0; j < kDist; ++j)                    // fifteen independent L2 loads per thread, in flight together
+  for (int j = 0; j < kDist; ++j) {                  // fifteen independent L2 loads per thread, in flight together
     xv[threadIdx.x + j * kThreads] = __ldcg(reinterpret_cast<const unsigned long long*>(&a.st->hist[threadIdx.x + j * kThreads]));
+    live |= row_active(a, j) ? 1u << j : 0u;
+  }
+  if (threadIdx.x < 48) res[threadIdx.x] = 0ull;
   __syncthreads();
-  xchg_reduce_u64<kXSum, 2>(xv, kDist * 256, a.x, 2 + pass);
+  xchg_reduce_scatter_u64<2>(xv, kDist, 256, live, a.x, 2 + 2 * pass);
   // Threshold digit of every distribution: the largest bin b >= 1 whose suffix sum S(b) = sum of bins >= b reaches
   // the target (bin 0 when none does).  One warp per distribution; a lane holds eight bins and their suffix sums.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int r = warp; r < kDist; r += kThreads / 32) {
-    if (!row_active(a, r)) continue;                                   // uniform over the warp
+    if (!((live >> r) & 1u) || r % tp != rank) continue;                // uniform over the warp
     const double top_p = (double)a.params[1];
     const unsigned long long target = (unsigned long long)ceil(top_p * (double)ldg2(&a.st->total[r]));
     const unsigned long long above = ldg2(&a.st->above[r]);
@@ -304,11 +313,16 @@ __device__ __forceinline__ void post_hist(const SamplerArgs& a, uint64_t* xv, in
       if (i == (b & 7)) { cum = higher + suf[i]; in_bin = bin[i]; }
     cum = __shfl_sync(0xffffffffu, cum, owner);
     in_bin = __shfl_sync(0xffffffffu, in_bin, owner);
-    if (lane == 0) {
-      a.st->above[r] = above + cum - in_bin;
-      a.st->prefix[r] = ldg2(&a.st->prefix[r]) | ((unsigned int)b << shift);
-      if (pass == 3) a.st->kept[r] = above + cum;      // Z: everything with e >= tau
-    }
+    if (lane == 0) { res[r] = cum; res[16 + r] = in_bin; res[32 + r] = (unsigned long long)b; }
+  }
+  __syncthreads();
+  xchg_reduce_u64<kXSum>(res, 48, a.x, 3 + 2 * pass);   // every entry has one non-zero contributor
+  if (threadIdx.x < kDist && ((live >> threadIdx.x) & 1u)) {
+    const int r = threadIdx.x;
+    const unsigned long long above = ldg2(&a.st->above[r]);
+    a.st->above[r] = above + res[r] - res[16 + r];
+    a.st->prefix[r] = ldg2(&a.st->prefix[r]) | ((unsigned int)res[32 + r] << shift);
+    if (pass == 3) a.st->kept[r] = above + res[r];     // Z: everything with e >= tau
   }
   __syncthreads();
 #pragma unroll
@@ -340,7 +354,7 @@ __device__ __forceinline__ void do_accept(const SamplerArgs& a, uint64_t* xv) {
     }
   }
   __syncthreads();
-  xchg_reduce_u64<kXSum>(xv, 8, a.x, 6);
+  xchg_reduce_u64<kXSum>(xv, 8, a.x, 10);
   if (threadIdx.x == 0) {
     const unsigned long long seed = *a.seed;
     const uint32_t round = (uint32_t)a.ctrl[NRT_CTRL_ROUND];
@@ -449,7 +463,7 @@ __device__ __forceinline__ void do_draw(const SamplerArgs& a, int tiles, int dom
     s_tok = -1;
   }
   __syncthreads();
-  xchg_reduce_u64<kXSum>(xv, 16, a.x, 7);         // everyone learns every rank's totals
+  xchg_reduce_u64<kXSum>(xv, 16, a.x, 11);        // everyone learns every rank's totals
   unsigned long long total = 0ull, before = 0ull;
   for (int r = 0; r < a.x.tp; ++r) total += xv[r];
   const bool from_p = total == 0ull;               // empty residual (p' <= q' everywhere): draw from p'
@@ -514,7 +528,7 @@ __device__ __forceinline__ void do_draw(const SamplerArgs& a, int tiles, int dom
   __syncthreads();
   if (threadIdx.x < 16) xv[threadIdx.x] = (threadIdx.x == 0 && s_tok >= 0) ? (uint64_t)(s_tok + 1) : 0ull;
   __syncthreads();
-  xchg_reduce_u64<kXSum>(xv, 1, a.x, 8);
+  xchg_reduce_u64<kXSum>(xv, 1, a.x, 12);
   if (threadIdx.x == 0) {
     int tok = (int)xv[0] - 1;
     if (tok < 0) tok = 0;                          // unreachable while the kept set is non-empty
@@ -655,7 +669,7 @@ __global__ void tail_commit_kernel(const TailArgs a) {
     xv[threadIdx.x] = v;
   }
   __syncthreads();
-  xchg_reduce_u64<kXMax>(xv, 3, a.x, 9);
+  xchg_reduce_u64<kXMax>(xv, 3, a.x, 13);
   __syncthreads();
   const bool cancel_any = xv[0] != 0ull, failed_any = xv[1] != 0ull;
   if (threadIdx.x != 0) return;
