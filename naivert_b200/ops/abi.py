@@ -6,10 +6,15 @@ order, scalar / pointer / array / nested-struct kinds), computes the layout a 64
 compares names, offsets and total size with the ctypes classes - on the CPU, without building or loading the library
 (at load time the sizes are checked once more against ``nrt_*_args_size`` of the built library).
 
-    python -m naivert_b200.ops.abi          # prints one line per struct, exit 1 on a mismatch
+    python -m naivert_b200.ops.abi                 # prints one line per struct, exit 1 on a mismatch
+    python -m naivert_b200.ops.abi --emit FILE     # writes the ctypes classes generated from the CUDA sources
+
+The same parse also generates bindings: ``generate(name)`` builds the ctypes class of a struct from its C
+declaration, ``emit_module()`` writes all of them as Python source.  A binding for a new kernel starts from the
+emitted class; the test suite checks that every hand-kept mirror equals its generated class field by field.
 
 Reference counterpart: naivert/kernels/opgen.py generates entry and binding sources from op descriptors; here the
-sources are the description and the bindings are checked against them.
+CUDA sources are the description, and bindings are generated from and checked against them.
 """
 from __future__ import annotations
 
@@ -40,9 +45,16 @@ SCALARS = {"int": 4, "unsigned": 4, "unsigned int": 4, "uint32_t": 4, "int32_t":
 CONSTANTS = {"kMaxPeers": 8, "kXchgPeers": 8}
 
 
+CTYPES = {"int": "c_int", "unsigned": "c_uint", "unsigned int": "c_uint", "uint32_t": "c_uint32", "int32_t": "c_int32",
+          "float": "c_float", "double": "c_double", "long long": "c_longlong", "unsigned long long": "c_ulonglong",
+          "uint64_t": "c_uint64", "int64_t": "c_int64", "size_t": "c_size_t", "unsigned short": "c_ushort",
+          "uint16_t": "c_uint16", "uint8_t": "c_uint8", "char": "c_char", "unsigned char": "c_ubyte", "bool": "c_bool"}
+
+
 class Field:
-    def __init__(self, name: str, size: int, align: int, kind: str):
+    def __init__(self, name: str, size: int, align: int, kind: str, ctype: str = "", count: int = 1):
         self.name, self.size, self.align, self.kind = name, size, align, kind
+        self.ctype, self.count = ctype, count           # C element type ("*" for any pointer) and array length
 
 
 def _strip_comments(text: str) -> str:
@@ -102,7 +114,7 @@ def parse_fields(body: str, known: Dict[str, Tuple[int, int]]) -> List[Field]:
                 kind = "struct"
             else:
                 raise ValueError(f"unknown type {ctype!r} in {decl!r}")
-            fields.append(Field(name, size * count, align, kind if count == 1 else kind + "[]"))
+            fields.append(Field(name, size * count, align, kind if count == 1 else kind + "[]", "*" if ptr else ctype, count))
     return fields
 
 
@@ -115,6 +127,61 @@ def layout(fields: List[Field]) -> Tuple[List[Tuple[str, int, int]], int, int]:
         off += f.size
         amax = max(amax, f.align)
     return out, (off + amax - 1) // amax * amax, amax
+
+
+ORDER = ["FabricArgs", "AttnPostArgs", "XchgArgs", "GemmArgs", "RouterArgs", "MoeArgs"]
+
+
+def _ordered() -> List[str]:
+    return ORDER + [n for n in STRUCTS if n not in ORDER]
+
+
+def parse_all() -> Dict[str, List[Field]]:
+    """Fields of every argument struct, nested structs resolved in dependency order."""
+    known: Dict[str, Tuple[int, int]] = {}
+    out: Dict[str, List[Field]] = {}
+    for name in _ordered():
+        body = struct_body(os.path.join(CSRC, STRUCTS[name][0]), name)
+        if body is None:
+            raise ValueError(f"{name}: not found in {STRUCTS[name][0]}")
+        out[name] = parse_fields(body, known)
+        _, size, align = layout(out[name])
+        known[name] = (size, align)
+    return out
+
+
+def generate(name: str, parsed: Optional[Dict[str, List[Field]]] = None, _cache: Optional[dict] = None):
+    """The ctypes.Structure class of C struct ``name``, built from its declaration in the CUDA sources (pointers become
+    ``c_void_p``, nested argument structs their generated classes)."""
+    parsed = parsed or parse_all()
+    cache = _cache if _cache is not None else {}
+    if name in cache:
+        return cache[name]
+    fields = []
+    for f in parsed[name]:
+        if f.ctype == "*":
+            t = C.c_void_p
+        elif f.ctype in CTYPES:
+            t = getattr(C, CTYPES[f.ctype])
+        else:
+            t = generate(f.ctype, parsed, cache)
+        fields.append((f.name, t * f.count if f.count > 1 else t))
+    cache[name] = type(name, (C.Structure,), {"_fields_": fields})
+    return cache[name]
+
+
+def emit_module() -> str:
+    """Python source of all generated classes (the starting point of a new binding)."""
+    parsed = parse_all()
+    lines = ['"""ctypes mirrors of the kernels\' argument structs - generated by ``python -m naivert_b200.ops.abi --emit``."""',
+             "import ctypes as C", ""]
+    for name in _ordered():
+        lines += ["", f"class {name}(C.Structure):      # {STRUCTS[name][0]}", "    _fields_ = ["]
+        for f in parsed[name]:
+            t = "C.c_void_p" if f.ctype == "*" else "C." + CTYPES[f.ctype] if f.ctype in CTYPES else f.ctype
+            lines.append(f'        ("{f.name}", {t}{" * " + str(f.count) if f.count > 1 else ""}),')
+        lines.append("    ]")
+    return "\n".join(lines) + "\n"
 
 
 def check_all() -> List[str]:
@@ -152,6 +219,10 @@ def check_all() -> List[str]:
 
 
 def main() -> int:
+    if len(sys.argv) >= 3 and sys.argv[1] == "--emit":
+        with open(sys.argv[2], "w") as f:
+            f.write(emit_module())
+        return 0
     problems = check_all()
     print("\n".join(check_all.report))
     for p in problems:

@@ -212,3 +212,29 @@ def test_ctypes_mirrors_match_the_c_argument_structs():
     assert lay == [("a", 0, 4), ("p", 8, 8), ("pad", 16, 3)] and size == 24 and align == 8
     outer = abi.parse_fields("Inner x[2]; unsigned long long t; uint16_t h;", {"Inner": (24, 8)})
     assert abi.layout(outer)[0] == [("x", 0, 48), ("t", 48, 8), ("h", 56, 2)] and abi.layout(outer)[1] == 64
+
+
+def test_bindings_generated_from_the_cuda_sources_equal_the_kept_mirrors(tmp_path):
+    """``abi.generate`` / ``abi --emit`` build ctypes classes from the C declarations; every class used by the launch
+    wrappers has the same field names, offsets, sizes and total size as its generated counterpart."""
+    import ctypes as C
+    import importlib.util
+    from naivert_b200.ops import abi, kernels as K
+    out = tmp_path / "generated_abi.py"
+    out.write_text(abi.emit_module())
+    sp = importlib.util.spec_from_file_location("generated_abi", out)
+    gen = importlib.util.module_from_spec(sp)
+    sp.loader.exec_module(gen)
+
+    def lay(cls):
+        return [(n, getattr(cls, n).offset, getattr(cls, n).size) for n, _ in cls._fields_]
+
+    parsed, cache = abi.parse_all(), {}
+    for name, (_, cls_name) in abi.STRUCTS.items():
+        kept, emitted, built = getattr(K, cls_name), getattr(gen, name), abi.generate(name, parsed, cache)
+        assert lay(kept) == lay(emitted) == lay(built), name
+        assert C.sizeof(kept) == C.sizeof(emitted) == C.sizeof(built), name
+    # nested argument structs are the generated classes themselves, pointers are void pointers
+    g = abi.generate("GemmArgs", parsed, cache)
+    kinds = dict(g._fields_)
+    assert any(t is cache["FabricArgs"] for t in kinds.values()) and C.c_void_p in kinds.values()
