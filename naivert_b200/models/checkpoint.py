@@ -424,6 +424,8 @@ def load_rank_weights(spec: ModelSpec, root: str, rank: int, tp: int, device="cp
     ident.require(expect)
     validate_target_layout(spec, ckpt)
     w = load_rank_weights_sliced(spec, ckpt, rank, tp)
+    from .tensor_abi import check_rank_weights
+    check_rank_weights(spec, w, rank, tp)                       # every slot present with the shape the kernels expect
     return _to_device(w, device), ident
 
 

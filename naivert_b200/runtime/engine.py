@@ -70,6 +70,12 @@ class Engine:
             pdl = os.environ.get("NAIVERT_PDL", "1") == "1"
         if spec.draft is None:
             raise RuntimeContractError("the engine needs a model with a draft specification")
+        # fail closed before anything is captured if the loaded library was built from other sources than this package
+        from ..ops import kernels as K, variants
+        try:
+            variants.require_entries(K.lib(), variants.STEP_VARIANTS + (variants.PREFILL_VARIANTS if prefill_chunk else ()))
+        except ValueError as e:
+            raise RuntimeContractError(str(e)) from e
         fabric = Fabric(rank, tp, max(spec.hidden, spec.draft.hidden), group=group, device=device)
         if shape_tp:
             if tp != 1:

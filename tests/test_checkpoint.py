@@ -180,3 +180,58 @@ def test_header_rejects_overlapping_payload(tmp_path):
     p.write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 20)
     with pytest.raises(ck.CheckpointError):
         ck.read_header(str(p))
+
+
+def test_rank_tensor_abi_describes_the_sharded_weights():
+    """The slot table computed from the specification alone matches what sharding real tensors produces, at every
+    tensor-parallel degree, and a wrong slice is named by its slot."""
+    import pytest
+    import torch
+    from naivert_b200.models import weights as W
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    from naivert_b200.models.registry import resolve_model
+    from naivert_b200.models.tensor_abi import RankTensorAbi, TensorSlot, check_rank_weights, rank_tensor_abi
+    spec = small_w8a8_spec(4)
+    full = W.prepare_weights(spec, W.init_state_dict(spec))
+    for tp in (1, 2, 4, 8):
+        for rank in {0, tp - 1}:
+            w = W.shard_weights(spec, full, rank, tp)
+            abi = check_rank_weights(spec, w, rank, tp)
+            tensors = 0
+
+            def count(d):
+                nonlocal tensors
+                for v in d.values() if isinstance(d, dict) else d:
+                    if isinstance(v, (dict, list)):
+                        count(v)
+                    elif isinstance(v, torch.Tensor):
+                        tensors += 1
+            count(w)
+            assert tensors == len(abi.domain("parameter"))             # nothing in the dictionary is undescribed
+            assert abi.parameter_bytes == sum(s.nbytes for s in abi.slots if s.domain == "parameter") > 0
+    w = W.shard_weights(spec, full, 1, 2)
+    w["layers"][1]["gate"]["w"] = w["layers"][1]["gate"]["w"][:, :-128]
+    with pytest.raises(ValueError, match=r"layers\.1\.gate\.w has shape"):
+        check_rank_weights(spec, w, 1, 2)
+    w = W.shard_weights(spec, full, 0, 2)
+    del w["layers"][0]["iwq"]
+    with pytest.raises(ValueError, match=r"layers\.0\.iwq is missing"):
+        check_rank_weights(spec, w, 0, 2)
+    w = W.shard_weights(spec, full, 0, 2)
+    w["layers"][2]["wq"] = w["layers"][2]["wq"].float()
+    with pytest.raises(ValueError, match="element type"):
+        check_rank_weights(spec, w, 0, 2)
+    # planning without tensors: the full model at 8 ranks, with a one-million-token context
+    big = resolve_model("naive-n0.5")
+    abi = rank_tensor_abi(big, 3, 8, capacity=1 << 20)
+    assert 38e9 < abi.parameter_bytes < 45e9                           # ~40 GB of weights per rank
+    assert 7e9 < abi.cache_bytes < 7.6e9                               # target KV + indexer keys (the draft adds ~2.7 GB)
+    assert abi.slot("layers.1.gate.w").shape == (256, 256, 4096) and abi.slot("layers.0.ik").domain == "cache"
+    assert [s.index for s in abi.domain("cache")] == list(range(len(abi.domain("cache"))))
+    with pytest.raises(ValueError, match="unique"):
+        RankTensorAbi("x", (TensorSlot("a", "parameter", 0, (1,), "bf16", 16, "row_major"),
+                            TensorSlot("a", "parameter", 1, (1,), "bf16", 16, "row_major")))
+    with pytest.raises(ValueError, match="cover"):
+        RankTensorAbi("x", (TensorSlot("a", "cache", 1, (1,), "bf16", 16, "row_major"),))
+    with pytest.raises(ValueError):
+        rank_tensor_abi(big, 8, 8)

@@ -238,3 +238,40 @@ def test_bindings_generated_from_the_cuda_sources_equal_the_kept_mirrors(tmp_pat
     g = abi.generate("GemmArgs", parsed, cache)
     kinds = dict(g._fields_)
     assert any(t is cache["FabricArgs"] for t in kinds.values()) and C.c_void_p in kinds.values()
+
+
+def test_kernel_variants_fail_closed():
+    from dataclasses import replace
+    from naivert_b200.ops import variants as V
+    table = V.variants()
+    assert len(table) >= 25 and all(v.variant_id.endswith(f".sm100a.abi{v.abi_version}") for v in table.values())
+    assert len({v.entry for v in table.values()}) == len(table)
+    for e in V.STEP_VARIANTS + V.PREFILL_VARIANTS:
+        assert V.by_entry(e).entry == e
+    g = V.by_entry("nrt_gemm_launch")
+    assert g.args_bytes and g.max_rows == 16
+    assert V.require_variant(g, replace(g)) == g
+    with pytest.raises(ValueError, match="differs from the library"):
+        V.require_variant(g, replace(g, args_bytes=g.args_bytes + 8))
+    with pytest.raises(ValueError, match="differs"):
+        V.require_variant(g, replace(g, abi_version=g.abi_version + 1, variant_id=f"x.sm100a.abi{g.abi_version + 1}"))
+    with pytest.raises(ValueError):
+        V.KernelVariant("gemm.sm90a.abi1", "f")
+    with pytest.raises(ValueError):
+        V.KernelVariant("gemm.sm100a.abi1", "f", args_struct="GemmArgs")
+
+    class FakeLib:                                   # a library built before nrt_moe_layer existed, with an older GemmArgs
+        def nrt_gemm_launch(self): ...
+        def nrt_gemm_args_size(self): return g.args_bytes - 16
+    with pytest.raises(ValueError, match="exports no nrt_moe_layer"):
+        V.library_variant(FakeLib(), V.by_entry("nrt_moe_layer"))
+    with pytest.raises(ValueError, match="argument bytes"):
+        V.require_entries(FakeLib(), ["nrt_gemm_launch"])
+    # the built library, when present, provides every variant with the expected ABI
+    from naivert_b200.ops import kernels as K
+    try:
+        lib = K.lib()
+    except Exception:
+        return
+    assert V.check_library(lib) == []
+    assert len(V.require_entries(lib, V.STEP_VARIANTS + V.PREFILL_VARIANTS)) == len(V.STEP_VARIANTS + V.PREFILL_VARIANTS)
