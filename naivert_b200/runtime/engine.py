@@ -73,7 +73,11 @@ class Engine:
         # fail closed before anything is captured if the loaded library was built from other sources than this package
         from ..ops import kernels as K, variants
         try:
-            variants.require_entries(K.lib(), variants.STEP_VARIANTS + (variants.PREFILL_VARIANTS if prefill_chunk else ()))
+            from .modes import MODES
+            need = MODES["speculative_round"].entries + MODES["greedy_step"].entries
+            if prefill_chunk:
+                need += MODES["prefill_native"].entries
+            variants.require_entries(K.lib(), dict.fromkeys(need))
         except ValueError as e:
             raise RuntimeContractError(str(e)) from e
         fabric = Fabric(rank, tp, max(spec.hidden, spec.draft.hidden), group=group, device=device)

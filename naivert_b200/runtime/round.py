@@ -25,6 +25,7 @@ from ..models.spec import ModelSpec, SamplingParams
 from ..ops import kernels as K
 from .contract import (CTRL_CAPACITY, CTRL_CURSOR, CTRL_MAX_TOKENS, CTRL_PROMPT_CTX, STOP_REASONS)
 from .draft import DraftRuntime
+from .modes import request_fits
 from .target import PAD_ROWS, TargetRuntime
 
 RING_SIZE = 1024
@@ -195,7 +196,7 @@ class SpeculativeRound:
         ``start_pos`` context rows are already valid in the caches (a restored prefix): replay
         starts there."""
         n = int(prompt.numel())
-        if n < 1 or n + max_tokens + 2 * PAD_ROWS > self.capacity:
+        if not request_fits(n, max_tokens, self.capacity, PAD_ROWS):
             raise RuntimeContractError(f"prompt {n} + decode {max_tokens} does not fit capacity {self.capacity}")
         self.set_sampling(sp)
         self.ring.clear()

@@ -275,3 +275,45 @@ def test_kernel_variants_fail_closed():
         return
     assert V.check_library(lib) == []
     assert len(V.require_entries(lib, V.STEP_VARIANTS + V.PREFILL_VARIANTS)) == len(V.STEP_VARIANTS + V.PREFILL_VARIANTS)
+
+
+def test_decode_modes_and_call_plans():
+    import re
+    from naivert_b200.models.registry import resolve_model
+    from naivert_b200.ops import variants as V
+    from naivert_b200.runtime import modes as M
+    spec = resolve_model("naive-n0.5")
+    # every launcher a mode names is a known kernel variant
+    for m in M.MODES.values():
+        assert m.pointer_fields == M.POINTER_FIELDS
+        for e in m.entries:
+            assert V.by_entry(e).entry == e
+    greedy, rnd = M.MODES["greedy_step"], M.MODES["speculative_round"]
+    null = {b.name for b in greedy.buffers if b.storage == "null"}
+    assert null == M.DRAFT_ONLY | {"host_ring"} and all(b.storage != "null" for b in rnd.buffers)
+    assert [b.storage for b in rnd.buffers if b.name == "block_ids"] == ["borrowed"]
+    # call-index plans: unique, inside one epoch, consecutive calls in different slabs
+    plan = M.allreduce_call_plan(spec)
+    assert len(plan) == 2 * spec.layer_count + 1 + 2 * spec.draft.layer_count
+    assert M.layer_call_tags(20) == (40, 41) and dict(plan)["draft.input"] == M.DRAFT_CALL_BASE
+    xp = dict(M.exchange_call_plan())
+    assert xp["sampler.nucleus3.digit"] == 9 and xp["tail.pause_consensus"] == 13 and xp["markov.6"] == 22
+    with pytest.raises(ValueError, match="same slab"):
+        M._check_plan([("a", 2), ("b", 6)], 64, 4, "exchange")
+    with pytest.raises(ValueError, match="used by"):
+        M._check_plan([("a", 2), ("b", 3), ("c", 2)], 64, 4, "exchange")
+    with pytest.raises(ValueError, match="outside"):
+        M._check_plan([("a", 64)], 64, 4, "exchange")
+    # the plan is what the sources use
+    csrc = os.path.join(ROOT, "naivert_b200", "csrc")
+    samp = open(os.path.join(csrc, "sampler.cu")).read()
+    used = set(re.findall(r"a\.x, (\d+)\)", samp)) | set(re.findall(r"a\.x, (\d \+ 2 \* pass)\)", samp))
+    assert used == {"0", "1", "2 + 2 * pass", "3 + 2 * pass", "10", "11", "12", "13"}
+    assert "16 + step" in open(os.path.join(csrc, "draft.cu")).read()
+    src = open(os.path.join(ROOT, "naivert_b200", "runtime", "draft.py")).read()
+    assert f"DRAFT_CALL_BASE = {M.DRAFT_CALL_BASE}" in src
+    assert "epoch) * 1024u" in open(os.path.join(csrc, "gemm.cuh")).read()
+    assert f"kXchgSlabs = {M.XCHG_SLABS}" in open(os.path.join(csrc, "fabric.cuh")).read()
+    # capacity rule
+    assert M.request_fits(8192, 1024, 8192 + 1024 + 32) and not M.request_fits(8192, 1024, 8192 + 1024 + 31)
+    assert not M.request_fits(0, 10, 1000)
