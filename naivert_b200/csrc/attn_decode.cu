@@ -144,8 +144,9 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(const AttnArgs a) {
   auto issue = [&](int c0, int stage, int which) {
     const int t = tid >> 1, half = tid & 1;
     const int j = c0 + t;
-    const bool valid = j < count;
+    bool valid = j < count;
     const int id = valid ? kl.id(j) : 0;
+    valid = valid && (id < 0 || NRT_INDEX_OK(id, pos + 1, kBoundsAttnKey));   // a key of the cache is never beyond the query
     const bool own = id < 0 || (a.mode != 1 && id >= p0);       // a row of the running step
     const bool take = which == 2 || (which == 1) == own;
     if (!take) return;
@@ -400,6 +401,7 @@ int launch_decode(const AttnArgs& a, int splits, cudaStream_t stream, int pdl) {
 }  // namespace
 
 extern "C" int nrt_attn_decode_args_size() { return (int)sizeof(AttnArgs); }
+NRT_BOUNDS_EXPORT(attn_decode)
 // floats of `part` needed for (rows, kv_heads, splits)
 extern "C" long long nrt_attn_decode_part_floats(int rows, int kv_heads, int splits) {
   return (long long)rows * kv_heads * splits * kM * kPartStride;

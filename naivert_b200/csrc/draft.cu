@@ -62,6 +62,7 @@ __global__ void __launch_bounds__(256) markov_step_kernel(const MarkovArgs a, in
   griddep_wait();
   griddep_launch();
   int prev = a.block_ids[step];
+  (void)NRT_INDEX_OK(prev, a.vocab, kBoundsMarkovPrev);
   prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
   for (int i = threadIdx.x; i < a.rank_dim; i += 256) w1s[i] = __bfloat162float(a.w1[(size_t)prev * a.rank_dim + i]);
   if (threadIdx.x == 0) sbest = 0ull;
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(256, 2) markov_chain_kernel(const MarkovArgs a
   const uint32_t round = (uint32_t)a.ctrl[NRT_CTRL_ROUND];
   for (int step = 0; step < steps; ++step) {
     int prev = step == 0 ? a.block_ids[0] : __ldcg(a.block_ids + step);
+    (void)NRT_INDEX_OK(prev, a.vocab, kBoundsMarkovPrev);
     prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
     float base[4];
     if (fast) {
@@ -276,6 +278,7 @@ extern "C" int nrt_draft_block_input(const int* block_ids, const void* embed, co
                     (const __nv_bfloat16*)embed, (const __nv_bfloat16*)mask, (__nv_bfloat16*)x, hidden, rows, vocab);
 }
 extern "C" int nrt_markov_args_size() { return (int)sizeof(MarkovArgs); }
+NRT_BOUNDS_EXPORT(draft)
 // steps proposals in one launch.  `sync`: two 64-bit words (arrival counter, step generation), zero-initialised once.
 extern "C" int nrt_markov_chain(const void* args, int steps, void* sync, void* stream, int pdl) {
   MarkovArgs a;

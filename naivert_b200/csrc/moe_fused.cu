@@ -182,6 +182,11 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
     gen = sm.gen;
   }
   if (tid == 0) NRT_STAMP(3);
+#ifdef NRT_BOUNDS_CHECK
+  for (int i = tid; i < n_active; i += kMoeThreads)
+    if (!NRT_INDEX_OK(sm.active[i], p.r.experts, kBoundsExpert)) sm.active[i] = 0;
+  __syncthreads();
+#endif
 
   const int kbH = p.r.hidden / 128;                         // K blocks of gate/up
   const int kbI = p.inter / 128;                            // K blocks of down = gate/up tiles per expert
@@ -518,6 +523,7 @@ moe_layer_kernel(const __grid_constant__ CUtensorMap tmGate, const __grid_consta
 }  // namespace
 
 extern "C" int nrt_moe_args_size() { return (int)sizeof(MoeArgs); }
+NRT_BOUNDS_EXPORT(moe_fused)
 extern "C" int nrt_moe_slot_flag_words() { return kSlotsMax * kGuTilesMax; }
 extern "C" long long nrt_moe_part_floats(int hidden) { return (long long)(hidden / 128) * (kRanges - 1) * kArRows * kTileN; }
 

@@ -32,6 +32,34 @@ __device__ __forceinline__ void report(uint32_t* status, uint32_t site) {
   if (status) atomicCAS(status, 0u, site);
 }
 
+// ----------------------------------------------------------------------------- debug bounds checks
+// In a library built with -DNRT_BOUNDS_CHECK (python -m naivert_b200.ops.build --bounds) every index that comes out of
+// data - selected key ids, expert ids, token ids - is tested before it addresses memory.  A violation records
+// (site, index) in a word of the translation unit, first one wins, and the access is skipped or clamped, so the
+// context stays usable and the host reads what went wrong (nrt_bounds_<unit>() returns and clears the word).  In the
+// regular build the test is the constant `true` and the word does not exist.
+enum BoundsSite : uint32_t { kBoundsAttnKey = 1, kBoundsExpert = 2, kBoundsToken = 3, kBoundsMarkovPrev = 4 };
+#ifdef NRT_BOUNDS_CHECK
+static __device__ unsigned long long g_bounds_first = 0ull;
+__device__ __forceinline__ bool index_ok(long long i, long long n, uint32_t site) {
+  if (i >= 0 && i < n) return true;
+  atomicCAS(&g_bounds_first, 0ull, ((unsigned long long)(site | 0x80000000u) << 32) | (unsigned long long)(uint32_t)i);
+  return false;
+}
+#define NRT_INDEX_OK(i, n, site) nrt::index_ok((long long)(i), (long long)(n), (site))
+#define NRT_BOUNDS_EXPORT(unit)                                                     \
+  extern "C" unsigned long long nrt_bounds_##unit() {                               \
+    unsigned long long v = 0ull, z = 0ull;                                          \
+    if (cudaMemcpyFromSymbol(&v, nrt::g_bounds_first, sizeof(v)) != cudaSuccess) return ~0ull; \
+    cudaMemcpyToSymbol(nrt::g_bounds_first, &z, sizeof(z));                         \
+    return v;                                                                       \
+  }
+#else
+#define NRT_INDEX_OK(i, n, site) true
+#define NRT_BOUNDS_EXPORT(unit) \
+  extern "C" unsigned long long nrt_bounds_##unit() { return 0ull; }
+#endif
+
 // ----------------------------------------------------------------------------- misc
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

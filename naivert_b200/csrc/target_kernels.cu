@@ -69,6 +69,7 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const __nv_bfl
   const int r = blockIdx.x;
   if (r >= rows) return;
   int t = tokens[r];
+  (void)NRT_INDEX_OK(t, vocab, kBoundsToken);                 // recorded in the checking build; clamped in every build
   t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
   const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)t * hidden);
   uint4* dst = reinterpret_cast<uint4*>(x + (size_t)r * hidden);
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(128) step_prologue_kernel(const PrologueArgs a
   if (r < a.rows) {
     if (a.mode == 0 || r == 0) {
       int t = a.tokens[r];
+      (void)NRT_INDEX_OK(t, a.vocab, kBoundsToken);
       t = t < 0 ? 0 : (t >= a.vocab ? a.vocab - 1 : t);
       src = reinterpret_cast<const uint4*>(a.table + (size_t)t * a.hidden);
     } else {
@@ -910,6 +912,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterArgs a_in) {
 // ============================================================================= C ABI
 #define S(stream) reinterpret_cast<cudaStream_t>(stream)
 
+NRT_BOUNDS_EXPORT(target_kernels)
 extern "C" int nrt_embed_rows(const int* tokens, const void* table, void* x, int hidden, int rows, int vocab,
                               void* stream, int pdl) {
   return launch_pdl(embed_rows_kernel, dim3(rows > kMaxRows ? rows : kMaxRows), dim3(128), 0, S(stream), pdl != 0, tokens,

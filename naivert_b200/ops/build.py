@@ -30,6 +30,15 @@ _ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_ROOT, "csrc")
 LIB_DIR = os.path.join(_ROOT, "_lib")
 LIB_NAME = "libnaivert_b200.so"
+# The checking flavour: the same sources with -DNRT_BOUNDS_CHECK (every data-derived index is tested before use and the
+# first violation is recorded, csrc/ptx.cuh).  Built on request (``python -m naivert_b200.ops.build --bounds``) beside the
+# regular library and loaded instead of it when NAIVERT_BOUNDS_CHECK=1.
+BOUNDS_LIB_NAME = "libnaivert_b200_bounds.so"
+BOUNDS_UNITS = ("attn_decode", "moe_fused", "target_kernels", "draft")      # translation units that export nrt_bounds_<unit>
+
+
+def bounds_flavour() -> bool:
+    return os.environ.get("NAIVERT_BOUNDS_CHECK", "0") == "1"
 
 
 @dataclass(frozen=True)
@@ -84,17 +93,17 @@ def is_current() -> bool:
     return bool(m) and m.get("digest") == source_digest() and os.path.isfile(os.path.join(LIB_DIR, LIB_NAME))
 
 
-def compile_library(verbose: bool = False, ptxas_info: bool = False) -> str:
-    """Compile every .cu under csrc/ (objects in parallel) and link the shared library."""
+def compile_library(verbose: bool = False, ptxas_info: bool = False, bounds: bool = False) -> str:
+    """Compile every .cu under csrc/ (objects in parallel) and link the shared library (``bounds``: the checking flavour)."""
     nvcc = find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build the sm_100a kernels")
     os.makedirs(LIB_DIR, exist_ok=True)
-    obj_dir = os.path.join(LIB_DIR, "obj")
+    obj_dir = os.path.join(LIB_DIR, "obj_bounds" if bounds else "obj")
     os.makedirs(obj_dir, exist_ok=True)
     units = [s for s in source_inventory() if s.endswith(".cu")]
     rdc_units = [u for u in units if os.path.basename(u).startswith("rdc_")]
-    flags = ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else [])
+    flags = ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + (["-DNRT_BOUNDS_CHECK"] if bounds else [])
 
     def one(rel):
         obj = os.path.join(obj_dir, rel.replace("/", "_") + ".o")
@@ -110,7 +119,7 @@ def compile_library(verbose: bool = False, ptxas_info: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, len(units))) as ex:
         objs = list(ex.map(one, units))
-    out = os.path.join(LIB_DIR, LIB_NAME)
+    out = os.path.join(LIB_DIR, BOUNDS_LIB_NAME if bounds else LIB_NAME)
     link = [nvcc] + ARCH_FLAGS + ["-shared", "-o", out] + objs + ["-lcudart"]
     if rdc_units:
         link.insert(1, "-rdc=true")
@@ -119,7 +128,7 @@ def compile_library(verbose: bool = False, ptxas_info: bool = False) -> str:
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stderr[-4000:]}")
     man = KernelBuildManifest(source_digest(), source_inventory(), flags, nvcc)
-    with open(man.path(), "w") as f:
+    with open(os.path.join(LIB_DIR, "manifest_bounds.json") if bounds else man.path(), "w") as f:
         json.dump(asdict(man), f, indent=1)
     return out
 
@@ -132,6 +141,16 @@ def load_library(rebuild: Optional[bool] = None) -> ctypes.CDLL:
     global _LIB
     if _LIB is not None:
         return _LIB
+    if bounds_flavour():
+        path = os.path.join(LIB_DIR, BOUNDS_LIB_NAME)
+        man = os.path.join(LIB_DIR, "manifest_bounds.json")
+        cur = os.path.isfile(path) and os.path.isfile(man) and json.load(open(man)).get("digest") == source_digest()
+        if not cur:
+            if find_nvcc() is None:
+                raise RuntimeError(f"{path} is missing or stale and cannot be built here")
+            compile_library(bounds=True)
+        _LIB = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+        return _LIB
     path = os.path.join(LIB_DIR, LIB_NAME)
     stale = not is_current()
     if rebuild or (rebuild is None and stale and find_nvcc() is not None):
@@ -140,3 +159,22 @@ def load_library(rebuild: Optional[bool] = None) -> ctypes.CDLL:
         raise RuntimeError(f"{path} is missing and cannot be built here; the CUDA kernels have no fallback")
     _LIB = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
     return _LIB
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(description="Build the sm_100a kernel library in-tree.")
+    ap.add_argument("--bounds", action="store_true", help="build the index-checking flavour (libnaivert_b200_bounds.so) as well")
+    ap.add_argument("--only-bounds", action="store_true", help="build only the index-checking flavour")
+    ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / shared memory per kernel")
+    a = ap.parse_args(argv)
+    if not a.only_bounds:
+        print(compile_library(ptxas_info=a.ptxas_info))
+    if a.bounds or a.only_bounds:
+        print(compile_library(ptxas_info=a.ptxas_info, bounds=True))
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main())

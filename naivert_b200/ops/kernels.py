@@ -91,6 +91,25 @@ class MoeArgs(C.Structure):
 
 _lib = None
 
+BOUNDS_SITES = {1: "attention key id beyond the query position", 2: "expert id", 3: "token id", 4: "Markov previous-token id"}
+
+
+def bounds_violations() -> list:
+    """(translation unit, site description, offending index) of the first out-of-range index each translation unit of
+    the checking flavour recorded since the last call (the words are cleared).  The regular library reports none."""
+    from .build import BOUNDS_UNITS
+    L = lib()
+    out = []
+    for unit in BOUNDS_UNITS:
+        f = getattr(L, "nrt_bounds_" + unit)
+        f.restype = C.c_ulonglong
+        v = int(f())
+        if v == (1 << 64) - 1:
+            raise RuntimeError(f"the bounds word of {unit} could not be read")
+        if v:
+            out.append((unit, BOUNDS_SITES.get((v >> 32) & 0x7FFFFFFF, "unknown site"), int(C.c_int32(v & 0xFFFFFFFF).value)))
+    return out
+
 
 def lib():
     global _lib

@@ -91,3 +91,31 @@ def test_step_outputs_stay_inside_their_buffers():
     rt.fab.check()
     assert torch.isfinite(rt.logits[:8]).all()
     pool.verify()
+
+
+@pytest.mark.gpu
+def test_index_checking_build_records_the_first_bad_index_and_stays_clean_on_a_real_decode():
+    """The -DNRT_BOUNDS_CHECK flavour of the library (same sources) tests every data-derived index before use.  A decode
+    that crosses the sparse-attention boundary leaves the bounds words empty; a token id beyond the vocabulary - clamped
+    before the gather in every build, so nothing is read out of range - is recorded with its site and value, once."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from naivert_b200.ops import build as B
+    lib = os.path.join(B.LIB_DIR, B.BOUNDS_LIB_NAME)
+    man = os.path.join(B.LIB_DIR, "manifest_bounds.json")
+    if not (os.path.isfile(lib) and os.path.isfile(man) and json.load(open(man)).get("digest") == B.source_digest()):
+        pytest.skip("the checking flavour is not built (python -m naivert_b200.ops.build --bounds)")
+    env = dict(os.environ, NAIVERT_BOUNDS_CHECK="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "tests", "bounds_worker.py")], env=env, cwd=root,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("BOUNDS ")][-1]
+    out = json.loads(line[len("BOUNDS "):])
+    assert out["library"] == B.BOUNDS_LIB_NAME and out["tokens"] == 48
+    assert out["clean_run"] == []
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    assert out["after_bad_token"] == [["target_kernels", "token id", small_w8a8_spec(4).vocab + 5]]
+    assert out["cleared"] == [] and out["row_is_last_table_row"]
