@@ -1,9 +1,12 @@
 """Child process of the index-checking test: loads the checking flavour of the kernel library (NAIVERT_BOUNDS_CHECK=1 is
 set by the parent), decodes with a small model and prints what the bounds words recorded."""
 import json
+import os
 import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def main() -> int:
@@ -21,6 +24,7 @@ def main() -> int:
     eng = Engine.build(spec, capacity=1024, device=dev, weights=shard_weights(spec, w, 0, 1),
                        draft_weights=shard_draft_weights(spec, dw, 0, 1))
     out = {"library": K.lib()._name.rsplit("/", 1)[-1]}
+    eng.round.stop_ids.fill_(-1)                                            # no early stop: all 48 tokens are decoded
     try:
         g = torch.Generator().manual_seed(0)
         prompt = torch.randint(0, spec.vocab, (300,), generator=g)          # beyond the indexer's top-k: selected keys are used
