@@ -11,6 +11,7 @@ ARGS=(--host "${NAIVERT_HOST:-0.0.0.0}" --port "${NAIVERT_PORT:-8080}" --model "
 [[ -n "${NAIVERT_SERVED_MODEL_NAME:-}" ]] && ARGS+=(--served-model-name "$NAIVERT_SERVED_MODEL_NAME")
 [[ -n "${NAIVERT_CAPACITY:-}" ]] && ARGS+=(--capacity "$NAIVERT_CAPACITY")
 [[ -n "${NAIVERT_MAX_DECODE_TOKENS:-}" ]] && ARGS+=(--max-decode-tokens "$NAIVERT_MAX_DECODE_TOKENS")
+[[ -n "${NAIVERT_OUTPUT_CAPACITY:-}" ]] && ARGS+=(--output-capacity "$NAIVERT_OUTPUT_CAPACITY")
 [[ -n "${NAIVERT_STORE_GB:-}" ]] && ARGS+=(--store-gb "$NAIVERT_STORE_GB")
 [[ -n "${NAIVERT_QUEUE_DEPTH:-}" ]] && ARGS+=(--queue-depth "$NAIVERT_QUEUE_DEPTH")
 [[ -n "${NAIVERT_SEED:-}" ]] && ARGS+=(--seed "$NAIVERT_SEED")

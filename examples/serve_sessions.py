@@ -26,12 +26,18 @@ def parse_args(argv=None):
     ap.add_argument("--cors-credentials", action="store_true")
     ap.add_argument("--model", default="naive-n0.5", help="registry name of the architecture")
     ap.add_argument("--target", default=os.environ.get("NAIVERT_TARGET_CHECKPOINT"), help="target checkpoint directory or short name")
-    ap.add_argument("--draft", default=os.environ.get("NAIVERT_DRAFT_CHECKPOINT"), help="draft checkpoint directory or short name")
+    ap.add_argument("--draft", "--checkpoint", dest="draft", default=os.environ.get("NAIVERT_DRAFT_CHECKPOINT"),
+                    help="draft checkpoint directory or short name")
+    ap.add_argument("--list-weights", action="store_true",
+                    help="print the checkpoints found under NAIVERT_MODEL_ROOTS / NAIVERT_DRAFT_ROOTS and exit")
     ap.add_argument("--random-init", action="store_true", help="draw weights on device instead of loading checkpoints")
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to its first N layers")
     ap.add_argument("--served-model-name", default=None)
     ap.add_argument("--max-decode-tokens", type=int, default=524288)
     ap.add_argument("--capacity", type=int, default=1048576, help="KV positions per sequence")
+    ap.add_argument("--output-capacity", type=int, default=None,
+                    help="most tokens one request may generate; --max-decode-tokens is capped to it (the host ring "
+                         "holds round records and is drained while the request runs, so it does not bound the output)")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--temperature", type=float, default=1.0)
     ap.add_argument("--top-p", type=float, default=0.95)
@@ -47,6 +53,10 @@ def parse_args(argv=None):
     ap.add_argument("--prefill-experts", choices=("tp", "ep"), default="tp",
                     help="ep: a second, expert-parallel copy of the experts (random-init only; doubles expert memory)")
     ap.add_argument("--prefill-warm-chunks", action="store_true", help="run every native chunk size once before serving")
+    ap.add_argument("--draft-ingest", choices=("batched", "loop"), default="batched",
+                    help="accepted for command-line compatibility: the draft's K/V of a prompt is written by whichever path "
+                         "ingests the prompt (per chunk with --prefill native, per eight-row step with verify8); "
+                         "'loop' with --prefill native only logs that the chunk path stays batched")
     ap.add_argument("--dump-tokens", default=None, help="append the output token ids of every request to this JSONL file")
     ap.add_argument("--thinking", action="store_true", help="enable thinking by default in the chat template")
     ap.add_argument("--log-level", default="info")
@@ -55,7 +65,15 @@ def parse_args(argv=None):
 
 def main(argv=None) -> int:
     a = parse_args(argv)
+    if a.list_weights:
+        from naivert_b200.models.checkpoint import list_weights
+        print(list_weights())
+        return 0
+    if a.output_capacity is not None:
+        a.max_decode_tokens = min(a.max_decode_tokens, max(1, a.output_capacity))
     logging.basicConfig(level=a.log_level.upper(), format="%(asctime)s %(name)s %(levelname)s %(message)s")
+    if a.draft_ingest == "loop" and a.prefill == "native":
+        logging.getLogger("naivert_b200.serve").warning("--draft-ingest loop: the native chunk path writes the draft K/V per chunk")
     import torch
     import torch.distributed as dist
 

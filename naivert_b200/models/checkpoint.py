@@ -154,6 +154,31 @@ def resolve_checkpoint(name_or_path: str, roots_env: str = "NAIVERT_MODEL_ROOTS"
     raise CheckpointError(f"checkpoint {name_or_path!r} not found (searched {cands})")
 
 
+def list_weights(model_roots_env: str = "NAIVERT_MODEL_ROOTS", draft_roots_env: str = "NAIVERT_DRAFT_ROOTS") -> str:
+    """The checkpoints found under the root directories, as the short names ``resolve_checkpoint`` accepts: targets
+    are directories (or their newest ``step_*`` child) with ``config.json`` and a shard index, drafts directories with
+    ``config.json`` and a single ``model.safetensors`` (``--list-weights`` of examples/serve_sessions.py:57-72)."""
+    def roots(env):
+        return [r for r in os.environ.get(env, "").split(":") if r and os.path.isdir(r)]
+
+    lines = ["targets (--target):"]
+    for base in roots(model_roots_env):
+        for name in sorted(os.listdir(base)):
+            try:
+                d = resolve_checkpoint(os.path.join(base, name))
+            except CheckpointError:
+                continue
+            if os.path.isfile(os.path.join(d, "config.json")) and os.path.isfile(os.path.join(d, INDEX_NAME)):
+                lines.append(f"  {name:48s} {d}")
+    lines.append("drafts (--draft):")
+    for base in roots(draft_roots_env):
+        for name in sorted(os.listdir(base)):
+            d = os.path.join(base, name)
+            if os.path.isfile(os.path.join(d, "config.json")) and os.path.isfile(os.path.join(d, "model.safetensors")):
+                lines.append(f"  {name:48s} {d}")
+    return "\n".join(lines)
+
+
 # --------------------------------------------------------------------------- config.json
 def target_config(spec: ModelSpec) -> dict:
     dsa, swa = spec.attention[FULL_DSA], spec.attention[SLIDING_WINDOW]

@@ -235,3 +235,35 @@ def test_rank_tensor_abi_describes_the_sharded_weights():
         RankTensorAbi("x", (TensorSlot("a", "cache", 1, (1,), "bf16", 16, "row_major"),))
     with pytest.raises(ValueError):
         rank_tensor_abi(big, 8, 8)
+
+
+def test_list_weights_and_server_flags(tmp_path, monkeypatch, capsys):
+    """``--list-weights`` prints the short names the resolver accepts; ``--checkpoint`` is the draft's second name and
+    ``--output-capacity`` caps the per-request output."""
+    import importlib.util
+    import os
+    from naivert_b200.models import checkpoint as ck
+    models, drafts = tmp_path / "models", tmp_path / "drafts"
+    (models / "flash" / "step_7").mkdir(parents=True)
+    (models / "flash" / "step_12").mkdir()
+    for d in (models / "flash" / "step_7", models / "flash" / "step_12"):
+        (d / "config.json").write_text("{}")
+        (d / ck.INDEX_NAME).write_text("{}")
+    (models / "notes").mkdir()                                   # not a checkpoint
+    (drafts / "markov-a").mkdir(parents=True)
+    (drafts / "markov-a" / "config.json").write_text("{}")
+    (drafts / "markov-a" / "model.safetensors").write_bytes(b"")
+    monkeypatch.setenv("NAIVERT_MODEL_ROOTS", str(models))
+    monkeypatch.setenv("NAIVERT_DRAFT_ROOTS", str(drafts) + ":" + str(tmp_path / "absent"))
+    text = ck.list_weights()
+    assert "flash" in text and text.count("step_12") == 1 and "step_7" not in text and "notes" not in text
+    assert "markov-a" in text.split("drafts (--draft):")[1]
+    assert ck.resolve_checkpoint("flash").endswith("step_12")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sp = importlib.util.spec_from_file_location("serve_sessions_cli", os.path.join(root, "examples", "serve_sessions.py"))
+    cli = importlib.util.module_from_spec(sp)
+    sp.loader.exec_module(cli)
+    a = cli.parse_args(["--checkpoint", "markov-a", "--output-capacity", "4096", "--draft-ingest", "loop"])
+    assert a.draft == "markov-a" and a.output_capacity == 4096 and a.draft_ingest == "loop"
+    assert cli.main(["--list-weights"]) == 0
+    assert "targets (--target):" in capsys.readouterr().out
