@@ -81,6 +81,18 @@ def select_resume(entries: Dict[str, ParkedPrefix], tokens: Sequence[int], sessi
     return best
 
 
+def best_prefix_match(entries: Dict[str, "ParkedPrefix"], tokens: Sequence[int]) -> Optional[tuple]:
+    """(key, common prefix length) of the parked entry that shares the longest prefix with ``tokens``, or None.  Only a
+    diagnostic: when nothing resumes, the entry that came closest says where the client's re-rendered history first
+    departs from what the model produced (naivert/backends/naive_n0p5_session_engine.py:88-99)."""
+    best = None
+    for key, e in entries.items():
+        c = common_prefix(e.tokens[:e.position], tokens)
+        if best is None or c > best[1]:
+            best = (key, c)
+    return best
+
+
 def park_name(entries: Dict[str, ParkedPrefix], session_id: Optional[str], tokens: Sequence[int]) -> str:
     """Name under which a finished request is parked: the session key when the stored sequence is a
     prefix of the new one (the conversation continued), else a ``key#N`` sibling (it branched)."""

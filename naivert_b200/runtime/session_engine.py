@@ -12,6 +12,7 @@ resume selection, :123-212 prefill cost model and path policy, :263-340 step loo
 """
 from __future__ import annotations
 
+import logging
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
@@ -20,8 +21,10 @@ import torch
 
 from ..models.spec import FULL_DSA, SamplingParams
 from .engine import Engine
-from .prefix_store import PrefixStore, common_prefix, park_name, select_resume
+from .prefix_store import PrefixStore, best_prefix_match, common_prefix, park_name, select_resume
 from .round import RuntimeContractError
+
+log = logging.getLogger("naivert_b200.session")
 
 # Measured on B200 (ms); inputs of the resume / prefill-path policy.
 REPLAY_MS_PER_TOKEN = 1.2            # 8-row verify replay per prompt token (tp8, 48 layers: 9.6 ms per 8 rows)
@@ -250,6 +253,12 @@ class SessionEngine:
             gb = self.store.entries[choice.key].nbytes() / (1 << 30)
             if prefill_estimate(n - 1, "replay") - prefill_estimate(new_after, "replay") > gb * RESTORE_MS_PER_GB:
                 start = self.store.restore(choice)
+        near = None
+        if start == 0 and self.store.entries:
+            near = best_prefix_match(self.store.entries, tokens)
+            if near is not None and near[1] >= 16:
+                log.info("no parked prefix resumes this prompt; closest is %s: %d of its %d parked tokens match, the prompt "
+                         "departs at token %d", near[0], near[1], self.store.entries[near[0]].position, near[1])
         t1 = time.perf_counter()
         path = prefill_path(n - 1 - start, self.resume_policy, native_ready=self.engine.prefill is not None)
         prompt = torch.tensor(tokens, dtype=torch.int32)
@@ -263,7 +272,8 @@ class SessionEngine:
         # is parked (a checkpoint filed under the bare session key could end up beside another branch's tokens)
         ring_ck = self.store.make_checkpoint(n - 1) if n - 1 >= 16 else None
         info = {"path": path, "restore_ms": round((t1 - t0) * 1e3, 3), "init_ms": round((t2 - t1) * 1e3, 3),
-                "resumed_from": choice.key if start else None, "estimate_ms": round(prefill_estimate(n - 1 - start, path), 2),
+                "resumed_from": choice.key if start else None,
+                "closest_parked": {"key": near[0], "common_tokens": near[1]} if near is not None else None, "estimate_ms": round(prefill_estimate(n - 1 - start, path), 2),
                 "phases": {"restore_ms": round((t1 - t0) * 1e3, 3), "executor_ms": self.engine.last_prefill.get("executor_ms", 0.0),
                            "native_rows": self.engine.last_prefill.get("native_rows", 0), "replay_rows": n - 1 - replay_from,
                            "init_ms": round((t2 - t1) * 1e3, 3)}}

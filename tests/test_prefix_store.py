@@ -144,3 +144,14 @@ def test_align_prompt_keeps_sampled_ids_of_a_parked_history():
     assert se.align_prompt(canonical, "S") == canonical
     se.tokenizer = None
     assert se.align_prompt(canonical, "S", text=text) == canonical
+
+
+def test_best_prefix_match_is_the_closest_parked_entry():
+    from naivert_b200.runtime.prefix_store import best_prefix_match
+    entries = {"a": ParkedPrefix("a", list(range(100)), 99, [], []),
+               "b": ParkedPrefix("b", list(range(40)) + [7] * 60, 99, [], []),
+               "c": ParkedPrefix("c", list(range(100)), 30, [], [])}          # only 30 positions are parked
+    assert best_prefix_match(entries, list(range(60)) + [1, 2]) == ("a", 60)
+    assert best_prefix_match(entries, list(range(40)) + [7, 7, 9]) == ("b", 42)
+    assert best_prefix_match({"c": entries["c"]}, list(range(100))) == ("c", 30)
+    assert best_prefix_match({}, [1, 2]) is None and best_prefix_match(entries, [5])[1] == 0
