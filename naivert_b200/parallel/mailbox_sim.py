@@ -5,7 +5,9 @@ The model follows the device code word for word at the protocol level - 64-bit w
 slab = call % 4, tag = epoch * 1024 + call + 1, bounded waits that record the first failing site in
 a status word and make every later wait return at once - so the failure paths that must never be
 provoked on a GPU of the shared pool (a rank that never publishes, a rank that leaves between
-steps) are exercised here.
+steps) are exercised here.  The small-message exchange of the sampler / Markov head (``SimExchange``: all-to-all and
+reduce-scatter forms, tag = epoch * 64 + call + 1) is modelled the same way; the tests run a whole round's call plan
+under random rank skew and show what the slab rule (consecutive calls differ modulo 4) protects against.
 
 Parity: naivert/common/tp8_mailbox.cuh:122-195 (bounded waits + watchdog word); failures are injected on
 the host only (a simulated rank withholds one publish).
@@ -115,4 +117,98 @@ def run_ranks(tp: int, fn: Callable[[int], object]) -> List[object]:
         t.join()
     if errs:
         raise errs[0]
+    return out
+
+
+# --------------------------------------------------------------------------- small exchange (csrc/fabric.cuh)
+SITE_RENDEZVOUS = 0x700
+XCHG_SLABS = 4
+
+
+class SimExchange:
+    """The small-message boxes of ``tp`` simulated ranks: box[dst][slab][src][value index] -> (tag, value).  A value
+    is one 64-bit integer here (the device splits it into two tagged 32-bit words; both carry the same tag)."""
+
+    def __init__(self, tp: int, max_values: int = 4096):
+        self.tp, self.max_values = tp, max_values
+        self.tag = np.zeros((tp, XCHG_SLABS, tp, max_values), dtype=np.uint32)
+        self.val = np.zeros((tp, XCHG_SLABS, tp, max_values), dtype=np.uint64)
+        self.status = np.zeros(tp, dtype=np.uint32)
+        self.epoch = np.ones(tp, dtype=np.uint32)
+        self.lock = threading.Lock()
+
+    def report(self, rank: int, site: int) -> None:
+        with self.lock:
+            if self.status[rank] == 0:
+                self.status[rank] = site
+
+
+def _collect(x: SimExchange, rank: int, idx: np.ndarray, tag, slab: int, call: int, timeout_s: float):
+    """Poll this rank's box until every peer's words for the value indices ``idx`` carry ``tag``; -> [tp, len(idx)] or None."""
+    got = np.zeros((x.tp, len(idx)), dtype=np.uint64)
+    missing = [s for s in range(x.tp) if s != rank] if len(idx) else []
+    deadline = time.monotonic() + timeout_s
+    while missing:
+        if x.status[rank] != 0:
+            return None
+        for s in list(missing):
+            if np.all(x.tag[rank, slab, s, idx] == tag):
+                got[s] = x.val[rank, slab, s, idx]
+                missing.remove(s)
+        if missing and time.monotonic() > deadline:
+            x.report(rank, SITE_RENDEZVOUS | call)
+            return None
+        if missing:
+            time.sleep(1e-4)
+    return got
+
+
+def xchg_reduce(x: SimExchange, rank: int, vals: np.ndarray, call: int, op: str = "sum", timeout_s: float = 1.0,
+                delay_s: float = 0.0) -> Optional[np.ndarray]:
+    """All-to-all form: every rank pushes all values to every peer and reduces locally."""
+    if x.tp <= 1:
+        return vals.copy()
+    tag, slab = np.uint32(int(x.epoch[rank]) * 64 + call + 1), call % XCHG_SLABS
+    idx = np.arange(len(vals))
+    if delay_s:
+        time.sleep(delay_s)
+    for d in range(1, x.tp):
+        peer = (rank + d) % x.tp
+        x.val[peer, slab, rank, idx] = vals
+        x.tag[peer, slab, rank, idx] = tag
+    got = _collect(x, rank, idx, tag, slab, call, timeout_s)
+    if got is None:
+        return None
+    got[rank] = vals
+    return got.sum(0, dtype=np.uint64) if op == "sum" else got.max(0)
+
+
+def xchg_reduce_scatter(x: SimExchange, rank: int, vals: np.ndarray, groups: int, gsize: int, live: int, call: int,
+                        timeout_s: float = 1.0, delay_s: float = 0.0) -> Optional[np.ndarray]:
+    """Reduce-scatter form: group g (values g * gsize ..) is owned by rank g % tp; values of live groups go to their
+    owners only, an owner's groups come back summed, the others keep the local values."""
+    if x.tp <= 1:
+        return vals.copy()
+    tag, slab = np.uint32(int(x.epoch[rank]) * 64 + call + 1), call % XCHG_SLABS
+    if delay_s:
+        time.sleep(delay_s)
+    out = vals.copy()
+    own_idx = []
+    for g in range(groups):
+        if not (live >> g) & 1:
+            continue
+        idx = np.arange(g * gsize, (g + 1) * gsize)
+        owner = g % x.tp
+        if owner == rank:
+            own_idx.append(idx)
+        else:
+            x.val[owner, slab, rank, idx] = vals[idx]
+            x.tag[owner, slab, rank, idx] = tag
+    if own_idx:
+        idx = np.concatenate(own_idx)
+        got = _collect(x, rank, idx, tag, slab, call, timeout_s)
+        if got is None:
+            return None
+        got[rank] = vals[idx]
+        out[idx] = got.sum(0, dtype=np.uint64)
     return out

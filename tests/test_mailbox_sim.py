@@ -60,3 +60,78 @@ def test_stale_generation_is_never_mistaken():
     fab.epoch[:] += 1                                       # same call index, next epoch: old words must not match
     outs = run_ranks(tp, lambda r: all_reduce(fab, r, parts[r], resid, 0, timeout_s=0.2, publish=(r == 0)))
     assert outs[0] is None and outs[1] is not None
+
+
+def test_small_exchange_round_follows_the_call_plan_under_skew():
+    """One round's small exchanges (Markov steps, sampler maxima / totals, four nucleus passes as reduce-scatter to the
+    owning rank + digit broadcast, accept, draw, tail) run by eight skewed ranks in the order and with the call indices
+    of ``runtime.modes.exchange_call_plan``: every rank ends with the same, correct values and nothing times out."""
+    import time
+    from naivert_b200.parallel.mailbox_sim import SimExchange, xchg_reduce, xchg_reduce_scatter
+    from naivert_b200.runtime.modes import exchange_call_plan
+    tp, groups, gsize = 8, 15, 32
+    x = SimExchange(tp)
+    plan = exchange_call_plan()
+    rng = np.random.default_rng(0)
+    hist = rng.integers(0, 1 << 40, size=(4, tp, groups * gsize), dtype=np.uint64)
+    small = rng.integers(0, 1 << 30, size=(len(plan), tp, 16), dtype=np.uint64)
+    want_hist = hist.sum(1, dtype=np.uint64)
+
+    def rank_body(r):
+        lrng = np.random.default_rng(100 + r)
+        seen = []
+        for i, (name, call) in enumerate(plan):
+            if lrng.random() < 0.3:
+                time.sleep(float(lrng.random()) * 2e-3)                   # skew between ranks, different every call
+            if "bins_to_owner" in name:
+                p = int(name[len("sampler.nucleus")])
+                out = xchg_reduce_scatter(x, r, hist[p, r], groups, gsize, (1 << groups) - 1, call)
+                assert out is not None, name
+                for g in range(groups):
+                    sl = slice(g * gsize, (g + 1) * gsize)
+                    want = want_hist[p, sl] if g % tp == r else hist[p, r, sl]
+                    assert np.array_equal(out[sl], want), (name, g)
+            else:
+                out = xchg_reduce(x, r, small[i, r], call, op="max" if name.startswith("markov") else "sum")
+                assert out is not None, name
+                seen.append(out)
+        return seen
+
+    outs = run_ranks(tp, rank_body)
+    assert not x.status.any()
+    for r in range(1, tp):
+        for a, b in zip(outs[0], outs[r]):
+            assert np.array_equal(a, b)
+
+
+def test_consecutive_calls_in_one_slab_can_lose_words():
+    """Why the plan keeps consecutive calls in different slabs: a fast rank that has finished call n (a reduce-scatter it
+    owns nothing of) pushes call n + 1 over the words a slow owner has not read yet."""
+    import time
+    from naivert_b200.parallel.mailbox_sim import SITE_RENDEZVOUS, SimExchange, xchg_reduce, xchg_reduce_scatter
+    tp, gsize = 2, 8
+    x = SimExchange(tp)
+    vals = [np.arange(gsize, dtype=np.uint64) + 10 * r for r in range(tp)]
+
+    def body(r):
+        if r == 0:                                   # owner of group 0, late
+            time.sleep(0.2)
+            return xchg_reduce_scatter(x, 0, vals[0], 1, gsize, 1, call=2, timeout_s=0.3)
+        xchg_reduce_scatter(x, 1, vals[1], 1, gsize, 1, call=2)          # pushes to rank 0, owns nothing, returns
+        return xchg_reduce(x, 1, vals[1], call=6, timeout_s=0.3)         # same slab (6 % 4 == 2), same value indices
+    outs = run_ranks(tp, body)
+    assert outs[0] is None and x.status[0] == (SITE_RENDEZVOUS | 2)      # the owner never sees call 2's words
+    # with the next call in another slab nothing is lost
+    x = SimExchange(tp)
+
+    def body_ok(r):
+        if r == 0:
+            time.sleep(0.2)
+            a = xchg_reduce_scatter(x, 0, vals[0], 1, gsize, 1, call=2, timeout_s=1.0)
+            b = xchg_reduce(x, 0, vals[0], call=3, timeout_s=1.0)
+            return a, b
+        a = xchg_reduce_scatter(x, 1, vals[1], 1, gsize, 1, call=2)
+        b = xchg_reduce(x, 1, vals[1], call=3, timeout_s=1.0)
+        return a, b
+    outs = run_ranks(tp, body_ok)
+    assert np.array_equal(outs[0][0], vals[0] + vals[1]) and np.array_equal(outs[0][1], outs[1][1]) and not x.status.any()
