@@ -3,15 +3,43 @@ import { RequestQueue } from "./queue.js";
 import { curvePoints, thin } from "./curve.js";
 import { renderMarkdown } from "./markdown.js";
 import { normalizeBase, buildRequest, assistantTurn, describeHealth, statsLine } from "./core.js";
+import { authHeaders, clearAuth, loadAuth, messagesOptions, parseQuickSetup, saveAuth } from "./endpoint.js";
+import { checkConnection } from "./connection.js";
 
 const $ = (id) => document.getElementById(id);
 let controller = null;
 const history = [];
 const base = () => normalizeBase($("base").value);
+const auth = () => ({ kind: $("authkind").value, user: $("authuser").value, secret: $("authsecret").value, cookies: $("authcookies").checked });
+function showAuth(a) {
+  $("authkind").value = a.kind || "none"; $("authuser").value = a.user || ""; $("authsecret").value = a.secret || ""; $("authcookies").checked = Boolean(a.cookies);
+}
+showAuth(loadAuth($("base").value));
+$("base").onchange = () => showAuth(loadAuth($("base").value));
+$("quick").onkeydown = (ev) => {
+  if (ev.key !== "Enter") return;
+  try {
+    const q = parseQuickSetup($("quick").value);
+    $("base").value = q.endpoint; showAuth(q.auth);
+    if (q.model) $("model").value = q.model;
+    $("quick").value = ""; $("conn").textContent = "applied; press Check connection";
+  } catch (e) { $("conn").textContent = e.message; }
+};
+$("check").onclick = async () => {
+  $("conn").textContent = "checking…";
+  try {
+    const r = await checkConnection({ endpoint: $("base").value, model: $("model").value, auth: auth(), sessionId: $("session").value });
+    $("conn").textContent = r.message;
+    if (r.ok) saveAuth($("base").value, auth());
+  } catch (e) { $("conn").textContent = e.message; }
+};
+$("forget").onclick = () => { clearAuth(); showAuth({ kind: "none" }); $("conn").textContent = "credentials forgotten"; };
 
 async function health() {
   try {
-    const r = await fetch(base() + "/health");
+    let headers = {};
+    try { headers = authHeaders(auth()); } catch (e) { headers = {}; }
+    const r = await fetch(base() + "/health", { headers });
     $("health").textContent = "health: " + describeHealth(await r.json());
   } catch (e) { $("health").textContent = "health: " + describeHealth(null); }
 }
@@ -42,7 +70,8 @@ async function run(prompt) {
   const blocks = [];
   let current = null, firstContent = null;
   try {
-    const r = await fetch(base() + "/v1/messages", { method: "POST", signal: controller.signal, headers, body: JSON.stringify(body) });
+    const opts = messagesOptions(auth(), $("session").value, headers);
+    const r = await fetch(base() + "/v1/messages", Object.assign(opts, { signal: controller.signal, body: JSON.stringify(body) }));
     if (!r.ok) { out.appendChild(document.createTextNode(`[${r.status}] ${await r.text()}\n`)); history.pop(); return; }
     const reader = r.body.getReader(), dec = new TextDecoder();
     for (;;) {
