@@ -97,7 +97,7 @@ class Fabric:
     def check(self) -> None:
         code = int(self.status[0])
         if code:
-            raise RuntimeError(f"device wait gave up at site 0x{code:x} (rank {self.rank})")
+            raise RuntimeError(f"device wait gave up at site 0x{code:x} (rank {self.rank}): {explain_status(code)}")
 
     def close(self) -> None:
         L = K.lib()
@@ -106,3 +106,57 @@ class Fabric:
         for p in self._local:
             L.nrt_ipc_free(C.c_void_p(p))
         self._opened, self._local = [], []
+
+
+
+# status word = site class (bits 8..11, csrc/ptx.cuh) | detail (low byte)
+_SITE_CLASSES = {
+    0x100: "a consumer waited for a TMA stage that never filled (detail: stage; 0x10+: MoE down slots, 0x40: operand build, 0x80: sweep queries)",
+    0x200: "a producer waited for a pipeline stage that was never released (detail: stage; 0x10+: MoE down slots)",
+    0x300: "an epilogue waited for an accumulator commit (detail: TMEM buffer; 0x10+: MoE down)",
+    0x400: "the MMA issuer waited for an accumulator buffer (detail: TMEM buffer; 0x10+: MoE down)",
+    0x500: "a peer's tagged mailbox word did not arrive",
+    0x600: "a cluster partner did not arrive",
+    0x700: "a small-message exchange did not complete",
+    0x800: "an in-grid hand-over did not complete",
+}
+
+
+def explain_status(code: int) -> str:
+    """What a non-zero status word says: which bounded device wait gave up first (site codes of csrc/ptx.cuh and the
+    details the kernels add to them)."""
+    code = int(code)
+    if code == 0:
+        return "ok"
+    cls, detail = code & 0xF00, code & 0xFF
+    text = _SITE_CLASSES.get(cls, "unknown site class")
+    if cls == 0x500:
+        if detail & 0x80:
+            text += f": expert-parallel return slot {detail & 0x7F} (a rank did not push its expert output)"
+        elif detail & 0x60 == 0x60:
+            text += f": all-gather flag of source rank {detail & 0x1F}"
+        elif detail & 0x40:
+            text += f": all-gather rows of source rank {detail & 0x1F}"
+        else:
+            text += f": all-reduce, first missing word slot {detail - 1} of the poll mask" if detail else ""
+    elif cls == 0x700:
+        names = {0: "sampler maxima", 1: "sampler totals", 10: "acceptance", 11: "rank totals of the draw", 12: "drawn token",
+                 13: "tail pause consensus", 60: "greedy arg-max"}
+        if 2 <= detail <= 9:
+            what = f"nucleus pass {(detail - 2) // 2}: " + ("bins to the owning rank" if detail % 2 == 0 else "threshold digit")
+        elif 16 <= detail <= 23:
+            what = f"Markov step {detail - 16}"
+        elif 32 <= detail <= 47:
+            what = "expert-parallel token counts"
+        else:
+            what = names.get(detail, f"call {detail}")
+        text += f": {what}"
+    elif cls == 0x800:
+        if detail & 0x40:
+            text += f": sampler phase {detail & 0x3F}"
+        elif detail & 0x20:
+            text += f": Markov step {detail & 0x1F}"
+        else:
+            text += {1: ": fused MoE arrival (scores of all CTAs)", 2: ": fused MoE gate/up tile flag",
+                     3: ": fused MoE expert-range partial"}.get(detail, f": detail {detail}")
+    return text

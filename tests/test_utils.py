@@ -317,3 +317,20 @@ def test_decode_modes_and_call_plans():
     # capacity rule
     assert M.request_fits(8192, 1024, 8192 + 1024 + 32) and not M.request_fits(8192, 1024, 8192 + 1024 + 31)
     assert not M.request_fits(0, 10, 1000)
+
+
+def test_status_words_are_explained():
+    from naivert_b200.parallel.fabric import explain_status
+    assert explain_status(0) == "ok"
+    assert "nucleus pass 2: bins to the owning rank" in explain_status(0x700 | 6)
+    assert "threshold digit" in explain_status(0x700 | 3) and "Markov step 3" in explain_status(0x700 | 19)
+    assert "tail pause consensus" in explain_status(0x700 | 13) and "arg-max" in explain_status(0x700 | 60)
+    assert "sampler phase 2" in explain_status(0x800 | 0x42) and "Markov step 3" in explain_status(0x800 | 0x23)
+    assert "fused MoE arrival" in explain_status(0x801) and "mailbox" in explain_status(0x501)
+    assert "return slot 3" in explain_status(0x583) and "all-gather flag of source rank 2" in explain_status(0x562)
+    assert "unknown" in explain_status(0x999)
+    # the classes are the enumerators of the device header
+    src = open(os.path.join(ROOT, "naivert_b200", "csrc", "ptx.cuh")).read()
+    for name, value in (("kSiteTmaFull", 0x100), ("kSiteStageEmpty", 0x200), ("kSiteAccFull", 0x300), ("kSiteAccEmpty", 0x400),
+                        ("kSiteMailbox", 0x500), ("kSiteCluster", 0x600), ("kSiteRendezvous", 0x700), ("kSiteGrid", 0x800)):
+        assert f"{name} = 0x{value:x}" in src
