@@ -50,6 +50,13 @@ def compile_all() -> dict:
         res["bindings"] = "ok"
     except OSError as e:
         res["bindings"] = f"not loadable here ({e})"
+        return res
+    # argument structs against the sources, and every kernel variant the runtimes ask for against the built library
+    from naivert_b200.ops import abi, variants
+    res["abi_mismatches"] = abi.check_all()
+    res["variant_problems"] = variants.check_library(kernels.lib())
+    res["variants"] = sorted(variants.variants())
+    res["ok"] = not res["abi_mismatches"] and not res["variant_problems"]
     return res
 
 
@@ -86,7 +93,9 @@ def main() -> int:
         print(json.dumps(r, indent=1))
         rc |= 0 if r["ok"] else 1
     if a.compile:
-        print(json.dumps(compile_all(), indent=1))
+        r = compile_all()
+        print(json.dumps(r, indent=1))
+        rc |= 0 if r.get("ok", True) else 1
     if a.serve_smoke:
         r = serve_smoke()
         print(json.dumps(r, indent=1))
