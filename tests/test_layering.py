@@ -60,3 +60,43 @@ def test_no_committed_module_reaches_into_working_files():
                 if f.endswith(".py") and f != "test_layering.py":
                     text = open(os.path.join(dp, f)).read()
                     assert "_work/" not in text and "_work." not in text and '"_work"' not in text, os.path.join(dp, f)
+
+
+FORBIDDEN_TOP_LEVEL = {"triton", "tilelang", "tvm", "jax", "flash_attn", "flashinfer", "vllm", "cutlass", "deep_gemm", "sgl_kernel"}
+
+
+def test_no_compatibility_layer_or_kernel_library_is_imported():
+    """The compute path is this repository's own sm_100a kernels: no module of the package, the benchmark or the
+    examples imports a kernel DSL, a multi-backend layer or a third-party kernel library (the reference guards its
+    tree the same way with an import hook: tests/support/external_dependency_guard.py)."""
+    top = os.path.dirname(ROOT)
+    files = [os.path.join(top, "bench.py"), os.path.join(top, "__graft_entry__.py")]
+    for base in (ROOT, os.path.join(top, "examples"), os.path.join(top, "devops")):
+        for dp, _, fs in os.walk(base):
+            files += [os.path.join(dp, f) for f in fs if f.endswith(".py")]
+    bad = []
+    for path in files:
+        tree = ast.parse(open(path).read())
+        for node in ast.walk(tree):
+            names = []
+            if isinstance(node, ast.Import):
+                names = [a.name for a in node.names]
+            elif isinstance(node, ast.ImportFrom) and node.level == 0 and node.module:
+                names = [node.module]
+            elif isinstance(node, ast.Call) and getattr(node.func, "id", getattr(node.func, "attr", "")) in ("import_module", "__import__"):
+                names = [a.value for a in node.args[:1] if isinstance(a, ast.Constant) and isinstance(a.value, str)]
+            for n in names:
+                if n.split(".")[0] in FORBIDDEN_TOP_LEVEL:
+                    bad.append(f"{os.path.relpath(path, top)} imports {n}")
+    assert not bad, bad
+    assert len(files) > 40
+
+
+def test_no_torch_compile_on_any_path():
+    top = os.path.dirname(ROOT)
+    for dp, _, fs in os.walk(ROOT):
+        for f in fs:
+            if f.endswith(".py"):
+                src = open(os.path.join(dp, f)).read()
+                assert "torch.compile(" not in src and "@torch.compile" not in src, os.path.join(dp, f)
+    assert "torch.compile(" not in open(os.path.join(top, "bench.py")).read()
