@@ -334,3 +334,32 @@ def test_status_words_are_explained():
     for name, value in (("kSiteTmaFull", 0x100), ("kSiteStageEmpty", 0x200), ("kSiteAccFull", 0x300), ("kSiteAccEmpty", 0x400),
                         ("kSiteMailbox", 0x500), ("kSiteCluster", 0x600), ("kSiteRendezvous", 0x700), ("kSiteGrid", 0x800)):
         assert f"{name} = 0x{value:x}" in src
+
+
+def test_fabric_byte_formulas_match_the_device_layout():
+    """The host sizes the peer-mapped regions; the kernels address them.  Both sides are derived here from the same
+    constants, read out of the CUDA sources: the last word any kernel can address lies inside the allocation."""
+    import re
+    from naivert_b200.ops import kernels as K
+    from naivert_b200.parallel import fabric as F
+    gem = open(os.path.join(ROOT, "naivert_b200", "csrc", "gemm.cuh")).read()
+    fab = open(os.path.join(ROOT, "naivert_b200", "csrc", "fabric.cuh")).read()
+
+    def const(src, name):
+        return int(re.search(rf"constexpr int {name} = (\d+);", src).group(1))
+    assert const(gem, "kMaxPeers") == K.K_MAX_PEERS and const(gem, "kMailboxSlabs") == K.K_MAILBOX_SLABS
+    assert "constexpr int kRowPairs = kTok / 2;" in gem and const(gem, "kTok") // 2 == K.K_ROW_PAIRS
+    assert const(gem, "kArRows") // 2 <= K.K_ROW_PAIRS
+    words, slabs, peers = const(fab, "kXchgMaxWords"), const(fab, "kXchgSlabs"), const(fab, "kXchgPeers")
+    for tp in (2, 4, 8):
+        for feats in (4096, 8192):
+            # all-reduce mailbox: word index (slab * tp + source) * kRowPairs * features + pair * features + feature
+            last = ((K.K_MAILBOX_SLABS - 1) * tp + tp - 1) * K.K_ROW_PAIRS * feats + (K.K_ROW_PAIRS - 1) * feats + feats - 1
+            assert (last + 1) * 8 == F.mailbox_bytes(tp, feats)
+        # small exchange: word index ((slab * tp + source) * kXchgMaxWords + i) * 2 + half
+        last = (((slabs - 1) * tp + tp - 1) * words + words - 1) * 2 + 1
+        assert (last + 1) * 8 == F.xchg_bytes(tp)
+    assert peers == K.K_MAX_PEERS
+    # the largest exchange of a round (15 distributions x 256 bins) fits the value range of one call
+    samp = open(os.path.join(ROOT, "naivert_b200", "csrc", "sampler.cu")).read()
+    assert "kRowsP = 8, kRowsQ = 7" in samp and 15 * 256 <= words
