@@ -282,3 +282,33 @@ def test_anthropic_sdk_round_trip(server):
         with client.messages.stream(model="naive-n0.5", max_tokens=64, messages=[{"role": "user", "content": "again"}]) as s:
             assert "".join(s.text_stream) == "SDK says hi."
     assert eng.opened[-2][3].seed == 4 and abs(eng.opened[-2][3].temperature - 0.4) < 1e-9
+
+
+def test_studio_smoke_bench_compares_json_sse_and_proxy(server):
+    """The Studio's smoke benchmark against the fake-engine server: JSON, SSE and SSE through the local proxy give the
+    same text for the same seed; a wrong model name is reported as a failed mode."""
+    import importlib.util
+    import os
+    base, eng = server
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def load(name):
+        sp = importlib.util.spec_from_file_location(name, os.path.join(root, "apps", "studio", name + ".py"))
+        m = importlib.util.module_from_spec(sp)
+        sp.loader.exec_module(m)
+        return m
+    bench, proxy_mod = load("smoke_bench"), load("local_server")
+    eng.reply = "<svg><circle r='3'/></svg>"
+    proxy = proxy_mod.serve(base, port=0)
+    threading.Thread(target=proxy.serve_forever, daemon=True).start()
+    try:
+        rep = bench.run(base, f"http://127.0.0.1:{proxy.server_address[1]}", max_tokens=256)
+        assert rep["ok"] and rep["texts_identical"] and set(rep["modes"]) == {"json", "sse", "sse_via_proxy"}
+        for r in rep["modes"].values():
+            assert r["status"] == 200 and r["complete"] and r["stop_reason"] == "end_turn" and r["chars"] == len(eng.reply)
+            assert r["device_tok_s"] == 1234.5 and r["output_tokens"] == len(eng.reply) + 1 and r["first_content_ms"] is not None
+        bad = bench.run(base, model="no-such-model", max_tokens=16)
+        assert not bad["ok"] and bad["modes"]["sse"]["status"] == 404
+        assert bench.main(["--api", base, "--max-tokens", "64"]) == 0
+    finally:
+        proxy.shutdown()
