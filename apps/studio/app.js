@@ -3,8 +3,8 @@ import { RequestQueue } from "./queue.js";
 import { curvePoints, thin } from "./curve.js";
 import { renderMarkdown } from "./markdown.js";
 import { normalizeBase, buildRequest, assistantTurn, describeHealth, statsLine } from "./core.js";
-import { authHeaders, clearAuth, loadAuth, messagesOptions, parseQuickSetup, saveAuth } from "./endpoint.js";
-import { checkConnection } from "./connection.js";
+import { clearAuth, loadAuth, messagesOptions, parseQuickSetup, saveAuth } from "./endpoint.js";
+import { HealthWatcher, probeInference } from "./connection.js";
 
 const $ = (id) => document.getElementById(id);
 let controller = null;
@@ -28,22 +28,16 @@ $("quick").onkeydown = (ev) => {
 $("check").onclick = async () => {
   $("conn").textContent = "checking…";
   try {
-    const r = await checkConnection({ endpoint: $("base").value, model: $("model").value, auth: auth(), sessionId: $("session").value });
+    const r = await probeInference({ endpoint: $("base").value, model: $("model").value, auth: auth(), sessionId: $("session").value });
     $("conn").textContent = r.message;
     if (r.ok) saveAuth($("base").value, auth());
   } catch (e) { $("conn").textContent = e.message; }
 };
 $("forget").onclick = () => { clearAuth(); showAuth({ kind: "none" }); $("conn").textContent = "credentials forgotten"; };
 
-async function health() {
-  try {
-    let headers = {};
-    try { headers = authHeaders(auth()); } catch (e) { headers = {}; }
-    const r = await fetch(base() + "/health", { headers });
-    $("health").textContent = "health: " + describeHealth(await r.json());
-  } catch (e) { $("health").textContent = "health: " + describeHealth(null); }
-}
-setInterval(health, 2000); health();
+const watcher = new HealthWatcher(() => ({ endpoint: $("base").value, auth: auth() }),
+  (state, json) => { $("health").textContent = "health: " + (json ? describeHealth(json) : describeHealth(null)); });
+watcher.start();
 
 function drawCurve(points) {
   const c = $("curve"), g = c.getContext("2d");

@@ -1,43 +1,98 @@
-// Connection check through the inference route itself: gateways in front of the server often expose neither
-// /health nor /v1/models, so a one-token streamed request is what proves that the endpoint, the credentials, the
-// model name and CORS are right.
+// Two ways of knowing whether the server is there.
+//
+// probeInference(): a one-token streamed request through /v1/messages.  Gateways in front of the server often expose
+// neither /health nor /v1/models, so the inference route itself is what proves endpoint, credentials, model name and
+// CORS at once.
+//
+// HealthWatcher: polls /health while the page is open; backs off (2 s -> 30 s) while the server is unreachable and
+// reports only changes of state.
 import { SseParser } from "./sse.js";
-import { apiUrl, messagesOptions } from "./endpoint.js";
+import { apiUrl, authHeaders, messagesOptions } from "./endpoint.js";
+
+const STATUS_TEXT = new Map([
+  [401, "authentication rejected: check the credentials"],
+  [403, "authentication rejected: check the credentials"],
+  [404, "unknown model or route: check the model name and the endpoint"],
+  [429, "server reachable, its queue or rate limit is full"],
+  [529, "server reachable, its queue or rate limit is full"],
+  [503, "server reachable, still loading or shutting down"],
+]);
 
 export function explainStatus(status) {
-  if (status === 401 || status === 403) return "authentication rejected: check the credentials";
-  if (status === 404) return "unknown model or route: check the model name and the endpoint";
-  if (status === 429 || status === 529) return "server reachable, its queue or rate limit is full";
-  if (status === 503) return "server reachable, still loading or shutting down";
-  return "request rejected: check the model and the gateway configuration";
+  return STATUS_TEXT.get(status) || "request rejected: check the model and the gateway configuration";
 }
 
-export async function checkConnection({ endpoint, model, auth, sessionId, fetcher, timeoutMs = 20000, now = () => Date.now() }) {
-  const doFetch = fetcher || globalThis.fetch.bind(globalThis);
-  const controller = new AbortController();
-  const timer = setTimeout(() => controller.abort(), timeoutMs);
-  const t0 = now();
+async function eventNames(response) {
+  const names = [];
+  const parser = new SseParser(), utf8 = new TextDecoder();
+  const reader = response.body.getReader();
+  for (let chunk = await reader.read(); !chunk.done; chunk = await reader.read()) {
+    for (const ev of parser.feed(utf8.decode(chunk.value, { stream: true }))) names.push(ev.event);
+  }
+  return names;
+}
+
+function streamIsComplete(names) {
+  if (names.includes("error")) return false;
+  return names.length >= 3 && names[0] === "message_start" && names[names.length - 1] === "message_stop" && names.includes("message_delta");
+}
+
+export async function probeInference(cfg) {
+  const fetcher = cfg.fetcher || globalThis.fetch.bind(globalThis);
+  const limitMs = cfg.timeoutMs === undefined ? 20000 : cfg.timeoutMs;
+  const clock = cfg.now || (() => Date.now());
+  const abort = new AbortController();
+  const timer = setTimeout(() => abort.abort(), limitMs);
+  const started = clock();
+  const request = Object.assign(messagesOptions(cfg.auth, cfg.sessionId), {
+    signal: abort.signal,
+    body: JSON.stringify({ model: cfg.model, max_tokens: 1, stream: true, thinking: { type: "disabled" },
+                           messages: [{ role: "user", content: "Reply OK." }] }),
+  });
   try {
-    const body = { model, max_tokens: 1, stream: true, thinking: { type: "disabled" }, messages: [{ role: "user", content: "Reply OK." }] };
-    const r = await doFetch(apiUrl(endpoint, "/v1/messages"), Object.assign(messagesOptions(auth, sessionId), { signal: controller.signal, body: JSON.stringify(body) }));
-    if (!r.ok) {
-      if (r.body && r.body.cancel) { try { await r.body.cancel(); } catch (e) { /* already closed */ } }
-      return { ok: false, message: `HTTP ${r.status}: ${explainStatus(r.status)}` };
+    const response = await fetcher(apiUrl(cfg.endpoint, "/v1/messages"), request);
+    if (!response.ok) {
+      if (response.body && response.body.cancel) { try { await response.body.cancel(); } catch (e) { /* already closed */ } }
+      return { ok: false, message: `HTTP ${response.status}: ${explainStatus(response.status)}` };
     }
-    const parser = new SseParser(), dec = new TextDecoder();
-    const seen = [];
-    const reader = r.body.getReader();
-    for (;;) {
-      const { done, value } = await reader.read();
-      if (done) break;
-      for (const { event } of parser.feed(dec.decode(value, { stream: true }))) seen.push(event);
-    }
-    const complete = seen[0] === "message_start" && seen.includes("message_delta") && seen[seen.length - 1] === "message_stop" && !seen.includes("error");
-    if (!complete) return { ok: false, message: "the server answered, but the Messages stream did not complete" };
-    return { ok: true, message: `connected, streaming verified in ${((now() - t0) / 1000).toFixed(2)} s` };
+    if (!streamIsComplete(await eventNames(response))) return { ok: false, message: "the server answered, but the Messages stream did not complete" };
+    return { ok: true, message: `connected, streaming verified in ${((clock() - started) / 1000).toFixed(2)} s` };
   } catch (e) {
-    if (controller.signal.aborted) return { ok: false, message: `no answer within ${timeoutMs / 1000} s: the server may be queued or down` };
+    if (abort.signal.aborted) return { ok: false, message: `no answer within ${limitMs / 1000} s: the server may be queued or down` };
     if (e instanceof TypeError) return { ok: false, message: "the browser cannot reach the API: check CORS / OPTIONS on the gateway, HTTPS and the network" };
     return { ok: false, message: "the server answered with an invalid Messages stream" };
   } finally { clearTimeout(timer); }
+}
+export const checkConnection = probeInference;
+
+export class HealthWatcher {
+  // getTarget() -> { endpoint, auth }; onChange(state, json) is called when the state string changes.
+  constructor(getTarget, onChange, opts = {}) {
+    this.getTarget = getTarget; this.onChange = onChange;
+    this.fetcher = opts.fetcher || ((...a) => globalThis.fetch(...a));
+    this.baseMs = opts.baseMs || 2000; this.maxMs = opts.maxMs || 30000;
+    this.delay = this.baseMs; this.state = null; this.timer = null; this.stopped = true;
+    this.schedule = opts.schedule || ((fn, ms) => setTimeout(fn, ms));
+  }
+  async pollOnce() {
+    let state = "unreachable", json = null;
+    try {
+      const { endpoint, auth } = this.getTarget();
+      let headers = {};
+      try { headers = authHeaders(auth); } catch (e) { headers = {}; }
+      const r = await this.fetcher(apiUrl(endpoint, "/health"), { headers });
+      json = await r.json();
+      state = String(json.status || (r.ok ? "ok" : "error"));
+    } catch (e) { state = "unreachable"; }
+    this.delay = state === "unreachable" ? Math.min(this.maxMs, this.delay * 2) : this.baseMs;
+    if (state !== this.state) { this.state = state; this.onChange(state, json); }
+    return state;
+  }
+  start() {
+    if (!this.stopped) return;
+    this.stopped = false;
+    const tick = async () => { if (this.stopped) return; await this.pollOnce(); if (!this.stopped) this.timer = this.schedule(tick, this.delay); };
+    tick();
+  }
+  stop() { this.stopped = true; if (this.timer !== null && typeof clearTimeout === "function") clearTimeout(this.timer); this.timer = null; }
 }

@@ -47,7 +47,7 @@ test("request building", () => {
 });
 
 import { normalizeEndpoint, apiUrl, authHeaders, messagesOptions, saveAuth, loadAuth, clearAuth, parseQuickSetup } from "./endpoint.js";
-import { checkConnection, explainStatus } from "./connection.js";
+import { checkConnection, explainStatus, HealthWatcher } from "./connection.js";
 
 function memoryStorage() {
   const m = new Map();
@@ -109,4 +109,21 @@ test("connection check goes through the inference route", async () => {
   const cors = await checkConnection({ endpoint: "http://h:1", model: "m", fetcher: async () => { throw new TypeError("failed to fetch"); } });
   assert.match(cors.message, /CORS/);
   assert.match(explainStatus(529), /queue/);
+});
+
+test("health watcher reports changes only and backs off while unreachable", async () => {
+  const answers = [() => { throw new TypeError("down"); }, () => { throw new TypeError("down"); },
+                   () => ({ ok: true, json: async () => ({ status: "loading" }) }), () => ({ ok: true, json: async () => ({ status: "ok", slot: "IDLE" }) }),
+                   () => ({ ok: true, json: async () => ({ status: "ok", slot: "IDLE" }) })];
+  const seen = [];
+  let calls = 0, lastUrl = null, lastHeaders = null;
+  const w = new HealthWatcher(() => ({ endpoint: "http://h:1", auth: { kind: "bearer", secret: "k" } }), (state) => seen.push(state),
+    { fetcher: async (url, opt) => { lastUrl = url; lastHeaders = opt.headers; return answers[calls++](); }, baseMs: 100, maxMs: 350 });
+  await w.pollOnce(); assert.equal(w.delay, 200);
+  await w.pollOnce(); assert.equal(w.delay, 350);
+  await w.pollOnce(); assert.equal(w.delay, 100);
+  await w.pollOnce(); await w.pollOnce();
+  assert.deepEqual(seen, ["unreachable", "loading", "ok"]);
+  assert.equal(lastUrl, "http://h:1/health");
+  assert.equal(lastHeaders.authorization, "Bearer k");
 });
