@@ -68,7 +68,8 @@ def test_compose_file_is_consistent_with_the_entrypoint():
     import re
     import yaml
     doc = yaml.safe_load(open(os.path.join(ROOT, "devops", "docker-compose.yml")))
-    svc = doc["services"]["naivert-b200"]
+    svc = doc["services"]["server"]
+    assert svc["container_name"] == "naivert-b200" and "python -c" in svc["healthcheck"]["test"]
     assert svc["ipc"] == "host" and svc["build"]["dockerfile"] == "devops/Dockerfile"
     assert svc["deploy"]["resources"]["reservations"]["devices"][0]["capabilities"] == ["gpu"]
     entry = open(os.path.join(ROOT, "devops", "entrypoint.sh")).read()
