@@ -108,7 +108,6 @@ class Fabric:
         self._opened, self._local = [], []
 
 
-
 # status word = site class (bits 8..11, csrc/ptx.cuh) | detail (low byte)
 _SITE_CLASSES = {
     0x100: "a consumer waited for a TMA stage that never filled (detail: stage; 0x10+: MoE down slots, 0x40: operand build, 0x80: sweep queries)",
