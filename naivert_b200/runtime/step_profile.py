@@ -82,7 +82,8 @@ def report_sampler_stamps(buf: torch.Tensor) -> List[str]:
 
 def report_stamps(bufs: Dict[str, torch.Tensor], layer: int) -> List[str]:
     import numpy as np
-    torch.cuda.synchronize()
+    if any(b.is_cuda for b in bufs.values()):
+        torch.cuda.synchronize()
     lines: List[str] = []
     T = {k: b.view(300, 16).cpu().numpy() for k, b in bufs.items()}
     t0 = min(t[:, 0][t[:, 0] > 0].min() for t in T.values() if (t[:, 0] > 0).any())
@@ -104,12 +105,13 @@ def report_stamps(bufs: Dict[str, torch.Tensor], layer: int) -> List[str]:
         lines.append(f"layer {layer} {k[5:]}: {len(t)} CTAs; us after the layer's first stamp (median over CTAs / last CTA)")
         order = sorted(range(16), key=lambda i: np.median(t[:, i][t[:, i] > t0]) if (t[:, i] > t0).any() else 1e30)
         for i in order:
+            if names is None and i == 10:           # a count, not a time
+                if t[:, 10].max() > 0:
+                    lines.append(f"   {'mailbox sweeps (max)':26s} {int(t[:, 10].max()):8d}")
+                continue
             col = t[:, i]
             col = col[col > t0]                     # stamps of earlier replays (a CTA that was not last this time) lie before t0
             if len(col) == 0:
-                continue
-            if names is None and i == 10:
-                lines.append(f"   {'mailbox sweeps (max)':26s} {int(t[:, 10].max()):8d}")
                 continue
             label = names.get(i, str(i)) if names else STAMP_NAMES["gemm"][i] if i < 12 else {12: "row scales ready", 14: "operand stored"}.get(i, str(i))
             lines.append(f"   {label:26s} {(np.median(col) - t0) / 1e3:8.2f} / {(col.max() - t0) / 1e3:8.2f}   ({len(col)} CTAs)")

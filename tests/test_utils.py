@@ -363,3 +363,34 @@ def test_fabric_byte_formulas_match_the_device_layout():
     # the largest exchange of a round (15 distributions x 256 bins) fits the value range of one call
     samp = open(os.path.join(ROOT, "naivert_b200", "csrc", "sampler.cu")).read()
     assert "kRowsP = 8, kRowsQ = 7" in samp and 15 * 256 <= words
+
+
+def test_stamp_reports_from_synthetic_buffers():
+    """The phase reports of the step profiler read plain buffers of %globaltimer stamps: median / last CTA per phase,
+    relative to the layer's first stamp; stamps older than that (a CTA that was not last in this replay) are ignored."""
+    import torch
+    from naivert_b200.runtime.step_profile import report_sampler_stamps, report_stamps
+    t0 = 1_000_000
+    gemm = torch.zeros(300 * 16, dtype=torch.int64)
+    g = gemm.view(300, 16)
+    for cta in range(4):
+        g[cta, 0] = t0 + 100 * cta                    # entry
+        g[cta, 2] = t0 + 2000 + 100 * cta             # upstream done
+        g[cta, 11] = t0 + 9000 + 1000 * cta           # epilogue done
+    g[0, 9] = t0 - 500                                # a stale stamp of an earlier replay
+    g[1, 10] = 7                                      # mailbox sweeps
+    g[1, 3] = t0 + 3000
+    lines = report_stamps({"args_o": gemm}, 20)
+    text = "\n".join(lines)
+    assert "layer 20 o: 4 CTAs" in lines[0]
+    assert any("upstream done" in l and "2.15 /     2.30" in l for l in lines), text
+    assert any("epilogue done" in l and "12.00" in l for l in lines), text
+    assert any("mailbox sweeps (max)" in l and l.strip().endswith("7") for l in lines), text
+    assert not any("peer words arrived" in l for l in lines), text          # the stale stamp lies before the layer's first
+    samp = torch.zeros(32, dtype=torch.int64)
+    assert report_sampler_stamps(samp) == []
+    samp[30] = t0
+    for ph in range(7):
+        samp[2 * ph], samp[2 * ph + 1] = t0 + 10_000 * ph + 3000, t0 + 10_000 * ph + 8000
+    out = report_sampler_stamps(samp)
+    assert len(out) == 8 and "maxima" in out[1] and "3.00 /     8.00" in out[1] and "63.00 /    68.00" in out[7]
