@@ -126,3 +126,34 @@ def test_studio_local_server_serves_files_and_proxies_streams():
         assert r.status == 405
     finally:
         srv.shutdown(); api.shutdown()
+
+
+def test_reference_retarget_edits_only_the_architecture_strings(tmp_path, monkeypatch):
+    """The comparison arm runs a copy of the reference in which only the architecture strings differ: every edited
+    line is reported, other files are byte-identical, the prefill-only vendored trees are left out."""
+    import importlib.util
+    sp = importlib.util.spec_from_file_location("retarget_reference", os.path.join(ROOT, "baseline", "retarget_reference.py"))
+    mod = importlib.util.module_from_spec(sp)
+    sp.loader.exec_module(mod)
+    src = tmp_path / "src"
+    (src / "naivert" / "kernels").mkdir(parents=True)
+    (src / "naivert" / "prefill" / "kernels" / "fa4").mkdir(parents=True)
+    (src / "devops").mkdir()
+    builder = "FLAGS = ['-gencode', 'arch=compute_103a,code=sm_103a']\nKEEP = 1\nARCH_LIST = '10.3a'\n"
+    (src / "naivert" / "kernels" / "build.py").write_text(builder)
+    (src / "naivert" / "kernels" / "body.cuh").write_text("// compute_103a stays in non-script sources\n")
+    (src / "naivert" / "prefill" / "kernels" / "fa4" / "x.py").write_text("compute_103a\n")
+    (src / "devops" / "Dockerfile").write_text("ENV TORCH_CUDA_ARCH_LIST='10.3a'\n")
+    (src / "README.md").write_text("untouched compute_103a\n")
+    monkeypatch.setattr(mod, "DEST", str(tmp_path / "copy"))
+    edits = mod.retarget(str(src))
+    dest = tmp_path / "copy"
+    assert sorted((e[0], e[1]) for e in edits) == [("devops/Dockerfile", 1), ("naivert/kernels/build.py", 1), ("naivert/kernels/build.py", 3)]
+    assert (dest / "naivert" / "kernels" / "build.py").read_text() == builder.replace("compute_103a", "compute_100a").replace(
+        "sm_103a", "sm_100a").replace("'10.3a'", "'10.0a'")
+    assert (dest / "naivert" / "kernels" / "body.cuh").read_text() == (src / "naivert" / "kernels" / "body.cuh").read_text()
+    assert (dest / "README.md").read_text() == "untouched compute_103a\n"
+    assert not (dest / "naivert" / "prefill" / "kernels").exists()
+    assert all("103a" not in e[3] and "10.3a" not in e[3] for e in edits)
+    # running it again replaces the copy instead of layering edits
+    assert len(mod.retarget(str(src))) == 3
