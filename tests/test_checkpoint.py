@@ -267,3 +267,43 @@ def test_list_weights_and_server_flags(tmp_path, monkeypatch, capsys):
     assert a.draft == "markov-a" and a.output_capacity == 4096 and a.draft_ingest == "loop"
     assert cli.main(["--list-weights"]) == 0
     assert "targets (--target):" in capsys.readouterr().out
+
+
+def test_device_init_has_the_sharded_layout_and_replicates_what_must_be_equal():
+    """The benchmark's weights are drawn per rank in the sharded layout: they fill the slot table of every TP degree,
+    replicated tensors are identical on all ranks, sharded ones differ, and the draw is reproducible."""
+    import torch
+    from naivert_b200.models.device_init import init_draft_rank_weights_device, init_rank_weights_device
+    from naivert_b200.models.naive_n0p5 import small_w8a8_spec
+    from naivert_b200.models.tensor_abi import check_rank_weights
+    from naivert_b200.models import weights as W
+    spec = small_w8a8_spec(4)
+    for tp in (1, 2, 4, 8):
+        ws = [init_rank_weights_device(spec, r, tp, seed=0, device="cpu") for r in sorted({0, tp - 1})]
+        for r, w in zip(sorted({0, tp - 1}), ws):
+            check_rank_weights(spec, w, r, tp)
+        if tp > 1:
+            a, b = ws
+            assert torch.equal(a["embed"], b["embed"]) and torch.equal(a["norm"], b["norm"])
+            assert torch.equal(a["layers"][1]["router_w"], b["layers"][1]["router_w"])          # replicated
+            assert torch.equal(a["layers"][0]["iwq"], b["layers"][0]["iwq"])
+            assert not torch.equal(a["layers"][1]["wq"], b["layers"][1]["wq"])                   # sharded
+            assert not torch.equal(a["lm_head"], b["lm_head"])
+    again = init_rank_weights_device(spec, 1, 2, seed=0, device="cpu")
+    first = init_rank_weights_device(spec, 1, 2, seed=0, device="cpu")
+    assert torch.equal(again["layers"][2]["gate"]["w"].view(torch.uint8), first["layers"][2]["gate"]["w"].view(torch.uint8))
+    other = init_rank_weights_device(spec, 1, 2, seed=5, device="cpu")
+    assert not torch.equal(other["lm_head"], first["lm_head"])
+    # the draft's device init has the structure of the sharded prepared draft weights
+    dref = W.shard_draft_weights(spec, W.prepare_draft_weights(spec, W.init_draft_state_dict(spec)), 1, 2)
+    ddev = init_draft_rank_weights_device(spec, 1, 2, device="cpu")
+
+    def shapes(d, pre=""):
+        out = {}
+        for k, v in (d.items() if isinstance(d, dict) else enumerate(d)):
+            if isinstance(v, (dict, list)):
+                out.update(shapes(v, f"{pre}{k}."))
+            elif isinstance(v, torch.Tensor):
+                out[f"{pre}{k}"] = (tuple(v.shape), str(v.dtype))
+        return out
+    assert shapes(dref) == shapes(ddev)
