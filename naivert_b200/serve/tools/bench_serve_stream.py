@@ -55,11 +55,11 @@ class _Engine:
         return _Session(max_decode, self.per)
 
 
-def main() -> int:
+def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=20000)
     ap.add_argument("--per-step", type=int, default=4)
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
     import httpx
     import uvicorn
     eng = _Engine(a.per_step)

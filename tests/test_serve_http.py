@@ -312,3 +312,12 @@ def test_studio_smoke_bench_compares_json_sse_and_proxy(server):
         assert bench.main(["--api", base, "--max-tokens", "64"]) == 0
     finally:
         proxy.shutdown()
+
+
+def test_stream_ceiling_tool_counts_every_delta(capsys):
+    """The host-path ceiling tool streams from an instant fake engine: all tokens arrive as deltas and the rate it
+    reports is far above any device rate (the serving layer is not the bottleneck of a single stream)."""
+    from naivert_b200.serve.tools import bench_serve_stream
+    assert bench_serve_stream.main(["--tokens", "2000", "--per-step", "4"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["tokens"] == 2000 and rep["delta_events"] == 500 and rep["tokens_per_s"] > 5000
